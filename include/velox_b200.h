@@ -1,0 +1,150 @@
+/*
+ * velox_b200 -- C ABI of the B200 (sm_100a) quantized-linear library.
+ *
+ * Plain pointers and sizes only; every pointer is a DEVICE pointer unless stated otherwise,
+ * `stream` is a cudaStream_t passed as void*.  The caller owns every buffer; the library
+ * allocates no device memory.  All entry points enqueue work on `stream` and return without
+ * synchronising.
+ *
+ * Return value: 0 = OK; negative = argument error (nothing was launched, see vx_last_error());
+ * positive = CUDA runtime error code.
+ *
+ * Each entry point names the interface of the reference project (velox-voice) it replaces.
+ */
+#ifndef VELOX_B200_H_
+#define VELOX_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VX_ABI_VERSION 1
+
+/* Quantization formats.  values / scale / natural scale layout
+ *  ROWSCALE   E2M1, one UE8M0 per row                      u8 [R]
+ *  BLK16_A    E2M1, UE8M0 per 16 cols shared by a row pair u8 [K/16][R/2]  (kb-major)
+ *  BLK16_B    E2M1, UE8M0 per 16 cols per row              u8 [K/16][R]    (kb-major)
+ *  MX32       E2M1, UE8M0 per 32 cols                      u8 [R][K/32]
+ *  NV16       E2M1, E4M3 per 16 cols + fp32 tensor scale   u8 [R][K/16], amax f32[1]
+ *  FP8_1X128  E4M3 values, fp32 scale per 1x128            f32 [R][K/128]
+ * E2M1 codes are packed two per byte, low nibble = even k, nibble = sign<<3 | magnitude.
+ */
+enum vx_fmt {
+  VX_FMT_ROWSCALE = 0,
+  VX_FMT_BLK16_A = 1,
+  VX_FMT_BLK16_B = 2,
+  VX_FMT_MX32 = 3,
+  VX_FMT_NV16 = 4,
+  VX_FMT_FP8_1X128 = 5
+};
+
+enum vx_dtype { VX_F32 = 0, VX_BF16 = 1, VX_FP4 = 2 /* fused re-quantized output */ };
+
+enum vx_epilogue {
+  VX_EPI_NONE = 0,      /* out = acc (* scales)                      */
+  VX_EPI_BIAS = 1,      /* out = acc + bias[n]                       */
+  VX_EPI_BIAS_SWISH = 2,/* out = silu(acc + bias[n])                 */
+  VX_EPI_BIAS_GLU = 3,  /* out[:, j] = (acc_a + b_a) * sigmoid(acc_b + b_b), GLU-interleaved weights */
+  VX_EPI_BIAS_RESIDUAL = 4 /* out = residual + alpha * (acc + bias[n]) */
+};
+
+/* Scale factors in the layout the block-scaled tensor-core MMA consumes ("SF atoms"):
+ * tiles of 128 rows x 4 consecutive K-blocks, 512 bytes each, byte offset inside a tile
+ *   (r % 32) * 16 + ((r / 32) % 4) * 4 + (kb % 4);
+ * tiles ordered [ceil(R/128)][kg] with kg = vx_sf_kgroups(fmt, K); unused bytes are zero.
+ */
+int64_t vx_sf_kgroups(int fmt, int64_t K);
+int64_t vx_sf_bytes(int fmt, int64_t R, int64_t K);
+
+/* Quantize + pack the rows of x [M,K] (row stride ldx elements, dtype VX_F32 or VX_BF16).
+ * Replaces per_row_col_quantize / triton_quantize_w (veloxvoice/kernels/ops/triton_ops.py:92-129)
+ * and mxfp4_block_quantize (triton_ops.py:261-293); MX32 / NV16 / FP8_1X128 extend the same rules.
+ *   codes      u8 [M, K/2] (E2M1 formats) or u8 [M, K] (FP8), row stride ldc BYTES
+ *   scales     natural layout (table above), may be NULL
+ *   scales_sf  SF-atom layout (block E2M1 formats only), may be NULL
+ *   amax       NV16 only: f32[1] holding the tensor's max |x| (see vx_amax); read, not written
+ * K % 8 == 0 (and the format's block size must divide K); x rows 16-byte aligned.
+ */
+int vx_quantize_pack(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, int fmt,
+                     void* codes, int64_t ldc, void* scales, void* scales_sf, const float* amax,
+                     void* stream);
+
+/* LayerNorm (fp32 statistics, eps, gamma/beta f32[K]) fused in front of vx_quantize_pack:
+ * replaces the LayerNorm launch (veloxvoice/kernels/csrc/velox_layernorm.cu:13-58,
+ * fused_layernorm in veloxvoice/kernels/ops/cuda_ops.py:204-210) followed by the quantizer
+ * launch (veloxvoice/models/wenet/torch_conformer.py:251-262).  K <= 2048.
+ *   y      optional [M,K] copy of the normalised rows (y_dtype VX_F32 or VX_BF16, row stride
+ *          ldy elements), may be NULL;
+ *   codes  may be NULL when y is given: plain LayerNorm, nothing is quantized.
+ */
+int vx_ln_quantize_pack(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx,
+                        const float* gamma, const float* beta, float eps, int fmt, void* codes,
+                        int64_t ldc, void* scales, void* scales_sf, const float* amax, void* y,
+                        int y_dtype, int64_t ldy, void* stream);
+
+/* max |x| over a tensor into amax_out[0] (f32, overwritten).  No reference counterpart
+ * (the reference has no per-tensor scale); needed by NV16. */
+int vx_amax(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, float* amax_out,
+            void* stream);
+
+/* Natural-layout block scales -> SF atoms (weights quantized elsewhere, or scales produced
+ * by the reference's quantizers).  fmt in {BLK16_A, BLK16_B, MX32, NV16}. */
+int vx_sf_from_natural(int fmt, const void* scales, int64_t R, int64_t K, void* scales_sf,
+                       void* stream);
+
+/* Block-scaled GEMM  D[M,N] = epilogue( A[M,K] . B[N,K]^T ).
+ * Replaces velox_dgx_mxfp4_gemm / velox_dgx_mxfp4_blkscale_gemm
+ * (veloxvoice/kernels/csrc/dgx/dgx_mxfp4_gemm.cu:61-111,135-180; Python wrappers
+ * dgx_mxfp4_gemm / dgx_mxfp4_blkscale_gemm in veloxvoice/kernels/ops/cuda_ops.py:626-645,679-702)
+ * plus the bias / SiLU / GLU / residual launches that follow them in the model
+ * (veloxvoice/models/wenet/torch_conformer.py:265-266,657-658,706,594-633).
+ */
+typedef struct vx_gemm_desc {
+  int32_t struct_size; /* sizeof(vx_gemm_desc) */
+  int32_t fmt;         /* vx_fmt of both operands (BLK16_A means A side "A", B side "B") */
+  int64_t M, N, K;
+  const void* a_codes; /* u8 [M, K/2] or [M, K] (FP8) */
+  int64_t lda;         /* bytes per row, multiple of 16 */
+  const void* b_codes; /* u8 [N, K/2] or [N, K] */
+  int64_t ldb;
+  const void* a_scales; /* ROWSCALE: u8 [M]; block E2M1 formats: SF atoms; FP8: f32 [M,K/128] */
+  const void* b_scales; /* same for the N side */
+  const float* a_amax;  /* NV16: f32[1] tensor amax of A (global scale = amax / 2688) */
+  const float* b_amax;
+  int32_t epilogue;     /* vx_epilogue */
+  int32_t out_dtype;    /* vx_dtype */
+  void* out;            /* [M, N'] (N' = N/2 for GLU); FP4: u8 [M, N'/2] */
+  int64_t ldo;          /* elements (bytes for FP4 codes) */
+  const float* bias;    /* f32 [N] or NULL */
+  const void* residual; /* [M, N] or NULL */
+  int32_t residual_dtype;
+  int32_t out_fmt;      /* FP4 output: MX32 or NV16 */
+  int64_t ldr;          /* elements */
+  float alpha;          /* BIAS_RESIDUAL */
+  int32_t flags;        /* VX_GEMM_* */
+  void* out_scales_sf;  /* FP4 output: SF atoms of the output rows */
+  void* out_scales;     /* FP4 output: natural layout, may be NULL */
+  const float* out_amax;/* FP4 NV16 output: f32[1] static tensor amax */
+} vx_gemm_desc;
+
+#define VX_GEMM_DIRECT_STORE 1 /* bypass the shared-memory staged TMA store */
+
+int vx_bsgemm(const vx_gemm_desc* desc, void* stream);
+
+/* Tensor-core peak probe: times `iters` back-to-back MMAs (no memory traffic) per SM.
+ * kind 0 = FP4 block-scaled (kind::mxf4nvf4), 1 = FP8 (kind::f8f6f4).  Host pointer out. */
+int vx_mma_peak_probe(int kind, int n_tile, int iters, float* tflops_out);
+
+/* Device-side status word of the last kernels (0 = OK; nonzero = a bounded wait expired:
+ * (code<<24)|(site<<16)|block).  Synchronises the device.  Host pointer out. */
+int vx_device_status(int* status_out);
+
+const char* vx_last_error(void);
+int vx_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VELOX_B200_H_ */

@@ -1,0 +1,126 @@
+"""GEMM, epilogue and LayerNorm references (numpy / torch-CPU).  TEST INFRASTRUCTURE.
+
+Follows, in the reference project:
+
+* GEMM result of the per-row-scaled FP4 path: ``raw = unpack(xq) @ unpack(wq).T`` then
+  ``raw * 2**(sa-127)[:, None] * 2**(sb-127)[None, :]``
+  (``tests/kernels/test_dgx_mxfp4_gemm.py:35-61``).
+* every other format: dequantize, then an fp32 matmul (the acceptance rule of the path).
+* bias add ``veloxvoice/models/wenet/torch_conformer.py:265-266``; FFN ``w2(silu(w1 x))``
+  ``:657-658``; half-step residual ``x + 0.5 * ff(...)`` ``:706,712``; GLU ``a * sigmoid(b)``
+  with ``b`` the second half of the channels ``:633`` and
+  ``veloxvoice/kernels/csrc/hopper/block/pwlin_glu_block_1p2c.h:77-85``.
+* LayerNorm ``veloxvoice/kernels/csrc/velox_layernorm.cu:52-57``.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import formats as F
+
+F32 = np.float32
+
+
+def matmul_f32(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """a [M,K] @ b[N,K].T in fp32 on the host cores."""
+    ta = torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32))
+    tb = torch.from_numpy(np.ascontiguousarray(b, dtype=np.float32))
+    return (ta @ tb.T).numpy()
+
+
+def gemm_rowscale_ref(xq, wq, sa, sb) -> np.ndarray:
+    """``torch_matmul_ref`` of the reference's FP4 GEMM test (unit-scale dot, scales after)."""
+    raw = matmul_f32(F.e2m1_decode(F.unpack_codes(xq)), F.e2m1_decode(F.unpack_codes(wq)))
+    return raw * F.ue8m0_decode(sa)[:, None] * F.ue8m0_decode(sb)[None, :]
+
+
+def gemm_ref(fmt: int, aq, asc, bq, bsc, ga=None, gb=None) -> np.ndarray:
+    """Dequantize-then-fp32-matmul reference for any format."""
+    if fmt == F.FMT_ROWSCALE:
+        return gemm_rowscale_ref(aq, bq, asc, bsc)
+    fb = F.FMT_BLK16_B if fmt == F.FMT_BLK16_A else fmt
+    return matmul_f32(F.dequantize(aq, asc, fmt, ga), F.dequantize(bq, bsc, fb, gb))
+
+
+def silu(x: np.ndarray) -> np.ndarray:
+    x = x.astype(np.float32)
+    return (x / (1.0 + np.exp(-x.astype(np.float64)))).astype(np.float32)
+
+
+def sigmoid(x: np.ndarray) -> np.ndarray:
+    return (1.0 / (1.0 + np.exp(-x.astype(np.float64)))).astype(np.float32)
+
+
+EPI_NONE, EPI_BIAS, EPI_BIAS_SWISH, EPI_BIAS_GLU, EPI_BIAS_RESIDUAL = range(5)
+
+
+def epilogue_ref(acc: np.ndarray, epi: int, bias=None, residual=None, alpha: float = 1.0) -> np.ndarray:
+    """fp32 epilogue on the logical (un-interleaved) accumulator [M, N]."""
+    z = acc.astype(np.float32)
+    if epi != EPI_NONE and bias is not None:
+        z = z + np.asarray(bias, dtype=np.float32)[None, :]
+    if epi == EPI_BIAS_SWISH:
+        z = silu(z)
+    elif epi == EPI_BIAS_GLU:
+        h = z.shape[1] // 2
+        z = z[:, :h] * sigmoid(z[:, h:])
+    elif epi == EPI_BIAS_RESIDUAL:
+        z = np.asarray(residual, dtype=np.float32) + F32(alpha) * z
+    return z.astype(np.float32)
+
+
+def to_bf16(x: np.ndarray) -> np.ndarray:
+    """Round fp32 -> bf16 (RN-even) and return as fp32."""
+    return torch.from_numpy(np.ascontiguousarray(x, dtype=np.float32)).bfloat16().float().numpy()
+
+
+def glu_interleave_rows(n_out: int, tile: int = 128) -> np.ndarray:
+    """Row order of GLU weights inside the GEMM: every `tile` rows hold tile/2 rows of the
+    value half followed by the matching tile/2 rows of the gate half."""
+    h = n_out // 2
+    half = tile // 2
+    idx = []
+    for t in range(0, h, half):
+        idx.extend(range(t, min(t + half, h)))
+        idx.extend(range(h + t, min(h + t + half, n_out)))
+    return np.asarray(idx, dtype=np.int64)
+
+
+def layernorm_ref(x, gamma, beta, eps: float = 1e-5) -> np.ndarray:
+    """Row LayerNorm with the fused CUDA kernel's exact fp32 operation order.
+
+    Formula of ``velox_layernorm.cu:52-57`` (``var = E[x^2] - mean^2`` clamped at 0).  The
+    order of the additions is this library's: lane ``l`` of 32 sums, chunk by chunk of 256
+    elements, its 8 consecutive elements ``[256 c + 8 l, +8)``; lanes are then combined by a
+    butterfly (xor 16, 8, 4, 2, 1).  ``rstd = 1 / sqrt(var + eps)`` with both operations
+    correctly rounded; no fused multiply-add anywhere.
+    """
+    x = F._f32(x)
+    M, K = x.shape
+    ch = -(-K // 256)
+    xp = np.zeros((M, ch * 256), dtype=np.float32)
+    xp[:, :K] = x
+    xl = xp.reshape(M, ch, 32, 8)
+    s = np.zeros((M, 32), dtype=np.float32)
+    sq = np.zeros((M, 32), dtype=np.float32)
+    for c in range(ch):
+        for j in range(8):
+            v = xl[:, c, :, j]
+            s = (s + v).astype(np.float32)
+            sq = (sq + (v * v).astype(np.float32)).astype(np.float32)
+    lanes = np.arange(32)
+    for o in (16, 8, 4, 2, 1):
+        s = (s + s[:, lanes ^ o]).astype(np.float32)
+        sq = (sq + sq[:, lanes ^ o]).astype(np.float32)
+    kf = F32(K)
+    mean = (s[:, 0] / kf).astype(np.float32)
+    var = np.maximum(((sq[:, 0] / kf).astype(np.float32) - (mean * mean).astype(np.float32)).astype(np.float32), F32(0))
+    rstd = (F32(1.0) / np.sqrt((var + F32(eps)).astype(np.float32)).astype(np.float32)).astype(np.float32)
+    g = np.asarray(gamma, dtype=np.float32)[None, :]
+    b = np.asarray(beta, dtype=np.float32)[None, :]
+    y = (x - mean[:, None]).astype(np.float32)
+    y = (y * rstd[:, None]).astype(np.float32)
+    y = (y * g).astype(np.float32)
+    return (y + b).astype(np.float32)

@@ -1,0 +1,872 @@
+// Block-scaled GEMMs on the 5th-generation tensor cores (tcgen05) with fused epilogues.
+//
+//   D[M,N] = epilogue( A[M,K] . B[N,K]^T )
+//   FP4 operands (E2M1, two per byte):  tcgen05.mma kind::mxf4nvf4.block_scale, scale factors
+//       (UE8M0 per 32 / per 16, or E4M3 per 16) read by the MMA from tensor memory;
+//   FP8 operands (E4M3, fp32 scale per 1x128): tcgen05.mma kind::f8f6f4, one accumulation
+//       group per 128-wide K block, promoted into fp32 registers with sa[m,kb] * sb[n,kb].
+//
+// One persistent CTA per SM, 6 warps:
+//   warp 0      TMA producer: A / B tiles (128 rows x 128 bytes, 128-byte swizzle) and the
+//               scale-factor atoms of the stage into a 4-deep shared-memory ring;
+//   warp 1      owns tensor memory; one elected thread copies scale factors shared -> tensor
+//               memory (tcgen05.cp) and issues the MMAs; tcgen05.commit releases ring slots
+//               and publishes finished accumulators;
+//   warps 2..5  epilogue: tcgen05.ld of a 128 x 128 fp32 accumulator (one row per thread),
+//               scales / bias / Swish / GLU / residual, then either a swizzled shared-memory
+//               staging buffer + TMA store (clipped at the tensor edge by hardware) or direct
+//               vector stores; optional re-quantization of the result to FP4.
+// Accumulators are double-buffered in tensor memory (2 x 128 columns), so the epilogue of
+// tile i overlaps the loads and MMAs of tile i + 1.
+//
+// Every mbarrier wait is bounded (vx_ptx.cuh); an expired wait sets the device status word
+// and the CTA drains and exits instead of hanging.
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <mutex>
+
+#include "vx_common.cuh"
+#include "vx_ptx.cuh"
+#include "vx_quant_math.cuh"
+
+namespace vx {
+namespace {
+
+constexpr int BM = 128;            // rows of A per tile = TMEM lanes
+constexpr int BN = 128;            // rows of B per tile = accumulator columns
+constexpr int STAGE_ROW_BYTES = 128;  // K bytes per stage: 256 FP4 or 128 FP8 elements
+constexpr int TILE_BYTES = BM * STAGE_ROW_BYTES;  // 16 KB
+constexpr int NSTAGE = 4;
+constexpr int SF_STAGE_MAX = 4 * 512;  // scale-factor atoms of one operand per stage
+constexpr int NUM_THREADS = 192;
+constexpr int EPI_WARP0 = 2;
+constexpr int STAGING_BYTES = 32 * 128;  // 32 rows x 128 bytes per epilogue warp and buffer
+constexpr int FP8_MAX_KB = 16;           // K <= 2048 for the FP8 path
+
+// tensor-memory columns
+constexpr int TM_ACC0 = 0, TM_SFA = 256, TM_SFB = 272, TM_COLS = 512;
+
+enum Kind { KIND_FP4_VEC2 = 0, KIND_FP4_VEC4 = 1, KIND_FP8 = 2 };
+
+struct GemmParams {
+  int64_t M, N, K;
+  int m_tiles, n_tiles, k_stages;
+  // scale factors
+  const uint8_t* sfa;     // SF atoms of A (block formats)
+  const uint8_t* sfb;
+  int64_t sf_kg;          // atoms per 128-row tile
+  int sf_unit;            // rowscale: unit scale factors in the MMA, row/col scales afterwards
+  int sf_e8m0;            // 1 = UE8M0, 0 = E4M3
+  const uint8_t* row_scale_u8;  // ROWSCALE: u8 [M]
+  const uint8_t* col_scale_u8;  // ROWSCALE: u8 [N]
+  const float* a_amax;    // NV16
+  const float* b_amax;
+  const float* fa;        // FP8: f32 [M, K/128]
+  const float* fb;        // FP8: f32 [N, K/128]
+  // epilogue
+  int out_dtype;          // vx_dtype
+  int tma_store;
+  void* out;
+  int64_t ldo;
+  const float* bias;
+  const void* residual;
+  int residual_dtype;
+  int64_t ldr;
+  float alpha;
+  int out_fmt;
+  uint8_t* out_sf;
+  uint8_t* out_scales;
+  int64_t out_sf_kg;
+  const float* out_amax;
+  int* status;
+};
+
+struct __align__(1024) SmemLayout {
+  uint8_t a[NSTAGE][TILE_BYTES];
+  uint8_t b[NSTAGE][TILE_BYTES];
+  uint8_t sfa[NSTAGE][SF_STAGE_MAX];
+  uint8_t sfb[NSTAGE][SF_STAGE_MAX];
+  uint8_t staging[4][2][STAGING_BYTES];
+  float fb[4][FP8_MAX_KB][BN];  // per epilogue warp: column scales of the current tile
+  uint64_t full[NSTAGE];
+  uint64_t empty[NSTAGE];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ float silu_f(float z) { return __fdividef(z, 1.0f + __expf(-z)); }
+__device__ __forceinline__ float sigmoid_f(float z) { return __fdividef(1.0f, 1.0f + __expf(-z)); }
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// ---------------------------------------------------------------------------------------
+// Epilogue of one 32-column chunk held in registers by one thread (one output row).
+//   z[i]  accumulator value of logical column `ncol0 + i` (after scales)
+//   For GLU the caller passes value and gate chunks and `ncol0` in OUTPUT columns.
+template <int EPI>
+struct ChunkOut {
+  // Applies bias / activation / residual in place.  `bias_col0` indexes the bias vector
+  // (accumulator column order), `out_col0` the output / residual column.
+  static __device__ __forceinline__ void apply(const GemmParams& p, float (&z)[32], float (&gate)[32],
+                                               int64_t row, int64_t bias_col0, int64_t gate_col0,
+                                               int64_t out_col0, bool row_ok) {
+    if constexpr (EPI != VX_EPI_NONE) {
+      if (p.bias) {
+        if (bias_col0 + 32 <= p.N) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + bias_col0 + i));
+            z[i] += b.x; z[i + 1] += b.y; z[i + 2] += b.z; z[i + 3] += b.w;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (bias_col0 + i < p.N) z[i] += __ldg(p.bias + bias_col0 + i);
+        }
+        if constexpr (EPI == VX_EPI_BIAS_GLU) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + gate_col0 + i));
+            gate[i] += b.x; gate[i + 1] += b.y; gate[i + 2] += b.z; gate[i + 3] += b.w;
+          }
+        }
+      }
+    }
+    if constexpr (EPI == VX_EPI_BIAS_SWISH) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) z[i] = silu_f(z[i]);
+    } else if constexpr (EPI == VX_EPI_BIAS_GLU) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) z[i] *= sigmoid_f(gate[i]);
+    } else if constexpr (EPI == VX_EPI_BIAS_RESIDUAL) {
+      if (row_ok) {
+        if (p.residual_dtype == VX_BF16) {
+          const __nv_bfloat16* r = static_cast<const __nv_bfloat16*>(p.residual) + row * p.ldr + out_col0;
+          if (out_col0 + 32 <= p.N && ((reinterpret_cast<uintptr_t>(r) & 15) == 0)) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              const uint4 u = *reinterpret_cast<const uint4*>(r + i);  // plain load: may alias `out`
+              const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                z[i + 2 * j] = fmaf(p.alpha, z[i + 2 * j], __uint_as_float(w[j] << 16));
+                z[i + 2 * j + 1] = fmaf(p.alpha, z[i + 2 * j + 1], __uint_as_float(w[j] & 0xffff0000u));
+              }
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (out_col0 + i < p.N) z[i] = fmaf(p.alpha, z[i], __bfloat162float(r[i]));
+          }
+        } else {
+          const float* r = static_cast<const float*>(p.residual) + row * p.ldr + out_col0;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (out_col0 + i < p.N) z[i] = fmaf(p.alpha, z[i], r[i]);
+        }
+      }
+    }
+  }
+};
+
+// Direct global stores of one chunk: fp32 / bf16 with 16-byte vectors when aligned.
+__device__ __forceinline__ void store_chunk_direct(const GemmParams& p, const float (&z)[32],
+                                                   int64_t row, int64_t col0, int64_t n_out) {
+  if (p.out_dtype == VX_BF16) {
+    __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + row * p.ldo + col0;
+    if (col0 + 32 <= n_out && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 8) {
+        uint4 u;
+        u.x = pack_bf16x2(z[i], z[i + 1]);
+        u.y = pack_bf16x2(z[i + 2], z[i + 3]);
+        u.z = pack_bf16x2(z[i + 4], z[i + 5]);
+        u.w = pack_bf16x2(z[i + 6], z[i + 7]);
+        *reinterpret_cast<uint4*>(o + i) = u;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < n_out) o[i] = __float2bfloat16_rn(z[i]);
+    }
+  } else {
+    float* o = static_cast<float*>(p.out) + row * p.ldo + col0;
+    if (col0 + 32 <= n_out && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 4)
+        *reinterpret_cast<float4*>(o + i) = make_float4(z[i], z[i + 1], z[i + 2], z[i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < n_out) o[i] = z[i];
+    }
+  }
+}
+
+// Re-quantize one 32-column chunk of an output row to E2M1 (MX32: one UE8M0 scale; NV16: two
+// E4M3 scales) -- the same arithmetic as the stand-alone quantizer.  Returns the scale bytes
+// (1 or 2, little end first) for the caller to assemble into SF words.
+__device__ __forceinline__ uint32_t store_chunk_fp4(const GemmParams& p, const float (&z)[32],
+                                                    int64_t row, int64_t col0, float g_out,
+                                                    bool row_ok) {
+  uint32_t w[4];
+  uint32_t sbytes;
+  if (p.out_fmt == VX_FMT_MX32) {
+    float a = fabsf(z[0]);
+#pragma unroll
+    for (int i = 1; i < 32; ++i) a = fmaxf(a, fabsf(z[i]));
+    uint32_t byte;
+    float rcp;
+    ue8m0_from_amax(a, byte, rcp);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float v[8] = {z[8 * q], z[8 * q + 1], z[8 * q + 2], z[8 * q + 3],
+                          z[8 * q + 4], z[8 * q + 5], z[8 * q + 6], z[8 * q + 7]};
+      w[q] = e2m1_pack8(v, rcp);
+    }
+    sbytes = byte;
+  } else {
+    sbytes = 0;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float a = fabsf(z[16 * h]);
+#pragma unroll
+      for (int i = 1; i < 16; ++i) a = fmaxf(a, fabsf(z[16 * h + i]));
+      uint32_t byte;
+      float rcp;
+      nv16_block(a, g_out, byte, rcp);
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int b = 16 * h + 8 * q;
+        const float v[8] = {z[b], z[b + 1], z[b + 2], z[b + 3], z[b + 4], z[b + 5], z[b + 6], z[b + 7]};
+        w[2 * h + q] = e2m1_pack8(v, rcp);
+      }
+      sbytes |= byte << (8 * h);
+    }
+  }
+  if (row_ok) {
+    uint8_t* o = static_cast<uint8_t*>(p.out) + row * p.ldo + (col0 >> 1);
+    *reinterpret_cast<uint4*>(o) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  return sbytes;
+}
+
+// ---------------------------------------------------------------------------------------
+template <int KIND, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+              const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  SmemLayout& sm = *reinterpret_cast<SmemLayout*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  constexpr bool FP8 = (KIND == KIND_FP8);
+  constexpr int VEC = (KIND == KIND_FP4_VEC4) ? 4 : 2;
+  constexpr int APS = (KIND == KIND_FP4_VEC4) ? 4 : 2;  // SF atoms per operand per stage
+  constexpr bool GLU = (EPI == VX_EPI_BIAS_GLU);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int total_tiles = p.m_tiles * p.n_tiles;
+
+  // ---- set-up
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NSTAGE; ++s) {
+      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&sm.tmem_full[a], 1);
+      mbar_init(&sm.tmem_empty[a], 4);
+    }
+    sm.abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+    if (p.tma_store) prefetch_tmap(&tmap_out);
+  }
+  if (!FP8 && p.sf_unit) {
+    // unit scale factors (UE8M0 0x7F = 1.0) for the per-row-scaled format
+    uint32_t* u = reinterpret_cast<uint32_t*>(&sm.sfa[0][0]);
+    for (int i = threadIdx.x; i < 512 / 4; i += NUM_THREADS) u[i] = 0x7F7F7F7Fu;
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc(&sm.tmem_base, TM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sm.tmem_base;
+
+  if (warp == 0) {
+    // =========================== TMA producer ===========================
+    if (lane == 0) {
+      uint32_t s = 0, ph = 0;
+      const uint32_t sf_bytes = (FP8 || p.sf_unit) ? 0u : static_cast<uint32_t>(2 * APS * 512);
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int mb = t / p.n_tiles, nb = t - mb * p.n_tiles;
+        for (int ks = 0; ks < p.k_stages; ++ks) {
+          if (!mbar_wait(&sm.empty[s], ph ^ 1, p.status, 1)) { ok = false; break; }
+          mbar_expect_tx(&sm.full[s], 2 * TILE_BYTES + sf_bytes);
+          tma_load_2d(sm.a[s], &tmap_a, ks * STAGE_ROW_BYTES, mb * BM, &sm.full[s]);
+          tma_load_2d(sm.b[s], &tmap_b, ks * STAGE_ROW_BYTES, nb * BN, &sm.full[s]);
+          if (sf_bytes) {
+            bulk_load(sm.sfa[s], p.sfa + (static_cast<int64_t>(mb) * p.sf_kg + ks * APS) * 512,
+                      APS * 512, &sm.full[s]);
+            bulk_load(sm.sfb[s], p.sfb + (static_cast<int64_t>(nb) * p.sf_kg + ks * APS) * 512,
+                      APS * 512, &sm.full[s]);
+          }
+          if (++s == NSTAGE) { s = 0; ph ^= 1; }
+        }
+      }
+      if (!ok) sm.abort_flag = 1;
+    }
+  } else if (warp == 1) {
+    // =========================== MMA issuer ===========================
+    if (lane == 0) {
+      uint32_t s = 0, ph = 0;
+      uint32_t group = 0;  // accumulation groups issued (FP4: one per tile; FP8: one per stage)
+      bool ok = true;
+      const uint32_t idesc_base =
+          FP8 ? make_idesc_f8(BM, BN) : make_idesc_mxf4(BM, BN, p.sf_e8m0 != 0);
+      if (!FP8 && p.sf_unit) {
+        const uint64_t d = make_desc_sf(smem_u32(&sm.sfa[0][0]));
+        tc_cp_32x128b_warpx4(tmem_base + TM_SFA, d);
+        tc_cp_32x128b_warpx4(tmem_base + TM_SFB, d);
+      }
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        for (int ks = 0; ks < p.k_stages; ++ks) {
+          const bool new_group = FP8 || ks == 0;
+          const uint32_t acc = group & 1;
+          if (new_group) {
+            if (!mbar_wait(&sm.tmem_empty[acc], ((group >> 1) & 1) ^ 1, p.status, 2)) { ok = false; break; }
+            tc_fence_after();
+          }
+          if (!mbar_wait(&sm.full[s], ph, p.status, 3)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sm.a[s]);
+          const uint32_t b_addr = smem_u32(sm.b[s]);
+          const uint32_t d_tmem = tmem_base + TM_ACC0 + acc * BN;
+          if constexpr (FP8) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              mma_f8(d_tmem, make_desc_k128(a_addr + j * 32), make_desc_k128(b_addr + j * 32),
+                     idesc_base, j != 0);
+          } else {
+            if (!p.sf_unit) {
+#pragma unroll
+              for (int a = 0; a < APS; ++a) {
+                tc_cp_32x128b_warpx4(tmem_base + TM_SFA + a * 4, make_desc_sf(smem_u32(&sm.sfa[s][a * 512])));
+                tc_cp_32x128b_warpx4(tmem_base + TM_SFB + a * 4, make_desc_sf(smem_u32(&sm.sfb[s][a * 512])));
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint32_t sf_col, sf_id;
+              if (p.sf_unit) { sf_col = 0; sf_id = 0; }
+              else if constexpr (VEC == 2) { sf_col = (j >> 1) * 4; sf_id = (j & 1) * 2; }
+              else { sf_col = j * 4; sf_id = 0; }
+              mma_mxf4<VEC>(d_tmem, make_desc_k128(a_addr + j * 32), make_desc_k128(b_addr + j * 32),
+                            idesc_with_sf_id(idesc_base, sf_id, sf_id), tmem_base + TM_SFA + sf_col,
+                            tmem_base + TM_SFB + sf_col, (ks | j) != 0);
+            }
+          }
+          tc_commit(&sm.empty[s]);  // ring slot reusable once these MMAs have read it
+          if (FP8 || ks == p.k_stages - 1) {
+            tc_commit(&sm.tmem_full[acc]);
+            ++group;
+          }
+          if (++s == NSTAGE) { s = 0; ph ^= 1; }
+        }
+      }
+      if (!ok) sm.abort_flag = 1;
+    }
+  } else {
+    // =========================== epilogue ===========================
+    const int q = warp & 3;                       // TMEM lane quadrant of this warp
+    const int ew = warp - EPI_WARP0;              // staging buffer owner
+    const int64_t n_out = GLU ? p.N / 2 : p.N;    // logical output columns
+    const int out_tile_cols = GLU ? BN / 2 : BN;
+    uint32_t group = 0;
+    uint32_t store_buf = 0;
+    bool ok = true;
+    float g_ab = 1.0f, g_out = 1.0f;
+    if (p.a_amax && p.b_amax) g_ab = nv16_global(__ldg(p.a_amax)) * nv16_global(__ldg(p.b_amax));
+    if (p.out_amax) g_out = nv16_global(__ldg(p.out_amax));
+    const int kb_count = FP8 ? p.k_stages : 0;
+
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const int mb = t / p.n_tiles, nb = t - mb * p.n_tiles;
+      const int64_t row = static_cast<int64_t>(mb) * BM + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+
+      float racc[FP8 ? BN : 1];
+      if constexpr (FP8) {
+        // per-tile column scales of B into this warp's shared-memory table: fb[kb][col]
+        __syncwarp();
+        for (int c4 = 0; c4 < 4; ++c4) {
+          const int col = c4 * 32 + lane;
+          const int64_t n = static_cast<int64_t>(nb) * BN + col;
+          for (int kb = 0; kb < kb_count; ++kb)
+            sm.fb[ew][kb][col] = n < p.N ? __ldg(p.fb + n * kb_count + kb) : 0.0f;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < BN; ++i) racc[i] = 0.0f;
+        for (int kb = 0; kb < kb_count && ok; ++kb) {
+          const uint32_t acc = group & 1;
+          if (!mbar_wait(&sm.tmem_full[acc], (group >> 1) & 1, p.status, 4)) { ok = false; break; }
+          tc_fence_after();
+          const float sa = row_ok ? __ldg(p.fa + row * kb_count + kb) : 0.0f;
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+            uint32_t r[32];
+            tc_ld_32x32b_x32(lane_addr + TM_ACC0 + acc * BN + cc * 32, r);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              racc[cc * 32 + i] = fmaf(__uint_as_float(r[i]), sa * sm.fb[ew][kb][cc * 32 + i], racc[cc * 32 + i]);
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sm.tmem_empty[acc]);
+          ++group;
+        }
+        if (!ok) break;
+      } else {
+        const uint32_t acc = group & 1;
+        if (!mbar_wait(&sm.tmem_full[acc], (group >> 1) & 1, p.status, 4)) { ok = false; break; }
+        tc_fence_after();
+      }
+      const uint32_t acc_col = TM_ACC0 + ((FP8 ? 0u : (group & 1)) * BN);
+
+      float row_scale = 1.0f;
+      if (!FP8 && p.sf_unit) row_scale = row_ok ? ue8m0_to_float(__ldg(p.row_scale_u8 + row)) : 0.0f;
+
+      uint32_t sf_word[2] = {0, 0};  // FP4 output: scale bytes of this row for this tile
+      constexpr int NCHUNK = GLU ? 2 : 4;
+#pragma unroll
+      for (int cc = 0; cc < NCHUNK; ++cc) {
+        float z[32], gate[32];
+        if constexpr (FP8) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) z[i] = racc[cc * 32 + i];
+          if constexpr (GLU) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) gate[i] = racc[64 + cc * 32 + i];
+          }
+        } else {
+          uint32_t r[32];
+          tc_ld_32x32b_x32(lane_addr + acc_col + cc * 32, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) z[i] = __uint_as_float(r[i]);
+          if constexpr (GLU) {
+            tc_ld_32x32b_x32(lane_addr + acc_col + 64 + cc * 32, r);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) gate[i] = __uint_as_float(r[i]);
+          }
+          if (p.sf_unit) {
+            // reference order: raw * row_scale * col_scale
+            const uint8_t* cs = p.col_scale_u8 + static_cast<int64_t>(nb) * BN + cc * 32;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int64_t n = static_cast<int64_t>(nb) * BN + cc * 32 + i;
+              const float c = n < p.N ? ue8m0_to_float(__ldg(cs + i)) : 0.0f;
+              z[i] = z[i] * row_scale * c;
+            }
+          } else if (p.a_amax) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) z[i] *= g_ab;
+            if constexpr (GLU) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) gate[i] *= g_ab;
+            }
+          }
+        }
+        const int64_t acc_col0 = static_cast<int64_t>(nb) * BN + cc * 32;           // bias index
+        const int64_t out_col0 = static_cast<int64_t>(nb) * out_tile_cols + cc * 32;  // output column
+        ChunkOut<EPI>::apply(p, z, gate, row, acc_col0, acc_col0 + 64, out_col0, row_ok);
+
+        if (p.out_dtype == VX_FP4) {
+          const uint32_t sb = store_chunk_fp4(p, z, row, out_col0, g_out, row_ok && out_col0 < n_out);
+          if (p.out_fmt == VX_FMT_MX32) sf_word[0] |= sb << (8 * cc);
+          else sf_word[cc >> 1] |= sb << (16 * (cc & 1));
+        } else if (p.tma_store) {
+          // stage 32 rows x 128 bytes per box with the 128-byte swizzle, then one TMA store
+          const int elt = p.out_dtype == VX_BF16 ? 2 : 4;
+          const int chunks_per_box = elt == 2 ? 2 : 1;  // 64 bf16 or 32 fp32 columns per box
+          const int sub = cc % chunks_per_box;
+          if (sub == 0) {
+            if (lane == 0) tma_store_wait_read<1>();  // the buffer used two boxes ago is free
+            __syncwarp();
+          }
+          uint8_t* buf = sm.staging[ew][store_buf];
+          if (elt == 2) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int c16 = sub * 4 + v;
+              uint4 u;
+              u.x = pack_bf16x2(z[8 * v], z[8 * v + 1]);
+              u.y = pack_bf16x2(z[8 * v + 2], z[8 * v + 3]);
+              u.z = pack_bf16x2(z[8 * v + 4], z[8 * v + 5]);
+              u.w = pack_bf16x2(z[8 * v + 6], z[8 * v + 7]);
+              *reinterpret_cast<uint4*>(buf + lane * 128 + ((c16 ^ (lane & 7)) << 4)) = u;
+            }
+          } else {
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+              *reinterpret_cast<float4*>(buf + lane * 128 + ((v ^ (lane & 7)) << 4)) =
+                  make_float4(z[4 * v], z[4 * v + 1], z[4 * v + 2], z[4 * v + 3]);
+          }
+          if (sub == chunks_per_box - 1) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            const int x = static_cast<int>(out_col0 - sub * 32);
+            if (lane == 0 && static_cast<int64_t>(mb) * BM + q * 32 < p.M && x < n_out) {
+              tma_store_2d(&tmap_out, x, mb * BM + q * 32, buf);
+              tma_store_commit();
+            }
+            store_buf ^= 1;
+          }
+        } else if (row_ok) {
+          store_chunk_direct(p, z, row, out_col0, n_out);
+        }
+      }
+      if constexpr (!FP8) {
+        // accumulator fully read: hand the TMEM buffer back to the MMA warp
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.tmem_empty[group & 1]);
+        ++group;
+      }
+      if (p.out_dtype == VX_FP4 && row_ok) {
+        const int words = p.out_fmt == VX_FMT_MX32 ? 1 : 2;
+        const int64_t kg0 = static_cast<int64_t>(nb) * words;
+        for (int w = 0; w < words; ++w) {
+          const int64_t kg = kg0 + w;
+          if (kg * 4 * (p.out_fmt == VX_FMT_MX32 ? 32 : 16) >= n_out) break;
+          *reinterpret_cast<uint32_t*>(p.out_sf + ((row >> 7) * p.out_sf_kg + kg) * 512 +
+                                       (row & 31) * 16 + ((row >> 5) & 3) * 4) = sf_word[w];
+          if (p.out_scales) {
+            const int64_t nblk = n_out / (p.out_fmt == VX_FMT_MX32 ? 32 : 16);
+            *reinterpret_cast<uint32_t*>(p.out_scales + row * nblk + kg * 4) = sf_word[w];
+          }
+        }
+      }
+    }
+    if (p.tma_store && lane == 0) tma_store_wait_all<0>();
+    if (!ok) sm.abort_flag = 1;
+  }
+
+  // ---- tear-down
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// MMA peak probe: each CTA issues `iters` MMAs on resident (zero) operands, no memory traffic.
+template <int KIND, int NT>
+__global__ void __launch_bounds__(128, 1) mma_probe_kernel(int iters, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* a = base;                   // 128 rows x 128 B
+  uint8_t* b = base + TILE_BYTES;      // NT rows x 128 B
+  uint8_t* sf = b + NT * 128;          // one SF atom (unit scales)
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_slot;
+  for (int i = threadIdx.x; i < (TILE_BYTES + NT * 128) / 4; i += blockDim.x)
+    reinterpret_cast<uint32_t*>(base)[i] = 0;
+  for (int i = threadIdx.x; i < 128; i += blockDim.x) reinterpret_cast<uint32_t*>(sf)[i] = 0x7F7F7F7Fu;
+  fence_proxy_async_smem();
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+  }
+  if (threadIdx.x < 32) {
+    tmem_alloc(&tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tb = tmem_slot;
+  if (threadIdx.x == 0) {
+    const uint32_t a_addr = smem_u32(a), b_addr = smem_u32(b);
+    if (KIND != KIND_FP8) {
+      const uint64_t d = make_desc_sf(smem_u32(sf));
+      for (int c = 0; c < 8; ++c) tc_cp_32x128b_warpx4(tb + 480 + c * 4, d);
+    }
+    const uint32_t idesc = KIND == KIND_FP8 ? make_idesc_f8(128, NT) : make_idesc_mxf4(128, NT, true);
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t d_tmem = tb;
+        if (KIND == KIND_FP8)
+          mma_f8(d_tmem, make_desc_k128(a_addr + j * 32), make_desc_k128(b_addr + j * 32), idesc, 1);
+        else
+          mma_mxf4<2>(d_tmem, make_desc_k128(a_addr + j * 32), make_desc_k128(b_addr + j * 32), idesc,
+                      tb + 480, tb + 480, 1);
+      }
+    }
+    tc_commit(&bar);
+    mbar_wait(&bar, 0, status, 9);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    tc_fence_after();
+    tmem_dealloc(tb, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Host side
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// 2-D row-major tensor [rows, cols] of `elt`-byte elements, row pitch `pitch_bytes`; box =
+// box_cols x box_rows with a 128-byte inner extent and the 128-byte swizzle.
+int make_tmap(CUtensorMap* m, CUtensorMapDataType dt, int elt, const void* ptr, int64_t rows,
+              int64_t cols, int64_t pitch_bytes, int box_cols, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return fail(-2, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_bytes)};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  (void)elt;
+  const CUresult r = fn(m, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(-3, "cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
+  return 0;
+}
+
+int* cached_status_ptr() {
+  static int* cache[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return device_status_ptr();
+  if (!cache[dev]) cache[dev] = device_status_ptr();
+  return cache[dev];
+}
+
+constexpr size_t kSmemBytes = sizeof(SmemLayout) + 1024;
+
+template <int KIND, int EPI>
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const GemmParams& p,
+           cudaStream_t st) {
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(bsgemm_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(kSmemBytes));
+  });
+  if (attr_err != cudaSuccess) return fail(static_cast<int>(attr_err), "cudaFuncSetAttribute: %s", cudaGetErrorString(attr_err));
+  int dev = 0, sms = 0;
+  VX_CUDA_OK(cudaGetDevice(&dev));
+  static int sm_cache[64] = {};
+  if (dev >= 0 && dev < 64 && sm_cache[dev]) sms = sm_cache[dev];
+  else {
+    VX_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    if (dev >= 0 && dev < 64) sm_cache[dev] = sms;
+  }
+  const int tiles = p.m_tiles * p.n_tiles;
+  const int grid = tiles < sms ? tiles : sms;
+  bsgemm_kernel<KIND, EPI><<<grid, NUM_THREADS, kSmemBytes, st>>>(ta, tb, to, p);
+  VX_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+template <int KIND>
+int dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to,
+                 const GemmParams& p, cudaStream_t st) {
+  switch (epi) {
+    case VX_EPI_NONE: return launch<KIND, VX_EPI_NONE>(ta, tb, to, p, st);
+    case VX_EPI_BIAS: return launch<KIND, VX_EPI_BIAS>(ta, tb, to, p, st);
+    case VX_EPI_BIAS_SWISH: return launch<KIND, VX_EPI_BIAS_SWISH>(ta, tb, to, p, st);
+    case VX_EPI_BIAS_GLU: return launch<KIND, VX_EPI_BIAS_GLU>(ta, tb, to, p, st);
+    case VX_EPI_BIAS_RESIDUAL: return launch<KIND, VX_EPI_BIAS_RESIDUAL>(ta, tb, to, p, st);
+    default: return fail(-1, "unknown epilogue %d", epi);
+  }
+}
+
+}  // namespace
+}  // namespace vx
+
+extern "C" {
+
+int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
+  using namespace vx;
+  if (!d) return fail(-1, "desc must not be NULL");
+  if (d->struct_size != static_cast<int32_t>(sizeof(vx_gemm_desc)))
+    return fail(-1, "vx_gemm_desc.struct_size=%d, expected %d", d->struct_size, (int)sizeof(vx_gemm_desc));
+  const int fmt = d->fmt;
+  if (!fmt_valid(fmt) || fmt == VX_FMT_BLK16_B) return fail(-1, "unsupported GEMM format %d", fmt);
+  const int64_t M = d->M, N = d->N, K = d->K;
+  if (M < 0 || N < 0 || K < 0) return fail(-1, "negative shape");
+  if (M == 0 || N == 0) return 0;
+  if (K == 0) return fail(-1, "K must be positive");
+  const bool fp8 = fmt == VX_FMT_FP8_1X128;
+  const int64_t row_bytes = fp8 ? K : K / 2;
+  if (fp8 ? (K % 128 != 0) : (K % 32 != 0))
+    return fail(-1, "K=%lld must be a multiple of %d", (long long)K, fp8 ? 128 : 32);
+  if (fp8 && K > FP8_MAX_KB * 128) return fail(-1, "FP8 path supports K <= %d", FP8_MAX_KB * 128);
+  if (!d->a_codes || !d->b_codes || !d->out) return fail(-1, "a_codes, b_codes and out must not be NULL");
+  if (!aligned16(d->a_codes) || !aligned16(d->b_codes) || d->lda % 16 != 0 || d->ldb % 16 != 0 ||
+      d->lda < row_bytes || d->ldb < row_bytes)
+    return fail(-1, "operand rows must be 16-byte aligned and at least %lld bytes", (long long)row_bytes);
+  if (!d->a_scales || !d->b_scales) return fail(-1, "a_scales and b_scales must not be NULL");
+  if (fmt == VX_FMT_NV16 && (!d->a_amax || !d->b_amax)) return fail(-1, "NV16 needs a_amax and b_amax");
+  if (fmt_has_sf(fmt) && (!aligned16(d->a_scales) || !aligned16(d->b_scales)))
+    return fail(-1, "SF atoms must be 16-byte aligned");
+  const int epi = d->epilogue;
+  if (epi < VX_EPI_NONE || epi > VX_EPI_BIAS_RESIDUAL) return fail(-1, "unknown epilogue %d", epi);
+  if (d->out_dtype != VX_F32 && d->out_dtype != VX_BF16 && d->out_dtype != VX_FP4)
+    return fail(-1, "unknown out_dtype %d", d->out_dtype);
+  if (d->bias && (reinterpret_cast<uintptr_t>(d->bias) & 15)) return fail(-1, "bias must be 16-byte aligned");
+  if (epi == VX_EPI_BIAS_GLU && (N % BN != 0)) return fail(-1, "GLU needs N %% 128 == 0 (interleaved halves)");
+  if (epi == VX_EPI_BIAS_RESIDUAL) {
+    if (!d->residual) return fail(-1, "residual must not be NULL");
+    if (d->residual_dtype != VX_F32 && d->residual_dtype != VX_BF16) return fail(-1, "bad residual dtype");
+  }
+  const int64_t n_out = epi == VX_EPI_BIAS_GLU ? N / 2 : N;
+
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.m_tiles = static_cast<int>((M + BM - 1) / BM);
+  p.n_tiles = static_cast<int>((N + BN - 1) / BN);
+  p.k_stages = static_cast<int>((row_bytes + STAGE_ROW_BYTES - 1) / STAGE_ROW_BYTES);
+  if (static_cast<int64_t>(p.m_tiles) * p.n_tiles > 0x7fffffff) return fail(-1, "too many tiles");
+  p.sf_kg = fmt_has_sf(fmt) ? sf_kgroups(fmt, K) : 0;
+  p.sf_unit = fmt == VX_FMT_ROWSCALE;
+  p.sf_e8m0 = fmt != VX_FMT_NV16;
+  if (fmt == VX_FMT_ROWSCALE) {
+    p.row_scale_u8 = static_cast<const uint8_t*>(d->a_scales);
+    p.col_scale_u8 = static_cast<const uint8_t*>(d->b_scales);
+  } else if (fp8) {
+    p.fa = static_cast<const float*>(d->a_scales);
+    p.fb = static_cast<const float*>(d->b_scales);
+  } else {
+    p.sfa = static_cast<const uint8_t*>(d->a_scales);
+    p.sfb = static_cast<const uint8_t*>(d->b_scales);
+  }
+  if (fmt == VX_FMT_NV16) { p.a_amax = d->a_amax; p.b_amax = d->b_amax; }
+  p.out_dtype = d->out_dtype;
+  p.out = d->out; p.ldo = d->ldo;
+  p.bias = d->bias;
+  p.residual = d->residual; p.residual_dtype = d->residual_dtype; p.ldr = d->ldr; p.alpha = d->alpha;
+  p.status = cached_status_ptr();
+
+  if (d->out_dtype == VX_FP4) {
+    if (d->out_fmt != VX_FMT_MX32 && d->out_fmt != VX_FMT_NV16) return fail(-1, "FP4 output: out_fmt must be MX32 or NV16");
+    if (epi == VX_EPI_BIAS_GLU || epi == VX_EPI_BIAS_RESIDUAL) return fail(-1, "FP4 output supports NONE / BIAS / BIAS_SWISH");
+    if (!d->out_scales_sf || !aligned16(d->out_scales_sf)) return fail(-1, "FP4 output needs out_scales_sf (16-byte aligned)");
+    if (d->out_fmt == VX_FMT_NV16 && !d->out_amax) return fail(-1, "NV16 output needs out_amax");
+    if (N % BN != 0) return fail(-1, "FP4 output needs N %% 128 == 0");
+    if (!aligned16(d->out) || d->ldo % 16 != 0 || d->ldo < N / 2) return fail(-1, "FP4 output rows must be 16-byte aligned");
+    p.out_fmt = d->out_fmt;
+    p.out_sf = static_cast<uint8_t*>(d->out_scales_sf);
+    p.out_scales = static_cast<uint8_t*>(d->out_scales);
+    p.out_sf_kg = sf_kgroups(d->out_fmt, N);
+    p.out_amax = d->out_amax;
+    if (p.out_scales && (reinterpret_cast<uintptr_t>(p.out_scales) & 3)) return fail(-1, "out_scales must be 4-byte aligned");
+  } else {
+    if (d->ldo < n_out) return fail(-1, "ldo=%lld < output columns %lld", (long long)d->ldo, (long long)n_out);
+  }
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (d->out_dtype == VX_FP4 && (M % BM != 0)) {
+    // SF rows of the last partial tile must read as zero
+    VX_CUDA_OK(cudaMemsetAsync(p.out_sf, 0, static_cast<size_t>(vx_sf_bytes(d->out_fmt, M, N)), st));
+  }
+
+  CUtensorMap ta, tb, to;
+  int rc = make_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d->a_codes, M, row_bytes, d->lda, 128, BM);
+  if (rc) return rc;
+  rc = make_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, d->b_codes, N, row_bytes, d->ldb, 128, BN);
+  if (rc) return rc;
+  const int oelt = d->out_dtype == VX_BF16 ? 2 : 4;
+  p.tma_store = 0;
+  if (d->out_dtype != VX_FP4 && !(d->flags & VX_GEMM_DIRECT_STORE) && aligned16(d->out) &&
+      (d->ldo * oelt) % 16 == 0) {
+    rc = make_tmap(&to, d->out_dtype == VX_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                   oelt, d->out, M, n_out, d->ldo * oelt, 128 / oelt, 32);
+    if (rc) return rc;
+    p.tma_store = 1;
+  } else {
+    to = ta;  // unused by the kernel
+  }
+
+  if (fp8) return dispatch_epi<KIND_FP8>(epi, ta, tb, to, p, st);
+  if (fmt == VX_FMT_ROWSCALE || fmt == VX_FMT_MX32) return dispatch_epi<KIND_FP4_VEC2>(epi, ta, tb, to, p, st);
+  return dispatch_epi<KIND_FP4_VEC4>(epi, ta, tb, to, p, st);
+}
+
+int vx_mma_peak_probe(int kind, int n_tile, int iters, float* tflops_out) {
+  using namespace vx;
+  if (!tflops_out || iters <= 0) return fail(-1, "bad arguments");
+  if (kind != 0 && kind != 1) return fail(-1, "kind must be 0 (FP4) or 1 (FP8)");
+  if (n_tile != 128 && n_tile != 256) return fail(-1, "n_tile must be 128 or 256");
+  int dev = 0, sms = 0;
+  VX_CUDA_OK(cudaGetDevice(&dev));
+  VX_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const size_t smem = TILE_BYTES + 256 * 128 + 512 + 1024;
+  void (*k)(int, int*) = nullptr;
+  if (kind == 0) k = n_tile == 128 ? mma_probe_kernel<KIND_FP4_VEC2, 128> : mma_probe_kernel<KIND_FP4_VEC2, 256>;
+  else k = n_tile == 128 ? mma_probe_kernel<KIND_FP8, 128> : mma_probe_kernel<KIND_FP8, 256>;
+  VX_CUDA_OK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  cudaEvent_t e0, e1;
+  VX_CUDA_OK(cudaEventCreate(&e0));
+  VX_CUDA_OK(cudaEventCreate(&e1));
+  int* status = cached_status_ptr();
+  k<<<sms, 128, smem>>>(iters / 8 + 1, status);  // warm-up
+  VX_CUDA_OK(cudaEventRecord(e0));
+  k<<<sms, 128, smem>>>(iters, status);
+  VX_CUDA_OK(cudaEventRecord(e1));
+  VX_CUDA_OK(cudaEventSynchronize(e1));
+  VX_CUDA_OK(cudaGetLastError());
+  float ms = 0.f;
+  VX_CUDA_OK(cudaEventElapsedTime(&ms, e0, e1));
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  const double k_per_mma = kind == 0 ? 64.0 : 32.0;
+  const double flops = 2.0 * 128.0 * n_tile * k_per_mma * 4.0 * iters * sms;
+  *tflops_out = static_cast<float>(flops / (ms * 1e-3) / 1e12);
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,479 @@
+// Activation / weight quantize + pack kernels (optionally fused behind LayerNorm), the
+// tensor amax reduction NV16 needs, and the natural -> SF-atom scale relayout.
+//
+// Rounding rules (bit-exact contract with the reference quantizers,
+// veloxvoice/kernels/ops/triton_ops.py:34-89 and :228-258):
+//   UE8M0:  s = max(amax / 6, 1e-6); e = ceil(log2 s) taken from the fp32 bit pattern;
+//           byte = clamp(e + 127, 0, 255); values are normalised by exactly 2^e.
+//   E2M1:   magnitude code = number of thresholds {0.25, 0.75, 1.25, 1.75, 2.5, 3.5} strictly
+//           exceeded (largest code emitted is 6); sign bit = (q < 0); low nibble = even k.
+// NV16 and FP8_1X128 have no reference counterpart; their arithmetic is spelled out at
+// nv16_block() / fp8_block() and uses only correctly rounded IEEE operations so that a CPU
+// restatement reproduces every byte.
+//
+// Work decomposition: one warp per row (per row PAIR for BLK16_A).  A row is cut into chunks
+// of 256 elements; in a chunk lane l owns elements [8 l, 8 l + 8): a bf16 row is read with one
+// 16-byte load per lane (512 contiguous bytes per warp), codes leave as one 32-bit store per
+// lane (128 contiguous bytes per warp).  Block maxima are warp-shuffle reductions over the
+// 2 / 4 / 16 lanes that share a scale.
+
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "vx_common.cuh"
+#include "vx_quant_math.cuh"
+
+namespace vx {
+namespace {
+
+struct QuantParams {
+  const void* x;
+  int64_t M, K, ldx;
+  uint8_t* codes;
+  int64_t ldc;
+  void* scales;   // natural layout or nullptr
+  uint8_t* sf;    // SF atoms or nullptr
+  int64_t sf_kg;  // atoms per 128-row tile
+  const float* amax;
+  const float* gamma;
+  const float* beta;
+  float eps;
+  void* y;
+  int y_bf16;
+  int64_t ldy;
+};
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p));
+  const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__device__ __forceinline__ float warp_max(float a) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+  return a;
+}
+
+__device__ __forceinline__ int64_t sf_offset(int64_t row, int64_t kgroup, int64_t sf_kg) {
+  return ((row >> 7) * sf_kg + kgroup) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4;
+}
+
+// Quantize one 256-element chunk of RP rows held in registers and store codes + scales.
+// `row_rcp` / `row_byte` are used by ROWSCALE only (the row maximum is known beforehand).
+template <int FMT, int RP>
+__device__ __forceinline__ void quant_chunk(const QuantParams& p, int64_t row0, int c, int lane,
+                                            float (&v)[RP][8], float row_rcp, float g) {
+  const int64_t k0 = static_cast<int64_t>(c) * 256 + lane * 8;
+  const bool active = k0 < p.K;
+  float a = amax8(v[0]);
+  if constexpr (RP == 2) a = fmaxf(a, amax8(v[1]));
+
+  if constexpr (FMT == VX_FMT_ROWSCALE) {
+    if (active) {
+      *reinterpret_cast<uint32_t*>(p.codes + row0 * p.ldc + (k0 >> 1)) = e2m1_pack8(v[0], row_rcp);
+    }
+  } else if constexpr (FMT == VX_FMT_FP8_1X128) {
+#pragma unroll
+    for (int o = 1; o < 16; o <<= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+    float scale, rcp;
+    fp8_block(a, scale, rcp);
+    if (active) {
+      *reinterpret_cast<uint2*>(p.codes + row0 * p.ldc + k0) = fp8_pack8(v[0], rcp);
+      if (p.scales && (lane & 15) == 0)
+        static_cast<float*>(p.scales)[row0 * (p.K >> 7) + (k0 >> 7)] = scale;
+    }
+  } else {
+    constexpr int BLK = (FMT == VX_FMT_MX32) ? 32 : 16;
+    constexpr int LPB = BLK / 8;  // lanes per block
+#pragma unroll
+    for (int o = 1; o < LPB; o <<= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+    uint32_t byte;
+    float rcp;
+    if constexpr (FMT == VX_FMT_NV16) nv16_block(a, g, byte, rcp);
+    else ue8m0_from_amax(a, byte, rcp);
+    if (!active) byte = 0;
+    const int64_t kb = k0 / BLK;  // block index along K
+#pragma unroll
+    for (int r = 0; r < RP; ++r) {
+      if (active)
+        *reinterpret_cast<uint32_t*>(p.codes + (row0 + r) * p.ldc + (k0 >> 1)) = e2m1_pack8(v[r], rcp);
+    }
+    if (p.scales && active && (lane % LPB) == 0) {
+      uint8_t* s = static_cast<uint8_t*>(p.scales);
+      if constexpr (FMT == VX_FMT_BLK16_A) s[kb * (p.M >> 1) + (row0 >> 1)] = byte;
+      else if constexpr (FMT == VX_FMT_BLK16_B) s[kb * p.M + row0] = byte;
+      else s[row0 * (p.K / BLK) + kb] = byte;
+    }
+    if (p.sf) {
+      // assemble the 4 scale bytes of one k-group into a word held by every lane of the group
+      uint32_t w = byte << (8 * ((lane / LPB) & 3));
+#pragma unroll
+      for (int o = LPB; o < 4 * LPB; o <<= 1) w |= __shfl_xor_sync(0xffffffffu, w, o);
+      if (active && (lane % (4 * LPB)) == 0) {
+        const int64_t kg = kb >> 2;
+#pragma unroll
+        for (int r = 0; r < RP; ++r)
+          *reinterpret_cast<uint32_t*>(p.sf + sf_offset(row0 + r, kg, p.sf_kg)) = w;
+      }
+    }
+  }
+}
+
+// Streaming quantizer (no LayerNorm): any K % 8 == 0.
+template <typename T, int FMT>
+__global__ void __launch_bounds__(256) quant_kernel(const QuantParams p) {
+  constexpr int RP = (FMT == VX_FMT_BLK16_A) ? 2 : 1;
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  const int64_t nunits = p.M / RP;
+  const int nchunks = static_cast<int>((p.K + 255) >> 8);
+  const T* x = static_cast<const T*>(p.x);
+  float g = 1.0f;
+  if constexpr (FMT == VX_FMT_NV16) g = nv16_global(__ldg(p.amax));
+
+  for (int64_t u = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+       u < nunits; u += warps) {
+    const int64_t row0 = u * RP;
+    float row_rcp = 0.0f;
+    if constexpr (FMT == VX_FMT_ROWSCALE) {
+      float a = 0.0f;
+      for (int c = 0; c < nchunks; ++c) {
+        const int64_t k0 = static_cast<int64_t>(c) * 256 + lane * 8;
+        if (k0 < p.K) {
+          float t[8];
+          load8(x + row0 * p.ldx + k0, t);
+          a = fmaxf(a, amax8(t));
+        }
+      }
+      a = warp_max(a);
+      uint32_t byte;
+      ue8m0_from_amax(a, byte, row_rcp);
+      if (p.scales && lane == 0) static_cast<uint8_t*>(p.scales)[row0] = static_cast<uint8_t>(byte);
+    }
+    for (int c = 0; c < nchunks; ++c) {
+      const int64_t k0 = static_cast<int64_t>(c) * 256 + lane * 8;
+      float v[RP][8];
+#pragma unroll
+      for (int r = 0; r < RP; ++r) {
+        if (k0 < p.K) load8(x + (row0 + r) * p.ldx + k0, v[r]);
+        else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[r][j] = 0.0f;
+        }
+      }
+      quant_chunk<FMT, RP>(p, row0, c, lane, v, row_rcp, g);
+    }
+  }
+}
+
+// LayerNorm + quantize, row resident in registers (CH chunks of 256 elements, K <= 256 CH).
+// Statistics follow the reference kernel's formula (velox_layernorm.cu:52-57):
+//   mean = sum / K; var = max(sumsq / K - mean^2, 0); y = (x - mean) * rstd * gamma + beta
+// with every operation individually rounded (no FMA contraction), rstd = 1 / sqrt(var + eps)
+// correctly rounded, lane-sequential partial sums and a butterfly (xor 16, 8, 4, 2, 1) warp
+// reduction -- an order a CPU restatement can follow exactly.
+template <typename T, int FMT, int CH>
+__global__ void __launch_bounds__(256) ln_quant_kernel(const QuantParams p) {
+  constexpr int RP = (FMT == VX_FMT_BLK16_A) ? 2 : 1;
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  const int64_t nunits = p.M / RP;
+  const T* x = static_cast<const T*>(p.x);
+  const float k_f = static_cast<float>(p.K);
+  float g = 1.0f;
+  if constexpr (FMT == VX_FMT_NV16) g = nv16_global(__ldg(p.amax));
+
+  for (int64_t u = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+       u < nunits; u += warps) {
+    const int64_t row0 = u * RP;
+    float v[CH][RP][8];
+#pragma unroll
+    for (int r = 0; r < RP; ++r) {
+      float s = 0.0f, sq = 0.0f;
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        const int64_t k0 = static_cast<int64_t>(c) * 256 + lane * 8;
+        if (k0 < p.K) load8(x + (row0 + r) * p.ldx + k0, v[c][r]);
+        else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[c][r][j] = 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          s = __fadd_rn(s, v[c][r][j]);
+          sq = __fadd_rn(sq, __fmul_rn(v[c][r][j], v[c][r][j]));
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, o));
+        sq = __fadd_rn(sq, __shfl_xor_sync(0xffffffffu, sq, o));
+      }
+      const float mean = __fdiv_rn(s, k_f);
+      const float var = fmaxf(__fsub_rn(__fdiv_rn(sq, k_f), __fmul_rn(mean, mean)), 0.0f);
+      const float rstd = __frcp_rn(__fsqrt_rn(__fadd_rn(var, p.eps)));
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        const int64_t k0 = static_cast<int64_t>(c) * 256 + lane * 8;
+        if (k0 < p.K) {
+          float ga[8], be[8];
+          load8(p.gamma + k0, ga);
+          load8(p.beta + k0, be);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            v[c][r][j] = __fadd_rn(
+                __fmul_rn(__fmul_rn(__fsub_rn(v[c][r][j], mean), rstd), ga[j]), be[j]);
+          if (p.y) {
+            if (p.y_bf16) {
+              uint4 u;
+              u.x = pack2_bf16(v[c][r][0], v[c][r][1]);
+              u.y = pack2_bf16(v[c][r][2], v[c][r][3]);
+              u.z = pack2_bf16(v[c][r][4], v[c][r][5]);
+              u.w = pack2_bf16(v[c][r][6], v[c][r][7]);
+              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.y) + (row0 + r) * p.ldy + k0) = u;
+            } else {
+              float4* yp = reinterpret_cast<float4*>(static_cast<float*>(p.y) + (row0 + r) * p.ldy + k0);
+              yp[0] = make_float4(v[c][r][0], v[c][r][1], v[c][r][2], v[c][r][3]);
+              yp[1] = make_float4(v[c][r][4], v[c][r][5], v[c][r][6], v[c][r][7]);
+            }
+          }
+        }
+      }
+    }
+    if (!p.codes) continue;  // plain LayerNorm
+    float row_rcp = 0.0f;
+    if constexpr (FMT == VX_FMT_ROWSCALE) {
+      float a = 0.0f;
+#pragma unroll
+      for (int c = 0; c < CH; ++c) a = fmaxf(a, amax8(v[c][0]));
+      a = warp_max(a);
+      uint32_t byte;
+      ue8m0_from_amax(a, byte, row_rcp);
+      if (p.scales && lane == 0) static_cast<uint8_t*>(p.scales)[row0] = static_cast<uint8_t>(byte);
+    }
+#pragma unroll
+    for (int c = 0; c < CH; ++c) quant_chunk<FMT, RP>(p, row0, c, lane, v[c], row_rcp, g);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) amax_kernel(const T* x, int64_t M, int64_t K, int64_t ldx,
+                                                   float* out) {
+  const int64_t per_row = K >> 3;
+  const int64_t total = M * per_row;
+  float a = 0.0f;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / per_row, k0 = (i - r * per_row) << 3;
+    float t[8];
+    load8(x + r * ldx + k0, t);
+    a = fmaxf(a, amax8(t));
+  }
+  a = warp_max(a);
+  // non-negative floats order like their bit patterns
+  if ((threadIdx.x & 31) == 0) atomicMax(reinterpret_cast<unsigned int*>(out), __float_as_uint(a));
+}
+
+// natural scale layout -> SF atoms.  One thread per (row, k-group).
+__global__ void sf_relayout_kernel(int fmt, const uint8_t* __restrict__ s, int64_t R, int64_t nkb,
+                                   uint8_t* __restrict__ sf, int64_t sf_kg) {
+  const int64_t ngroups = (nkb + 3) >> 2;
+  const int64_t total = R * ngroups;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t row = i % R, kg = i / R;
+    uint32_t w = 0;
+    for (int j = 0; j < 4; ++j) {
+      const int64_t kb = kg * 4 + j;
+      if (kb >= nkb) break;
+      uint32_t b;
+      if (fmt == VX_FMT_BLK16_A) b = s[kb * (R >> 1) + (row >> 1)];
+      else if (fmt == VX_FMT_BLK16_B) b = s[kb * R + row];
+      else b = s[row * nkb + kb];
+      w |= b << (8 * j);
+    }
+    *reinterpret_cast<uint32_t*>(sf + sf_offset(row, kg, sf_kg)) = w;
+  }
+}
+
+int grid_for_rows(int64_t units) {
+  // 8 warps per block; enough blocks to fill 148 SMs x 8 resident blocks, grid-stride beyond.
+  const int64_t blocks = (units + 7) / 8;
+  const int64_t cap = 148 * 8;
+  return static_cast<int>(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
+}
+
+template <typename T, int FMT>
+void launch_quant(const QuantParams& p, bool ln, cudaStream_t st) {
+  constexpr int RP = (FMT == VX_FMT_BLK16_A) ? 2 : 1;
+  const int grid = grid_for_rows(p.M / RP);
+  if (!ln) {
+    quant_kernel<T, FMT><<<grid, 256, 0, st>>>(p);
+  } else if (p.K <= 512) {
+    ln_quant_kernel<T, FMT, 2><<<grid, 256, 0, st>>>(p);
+  } else if (p.K <= 1024) {
+    ln_quant_kernel<T, FMT, 4><<<grid, 256, 0, st>>>(p);
+  } else {
+    ln_quant_kernel<T, FMT, 8><<<grid, 256, 0, st>>>(p);
+  }
+}
+
+template <typename T>
+int dispatch_fmt(int fmt, const QuantParams& p, bool ln, cudaStream_t st) {
+  switch (fmt) {
+    case VX_FMT_ROWSCALE: launch_quant<T, VX_FMT_ROWSCALE>(p, ln, st); break;
+    case VX_FMT_BLK16_A: launch_quant<T, VX_FMT_BLK16_A>(p, ln, st); break;
+    case VX_FMT_BLK16_B: launch_quant<T, VX_FMT_BLK16_B>(p, ln, st); break;
+    case VX_FMT_MX32: launch_quant<T, VX_FMT_MX32>(p, ln, st); break;
+    case VX_FMT_NV16: launch_quant<T, VX_FMT_NV16>(p, ln, st); break;
+    case VX_FMT_FP8_1X128: launch_quant<T, VX_FMT_FP8_1X128>(p, ln, st); break;
+    default: return fail(-1, "unknown format %d", fmt);
+  }
+  VX_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+int quantize_common(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, int fmt,
+                    void* codes, int64_t ldc, void* scales, void* scales_sf, const float* amax,
+                    bool ln, const float* gamma, const float* beta, float eps, void* y,
+                    int y_dtype, int64_t ldy, void* stream) {
+  if (!fmt_valid(fmt)) return fail(-1, "unknown format %d", fmt);
+  if (x_dtype != VX_F32 && x_dtype != VX_BF16) return fail(-1, "x_dtype must be VX_F32 or VX_BF16");
+  if (M < 0 || K < 0) return fail(-1, "negative shape");
+  if (M == 0 || K == 0) return 0;
+  if (!x) return fail(-1, "x must not be NULL");
+  if (!codes && !(ln && y)) return fail(-1, "codes must not be NULL");
+  if (!codes) { scales = nullptr; scales_sf = nullptr; if (fmt == VX_FMT_NV16) fmt = VX_FMT_MX32; ldc = 1 << 30; codes = nullptr; }
+  const int blk = fmt_block(fmt);
+  if (K % 8 != 0 || (blk && K % blk != 0))
+    return fail(-1, "K=%lld must be a multiple of 8 and of the scale block (%d)", (long long)K, blk);
+  if (fmt == VX_FMT_BLK16_A && (M & 1)) return fail(-1, "BLK16_A needs an even row count");
+  const int64_t esz = x_dtype == VX_BF16 ? 2 : 4;
+  if (ldx < K || !aligned16(x) || (ldx * esz) % 16 != 0)
+    return fail(-1, "x rows must be 16-byte aligned (ldx=%lld)", (long long)ldx);
+  const int64_t row_bytes = fmt == VX_FMT_FP8_1X128 ? K : K / 2;
+  if (codes && (ldc < row_bytes || ldc % 4 != 0 || (reinterpret_cast<uintptr_t>(codes) & 7) != 0 ||
+      (fmt == VX_FMT_FP8_1X128 && ldc % 8 != 0)))
+    return fail(-1, "codes rows must be >= %lld bytes and 4/8-byte aligned (ldc=%lld)",
+                (long long)row_bytes, (long long)ldc);
+  if (fmt == VX_FMT_NV16 && !amax) return fail(-1, "NV16 needs the tensor amax");
+  if (scales_sf && !fmt_has_sf(fmt)) return fail(-1, "format %d has no SF-atom layout", fmt);
+  if (scales_sf && (reinterpret_cast<uintptr_t>(scales_sf) & 15))
+    return fail(-1, "scales_sf must be 16-byte aligned");
+  if (fmt == VX_FMT_FP8_1X128 && scales && (reinterpret_cast<uintptr_t>(scales) & 3))
+    return fail(-1, "fp32 scales must be 4-byte aligned");
+  if (ln) {
+    if (!gamma || !beta) return fail(-1, "gamma and beta must not be NULL");
+    if (K > 2048) return fail(-1, "fused LayerNorm supports K <= 2048 (K=%lld)", (long long)K);
+    if (!aligned16(gamma) || !aligned16(beta)) return fail(-1, "gamma/beta must be 16-byte aligned");
+    if (y && y_dtype != VX_F32 && y_dtype != VX_BF16) return fail(-1, "y_dtype must be VX_F32 or VX_BF16");
+    if (y && (!aligned16(y) || ldy < K || (ldy * (y_dtype == VX_BF16 ? 2 : 4)) % 16 != 0))
+      return fail(-1, "y rows must be 16-byte aligned");
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  QuantParams p{};
+  p.x = x; p.M = M; p.K = K; p.ldx = ldx;
+  p.codes = static_cast<uint8_t*>(codes); p.ldc = ldc;
+  p.scales = scales; p.sf = static_cast<uint8_t*>(scales_sf);
+  p.sf_kg = sf_kgroups(fmt, K);
+  p.amax = amax; p.gamma = gamma; p.beta = beta; p.eps = eps; p.y = y; p.y_bf16 = (y_dtype == VX_BF16); p.ldy = ldy;
+  if (scales_sf) {
+    // rows / k-groups beyond the tensor must read as zero scale factors
+    const int64_t nkb = K / blk;
+    if ((M & 127) != 0 || p.sf_kg * 4 != nkb)
+      VX_CUDA_OK(cudaMemsetAsync(scales_sf, 0, static_cast<size_t>(vx_sf_bytes(fmt, M, K)), st));
+  }
+  return x_dtype == VX_BF16 ? dispatch_fmt<__nv_bfloat16>(fmt, p, ln, st)
+                            : dispatch_fmt<float>(fmt, p, ln, st);
+}
+
+}  // namespace
+}  // namespace vx
+
+extern "C" {
+
+int64_t vx_sf_kgroups(int fmt, int64_t K) { return vx::fmt_has_sf(fmt) ? vx::sf_kgroups(fmt, K) : 0; }
+
+int64_t vx_sf_bytes(int fmt, int64_t R, int64_t K) {
+  if (!vx::fmt_has_sf(fmt)) return 0;
+  return ((R + 127) / 128) * vx::sf_kgroups(fmt, K) * 512;
+}
+
+int vx_quantize_pack(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, int fmt,
+                     void* codes, int64_t ldc, void* scales, void* scales_sf, const float* amax,
+                     void* stream) {
+  return vx::quantize_common(x, x_dtype, M, K, ldx, fmt, codes, ldc, scales, scales_sf, amax, false,
+                             nullptr, nullptr, 0.f, nullptr, 0, 0, stream);
+}
+
+int vx_ln_quantize_pack(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx,
+                        const float* gamma, const float* beta, float eps, int fmt, void* codes,
+                        int64_t ldc, void* scales, void* scales_sf, const float* amax, void* y,
+                        int y_dtype, int64_t ldy, void* stream) {
+  return vx::quantize_common(x, x_dtype, M, K, ldx, fmt, codes, ldc, scales, scales_sf, amax, true,
+                             gamma, beta, eps, y, y_dtype, ldy, stream);
+}
+
+int vx_amax(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, float* amax_out,
+            void* stream) {
+  using namespace vx;
+  if (x_dtype != VX_F32 && x_dtype != VX_BF16) return fail(-1, "x_dtype must be VX_F32 or VX_BF16");
+  if (!amax_out) return fail(-1, "amax_out must not be NULL");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  VX_CUDA_OK(cudaMemsetAsync(amax_out, 0, sizeof(float), st));
+  if (M <= 0 || K <= 0) return 0;
+  const int64_t esz = x_dtype == VX_BF16 ? 2 : 4;
+  if (!x || K % 8 != 0 || !aligned16(x) || (ldx * esz) % 16 != 0 || ldx < K)
+    return fail(-1, "x must be 16-byte aligned rows with K %% 8 == 0");
+  const int64_t threads = M * (K >> 3);
+  int grid = static_cast<int>((threads + 255) / 256);
+  if (grid > 148 * 8) grid = 148 * 8;
+  if (x_dtype == VX_BF16)
+    amax_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), M, K, ldx, amax_out);
+  else
+    amax_kernel<<<grid, 256, 0, st>>>(static_cast<const float*>(x), M, K, ldx, amax_out);
+  VX_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+int vx_sf_from_natural(int fmt, const void* scales, int64_t R, int64_t K, void* scales_sf,
+                       void* stream) {
+  using namespace vx;
+  if (!fmt_has_sf(fmt)) return fail(-1, "format %d has no SF-atom layout", fmt);
+  if (R <= 0 || K <= 0) return 0;
+  if (!scales || !scales_sf || (reinterpret_cast<uintptr_t>(scales_sf) & 15))
+    return fail(-1, "scales / scales_sf must be non-NULL, scales_sf 16-byte aligned");
+  const int blk = fmt_block(fmt);
+  if (K % blk != 0) return fail(-1, "K must be a multiple of %d", blk);
+  if (fmt == VX_FMT_BLK16_A && (R & 1)) return fail(-1, "BLK16_A needs an even row count");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  VX_CUDA_OK(cudaMemsetAsync(scales_sf, 0, static_cast<size_t>(vx_sf_bytes(fmt, R, K)), st));
+  const int64_t nkb = K / blk;
+  const int64_t total = R * ((nkb + 3) / 4);
+  int grid = static_cast<int>((total + 255) / 256);
+  if (grid > 148 * 16) grid = 148 * 16;
+  sf_relayout_kernel<<<grid, 256, 0, st>>>(fmt, static_cast<const uint8_t*>(scales), R, nkb,
+                                           static_cast<uint8_t*>(scales_sf), sf_kgroups(fmt, K));
+  VX_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // extern "C"
