@@ -1,0 +1,98 @@
+"""The encoder linear stack on the GPU against the CPU oracle stack (BASELINE configs[3]/[4])."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import formats as F
+from oracle.stack import OracleStack
+
+pytestmark = pytest.mark.gpu
+
+
+def _np_weights(w):
+    return {k: v.numpy() for k, v in w.items()}
+
+
+@pytest.mark.parametrize("fmt", ["mx32", "fp8_1x128"])
+def test_stack_matches_oracle_and_argmax_agrees(fmt):
+    from velox_voice_b200 import _lib
+    from velox_voice_b200.stack import ConformerLinearStack, StackConfig, make_weights
+
+    cfg = StackConfig(blocks=12, fmt=fmt)
+    w = make_weights(cfg, seed=0)
+    stack = ConformerLinearStack(cfg, w)
+    torch.manual_seed(0)
+    T = 1000  # not a multiple of 128: exercises the ragged last tile everywhere
+    x = torch.randn(T, cfg.d_model).bfloat16()
+    pos = torch.randn(T, cfg.d_model).bfloat16().cuda()
+    logits, hidden = stack.forward(x.cuda().clone(), pos, return_hidden=True)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    assert logits.shape == (T, cfg.vocab) and logits.dtype == torch.bfloat16
+    oracle = OracleStack(_np_weights(w), F.FMT_NAMES[fmt],
+                         cfg.blocks, fuse_ffn=stack.fuse_ffn)
+    ref_logits, ref_hidden = oracle.forward(x.float().numpy(), return_hidden=True)
+    got = logits.float().cpu().numpy()
+    rel = np.abs(got - ref_logits).max() / np.abs(ref_logits).max()
+    agree = float((got.argmax(1) == ref_logits.argmax(1)).mean())
+    hid = np.abs(hidden.float().cpu().numpy() - ref_hidden).max() / np.abs(ref_hidden).max()
+    print(f"[{fmt}] logits rel err {rel:.4g}, hidden rel err {hid:.4g}, per-frame argmax agreement {agree:.5f}")
+    assert rel < 5e-2
+    assert agree >= 0.999
+
+
+def test_frame_shards_reproduce_the_single_gpu_bytes():
+    from velox_voice_b200.stack import ConformerLinearStack, StackConfig, make_weights, shard_rows
+
+    cfg = StackConfig(blocks=2, fmt="mx32")
+    stack = ConformerLinearStack(cfg, make_weights(cfg, seed=1))
+    torch.manual_seed(1)
+    T = 777
+    x = torch.randn(T, cfg.d_model).bfloat16().cuda()
+    full = stack.forward(x.clone())
+    parts = []
+    for r in range(4):
+        a, b = shard_rows(T, 4, r)
+        parts.append(stack.forward(x[a:b].clone()))
+    assert torch.equal(torch.cat(parts), full)
+
+
+def test_nv16_stack_runs_with_calibration():
+    from velox_voice_b200.stack import ConformerLinearStack, StackConfig, make_weights
+
+    cfg = StackConfig(blocks=2, fmt="nv16")
+    w = make_weights(cfg, seed=2)
+    stack = ConformerLinearStack(cfg, w)
+    torch.manual_seed(2)
+    x = torch.randn(512, cfg.d_model).bfloat16().cuda()
+    rec = stack.calibrate(x)
+    assert rec and all(v > 0 for v in rec.values())
+    logits = stack.forward(x.clone())
+    amax = {k: float(v.item()) for k, v in stack.amax.items()}
+    oracle = OracleStack(_np_weights(w), F.FMT_NV16, cfg.blocks, amax=amax)
+    ref = oracle.forward(x.float().cpu().numpy())
+    got = logits.float().cpu().numpy()
+    assert np.abs(got - ref).max() / np.abs(ref).max() < 5e-2
+    assert float((got.argmax(1) == ref.argmax(1)).mean()) >= 0.99
+
+
+def test_dense_linear_precision_modes():
+    """Mirror of the reference's TestDenseLinearPrecision (tests/kernels/test_power_mel_log.py:212-266)."""
+    from velox_voice_b200.linear import DenseLinear
+
+    torch.manual_seed(3)
+    w = torch.randn(64, 128)
+    b = torch.randn(64)
+    x = torch.randn(32, 128).cuda()
+    lin = DenseLinear(w, b).cuda()
+    lin.precision = "fp32"
+    assert torch.equal(lin(x), torch.nn.functional.linear(x, lin.weight, lin.bias))
+    for mode in ("mxfp4", "nvfp4"):
+        lin.precision = mode
+        y = lin(x)
+        assert y.shape == (32, 64) and y.dtype == torch.float32 and torch.isfinite(y).all()
+        y3 = lin(x.view(2, 16, 128))
+        assert y3.shape == (2, 16, 64)
+        ref = torch.nn.functional.linear(x, lin.weight, lin.bias)
+        assert (y - ref).abs().max() / ref.abs().max() < 0.35  # FP4 with per-row scales

@@ -6,16 +6,18 @@
 //   FP8 operands (E4M3, fp32 scale per 1x128): tcgen05.mma kind::f8f6f4, one accumulation
 //       group per 128-wide K block, promoted into fp32 registers with sa[m,kb] * sb[n,kb].
 //
-// One persistent CTA per SM, 6 warps:
+// One persistent CTA per SM, 18 warps:
 //   warp 0      TMA producer: A / B tiles (128 rows x 128 bytes, 128-byte swizzle) and the
 //               scale-factor atoms of the stage into a 4-deep shared-memory ring;
 //   warp 1      owns tensor memory; one elected thread copies scale factors shared -> tensor
 //               memory (tcgen05.cp) and issues the MMAs; tcgen05.commit releases ring slots
 //               and publishes finished accumulators;
-//   warps 2..5  epilogue: tcgen05.ld of a 128 x 128 fp32 accumulator (one row per thread),
-//               scales / bias / Swish / GLU / residual, then either a swizzled shared-memory
-//               staging buffer + TMA store (clipped at the tensor edge by hardware) or direct
-//               vector stores; optional re-quantization of the result to FP4.
+//   warps 2..17 epilogue: each warp reads a 32-lane x 32-column block of the 128 x 128 fp32
+//               accumulator (tcgen05.ld, one row per thread), applies scales / bias / Swish /
+//               GLU / residual, then either a swizzled shared-memory staging buffer + TMA
+//               store (clipped at the tensor edge by hardware) or direct vector stores;
+//               optional re-quantization of the result to FP4.  Sixteen warps (four per
+//               scheduler) hide the TMEM-load, shared-memory and MUFU latencies of each other.
 // Accumulators are double-buffered in tensor memory (2 x 128 columns), so the epilogue of
 // tile i overlaps the loads and MMAs of tile i + 1.
 //
@@ -42,9 +44,9 @@ constexpr int STAGE_ROW_BYTES = 128;  // K bytes per stage: 256 FP4 or 128 FP8 e
 constexpr int TILE_BYTES = BM * STAGE_ROW_BYTES;  // 16 KB
 constexpr int NSTAGE = 4;
 constexpr int SF_STAGE_MAX = 4 * 512;  // scale-factor atoms of one operand per stage
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 576;       // 2 + 16 warps
 constexpr int EPI_WARP0 = 2;
-constexpr int STAGING_BYTES = 32 * 128;  // 32 rows x 128 bytes per epilogue warp and buffer
+constexpr int STAGING_BYTES = 32 * 128;  // 32 rows x up to 128 bytes per epilogue warp
 constexpr int FP8_MAX_KB = 16;           // K <= 2048 for the FP8 path
 
 // tensor-memory columns
@@ -90,8 +92,7 @@ struct __align__(1024) SmemLayout {
   uint8_t b[NSTAGE][TILE_BYTES];
   uint8_t sfa[NSTAGE][SF_STAGE_MAX];
   uint8_t sfb[NSTAGE][SF_STAGE_MAX];
-  uint8_t staging[4][2][STAGING_BYTES];
-  float fb[4][FP8_MAX_KB][BN];  // per epilogue warp: column scales of the current tile
+  uint8_t staging[16][STAGING_BYTES];
   uint64_t full[NSTAGE];
   uint64_t empty[NSTAGE];
   uint64_t tmem_full[2];
@@ -100,8 +101,14 @@ struct __align__(1024) SmemLayout {
   int abort_flag;
 };
 
-__device__ __forceinline__ float silu_f(float z) { return __fdividef(z, 1.0f + __expf(-z)); }
-__device__ __forceinline__ float sigmoid_f(float z) { return __fdividef(1.0f, 1.0f + __expf(-z)); }
+// sigmoid(z) = 0.5 tanh(z / 2) + 0.5: one MUFU operation per element (tanh.approx, relative
+// error ~2^-11, below bf16 resolution) instead of an exponential plus a reciprocal.
+__device__ __forceinline__ float sigmoid_f(float z) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * z));
+  return fmaf(0.5f, t, 0.5f);
+}
+__device__ __forceinline__ float silu_f(float z) { return z * sigmoid_f(z); }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -285,7 +292,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&sm.tmem_full[a], 1);
-      mbar_init(&sm.tmem_empty[a], 4);
+      mbar_init(&sm.tmem_empty[a], 16);
     }
     sm.abort_flag = 0;
     mbar_fence_init();
@@ -394,50 +401,58 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     }
   } else {
     // =========================== epilogue ===========================
-    const int q = warp & 3;                       // TMEM lane quadrant of this warp
-    const int ew = warp - EPI_WARP0;              // staging buffer owner
+    // 16 warps; warp (q, cc) owns TMEM lanes [32 q, 32 q + 32) (the hardware ties a warp to
+    // the lane quadrant warp_id % 4) and accumulator columns [32 cc, 32 cc + 32).
+    const int q = warp & 3;
+    const int ew = warp - EPI_WARP0;
+    const int cc = ew >> 2;
     const int64_t n_out = GLU ? p.N / 2 : p.N;    // logical output columns
     const int out_tile_cols = GLU ? BN / 2 : BN;
+    const bool has_work = !GLU || cc < 2;         // GLU: chunks 2, 3 are the gates of 0, 1
     uint32_t group = 0;
-    uint32_t store_buf = 0;
     bool ok = true;
     float g_ab = 1.0f, g_out = 1.0f;
     if (p.a_amax && p.b_amax) g_ab = nv16_global(__ldg(p.a_amax)) * nv16_global(__ldg(p.b_amax));
     if (p.out_amax) g_out = nv16_global(__ldg(p.out_amax));
     const int kb_count = FP8 ? p.k_stages : 0;
+    uint8_t* buf = sm.staging[ew];
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
 
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const int mb = t / p.n_tiles, nb = t - mb * p.n_tiles;
       const int64_t row = static_cast<int64_t>(mb) * BM + q * 32 + lane;
       const bool row_ok = row < p.M;
-      const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+      const int64_t acc_col0 = static_cast<int64_t>(nb) * BN + cc * 32;             // accumulator / bias column
+      const int64_t out_col0 = static_cast<int64_t>(nb) * out_tile_cols + cc * 32;  // output column
 
-      float racc[FP8 ? BN : 1];
+      float z[32], gate[32];
       if constexpr (FP8) {
-        // per-tile column scales of B into this warp's shared-memory table: fb[kb][col]
-        __syncwarp();
-        for (int c4 = 0; c4 < 4; ++c4) {
-          const int col = c4 * 32 + lane;
-          const int64_t n = static_cast<int64_t>(nb) * BN + col;
-          for (int kb = 0; kb < kb_count; ++kb)
-            sm.fb[ew][kb][col] = n < p.N ? __ldg(p.fb + n * kb_count + kb) : 0.0f;
-        }
-        __syncwarp();
+        // promote each 128-wide K block: z += tmem * sa[row, kb] * sb[col, kb]
 #pragma unroll
-        for (int i = 0; i < BN; ++i) racc[i] = 0.0f;
-        for (int kb = 0; kb < kb_count && ok; ++kb) {
+        for (int i = 0; i < 32; ++i) { z[i] = 0.0f; gate[i] = 0.0f; }
+        const int64_t ncol = acc_col0 + lane;   // lane <-> column for the scale fetch
+        const int64_t gcol = ncol + 64;
+        for (int kb = 0; kb < kb_count; ++kb) {
           const uint32_t acc = group & 1;
           if (!mbar_wait(&sm.tmem_full[acc], (group >> 1) & 1, p.status, 4)) { ok = false; break; }
           tc_fence_after();
           const float sa = row_ok ? __ldg(p.fa + row * kb_count + kb) : 0.0f;
-#pragma unroll
-          for (int cc = 0; cc < 4; ++cc) {
-            uint32_t r[32];
+          const float sbv = ncol < p.N ? __ldg(p.fb + ncol * kb_count + kb) : 0.0f;
+          uint32_t r[32];
+          if (has_work) {
             tc_ld_32x32b_x32(lane_addr + TM_ACC0 + acc * BN + cc * 32, r);
             tc_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i)
-              racc[cc * 32 + i] = fmaf(__uint_as_float(r[i]), sa * sm.fb[ew][kb][cc * 32 + i], racc[cc * 32 + i]);
+              z[i] = fmaf(__uint_as_float(r[i]), sa * __shfl_sync(0xffffffffu, sbv, i), z[i]);
+            if constexpr (GLU) {
+              const float sbg = gcol < p.N ? __ldg(p.fb + gcol * kb_count + kb) : 0.0f;
+              tc_ld_32x32b_x32(lane_addr + TM_ACC0 + acc * BN + 64 + cc * 32, r);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                gate[i] = fmaf(__uint_as_float(r[i]), sa * __shfl_sync(0xffffffffu, sbg, i), gate[i]);
+            }
           }
           tc_fence_before();
           __syncwarp();
@@ -449,45 +464,32 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         const uint32_t acc = group & 1;
         if (!mbar_wait(&sm.tmem_full[acc], (group >> 1) & 1, p.status, 4)) { ok = false; break; }
         tc_fence_after();
-      }
-      const uint32_t acc_col = TM_ACC0 + ((FP8 ? 0u : (group & 1)) * BN);
-
-      float row_scale = 1.0f;
-      if (!FP8 && p.sf_unit) row_scale = row_ok ? ue8m0_to_float(__ldg(p.row_scale_u8 + row)) : 0.0f;
-
-      uint32_t sf_word[2] = {0, 0};  // FP4 output: scale bytes of this row for this tile
-      constexpr int NCHUNK = GLU ? 2 : 4;
-#pragma unroll
-      for (int cc = 0; cc < NCHUNK; ++cc) {
-        float z[32], gate[32];
-        if constexpr (FP8) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) z[i] = racc[cc * 32 + i];
-          if constexpr (GLU) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) gate[i] = racc[64 + cc * 32 + i];
-          }
-        } else {
+        if (has_work) {
           uint32_t r[32];
-          tc_ld_32x32b_x32(lane_addr + acc_col + cc * 32, r);
+          tc_ld_32x32b_x32(lane_addr + TM_ACC0 + acc * BN + cc * 32, r);
           tc_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; ++i) z[i] = __uint_as_float(r[i]);
           if constexpr (GLU) {
-            tc_ld_32x32b_x32(lane_addr + acc_col + 64 + cc * 32, r);
+            tc_ld_32x32b_x32(lane_addr + TM_ACC0 + acc * BN + 64 + cc * 32, r);
             tc_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i) gate[i] = __uint_as_float(r[i]);
           }
+        }
+        // accumulator chunk is in registers: hand the TMEM buffer back to the MMA warp
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.tmem_empty[acc]);
+        ++group;
+        if (has_work) {
           if (p.sf_unit) {
             // reference order: raw * row_scale * col_scale
-            const uint8_t* cs = p.col_scale_u8 + static_cast<int64_t>(nb) * BN + cc * 32;
+            const float row_scale = row_ok ? ue8m0_to_float(__ldg(p.row_scale_u8 + row)) : 0.0f;
+            const int64_t ncol = acc_col0 + lane;
+            const float csv = ncol < p.N ? ue8m0_to_float(__ldg(p.col_scale_u8 + ncol)) : 0.0f;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int64_t n = static_cast<int64_t>(nb) * BN + cc * 32 + i;
-              const float c = n < p.N ? ue8m0_to_float(__ldg(cs + i)) : 0.0f;
-              z[i] = z[i] * row_scale * c;
-            }
+            for (int i = 0; i < 32; ++i) z[i] = z[i] * row_scale * __shfl_sync(0xffffffffu, csv, i);
           } else if (p.a_amax) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) z[i] *= g_ab;
@@ -497,75 +499,59 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             }
           }
         }
-        const int64_t acc_col0 = static_cast<int64_t>(nb) * BN + cc * 32;           // bias index
-        const int64_t out_col0 = static_cast<int64_t>(nb) * out_tile_cols + cc * 32;  // output column
-        ChunkOut<EPI>::apply(p, z, gate, row, acc_col0, acc_col0 + 64, out_col0, row_ok);
+      }
+      if (!has_work) continue;
 
-        if (p.out_dtype == VX_FP4) {
-          const uint32_t sb = store_chunk_fp4(p, z, row, out_col0, g_out, row_ok && out_col0 < n_out);
-          if (p.out_fmt == VX_FMT_MX32) sf_word[0] |= sb << (8 * cc);
-          else sf_word[cc >> 1] |= sb << (16 * (cc & 1));
-        } else if (p.tma_store) {
-          // stage 32 rows x 128 bytes per box with the 128-byte swizzle, then one TMA store
-          const int elt = p.out_dtype == VX_BF16 ? 2 : 4;
-          const int chunks_per_box = elt == 2 ? 2 : 1;  // 64 bf16 or 32 fp32 columns per box
-          const int sub = cc % chunks_per_box;
-          if (sub == 0) {
-            if (lane == 0) tma_store_wait_read<1>();  // the buffer used two boxes ago is free
-            __syncwarp();
-          }
-          uint8_t* buf = sm.staging[ew][store_buf];
-          if (elt == 2) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              const int c16 = sub * 4 + v;
-              uint4 u;
-              u.x = pack_bf16x2(z[8 * v], z[8 * v + 1]);
-              u.y = pack_bf16x2(z[8 * v + 2], z[8 * v + 3]);
-              u.z = pack_bf16x2(z[8 * v + 4], z[8 * v + 5]);
-              u.w = pack_bf16x2(z[8 * v + 6], z[8 * v + 7]);
-              *reinterpret_cast<uint4*>(buf + lane * 128 + ((c16 ^ (lane & 7)) << 4)) = u;
-            }
+      ChunkOut<EPI>::apply(p, z, gate, row, acc_col0, acc_col0 + 64, out_col0, row_ok);
+
+      if (p.out_dtype == VX_FP4) {
+        const uint32_t sb = store_chunk_fp4(p, z, row, out_col0, g_out, row_ok && out_col0 < n_out);
+        if (row_ok && out_col0 < n_out) {
+          // this chunk's scale byte(s) inside the row's SF word(s)
+          if (p.out_fmt == VX_FMT_MX32) {
+            const int64_t kg = nb;  // 128 columns = 4 blocks of 32 = one k-group
+            p.out_sf[((row >> 7) * p.out_sf_kg + kg) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + cc] =
+                static_cast<uint8_t>(sb);
+            if (p.out_scales) p.out_scales[row * (n_out >> 5) + (out_col0 >> 5)] = static_cast<uint8_t>(sb);
           } else {
-#pragma unroll
-            for (int v = 0; v < 8; ++v)
-              *reinterpret_cast<float4*>(buf + lane * 128 + ((v ^ (lane & 7)) << 4)) =
-                  make_float4(z[4 * v], z[4 * v + 1], z[4 * v + 2], z[4 * v + 3]);
+            const int64_t kg = static_cast<int64_t>(nb) * 2 + (cc >> 1);  // 8 blocks of 16 = two k-groups
+            *reinterpret_cast<uint16_t*>(p.out_sf + ((row >> 7) * p.out_sf_kg + kg) * 512 + (row & 31) * 16 +
+                                         ((row >> 5) & 3) * 4 + (cc & 1) * 2) = static_cast<uint16_t>(sb);
+            if (p.out_scales)
+              *reinterpret_cast<uint16_t*>(p.out_scales + row * (n_out >> 4) + (out_col0 >> 4)) =
+                  static_cast<uint16_t>(sb);
           }
-          if (sub == chunks_per_box - 1) {
-            fence_proxy_async_smem();
-            __syncwarp();
-            const int x = static_cast<int>(out_col0 - sub * 32);
-            if (lane == 0 && static_cast<int64_t>(mb) * BM + q * 32 < p.M && x < n_out) {
-              tma_store_2d(&tmap_out, x, mb * BM + q * 32, buf);
-              tma_store_commit();
-            }
-            store_buf ^= 1;
-          }
-        } else if (row_ok) {
-          store_chunk_direct(p, z, row, out_col0, n_out);
         }
-      }
-      if constexpr (!FP8) {
-        // accumulator fully read: hand the TMEM buffer back to the MMA warp
-        tc_fence_before();
+      } else if (p.tma_store) {
+        // stage 32 rows x 32 columns (swizzled like the tensor map), then one TMA store
+        if (lane == 0) tma_store_wait_read<0>();  // the previous tile's box has left the buffer
         __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.tmem_empty[group & 1]);
-        ++group;
-      }
-      if (p.out_dtype == VX_FP4 && row_ok) {
-        const int words = p.out_fmt == VX_FMT_MX32 ? 1 : 2;
-        const int64_t kg0 = static_cast<int64_t>(nb) * words;
-        for (int w = 0; w < words; ++w) {
-          const int64_t kg = kg0 + w;
-          if (kg * 4 * (p.out_fmt == VX_FMT_MX32 ? 32 : 16) >= n_out) break;
-          *reinterpret_cast<uint32_t*>(p.out_sf + ((row >> 7) * p.out_sf_kg + kg) * 512 +
-                                       (row & 31) * 16 + ((row >> 5) & 3) * 4) = sf_word[w];
-          if (p.out_scales) {
-            const int64_t nblk = n_out / (p.out_fmt == VX_FMT_MX32 ? 32 : 16);
-            *reinterpret_cast<uint32_t*>(p.out_scales + row * nblk + kg * 4) = sf_word[w];
+        if (p.out_dtype == VX_BF16) {
+          // 64-byte rows, 64-byte swizzle: 16-byte slot index ^= (row >> 1) & 3
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 u;
+            u.x = pack_bf16x2(z[8 * v], z[8 * v + 1]);
+            u.y = pack_bf16x2(z[8 * v + 2], z[8 * v + 3]);
+            u.z = pack_bf16x2(z[8 * v + 4], z[8 * v + 5]);
+            u.w = pack_bf16x2(z[8 * v + 6], z[8 * v + 7]);
+            *reinterpret_cast<uint4*>(buf + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)) = u;
           }
+        } else {
+          // 128-byte rows, 128-byte swizzle: slot index ^= row & 7
+#pragma unroll
+          for (int v = 0; v < 8; ++v)
+            *reinterpret_cast<float4*>(buf + lane * 128 + ((v ^ (lane & 7)) << 4)) =
+                make_float4(z[4 * v], z[4 * v + 1], z[4 * v + 2], z[4 * v + 3]);
         }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && static_cast<int64_t>(mb) * BM + q * 32 < p.M && out_col0 < n_out) {
+          tma_store_2d(&tmap_out, static_cast<int>(out_col0), mb * BM + q * 32, buf);
+          tma_store_commit();
+        }
+      } else if (row_ok) {
+        store_chunk_direct(p, z, row, out_col0, n_out);
       }
     }
     if (p.tma_store && lane == 0) tma_store_wait_all<0>();
@@ -659,9 +645,10 @@ EncodeTiledFn get_encode_fn() {
 }
 
 // 2-D row-major tensor [rows, cols] of `elt`-byte elements, row pitch `pitch_bytes`; box =
-// box_cols x box_rows with a 128-byte inner extent and the 128-byte swizzle.
+// box_cols x box_rows; the inner extent in bytes equals the swizzle span (128 or 64).
 int make_tmap(CUtensorMap* m, CUtensorMapDataType dt, int elt, const void* ptr, int64_t rows,
-              int64_t cols, int64_t pitch_bytes, int box_cols, int box_rows) {
+              int64_t cols, int64_t pitch_bytes, int box_cols, int box_rows,
+              CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return fail(-2, "cuTensorMapEncodeTiled is not available from the driver");
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
@@ -670,7 +657,7 @@ int make_tmap(CUtensorMap* m, CUtensorMapDataType dt, int elt, const void* ptr, 
   const cuuint32_t estr[2] = {1, 1};
   (void)elt;
   const CUresult r = fn(m, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(-3, "cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
   return 0;
@@ -824,7 +811,8 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
   if (d->out_dtype != VX_FP4 && !(d->flags & VX_GEMM_DIRECT_STORE) && aligned16(d->out) &&
       (d->ldo * oelt) % 16 == 0) {
     rc = make_tmap(&to, d->out_dtype == VX_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
-                   oelt, d->out, M, n_out, d->ldo * oelt, 128 / oelt, 32);
+                   oelt, d->out, M, n_out, d->ldo * oelt, 32, 32,
+                   d->out_dtype == VX_BF16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     p.tma_store = 1;
   } else {

@@ -26,17 +26,18 @@ __device__ __forceinline__ void ue8m0_from_amax(float amax, uint32_t& byte, floa
   rcp = ef <= 253u ? __uint_as_float((254u - ef) << 23) : 0.0f;
 }
 
-// Magnitude code of |q| (count of thresholds strictly exceeded), without compares:
-// adding 2^23 with round-up leaves ceil(t) in the low mantissa bits.
+// Magnitude code of |q| (count of thresholds strictly exceeded), without compares.
+// 2^23 + x rounded toward +inf leaves ceil(x) in the low mantissa bits, so
+//   #{k : 0.25 + 0.5 k < a, k = 0..3} = clamp(ceil(2 a - 0.5), 0, 4)
+//   #{2.5 < a, 3.5 < a}               = clamp(ceil(a - 2.5), 0, 2)
+// Each sum is formed with a single rounding; below 2^23 (negative x) the clamp yields 0.
 __device__ __forceinline__ uint32_t e2m1_mag(float a) {
-  a = fminf(a, 8.0f);
-  const float t = fmaf(a, 2.0f, -0.5f);  // thresholds 0.25 + 0.5 k  ->  integers
-  uint32_t lo = __float_as_uint(__fadd_ru(t, 8388608.0f));
-  lo = min(lo, 0x4B000004u);
-  const float t2 = a - 2.5f;  // thresholds 2.5, 3.5 -> 0, 1
-  uint32_t hi = __float_as_uint(__fadd_ru(t2, 8388608.0f));
-  hi = min(max(hi, 0x4B000000u), 0x4B000002u);
-  return (lo - 0x4B000000u) + (hi - 0x4B000000u);
+  constexpr uint32_t kMagic = 0x4B000000u;  // bit pattern of 2^23
+  uint32_t lo = __float_as_uint(__fmaf_ru(a, 2.0f, 8388607.5f));
+  lo = min(max(lo, kMagic), kMagic + 4u);
+  uint32_t hi = __float_as_uint(__fadd_ru(a, 8388605.5f));
+  hi = min(max(hi, kMagic), kMagic + 2u);
+  return (lo - kMagic) + (hi - kMagic);
 }
 __device__ __forceinline__ uint32_t e2m1_code(float q) {
   return e2m1_mag(fabsf(q)) | (q < 0.0f ? 8u : 0u);

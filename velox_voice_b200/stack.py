@@ -1,0 +1,276 @@
+"""The encoder's linear stack on the quantized path, and its frame-sharded multi-GPU driver.
+
+What runs per Conformer block (``veloxvoice/models/wenet/torch_conformer.py:705-713``):
+
+    x += 0.5 * w2(swish(w1(LN(x))))            macaron FFN      (:657-658, :706)
+    qkv = [lq|lk|lv](LN(x)); x += lo(ctx)      attention linears (:439-459, :519); lp(pos) (:472)
+    x += pw2(f(glu(pw1(LN(x)))))               conv-module pointwise convs (:594-642)
+    x += 0.5 * w2(swish(w1(LN(x))))            FFN              (:712)
+    x  = LN(x)                                 norm_final       (:713)
+
+followed by ``after_norm`` (:745) and the CTC head (:810-814).  Attention itself, the depthwise
+convolution and its norm/activation are NOT linear layers and are outside this library: the
+stack passes the value projection straight to ``lo`` and the GLU output straight to ``pw2``,
+so it measures and validates every linear of the encoder with the real operand shapes.
+
+Kernel sequence per block (14 launches; the reference issues >= 4 per linear):
+``ln_quant -> GEMM(bias, swish, FP4 out) -> GEMM(bias, 0.5 residual)`` for each FFN,
+``ln_quant -> GEMM(bias) [qkv] -> quant -> GEMM(bias, residual) [lo]``, ``GEMM [lp]``,
+``ln_quant -> GEMM(bias, GLU) -> quant -> GEMM(bias, residual)``, ``layernorm``.
+
+Multi-GPU: every operation is row-wise in the frames, so frames are cut into contiguous equal
+shards (:func:`shard_rows`), weights are replicated, and the only collective is the final
+gather of the logits (:func:`gather_rows`, NCCL through ``torch.distributed``).  The reference
+moves work between GPUs as files and subprocesses (``tools/bench_wenet_multi_worker.py:257-377``).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import ops
+from .linear import PackedLinear
+from .ops import FMT_FP8_1X128, FMT_MX32, FMT_NV16
+
+
+@dataclass
+class StackConfig:
+    d_model: int = 512
+    heads: int = 8
+    ffn: int = 2048
+    blocks: int = 12
+    conv_pw: int = 1024
+    vocab: int = 5538
+    fmt: str = "mx32"
+    eps: float = 1e-5
+    fuse_ffn: bool = True  # keep the FFN intermediate in FP4 (re-quantized in the up-GEMM epilogue)
+
+    def flops_per_frame(self) -> int:
+        """Algorithmic FLOPs of the linears per encoder frame (2 * N * K each)."""
+        d, f = self.d_model, self.ffn
+        per_block = 4 * (2 * d * f) + 2 * d * 3 * d + 2 * d * d + 2 * d * d + 2 * d * self.conv_pw + 2 * d * d
+        return self.blocks * per_block + 2 * d * self.vocab
+
+
+def make_weights(cfg: StackConfig, seed: int = 0) -> Dict[str, torch.Tensor]:
+    """Random-init fp32 weights of the stack on the CPU (N(0, 0.02), zero biases, LN = identity
+    affine), generated in a fixed order so every rank and the CPU oracle see the same values."""
+    g = torch.Generator().manual_seed(seed)
+    d, f = cfg.d_model, cfg.ffn
+
+    def w(n, k):
+        return torch.randn(n, k, generator=g) * 0.02
+
+    out: Dict[str, torch.Tensor] = {}
+    for i in range(cfg.blocks):
+        p = f"b{i}."
+        for ff in ("ffm", "ff"):
+            out[p + ff + ".w1"], out[p + ff + ".b1"] = w(f, d), torch.zeros(f)
+            out[p + ff + ".w2"], out[p + ff + ".b2"] = w(d, f), torch.zeros(d)
+        out[p + "qkv.w"], out[p + "qkv.b"] = w(3 * d, d), torch.zeros(3 * d)
+        out[p + "lo.w"], out[p + "lo.b"] = w(d, d), torch.zeros(d)
+        out[p + "lp.w"] = w(d, d)
+        out[p + "pw1.w"], out[p + "pw1.b"] = w(cfg.conv_pw, d), torch.zeros(cfg.conv_pw)
+        out[p + "pw2.w"], out[p + "pw2.b"] = w(d, cfg.conv_pw // 2), torch.zeros(d)
+        for n in ("ln_ffm", "ln_mha", "ln_conv", "ln_ff", "ln_final"):
+            out[p + n + ".g"], out[p + n + ".b"] = torch.ones(d), torch.zeros(d)
+    out["after.g"], out["after.b"] = torch.ones(d), torch.zeros(d)
+    out["ctc.w"], out["ctc.b"] = w(cfg.vocab, d), torch.zeros(cfg.vocab)
+    return out
+
+
+class ConformerLinearStack:
+    """All linears of the encoder on packed weights, fused quantize / GEMM / epilogue chain."""
+
+    def __init__(self, cfg: StackConfig, weights: Dict[str, torch.Tensor], device="cuda",
+                 amax: Optional[Dict[str, float]] = None):
+        self.cfg = cfg
+        self.fmt = ops._fmt(cfg.fmt)
+        if self.fmt not in (FMT_MX32, FMT_NV16, FMT_FP8_1X128):
+            raise ValueError("the stack runs in mx32, nv16 or fp8_1x128")
+        self.device = torch.device(device)
+        self.fuse_ffn = cfg.fuse_ffn and self.fmt != FMT_FP8_1X128
+        dev = self.device
+        self.p: Dict[str, PackedLinear] = {}
+        self.ln: Dict[str, Tuple[torch.Tensor, torch.Tensor]] = {}
+
+        def pack(name, wkey, bkey=None, glu=False):
+            wt = weights[wkey].to(dev)
+            bt = weights[bkey].to(dev) if bkey else None
+            self.p[name] = PackedLinear(wt, bt, self.fmt, glu=glu)
+
+        for i in range(cfg.blocks):
+            b = f"b{i}."
+            for ff in ("ffm", "ff"):
+                pack(b + ff + ".w1", b + ff + ".w1", b + ff + ".b1")
+                pack(b + ff + ".w2", b + ff + ".w2", b + ff + ".b2")
+            pack(b + "qkv", b + "qkv.w", b + "qkv.b")
+            pack(b + "lo", b + "lo.w", b + "lo.b")
+            pack(b + "lp", b + "lp.w")
+            pack(b + "pw1", b + "pw1.w", b + "pw1.b", glu=True)
+            pack(b + "pw2", b + "pw2.w", b + "pw2.b")
+            for n in ("ln_ffm", "ln_mha", "ln_conv", "ln_ff", "ln_final"):
+                self.ln[b + n] = (weights[b + n + ".g"].to(dev).float(), weights[b + n + ".b"].to(dev).float())
+        self.ln["after"] = (weights["after.g"].to(dev).float(), weights["after.b"].to(dev).float())
+        pack("ctc", "ctc.w", "ctc.b")
+        # NV16 needs a per-tensor amax for every activation it quantizes: calibrated once
+        self.amax: Dict[str, torch.Tensor] = {}
+        if amax:
+            for k, v in amax.items():
+                self.amax[k] = torch.tensor([v], dtype=torch.float32, device=dev)
+
+    # ---- helpers
+    def _amax(self, key: str, x: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        if self.fmt != FMT_NV16:
+            return None
+        t = self.amax.get(key)
+        if t is None:
+            raise RuntimeError(f"nv16 stack: no calibrated amax for {key!r} (run calibrate())")
+        return t
+
+    def _lnq(self, key: str, x: torch.Tensor):
+        g, b = self.ln[key]
+        return ops.ln_quantize(x, g, b, self.cfg.eps, self.fmt, amax_t=self._amax(key, None))
+
+    def _q(self, key: str, x: torch.Tensor):
+        return ops.quantize(x, self.fmt, natural=self.fmt == FMT_FP8_1X128, amax_t=self._amax(key, x))
+
+    def _ffn(self, b: str, ff: str, ln: str, x: torch.Tensor) -> torch.Tensor:
+        q = self._lnq(b + ln, x)
+        if self.fuse_ffn:
+            h = self.p[b + ff + ".w1"](q, act="swish", out_fmt=self.fmt, out_amax=self._amax(b + ff + ".h", None))
+        else:
+            h = self._q(b + ff + ".h", self.p[b + ff + ".w1"](q, act="swish"))
+        return self.p[b + ff + ".w2"](h, residual=x, alpha=0.5, out=x)
+
+    # ---- forward
+    def forward(self, x: torch.Tensor, pos: Optional[torch.Tensor] = None, *, return_hidden: bool = False):
+        """x: bf16 [T, d_model] residual stream (overwritten in place); returns bf16 logits [T, vocab]."""
+        cfg = self.cfg
+        if x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != cfg.d_model:
+            raise ValueError("x must be bf16 [T, d_model]")
+        d = cfg.d_model
+        pos_q = self._q("pos", pos) if pos is not None else None
+        for i in range(cfg.blocks):
+            b = f"b{i}."
+            x = self._ffn(b, "ffm", "ln_ffm", x)
+            q = self._lnq(b + "ln_mha", x)
+            qkv = self.p[b + "qkv"](q)
+            if pos_q is not None:
+                self.p[b + "lp"](pos_q)  # feeds the attention scores only
+            ctx = self._q(b + "ctx", qkv[:, 2 * d:])
+            x = self.p[b + "lo"](ctx, residual=x, alpha=1.0, out=x)
+            q = self._lnq(b + "ln_conv", x)
+            gl = self.p[b + "pw1"](q)
+            x = self.p[b + "pw2"](self._q(b + "glu", gl), residual=x, alpha=1.0, out=x)
+            x = self._ffn(b, "ff", "ln_ff", x)
+            g, be = self.ln[b + "ln_final"]
+            x = ops.layernorm(x, g, be, cfg.eps, out=x)
+        q = self._lnq("after", x)
+        logits = self.p["ctc"](q)
+        return (logits, x) if return_hidden else logits
+
+    __call__ = forward
+
+    def calibrate(self, x: torch.Tensor, pos: Optional[torch.Tensor] = None) -> Dict[str, float]:
+        """One bf16 pass with plain torch ops recording max |.| of every tensor the NV16 path
+        quantizes; fills ``self.amax`` (host sync; run once, outside any timed region)."""
+        cfg = self.cfg
+        rec: Dict[str, float] = {}
+
+        def ln(key, t):
+            g, b = self.ln[key]
+            y = torch.nn.functional.layer_norm(t.float(), (cfg.d_model,), g, b, cfg.eps)
+            rec[key] = float(y.abs().max())
+            return y
+
+        def lin(name, t):
+            q = self.p[name].q
+            w = ops._decode_e2m1(q.codes)  # dequantized weight rows (GLU rows stay interleaved)
+            from_e4m3 = q.scales.view(torch.float8_e4m3fn).float()
+            w = w * from_e4m3.repeat_interleave(16, dim=1) * (q.amax / 2688.0)
+            y = t.float() @ w.T
+            if self.p[name].bias is not None:
+                y = y + self.p[name].bias
+            return y
+
+        if self.fmt != FMT_NV16:
+            return rec
+        x = x.float().clone()
+        d = cfg.d_model
+        if pos is not None:
+            rec["pos"] = float(pos.abs().max())
+        for i in range(cfg.blocks):
+            b = f"b{i}."
+            for ff, lnk in (("ffm", "ln_ffm"),):
+                h = torch.nn.functional.silu(lin(b + ff + ".w1", ln(b + lnk, x)))
+                rec[b + ff + ".h"] = float(h.abs().max())
+                x = x + 0.5 * lin(b + ff + ".w2", h)
+            qkv = lin(b + "qkv", ln(b + "ln_mha", x))
+            ctx = qkv[:, 2 * d:]
+            rec[b + "ctx"] = float(ctx.abs().max())
+            x = x + lin(b + "lo", ctx)
+            z = lin(b + "pw1", ln(b + "ln_conv", x))
+            z = z.view(z.shape[0], -1, 2, 64)
+            gl = (z[:, :, 0] * torch.sigmoid(z[:, :, 1])).reshape(z.shape[0], -1)
+            rec[b + "glu"] = float(gl.abs().max())
+            x = x + lin(b + "pw2", gl)
+            h = torch.nn.functional.silu(lin(b + "ff.w1", ln(b + "ln_ff", x)))
+            rec[b + "ff.h"] = float(h.abs().max())
+            x = x + 0.5 * lin(b + "ff.w2", h)
+            g, be = self.ln[b + "ln_final"]
+            x = torch.nn.functional.layer_norm(x, (d,), g, be, cfg.eps)
+        ln("after", x)
+        for k, v in rec.items():
+            # head-room so that unseen frames rarely exceed the calibrated range
+            self.amax[k] = torch.tensor([v * 1.25], dtype=torch.float32, device=self.device)
+        return rec
+
+
+# --------------------------------------------------------------------------------------
+# frame sharding
+
+
+def shard_rows(total: int, world: int, rank: int, multiple: int = 2) -> Tuple[int, int]:
+    """Contiguous shard [start, stop) of ``total`` frames for ``rank`` of ``world``.
+
+    Shards are equal up to rounding to ``multiple`` frames (2 keeps the row pairs of the
+    per-16 "A"-side format inside one shard); trailing ranks may get fewer (or zero) frames.
+    """
+    if world < 1 or not (0 <= rank < world):
+        raise ValueError("bad world / rank")
+    per = -(-total // world)
+    per = -(-per // multiple) * multiple
+    start = min(rank * per, total)
+    stop = min(start + per, total)
+    return start, stop
+
+
+def shard_capacity(total: int, world: int, multiple: int = 2) -> int:
+    per = -(-total // world)
+    return -(-per // multiple) * multiple
+
+
+def gather_rows(local: torch.Tensor, total: int, world: int, rank: int, group=None) -> torch.Tensor:
+    """All-gather row shards (cut by :func:`shard_rows`) into the full [total, C] tensor.
+
+    One ``all_gather_into_tensor`` over equal-capacity slots (NCCL on GPUs, gloo on CPU); the
+    short last shards are padded in the slot and trimmed after the collective.
+    """
+    import torch.distributed as dist
+
+    cap = shard_capacity(total, world)
+    cols = local.shape[1]
+    slot = local
+    if local.shape[0] != cap or not local.is_contiguous():
+        slot = torch.zeros((cap, cols), dtype=local.dtype, device=local.device)
+        slot[: local.shape[0]] = local
+    full = torch.empty((world * cap, cols), dtype=local.dtype, device=local.device)
+    if world == 1:
+        full.copy_(slot)
+    else:
+        dist.all_gather_into_tensor(full, slot, group=group)
+    return full[:total]
