@@ -1,0 +1,409 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-linear path: encoder frames per second of the full linear stack.
+
+A step = one pass of the MXFP4 encoder linear stack (12 Conformer blocks' linears + CTC head,
+greedy argmax) over T encoder frames per GPU (default 90000 = one hour of 16 kHz audio,
+BASELINE configs[3]/[4]); synthetic ~N(0,1) bf16 features, random-init weights (seed 0).
+Frames are independent, so N GPUs each take their own T frames with replicated weights (weak
+scaling); the only collective is the gather of the per-frame CTC ids.
+
+    python bench.py --gpus 1 --steps 10 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference        # the path's CPU restatement on the host cores
+
+Prints ONE JSON line (rank 0).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "encoder_frames_per_s"
+UNIT = "frames/s"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--frames", type=int, default=90000, help="encoder frames per GPU")
+    ap.add_argument("--fmt", default="mx32", choices=["mx32", "nv16", "fp8_1x128"])
+    ap.add_argument("--blocks", type=int, default=12)
+    ap.add_argument("--cpu-frames", type=int, default=1024, help="frames of the CPU baseline sample")
+    ap.add_argument("--no-breakdown", action="store_true")
+    return ap.parse_args()
+
+
+def workload_name(a) -> str:
+    return (f"cfg4/cfg5 encoder linear stack, {a.fmt}, {a.blocks} blocks + CTC 512->5538, "
+            f"T={a.frames} frames per GPU (1-hour audio), attention/depthwise conv left out")
+
+
+# ----------------------------------------------------------------------------- clocks
+
+
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            p = [c.strip() for c in r.split(",")]
+            if len(p) < 9:
+                continue
+            try:
+                sm.append(float(p[1]))
+                mx.append(float(p[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, p[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ----------------------------------------------------------------------------- CPU arms
+
+_CPU_STACKS = {}
+
+
+def cpu_stack_sample(a, frames: int, repeats: int = 1):
+    """The path's CPU restatement (oracle: quantize -> dequantize -> fp32 matmul per linear)
+    on `frames` frames with every host thread torch can use.  Returns (frames/s, threads)."""
+    import numpy as np
+    import torch
+
+    from oracle import formats as F
+    from oracle.stack import OracleStack
+    from velox_voice_b200.stack import StackConfig, make_weights
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    cfg = StackConfig(blocks=a.blocks, fmt=a.fmt)
+    key = (a.blocks, a.fmt)
+    st = _CPU_STACKS.get(key)
+    if st is None:
+        w = {k: v.numpy() for k, v in make_weights(cfg, seed=0).items()}
+        # nv16: per-call (dynamic) tensor amax on the CPU
+        st = OracleStack(w, F.FMT_NAMES[a.fmt], cfg.blocks, amax={} if a.fmt == "nv16" else None)
+        st.forward(np.zeros((8, cfg.d_model), np.float32))  # quantize the weights once, untimed
+        _CPU_STACKS[key] = st
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(frames, cfg.d_model, generator=g).bfloat16().float().numpy()
+    t0 = time.perf_counter()
+    for _ in range(repeats):
+        st.forward(x)
+    dt = (time.perf_counter() - t0) / repeats
+    return frames / dt, torch.get_num_threads(), dt
+
+
+def run_reference(a):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    per_step = []
+    fps, threads, _ = cpu_stack_sample(a, a.cpu_frames)  # warm-up (weights quantized, pages touched)
+    for _ in range(max(a.warmup - 1, 0)):
+        cpu_stack_sample(a, 64)
+    t0 = time.perf_counter()
+    for _ in range(a.steps):
+        f, threads, dt = cpu_stack_sample(a, a.cpu_frames)
+        per_step.append(dt)
+    wall = time.perf_counter() - t0
+    dt = sum(per_step) / len(per_step)
+    value = a.cpu_frames / dt
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps,
+        "warmup": a.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(a), "sample": f"{a.cpu_frames} frames per step on the host cores"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": f"{a.cpu_frames} frames of the same stack per step (weights pre-quantized), "
+                                   f"{a.steps} steps, wall {wall:.1f} s"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- per-op breakdown
+
+
+def op_breakdown(stack, T, fmt_name):
+    """Times every distinct launch of one block (+ CTC) alone, L2 flushed before each timed
+    launch, and returns [(name, count_per_step, us, algorithmic_bytes, flops)]."""
+    import torch
+
+    from velox_voice_b200 import ops
+
+    cfg = stack.cfg
+    dev = stack.device
+    d, f, V = cfg.d_model, cfg.ffn, cfg.vocab
+    nb = cfg.blocks
+    fmt = stack.fmt
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    x = torch.randn(T, d, device=dev).bfloat16()
+    g, b = stack.ln["b0.ln_ffm"]
+    sfb = 1 / 32 if fmt_name == "mx32" else (1 / 16 if fmt_name == "nv16" else 4 / 128)
+    ebytes = 1.0 if fmt_name == "fp8_1x128" else 0.5
+
+    def qbytes(rows, k):
+        return rows * k * (ebytes + sfb)
+
+    am = stack.amax.get("b0.ln_ffm")
+    xq = ops.ln_quantize(x, g, b, cfg.eps, fmt, amax_t=am)
+    res = torch.randn(T, d, device=dev).bfloat16()
+    cases = []
+
+    def add(name, count, fn, nbytes, flops):
+        for _ in range(2):
+            fn()
+        ts = []
+        for _ in range(5):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        ts.sort()
+        cases.append((name, count, ts[len(ts) // 2], nbytes, flops))
+
+    add("ln_quantize [T,512]", 4 * nb + 1, lambda: ops.ln_quantize(x, g, b, cfg.eps, fmt, amax_t=am),
+        T * d * 2 + qbytes(T, d), 0)
+    add("quantize [T,512]", 2 * nb + 1, lambda: ops.quantize(x, fmt, natural=fmt_name == "fp8_1x128", amax_t=am),
+        T * d * 2 + qbytes(T, d), 0)
+    add("layernorm [T,512]", nb, lambda: ops.layernorm(x, g, b, cfg.eps, out=x), T * d * 4, 0)
+    w1, w2 = stack.p["b0.ffm.w1"], stack.p["b0.ffm.w2"]
+    if stack.fuse_ffn:
+        hq = w1(xq, act="swish", out_fmt=fmt, out_amax=stack.amax.get("b0.ffm.h"))
+        add("gemm ffn-up 512->2048 swish, FP4 out", 2 * nb,
+            lambda: w1(xq, act="swish", out_fmt=fmt, out_amax=stack.amax.get("b0.ffm.h")),
+            qbytes(T, d) + qbytes(f, d) + qbytes(T, f), 2 * T * d * f)
+    else:
+        h = w1(xq, act="swish")
+        hq = ops.quantize(h, fmt, natural=fmt_name == "fp8_1x128")
+        add("gemm ffn-up 512->2048 swish, bf16 out", 2 * nb, lambda: w1(xq, act="swish"),
+            qbytes(T, d) + qbytes(f, d) + T * f * 2, 2 * T * d * f)
+        add("quantize [T,2048]", 2 * nb, lambda: ops.quantize(h, fmt, natural=fmt_name == "fp8_1x128"),
+            T * f * 2 + qbytes(T, f), 0)
+    add("gemm ffn-down 2048->512 +0.5 residual", 2 * nb, lambda: w2(hq, residual=res, alpha=0.5, out=res),
+        qbytes(T, f) + qbytes(d, f) + T * d * 4, 2 * T * d * f)
+    add("gemm qkv 512->1536 bias", nb, lambda: stack.p["b0.qkv"](xq), qbytes(T, d) + qbytes(3 * d, d) + T * 3 * d * 2,
+        2 * T * d * 3 * d)
+    add("gemm lo/pw2 512->512 +residual", 2 * nb, lambda: stack.p["b0.lo"](xq, residual=res, alpha=1.0, out=res),
+        qbytes(T, d) + qbytes(d, d) + T * d * 4, 2 * T * d * d)
+    add("gemm lp 512->512", nb, lambda: stack.p["b0.lp"](xq), qbytes(T, d) + qbytes(d, d) + T * d * 2, 2 * T * d * d)
+    add("gemm pw1 512->1024 GLU", nb, lambda: stack.p["b0.pw1"](xq), qbytes(T, d) + qbytes(2 * d, d) + T * d * 2,
+        2 * T * d * 2 * d)
+    add("gemm ctc 512->5538 bias", 1, lambda: stack.p["ctc"](xq), qbytes(T, d) + qbytes(V, d) + T * V * 2, 2 * T * d * V)
+    del flush
+    return cases
+
+
+# ----------------------------------------------------------------------------- our arm
+
+
+def run_ours(a):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if a.gpus > 1 and world == 1:
+        # convenience: relaunch under torchrun
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={a.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", "29591", os.path.abspath(__file__)] + sys.argv[1:]
+        sys.exit(subprocess.call(cmd))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA GPU (there is no CPU fallback); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    from velox_voice_b200 import _lib, ops
+    from velox_voice_b200.stack import ConformerLinearStack, StackConfig, make_weights
+
+    T = a.frames
+    cfg = StackConfig(blocks=a.blocks, fmt=a.fmt)
+    stack = ConformerLinearStack(cfg, make_weights(cfg, seed=0), device=dev)
+    g = torch.Generator().manual_seed(1 + rank)
+    feats_host = torch.randn(T, cfg.d_model, generator=g).bfloat16().pin_memory()
+    pos = torch.randn(T, cfg.d_model, generator=g).bfloat16().to(dev)
+    if a.fmt == "nv16":
+        stack.calibrate(feats_host[:4096].to(dev), pos[:4096])
+    comp = stack.compile(T)
+    comp.pos.copy_(pos)
+    comp.x_in.copy_(feats_host)
+    ids_all = torch.empty((world * T,), dtype=torch.int32, device=dev)
+
+    def gather():
+        if world > 1:
+            dist.all_gather_into_tensor(ids_all, comp.ids)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident timing: inputs already in HBM
+    for _ in range(max(a.warmup, 3)):
+        comp.run()
+        gather()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(a.steps):
+        comp.run()
+        gather()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1))
+    clocks = sampler.stop() if rank == 0 else None
+    status = _lib.device_status()
+    ms_per_step = ms / a.steps
+    value = world * T * a.steps / (ms * 1e-3)
+
+    # ---- end to end through the public call: pinned host features in, host ids out
+    for _ in range(2):
+        comp.encode_ctc_host(feats_host)
+    barrier()
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(a.steps):
+        comp.encode_ctc_host(feats_host)
+        gather()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    e2e_ms = max_over_ranks(max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3))
+    e2e_value = world * T * a.steps / (e2e_ms * 1e-3)
+
+    line = None
+    if rank == 0:
+        flops_per_frame = cfg.flops_per_frame()
+        peaks = {}
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                peaks = json.load(f)
+        except Exception:
+            pass
+        hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+        peak_src = "measured (MEASURED_PEAKS.json)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
+        roofline, breakdown = None, None
+        if not a.no_breakdown:
+            cases = op_breakdown(stack, T, a.fmt)
+            total_us = sum(c * us for _, c, us, _, _ in cases)
+            breakdown = [{"op": n, "launches_per_step": c, "us": round(us, 1), "share": round(c * us / total_us, 3),
+                          "GBps": round(nb / us / 1e3, 1), "TFLOPs": round(fl / us / 1e6, 1)} for n, c, us, nb, fl in cases]
+            top = max(cases, key=lambda t: t[1] * t[2])
+            traffic = None
+            try:
+                with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
+                    traffic = json.load(f).get(top[0])
+            except Exception:
+                pass
+            ach = top[3] / top[2] / 1e3
+            roofline = {"kernel": top[0], "bound": "hbm", "achieved": round(ach, 1), "peak": hbm_peak, "unit": "GB/s",
+                        "frac": round(ach / hbm_peak, 4), "traffic": traffic, "peak_source": peak_src,
+                        "algorithmic_bytes_per_launch": int(top[3]), "us_per_launch": round(top[2], 1)}
+        cpu_fps, cores, cpu_dt = cpu_stack_sample(a, a.cpu_frames)
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": max(a.warmup, 3),
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": {"mx32": "fp4 (e2m1, ue8m0 per 32) x fp4 -> f32", "nv16": "fp4 (e2m1, e4m3 per 16) -> f32",
+                      "fp8_1x128": "fp8 (e4m3, f32 per 1x128) -> f32"}[a.fmt],
+            "data": "synthetic",
+            "config": {"workload": workload_name(a), "frames_per_gpu": T, "format": a.fmt, "blocks": a.blocks,
+                       "l2": "working set per launch > L2 (126 MB) at T=90000; per-op timings flush L2",
+                       "parallelism": f"frame shards x{world}, weights replicated, ids all-gather"},
+            "tflops": value * flops_per_frame / 1e12,
+            "flops_per_frame": flops_per_frame,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": T * cfg.d_model * 2, "d2h_bytes_per_step": T * 4,
+                    "ms_per_step": e2e_ms / a.steps},
+            "gpu_launches": comp.launches * a.steps,
+            "gpu_launches_per_step": comp.launches,
+            "device_status": status,
+            "clocks": clocks,
+            "roofline": roofline,
+            "breakdown": breakdown,
+            "cpu_baseline": {"value": cpu_fps, "unit": UNIT, "cores": cores, "kind": "port",
+                             "sample": f"{a.cpu_frames} frames of the same stack on the host cores ({cpu_dt:.1f} s)"},
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    a = parse()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)
+
+
+if __name__ == "__main__":
+    main()

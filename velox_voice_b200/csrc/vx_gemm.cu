@@ -101,14 +101,11 @@ struct __align__(1024) SmemLayout {
   int abort_flag;
 };
 
-// sigmoid(z) = 0.5 tanh(z / 2) + 0.5: one MUFU operation per element (tanh.approx, relative
-// error ~2^-11, below bf16 resolution) instead of an exponential plus a reciprocal.
-__device__ __forceinline__ float sigmoid_f(float z) {
-  float t;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * z));
-  return fmaf(0.5f, t, 0.5f);
-}
-__device__ __forceinline__ float silu_f(float z) { return z * sigmoid_f(z); }
+// sigmoid via ex2.approx + rcp.approx (relative error ~1e-6).  A tanh.approx formulation
+// needs one MUFU operation less but its 2^-11 error flips FP4 codes / bf16 roundings of the
+// re-quantized activations often enough to move CTC argmaxes; accuracy wins here.
+__device__ __forceinline__ float sigmoid_f(float z) { return __fdividef(1.0f, 1.0f + __expf(-z)); }
+__device__ __forceinline__ float silu_f(float z) { return __fdividef(z, 1.0f + __expf(-z)); }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);

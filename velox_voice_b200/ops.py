@@ -46,6 +46,24 @@ _SF_FORMATS = (FMT_BLK16_A, FMT_BLK16_B, FMT_MX32, FMT_NV16)
 _BLOCK = {FMT_BLK16_A: 16, FMT_BLK16_B: 16, FMT_NV16: 16, FMT_MX32: 32, FMT_FP8_1X128: 128}
 
 
+_launches = 0
+
+
+def _count(n: int = 1) -> None:
+    global _launches
+    _launches += n
+
+
+def launch_count() -> int:
+    """Kernels of this library launched since :func:`reset_launch_count` (host-side count)."""
+    return _launches
+
+
+def reset_launch_count() -> None:
+    global _launches
+    _launches = 0
+
+
 def _fmt(fmt) -> int:
     if isinstance(fmt, str):
         try:
@@ -140,6 +158,7 @@ def amax(x: torch.Tensor) -> torch.Tensor:
     out = torch.empty((1,), dtype=torch.float32, device=x.device)
     rc = _lib.load().vx_amax(x.data_ptr(), _dt(x, "x"), x.shape[0], x.shape[1], x.stride(0), out.data_ptr(), _stream())
     _lib.check(rc, "vx_amax")
+    _count()
     return out
 
 
@@ -166,6 +185,7 @@ def quantize(
         _ptr(scales), _ptr(sf_t), _ptr(amax_t), _stream(),
     )
     _lib.check(rc, "vx_quantize_pack")
+    _count()
     return Quantized(fmt, M, K, codes, scales, sf_t, amax_t)
 
 
@@ -202,6 +222,7 @@ def ln_quantize(
         _ptr(y), _dt(y, "y") if y is not None else 0, K, _stream(),
     )
     _lib.check(rc, "vx_ln_quantize_pack")
+    _count()
     q = Quantized(fmt, M, K, codes, scales, sf_t, amax_t)
     return (q, y) if y is not None else q
 
@@ -222,6 +243,7 @@ def layernorm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: flo
         None, 0, None, None, None, out2.data_ptr(), _dt(out2, "out"), out2.stride(0), _stream(),
     )
     _lib.check(rc, "vx_ln_quantize_pack")
+    _count()
     return out.view(shape)
 
 
@@ -234,6 +256,7 @@ def sf_from_natural(fmt, scales: torch.Tensor, rows: int, k: int) -> torch.Tenso
     kg = int(lib.vx_sf_kgroups(fmt, k))
     out = torch.empty(((rows + 127) // 128, kg, 512), dtype=torch.uint8, device=scales.device)
     _lib.check(lib.vx_sf_from_natural(fmt, scales.data_ptr(), rows, k, out.data_ptr(), _stream()), "vx_sf_from_natural")
+    _count()
     return out
 
 
@@ -318,6 +341,7 @@ def bsgemm(
         d.out_dtype, d.out, d.ldo = _dt(out, "out"), out.data_ptr(), out.stride(0)
         result = out
     _lib.check(_lib.load().vx_bsgemm(C.byref(d), _stream()), "vx_bsgemm")
+    _count()
     del keep
     return result
 
