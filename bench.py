@@ -44,6 +44,9 @@ def parse():
     ap.add_argument("--blocks", type=int, default=12)
     ap.add_argument("--cpu-frames", type=int, default=1024, help="frames of the CPU baseline sample")
     ap.add_argument("--no-breakdown", action="store_true")
+    ap.add_argument("--breakdown-only", action="store_true",
+                    help="time the individual launches only (profiling aid); prints one JSON line")
+    ap.add_argument("--ops", default="", help="with --breakdown-only: substring filter on the op name")
     return ap.parse_args()
 
 
@@ -174,7 +177,7 @@ def run_reference(a):
 # ----------------------------------------------------------------------------- per-op breakdown
 
 
-def op_breakdown(stack, T, fmt_name):
+def op_breakdown(stack, T, fmt_name, only=""):
     """Times every distinct launch of one block (+ CTC) alone, L2 flushed before each timed
     launch, and returns [(name, count_per_step, us, algorithmic_bytes, flops)]."""
     import torch
@@ -201,6 +204,8 @@ def op_breakdown(stack, T, fmt_name):
     cases = []
 
     def add(name, count, fn, nbytes, flops):
+        if only and only not in name:
+            return
         for _ in range(2):
             fn()
         ts = []
@@ -281,6 +286,12 @@ def run_ours(a):
     pos = torch.randn(T, cfg.d_model, generator=g).bfloat16().to(dev)
     if a.fmt == "nv16":
         stack.calibrate(feats_host[:4096].to(dev), pos[:4096])
+    if a.breakdown_only:
+        cases = op_breakdown(stack, T, a.fmt, a.ops)
+        print(json.dumps({"breakdown": [{"op": n, "launches_per_step": c, "us": round(us, 1),
+                                         "GBps": round(nb / us / 1e3, 1), "TFLOPs": round(fl / us / 1e6, 1)}
+                                        for n, c, us, nb, fl in cases]}), flush=True)
+        return
     comp = stack.compile(T)
     comp.pos.copy_(pos)
     comp.x_in.copy_(feats_host)

@@ -130,6 +130,7 @@ typedef struct vx_gemm_desc {
 } vx_gemm_desc;
 
 #define VX_GEMM_DIRECT_STORE 1 /* bypass the shared-memory staged TMA store */
+#define VX_GEMM_STREAM_B 2     /* never keep the B tile resident in shared memory */
 
 int vx_bsgemm(const vx_gemm_desc* desc, void* stream);
 

@@ -25,6 +25,7 @@ FMT_BY_NAME = {
 DT_F32, DT_BF16, DT_FP4 = 0, 1, 2
 EPI_NONE, EPI_BIAS, EPI_BIAS_SWISH, EPI_BIAS_GLU, EPI_BIAS_RESIDUAL = range(5)
 GEMM_DIRECT_STORE = 1
+GEMM_STREAM_B = 2
 
 EXPORTS = (
     "vx_abi_version",

@@ -42,15 +42,17 @@ constexpr int BM = 128;            // rows of A per tile = TMEM lanes
 constexpr int BN = 128;            // rows of B per tile = accumulator columns
 constexpr int STAGE_ROW_BYTES = 128;  // K bytes per stage: 256 FP4 or 128 FP8 elements
 constexpr int TILE_BYTES = BM * STAGE_ROW_BYTES;  // 16 KB
-constexpr int NSTAGE = 4;
 constexpr int SF_STAGE_MAX = 4 * 512;  // scale-factor atoms of one operand per stage
+constexpr int MAX_STAGES = 8;          // ring slots (the arena size decides how many are used)
+constexpr int ARENA_BYTES = 160 * 1024;
+constexpr int RESIDENT_MAX_KSTAGES = 4;                  // B kept in shared memory up to 4 K stages
 constexpr int NUM_THREADS = 576;       // 2 + 16 warps
 constexpr int EPI_WARP0 = 2;
 constexpr int STAGING_BYTES = 32 * 128;  // 32 rows x up to 128 bytes per epilogue warp
 constexpr int FP8_MAX_KB = 16;           // K <= 2048 for the FP8 path
 
 // tensor-memory columns
-constexpr int TM_ACC0 = 0, TM_SFA = 256, TM_SFB = 272, TM_COLS = 512;
+constexpr int TM_ACC0 = 0, TM_SFA = 256, TM_SFB = 272, TM_COLS = 512;  // SFB: up to 32 columns
 
 enum Kind { KIND_FP4_VEC2 = 0, KIND_FP4_VEC4 = 1, KIND_FP8 = 2 };
 
@@ -70,6 +72,11 @@ struct GemmParams {
   const float* fa;        // FP8: f32 [M, K/128]
   const float* fb;        // FP8: f32 [N, K/128]
   // epilogue
+  // shared-memory plan
+  int b_resident;         // 1: the CTA keeps its B tile (all K stages) in shared memory
+  int num_slots;          // ring slots in use
+  int a_slot_bytes;       // bytes of one operand tile + its scale-factor atoms in the arena
+  int tma_residual;       // 1: residual tiles are prefetched by TMA into the staging buffers
   int out_dtype;          // vx_dtype
   int tma_store;
   void* out;
@@ -87,18 +94,43 @@ struct GemmParams {
   int* status;
 };
 
+// Operand arena, two plans:
+//   streaming  slot s = [A tile 16K | SFA 2K | B tile 16K | SFB 2K], ARENA / 36K slots;
+//   B resident [B stage 0 .. k-1: tile 16K | SFB 2K] then slots [A tile 16K | SFA 2K].
 struct __align__(1024) SmemLayout {
-  uint8_t a[NSTAGE][TILE_BYTES];
-  uint8_t b[NSTAGE][TILE_BYTES];
-  uint8_t sfa[NSTAGE][SF_STAGE_MAX];
-  uint8_t sfb[NSTAGE][SF_STAGE_MAX];
+  uint8_t arena[ARENA_BYTES];
   uint8_t staging[16][STAGING_BYTES];
-  uint64_t full[NSTAGE];
-  uint64_t empty[NSTAGE];
+  uint64_t full[MAX_STAGES];
+  uint64_t empty[MAX_STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t b_full;
+  uint64_t res_full[16];
   uint32_t tmem_base;
   int abort_flag;
+};
+
+// Tile order.  Streaming: tiles round-robin over CTAs, n fastest (neighbouring CTAs share the
+// A tile through L2).  B resident: a CTA owns one n-block and walks down the m-blocks.
+struct TileWalk {
+  int nb_fixed, mb0, mb_step, t0, t_step, n_tiles, m_tiles, total, resident;
+  __device__ __forceinline__ TileWalk(const GemmParams& p) {
+    n_tiles = p.n_tiles; m_tiles = p.m_tiles; total = p.m_tiles * p.n_tiles; resident = p.b_resident;
+    nb_fixed = blockIdx.x % p.n_tiles;
+    mb0 = blockIdx.x / p.n_tiles;
+    mb_step = gridDim.x / p.n_tiles;
+    t0 = blockIdx.x; t_step = gridDim.x;
+  }
+  // i-th tile of this CTA; false when exhausted
+  __device__ __forceinline__ bool get(int i, int& mb, int& nb) const {
+    if (resident) {
+      mb = mb0 + i * mb_step; nb = nb_fixed;
+      return mb < m_tiles;
+    }
+    const int t = t0 + i * t_step;
+    mb = t / n_tiles; nb = t - mb * n_tiles;
+    return t < total;
+  }
 };
 
 // sigmoid via ex2.approx + rcp.approx (relative error ~1e-6).  A tanh.approx formulation
@@ -122,7 +154,8 @@ struct ChunkOut {
   // (accumulator column order), `out_col0` the output / residual column.
   static __device__ __forceinline__ void apply(const GemmParams& p, float (&z)[32], float (&gate)[32],
                                                int64_t row, int64_t bias_col0, int64_t gate_col0,
-                                               int64_t out_col0, bool row_ok) {
+                                               int64_t out_col0, bool row_ok, const uint8_t* res_smem,
+                                               int lane) {
     if constexpr (EPI != VX_EPI_NONE) {
       if (p.bias) {
         if (bias_col0 + 32 <= p.N) {
@@ -152,7 +185,19 @@ struct ChunkOut {
 #pragma unroll
       for (int i = 0; i < 32; ++i) z[i] *= sigmoid_f(gate[i]);
     } else if constexpr (EPI == VX_EPI_BIAS_RESIDUAL) {
-      if (row_ok) {
+      if (res_smem) {
+        // bf16 block staged by TMA: 64-byte rows, 16-byte slots swizzled by (row >> 1) & 3
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const uint4 u = *reinterpret_cast<const uint4*>(res_smem + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4));
+          const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            z[8 * v + 2 * j] = fmaf(p.alpha, z[8 * v + 2 * j], __uint_as_float(w[j] << 16));
+            z[8 * v + 2 * j + 1] = fmaf(p.alpha, z[8 * v + 2 * j + 1], __uint_as_float(w[j] & 0xffff0000u));
+          }
+        }
+      } else if (row_ok) {
         if (p.residual_dtype == VX_BF16) {
           const __nv_bfloat16* r = static_cast<const __nv_bfloat16*>(p.residual) + row * p.ldr + out_col0;
           if (out_col0 + 32 <= p.N && ((reinterpret_cast<uintptr_t>(r) & 15) == 0)) {
@@ -268,7 +313,8 @@ __device__ __forceinline__ uint32_t store_chunk_fp4(const GemmParams& p, const f
 template <int KIND, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-              const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
+              const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_res,
+              const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   SmemLayout& sm = *reinterpret_cast<SmemLayout*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -279,11 +325,21 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int total_tiles = p.m_tiles * p.n_tiles;
+  const TileWalk walk(p);
+  const int nslots = p.num_slots;
+  // arena addressing
+  const int b_res_bytes = p.b_resident ? p.k_stages * p.a_slot_bytes : 0;
+  const int slot_bytes = p.b_resident ? p.a_slot_bytes : 2 * p.a_slot_bytes;
+  auto slot_a = [&](int s2) -> uint8_t* { return sm.arena + b_res_bytes + s2 * slot_bytes; };
+  auto slot_sfa = [&](int s2) -> uint8_t* { return slot_a(s2) + TILE_BYTES; };
+  auto stage_b = [&](int s2, int ks) -> uint8_t* {
+    return p.b_resident ? sm.arena + ks * p.a_slot_bytes : slot_a(s2) + p.a_slot_bytes;
+  };
+  auto stage_sfb = [&](int s2, int ks) -> uint8_t* { return stage_b(s2, ks) + TILE_BYTES; };
 
   // ---- set-up
   if (threadIdx.x == 0) {
-    for (int s = 0; s < NSTAGE; ++s) {
+    for (int s = 0; s < MAX_STAGES; ++s) {
       mbar_init(&sm.full[s], 1);
       mbar_init(&sm.empty[s], 1);
     }
@@ -291,15 +347,19 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       mbar_init(&sm.tmem_full[a], 1);
       mbar_init(&sm.tmem_empty[a], 16);
     }
+    mbar_init(&sm.b_full, 1);
+    for (int w = 0; w < 16; ++w) mbar_init(&sm.res_full[w], 1);
     sm.abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
     if (p.tma_store) prefetch_tmap(&tmap_out);
+    if (p.tma_residual) prefetch_tmap(&tmap_res);
   }
+  uint8_t* unit_sf = sm.staging[0];  // rowscale only: one atom of 0x7F, copied to TMEM before any tile
   if (!FP8 && p.sf_unit) {
     // unit scale factors (UE8M0 0x7F = 1.0) for the per-row-scaled format
-    uint32_t* u = reinterpret_cast<uint32_t*>(&sm.sfa[0][0]);
+    uint32_t* u = reinterpret_cast<uint32_t*>(unit_sf);
     for (int i = threadIdx.x; i < 512 / 4; i += NUM_THREADS) u[i] = 0x7F7F7F7Fu;
     fence_proxy_async_smem();
   }
@@ -316,22 +376,36 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     // =========================== TMA producer ===========================
     if (lane == 0) {
       uint32_t s = 0, ph = 0;
-      const uint32_t sf_bytes = (FP8 || p.sf_unit) ? 0u : static_cast<uint32_t>(2 * APS * 512);
+      const bool with_sf = !(FP8 || p.sf_unit);
+      const uint32_t sf_bytes = with_sf ? static_cast<uint32_t>(APS * 512) : 0u;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const int mb = t / p.n_tiles, nb = t - mb * p.n_tiles;
+      int mb, nb;
+      if (p.b_resident && walk.get(0, mb, nb)) {
+        // the CTA's B tile: every K stage, once
+        mbar_expect_tx(&sm.b_full, p.k_stages * (TILE_BYTES + sf_bytes));
+        for (int ks = 0; ks < p.k_stages; ++ks) {
+          tma_load_2d(stage_b(0, ks), &tmap_b, ks * STAGE_ROW_BYTES, nb * BN, &sm.b_full);
+          if (with_sf)
+            bulk_load(stage_sfb(0, ks), p.sfb + (static_cast<int64_t>(nb) * p.sf_kg + ks * APS) * 512,
+                      APS * 512, &sm.b_full);
+        }
+      }
+      const uint32_t slot_tx = (p.b_resident ? 1u : 2u) * (TILE_BYTES + sf_bytes);
+      for (int i = 0; ok && walk.get(i, mb, nb); ++i) {
         for (int ks = 0; ks < p.k_stages; ++ks) {
           if (!mbar_wait(&sm.empty[s], ph ^ 1, p.status, 1)) { ok = false; break; }
-          mbar_expect_tx(&sm.full[s], 2 * TILE_BYTES + sf_bytes);
-          tma_load_2d(sm.a[s], &tmap_a, ks * STAGE_ROW_BYTES, mb * BM, &sm.full[s]);
-          tma_load_2d(sm.b[s], &tmap_b, ks * STAGE_ROW_BYTES, nb * BN, &sm.full[s]);
-          if (sf_bytes) {
-            bulk_load(sm.sfa[s], p.sfa + (static_cast<int64_t>(mb) * p.sf_kg + ks * APS) * 512,
+          mbar_expect_tx(&sm.full[s], slot_tx);
+          tma_load_2d(slot_a(s), &tmap_a, ks * STAGE_ROW_BYTES, mb * BM, &sm.full[s]);
+          if (with_sf)
+            bulk_load(slot_sfa(s), p.sfa + (static_cast<int64_t>(mb) * p.sf_kg + ks * APS) * 512,
                       APS * 512, &sm.full[s]);
-            bulk_load(sm.sfb[s], p.sfb + (static_cast<int64_t>(nb) * p.sf_kg + ks * APS) * 512,
-                      APS * 512, &sm.full[s]);
+          if (!p.b_resident) {
+            tma_load_2d(stage_b(s, ks), &tmap_b, ks * STAGE_ROW_BYTES, nb * BN, &sm.full[s]);
+            if (with_sf)
+              bulk_load(stage_sfb(s, ks), p.sfb + (static_cast<int64_t>(nb) * p.sf_kg + ks * APS) * 512,
+                        APS * 512, &sm.full[s]);
           }
-          if (++s == NSTAGE) { s = 0; ph ^= 1; }
+          if (++s == static_cast<uint32_t>(nslots)) { s = 0; ph ^= 1; }
         }
       }
       if (!ok) sm.abort_flag = 1;
@@ -344,12 +418,25 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       bool ok = true;
       const uint32_t idesc_base =
           FP8 ? make_idesc_f8(BM, BN) : make_idesc_mxf4(BM, BN, p.sf_e8m0 != 0);
+      const bool with_sf = !(FP8 || p.sf_unit);
+      int mb, nb;
       if (!FP8 && p.sf_unit) {
-        const uint64_t d = make_desc_sf(smem_u32(&sm.sfa[0][0]));
+        const uint64_t d = make_desc_sf(smem_u32(unit_sf));
         tc_cp_32x128b_warpx4(tmem_base + TM_SFA, d);
         tc_cp_32x128b_warpx4(tmem_base + TM_SFB, d);
       }
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      if (p.b_resident && walk.get(0, mb, nb)) {
+        if (!mbar_wait(&sm.b_full, 0, p.status, 5)) ok = false;
+        tc_fence_after();
+        if (ok && with_sf) {
+          // B's scale factors stay in tensor memory for the whole kernel
+          for (int ks = 0; ks < p.k_stages; ++ks)
+            for (int a = 0; a < APS; ++a)
+              tc_cp_32x128b_warpx4(tmem_base + TM_SFB + (ks * APS + a) * 4,
+                                   make_desc_sf(smem_u32(stage_sfb(0, ks) + a * 512)));
+        }
+      }
+      for (int i = 0; ok && walk.get(i, mb, nb); ++i) {
         for (int ks = 0; ks < p.k_stages; ++ks) {
           const bool new_group = FP8 || ks == 0;
           const uint32_t acc = group & 1;
@@ -359,8 +446,8 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
           }
           if (!mbar_wait(&sm.full[s], ph, p.status, 3)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(sm.a[s]);
-          const uint32_t b_addr = smem_u32(sm.b[s]);
+          const uint32_t a_addr = smem_u32(slot_a(s));
+          const uint32_t b_addr = smem_u32(stage_b(s, ks));
           const uint32_t d_tmem = tmem_base + TM_ACC0 + acc * BN;
           if constexpr (FP8) {
 #pragma unroll
@@ -368,11 +455,17 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
               mma_f8(d_tmem, make_desc_k128(a_addr + j * 32), make_desc_k128(b_addr + j * 32),
                      idesc_base, j != 0);
           } else {
-            if (!p.sf_unit) {
+            uint32_t sfb_base = TM_SFB;
+            if (with_sf) {
 #pragma unroll
-              for (int a = 0; a < APS; ++a) {
-                tc_cp_32x128b_warpx4(tmem_base + TM_SFA + a * 4, make_desc_sf(smem_u32(&sm.sfa[s][a * 512])));
-                tc_cp_32x128b_warpx4(tmem_base + TM_SFB + a * 4, make_desc_sf(smem_u32(&sm.sfb[s][a * 512])));
+              for (int a = 0; a < APS; ++a)
+                tc_cp_32x128b_warpx4(tmem_base + TM_SFA + a * 4, make_desc_sf(smem_u32(slot_sfa(s) + a * 512)));
+              if (p.b_resident) {
+                sfb_base = TM_SFB + ks * APS * 4;
+              } else {
+#pragma unroll
+                for (int a = 0; a < APS; ++a)
+                  tc_cp_32x128b_warpx4(tmem_base + TM_SFB + a * 4, make_desc_sf(smem_u32(stage_sfb(s, ks) + a * 512)));
               }
             }
 #pragma unroll
@@ -383,7 +476,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
               else { sf_col = j * 4; sf_id = 0; }
               mma_mxf4<VEC>(d_tmem, make_desc_k128(a_addr + j * 32), make_desc_k128(b_addr + j * 32),
                             idesc_with_sf_id(idesc_base, sf_id, sf_id), tmem_base + TM_SFA + sf_col,
-                            tmem_base + TM_SFB + sf_col, (ks | j) != 0);
+                            tmem_base + sfb_base + sf_col, (ks | j) != 0);
             }
           }
           tc_commit(&sm.empty[s]);  // ring slot reusable once these MMAs have read it
@@ -391,7 +484,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             tc_commit(&sm.tmem_full[acc]);
             ++group;
           }
-          if (++s == NSTAGE) { s = 0; ph ^= 1; }
+          if (++s == static_cast<uint32_t>(nslots)) { s = 0; ph ^= 1; }
         }
       }
       if (!ok) sm.abort_flag = 1;
@@ -415,12 +508,27 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     uint8_t* buf = sm.staging[ew];
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
 
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      const int mb = t / p.n_tiles, nb = t - mb * p.n_tiles;
+    int mb, nb;
+    uint32_t res_phase = 0;
+    uint8_t* res_buf = buf + STAGING_BYTES / 2;  // second half of the staging buffer
+    for (int it = 0; ok && walk.get(it, mb, nb); ++it) {
       const int64_t row = static_cast<int64_t>(mb) * BM + q * 32 + lane;
       const bool row_ok = row < p.M;
       const int64_t acc_col0 = static_cast<int64_t>(nb) * BN + cc * 32;             // accumulator / bias column
       const int64_t out_col0 = static_cast<int64_t>(nb) * out_tile_cols + cc * 32;  // output column
+      const bool box_ok = static_cast<int64_t>(mb) * BM + q * 32 < p.M && out_col0 < n_out;
+      bool res_pending = false;
+      if constexpr (EPI == VX_EPI_BIAS_RESIDUAL) {
+        // fetch this warp's 32 x 32 residual block now; it lands while the MMAs of the tile run
+        if (p.tma_residual && box_ok) {
+          if (lane == 0) {
+            tma_store_wait_read<0>();  // (the output box of the previous tile shares the staging buffer)
+            mbar_expect_tx(&sm.res_full[ew], 32 * 64);
+            tma_load_2d(res_buf, &tmap_res, static_cast<int>(out_col0), mb * BM + q * 32, &sm.res_full[ew]);
+          }
+          res_pending = true;
+        }
+      }
 
       float z[32], gate[32];
       if constexpr (FP8) {
@@ -499,7 +607,13 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       }
       if (!has_work) continue;
 
-      ChunkOut<EPI>::apply(p, z, gate, row, acc_col0, acc_col0 + 64, out_col0, row_ok);
+      const uint8_t* res_smem = nullptr;
+      if (res_pending) {
+        if (!mbar_wait(&sm.res_full[ew], res_phase, p.status, 6)) { ok = false; break; }
+        res_phase ^= 1;
+        res_smem = res_buf;
+      }
+      ChunkOut<EPI>::apply(p, z, gate, row, acc_col0, acc_col0 + 64, out_col0, row_ok, res_smem, lane);
 
       if (p.out_dtype == VX_FP4) {
         const uint32_t sb = store_chunk_fp4(p, z, row, out_col0, g_out, row_ok && out_col0 < n_out);
@@ -543,7 +657,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         }
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0 && static_cast<int64_t>(mb) * BM + q * 32 < p.M && out_col0 < n_out) {
+        if (lane == 0 && box_ok) {
           tma_store_2d(&tmap_out, static_cast<int>(out_col0), mb * BM + q * 32, buf);
           tma_store_commit();
         }
@@ -671,8 +785,8 @@ int* cached_status_ptr() {
 constexpr size_t kSmemBytes = sizeof(SmemLayout) + 1024;
 
 template <int KIND, int EPI>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const GemmParams& p,
-           cudaStream_t st) {
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const CUtensorMap& tr,
+           GemmParams& p, bool allow_resident, cudaStream_t st) {
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
@@ -688,22 +802,37 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, 
     VX_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     if (dev >= 0 && dev < 64) sm_cache[dev] = sms;
   }
+  // shared-memory plan: keep B resident when all of its K stages fit beside a useful ring
+  const bool with_sf = KIND != KIND_FP8 && !p.sf_unit;
+  p.a_slot_bytes = TILE_BYTES + (with_sf ? SF_STAGE_MAX : 0);
   const int tiles = p.m_tiles * p.n_tiles;
-  const int grid = tiles < sms ? tiles : sms;
-  bsgemm_kernel<KIND, EPI><<<grid, NUM_THREADS, kSmemBytes, st>>>(ta, tb, to, p);
+  int grid;
+  p.b_resident = allow_resident && p.k_stages <= RESIDENT_MAX_KSTAGES && p.n_tiles <= sms;
+  if (p.b_resident) {
+    int slots = (ARENA_BYTES - p.k_stages * p.a_slot_bytes) / p.a_slot_bytes;
+    p.num_slots = slots > MAX_STAGES ? MAX_STAGES : slots;
+    int groups = sms / p.n_tiles;
+    if (groups > p.m_tiles) groups = p.m_tiles;
+    grid = groups * p.n_tiles;
+  } else {
+    int slots = ARENA_BYTES / (2 * p.a_slot_bytes);
+    p.num_slots = slots > MAX_STAGES ? MAX_STAGES : slots;
+    grid = tiles < sms ? tiles : sms;
+  }
+  bsgemm_kernel<KIND, EPI><<<grid, NUM_THREADS, kSmemBytes, st>>>(ta, tb, to, tr, p);
   VX_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
 template <int KIND>
 int dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to,
-                 const GemmParams& p, cudaStream_t st) {
+                 const CUtensorMap& tr, GemmParams& p, bool res, cudaStream_t st) {
   switch (epi) {
-    case VX_EPI_NONE: return launch<KIND, VX_EPI_NONE>(ta, tb, to, p, st);
-    case VX_EPI_BIAS: return launch<KIND, VX_EPI_BIAS>(ta, tb, to, p, st);
-    case VX_EPI_BIAS_SWISH: return launch<KIND, VX_EPI_BIAS_SWISH>(ta, tb, to, p, st);
-    case VX_EPI_BIAS_GLU: return launch<KIND, VX_EPI_BIAS_GLU>(ta, tb, to, p, st);
-    case VX_EPI_BIAS_RESIDUAL: return launch<KIND, VX_EPI_BIAS_RESIDUAL>(ta, tb, to, p, st);
+    case VX_EPI_NONE: return launch<KIND, VX_EPI_NONE>(ta, tb, to, tr, p, res, st);
+    case VX_EPI_BIAS: return launch<KIND, VX_EPI_BIAS>(ta, tb, to, tr, p, res, st);
+    case VX_EPI_BIAS_SWISH: return launch<KIND, VX_EPI_BIAS_SWISH>(ta, tb, to, tr, p, res, st);
+    case VX_EPI_BIAS_GLU: return launch<KIND, VX_EPI_BIAS_GLU>(ta, tb, to, tr, p, res, st);
+    case VX_EPI_BIAS_RESIDUAL: return launch<KIND, VX_EPI_BIAS_RESIDUAL>(ta, tb, to, tr, p, res, st);
     default: return fail(-1, "unknown epilogue %d", epi);
   }
 }
@@ -815,10 +944,19 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
   } else {
     to = ta;  // unused by the kernel
   }
-
-  if (fp8) return dispatch_epi<KIND_FP8>(epi, ta, tb, to, p, st);
-  if (fmt == VX_FMT_ROWSCALE || fmt == VX_FMT_MX32) return dispatch_epi<KIND_FP4_VEC2>(epi, ta, tb, to, p, st);
-  return dispatch_epi<KIND_FP4_VEC4>(epi, ta, tb, to, p, st);
+  CUtensorMap tr = ta;
+  p.tma_residual = 0;
+  if (epi == VX_EPI_BIAS_RESIDUAL && p.tma_store && d->out_dtype == VX_BF16 && d->residual_dtype == VX_BF16 &&
+      aligned16(d->residual) && (d->ldr * 2) % 16 == 0) {
+    rc = make_tmap(&tr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, d->residual, M, N, d->ldr * 2, 32, 32,
+                   CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc) return rc;
+    p.tma_residual = 1;
+  }
+  const bool res = !(d->flags & VX_GEMM_STREAM_B);
+  if (fp8) return dispatch_epi<KIND_FP8>(epi, ta, tb, to, tr, p, res, st);
+  if (fmt == VX_FMT_ROWSCALE || fmt == VX_FMT_MX32) return dispatch_epi<KIND_FP4_VEC2>(epi, ta, tb, to, tr, p, res, st);
+  return dispatch_epi<KIND_FP4_VEC4>(epi, ta, tb, to, tr, p, res, st);
 }
 
 int vx_mma_peak_probe(int kind, int n_tile, int iters, float* tflops_out) {

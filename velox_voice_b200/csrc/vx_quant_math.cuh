@@ -26,26 +26,39 @@ __device__ __forceinline__ void ue8m0_from_amax(float amax, uint32_t& byte, floa
   rcp = ef <= 253u ? __uint_as_float((254u - ef) << 23) : 0.0f;
 }
 
-// Magnitude code of |q| (count of thresholds strictly exceeded), without compares.
-// 2^23 + x rounded toward +inf leaves ceil(x) in the low mantissa bits, so
-//   #{k : 0.25 + 0.5 k < a, k = 0..3} = clamp(ceil(2 a - 0.5), 0, 4)
-//   #{2.5 < a, 3.5 < a}               = clamp(ceil(a - 2.5), 0, 2)
-// Each sum is formed with a single rounding; below 2^23 (negative x) the clamp yields 0.
-__device__ __forceinline__ uint32_t e2m1_mag(float a) {
-  constexpr uint32_t kMagic = 0x4B000000u;  // bit pattern of 2^23
-  uint32_t lo = __float_as_uint(__fmaf_ru(a, 2.0f, 8388607.5f));
-  lo = min(max(lo, kMagic), kMagic + 4u);
-  uint32_t hi = __float_as_uint(__fadd_ru(a, 8388605.5f));
-  hi = min(max(hi, kMagic), kMagic + 2u);
-  return (lo - kMagic) + (hi - kMagic);
-}
-__device__ __forceinline__ uint32_t e2m1_code(float q) {
-  return e2m1_mag(fabsf(q)) | (q < 0.0f ? 8u : 0u);
+// E2M1 encode of 8 normalised values (q = v * rcp) into one 32-bit word, low nibble first.
+//
+// The reference rule -- magnitude code = number of thresholds {0.25, 0.75, 1.25, 1.75, 2.5,
+// 3.5} strictly exceeded, sign = (q < 0) -- is "round to nearest E2M1 value, ties toward zero,
+// capped at 4.0".  The hardware converter (cvt.rn.satfinite.e2m1x2.f32) rounds ties to even
+// and reaches 6.0, so it is fed a representative instead of q itself:
+//   n   = ceil(4 |q|) clamped to 16      (2^23 + x rounded toward +inf leaves ceil(x) in the
+//                                          low mantissa bits; all thresholds are multiples of 1/4)
+//   rep = n * 31/128                      strictly inside the interval that rounds, to nearest,
+//                                          to the reference's code for every n in 0..16
+// and rep carries q's sign bit.  q is formed as (v * rcp) + (+0) with two separate roundings:
+// a product that is -0 or underflows to -0 becomes +0, so the sign bit equals (q < 0) exactly
+// (a fused multiply-add would keep the sign of the unrounded product).
+__device__ __forceinline__ float e2m1_rep(float v, float rcp) {
+  const float q = __fadd_rn(__fmul_rn(v, rcp), 0.0f);
+  const float a4 = fminf(fabsf(q), 4.0f);
+  const float n23 = __fmaf_ru(a4, 4.0f, 8388608.0f);                // 2^23 + ceil(4 a4)
+  const float rep = __fmaf_rn(n23, 0.2421875f, -2031616.0f);        // n * 31/128, exact
+  return __uint_as_float(__float_as_uint(rep) | (__float_as_uint(q) & 0x80000000u));
 }
 __device__ __forceinline__ uint32_t e2m1_pack8(const float (&v)[8], float rcp) {
-  uint32_t w = 0;
+  float r[8];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) w |= e2m1_code(__fmul_rn(v[j], rcp)) << (4 * j);
+  for (int j = 0; j < 8; ++j) r[j] = e2m1_rep(v[j], rcp);
+  uint32_t w;
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+      "mov.b32 %0, {b0, b1, b2, b3};\n\t}"
+      : "=r"(w)
+      : "f"(r[0]), "f"(r[1]), "f"(r[2]), "f"(r[3]), "f"(r[4]), "f"(r[5]), "f"(r[6]), "f"(r[7]));
   return w;
 }
 

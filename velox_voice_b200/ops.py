@@ -40,6 +40,7 @@ from ._lib import (  # noqa: F401  (re-exported)
     FMT_NV16,
     FMT_ROWSCALE,
     GEMM_DIRECT_STORE,
+    GEMM_STREAM_B,
 )
 
 _SF_FORMATS = (FMT_BLK16_A, FMT_BLK16_B, FMT_MX32, FMT_NV16)
@@ -274,6 +275,7 @@ def bsgemm(
     out_amax: Optional[torch.Tensor] = None,
     out_natural: bool = False,
     direct_store: bool = False,
+    stream_b: bool = False,
 ):
     """``epilogue(A . B^T)``; A [M,K], B [N,K] quantized in the same format family.
 
@@ -314,7 +316,7 @@ def bsgemm(
         residual = _rows2d(residual, "residual")
         d.residual, d.residual_dtype, d.ldr = residual.data_ptr(), _dt(residual, "residual"), residual.stride(0)
         d.alpha = float(alpha)
-    d.flags = GEMM_DIRECT_STORE if direct_store else 0
+    d.flags = (GEMM_DIRECT_STORE if direct_store else 0) | (GEMM_STREAM_B if stream_b else 0)
     result = None
     if out_fmt is not None:
         ofmt = _fmt(out_fmt)
