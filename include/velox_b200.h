@@ -134,6 +134,15 @@ typedef struct vx_gemm_desc {
 
 int vx_bsgemm(const vx_gemm_desc* desc, void* stream);
 
+/* Phase trace of the GEMM pipeline (the reference has a compile-time %globaltimer trace of its
+ * Hopper QKV kernel, veloxvoice/kernels/csrc/hopper/block/wasp_producer.h:20-34).  While a
+ * device buffer of 3 * 32 * 8 u64 is registered, CTA 0 of every vx_bsgemm launch stamps the SM
+ * cycle counter at [role][tile][event]: role 0 = TMA producer (event k: slot for K stage k
+ * acquired), 1 = MMA issuer (0 accumulator free, 1 + k stage k landed, 6 tile committed),
+ * 2 = epilogue warp 0 (0 waiting, 1 accumulator ready, 2 TMEM read, 3 / 4 before / after the
+ * epilogue math, 5 staged, 6 store issued).  NULL switches it off. */
+int vx_set_trace_buffer(void* device_buffer, int64_t bytes);
+
 /* Tensor-core peak probe: times `iters` back-to-back MMAs (no memory traffic) per SM.
  * kind 0 = FP4 block-scaled (kind::mxf4nvf4), 1 = FP8 (kind::f8f6f4).  Host pointer out. */
 int vx_mma_peak_probe(int kind, int n_tile, int iters, float* tflops_out);

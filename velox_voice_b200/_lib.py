@@ -39,6 +39,7 @@ EXPORTS = (
     "vx_sf_from_natural",
     "vx_bsgemm",
     "vx_mma_peak_probe",
+    "vx_set_trace_buffer",
 )
 
 
@@ -121,6 +122,8 @@ def load(build_if_missing: bool = True) -> C.CDLL:
         lib.vx_sf_from_natural.argtypes = [i32, vp, i64, i64, vp, vp]
         lib.vx_bsgemm.restype = i32
         lib.vx_bsgemm.argtypes = [C.POINTER(GemmDesc), vp]
+        lib.vx_set_trace_buffer.restype = i32
+        lib.vx_set_trace_buffer.argtypes = [vp, i64]
         lib.vx_mma_peak_probe.restype = i32
         lib.vx_mma_peak_probe.argtypes = [i32, i32, i32, C.POINTER(C.c_float)]
         if lib.vx_abi_version() != 1:

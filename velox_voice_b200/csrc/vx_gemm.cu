@@ -77,6 +77,8 @@ struct GemmParams {
   int num_slots;          // ring slots in use
   int a_slot_bytes;       // bytes of one operand tile + its scale-factor atoms in the arena
   int tma_residual;       // 1: residual tiles are prefetched by TMA into the staging buffers
+  int dbg;                // ablation bits (investigation only)
+  unsigned long long* trace;  // phase trace buffer (CTA 0, first 32 tiles) or nullptr
   int out_dtype;          // vx_dtype
   int tma_store;
   void* out;
@@ -108,29 +110,6 @@ struct __align__(1024) SmemLayout {
   uint64_t res_full[16];
   uint32_t tmem_base;
   int abort_flag;
-};
-
-// Tile order.  Streaming: tiles round-robin over CTAs, n fastest (neighbouring CTAs share the
-// A tile through L2).  B resident: a CTA owns one n-block and walks down the m-blocks.
-struct TileWalk {
-  int nb_fixed, mb0, mb_step, t0, t_step, n_tiles, m_tiles, total, resident;
-  __device__ __forceinline__ TileWalk(const GemmParams& p) {
-    n_tiles = p.n_tiles; m_tiles = p.m_tiles; total = p.m_tiles * p.n_tiles; resident = p.b_resident;
-    nb_fixed = blockIdx.x % p.n_tiles;
-    mb0 = blockIdx.x / p.n_tiles;
-    mb_step = gridDim.x / p.n_tiles;
-    t0 = blockIdx.x; t_step = gridDim.x;
-  }
-  // i-th tile of this CTA; false when exhausted
-  __device__ __forceinline__ bool get(int i, int& mb, int& nb) const {
-    if (resident) {
-      mb = mb0 + i * mb_step; nb = nb_fixed;
-      return mb < m_tiles;
-    }
-    const int t = t0 + i * t_step;
-    mb = t / n_tiles; nb = t - mb * n_tiles;
-    return t < total;
-  }
 };
 
 // sigmoid via ex2.approx + rcp.approx (relative error ~1e-6).  A tanh.approx formulation
@@ -309,6 +288,16 @@ __device__ __forceinline__ uint32_t store_chunk_fp4(const GemmParams& p, const f
   return sbytes;
 }
 
+// Phase trace: SM cycle counter stamps of CTA 0's first 32 tiles, [role][tile][event].
+// roles: 0 producer, 1 MMA issuer, 2 epilogue warp 0.  Enabled by vx_set_trace_buffer().
+constexpr int TRACE_TILES = 32, TRACE_EVENTS = 8;
+__device__ __forceinline__ void trace_rec(const GemmParams& p, int role, int tile, int ev) {
+  if (p.trace && blockIdx.x == 0 && tile < TRACE_TILES)
+    p.trace[(role * TRACE_TILES + tile) * TRACE_EVENTS + ev] = clock64();
+}
+
+unsigned long long* g_trace_buffer = nullptr;
+
 // ---------------------------------------------------------------------------------------
 template <int KIND, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -325,17 +314,39 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const TileWalk walk(p);
   const int nslots = p.num_slots;
-  // arena addressing
-  const int b_res_bytes = p.b_resident ? p.k_stages * p.a_slot_bytes : 0;
-  const int slot_bytes = p.b_resident ? p.a_slot_bytes : 2 * p.a_slot_bytes;
-  auto slot_a = [&](int s2) -> uint8_t* { return sm.arena + b_res_bytes + s2 * slot_bytes; };
-  auto slot_sfa = [&](int s2) -> uint8_t* { return slot_a(s2) + TILE_BYTES; };
-  auto stage_b = [&](int s2, int ks) -> uint8_t* {
-    return p.b_resident ? sm.arena + ks * p.a_slot_bytes : slot_a(s2) + p.a_slot_bytes;
+  const bool resident = p.b_resident != 0;
+  const bool with_sf = !(FP8 || p.sf_unit);
+
+  // This CTA's tiles.  B resident: fixed n-block, m-blocks mb0, mb0 + mstep, ...; streaming:
+  // tiles t0, t0 + grid, ... with n fastest.  No division inside the loops.
+  const int total_tiles = p.m_tiles * p.n_tiles;
+  int my_tiles, mb0, nb0, mstep;
+  if (resident) {
+    nb0 = blockIdx.x % p.n_tiles;
+    mb0 = blockIdx.x / p.n_tiles;
+    mstep = gridDim.x / p.n_tiles;
+    my_tiles = mb0 < p.m_tiles ? (p.m_tiles - mb0 + mstep - 1) / mstep : 0;
+  } else {
+    mb0 = blockIdx.x / p.n_tiles;
+    nb0 = blockIdx.x - mb0 * p.n_tiles;
+    mstep = 0;
+    my_tiles = static_cast<int>(blockIdx.x) < total_tiles ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  }
+  const int step_m = resident ? mstep : static_cast<int>(gridDim.x) / p.n_tiles;
+  const int step_n = resident ? 0 : static_cast<int>(gridDim.x) % p.n_tiles;
+  // advance (mb, nb) to the CTA's next tile
+  auto next_tile = [&](int& mb, int& nb) {
+    mb += step_m;
+    nb += step_n;
+    if (nb >= p.n_tiles) { nb -= p.n_tiles; ++mb; }
   };
-  auto stage_sfb = [&](int s2, int ks) -> uint8_t* { return stage_b(s2, ks) + TILE_BYTES; };
+
+  // arena addressing (shared-memory byte addresses)
+  const uint32_t slot_bytes = resident ? p.a_slot_bytes : 2 * p.a_slot_bytes;
+  const uint32_t arena_u32 = smem_u32(sm.arena);
+  const uint32_t ring_u32 = arena_u32 + (resident ? p.k_stages * p.a_slot_bytes : 0);
+  uint8_t* ring_ptr = sm.arena + (resident ? p.k_stages * p.a_slot_bytes : 0);
 
   // ---- set-up
   if (threadIdx.x == 0) {
@@ -374,115 +385,139 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
 
   if (warp == 0) {
     // =========================== TMA producer ===========================
-    if (lane == 0) {
+    if (lane == 0 && my_tiles > 0) {
       uint32_t s = 0, ph = 0;
-      const bool with_sf = !(FP8 || p.sf_unit);
       const uint32_t sf_bytes = with_sf ? static_cast<uint32_t>(APS * 512) : 0u;
+      const int64_t sf_stage = APS * 512;
       bool ok = true;
-      int mb, nb;
-      if (p.b_resident && walk.get(0, mb, nb)) {
+      if (resident) {
         // the CTA's B tile: every K stage, once
         mbar_expect_tx(&sm.b_full, p.k_stages * (TILE_BYTES + sf_bytes));
         for (int ks = 0; ks < p.k_stages; ++ks) {
-          tma_load_2d(stage_b(0, ks), &tmap_b, ks * STAGE_ROW_BYTES, nb * BN, &sm.b_full);
+          uint8_t* dst = sm.arena + ks * p.a_slot_bytes;
+          tma_load_2d(dst, &tmap_b, ks * STAGE_ROW_BYTES, nb0 * BN, &sm.b_full);
           if (with_sf)
-            bulk_load(stage_sfb(0, ks), p.sfb + (static_cast<int64_t>(nb) * p.sf_kg + ks * APS) * 512,
+            bulk_load(dst + TILE_BYTES, p.sfb + (static_cast<int64_t>(nb0) * p.sf_kg) * 512 + ks * sf_stage,
                       APS * 512, &sm.b_full);
         }
       }
-      const uint32_t slot_tx = (p.b_resident ? 1u : 2u) * (TILE_BYTES + sf_bytes);
-      for (int i = 0; ok && walk.get(i, mb, nb); ++i) {
+      const uint32_t slot_tx = (resident ? 1u : 2u) * (TILE_BYTES + sf_bytes);
+      int mb = mb0, nb = nb0;
+      for (int i = 0; i < my_tiles && ok; ++i) {
+        const uint8_t* sfa_row = p.sfa + (static_cast<int64_t>(mb) * p.sf_kg) * 512;
+        const uint8_t* sfb_row = p.sfb + (static_cast<int64_t>(nb) * p.sf_kg) * 512;
         for (int ks = 0; ks < p.k_stages; ++ks) {
           if (!mbar_wait(&sm.empty[s], ph ^ 1, p.status, 1)) { ok = false; break; }
+          trace_rec(p, 0, i, ks < 4 ? ks : 3);
+          uint8_t* dst = ring_ptr + s * slot_bytes;
           mbar_expect_tx(&sm.full[s], slot_tx);
-          tma_load_2d(slot_a(s), &tmap_a, ks * STAGE_ROW_BYTES, mb * BM, &sm.full[s]);
-          if (with_sf)
-            bulk_load(slot_sfa(s), p.sfa + (static_cast<int64_t>(mb) * p.sf_kg + ks * APS) * 512,
-                      APS * 512, &sm.full[s]);
-          if (!p.b_resident) {
-            tma_load_2d(stage_b(s, ks), &tmap_b, ks * STAGE_ROW_BYTES, nb * BN, &sm.full[s]);
+          tma_load_2d(dst, &tmap_a, ks * STAGE_ROW_BYTES, mb * BM, &sm.full[s]);
+          if (with_sf) bulk_load(dst + TILE_BYTES, sfa_row + ks * sf_stage, APS * 512, &sm.full[s]);
+          if (!resident) {
+            tma_load_2d(dst + p.a_slot_bytes, &tmap_b, ks * STAGE_ROW_BYTES, nb * BN, &sm.full[s]);
             if (with_sf)
-              bulk_load(stage_sfb(s, ks), p.sfb + (static_cast<int64_t>(nb) * p.sf_kg + ks * APS) * 512,
-                        APS * 512, &sm.full[s]);
+              bulk_load(dst + p.a_slot_bytes + TILE_BYTES, sfb_row + ks * sf_stage, APS * 512, &sm.full[s]);
           }
           if (++s == static_cast<uint32_t>(nslots)) { s = 0; ph ^= 1; }
         }
+        next_tile(mb, nb);
       }
       if (!ok) sm.abort_flag = 1;
     }
   } else if (warp == 1) {
     // =========================== MMA issuer ===========================
-    if (lane == 0) {
+    // One thread; every instruction it executes is on the critical path of a tile (K = 512
+    // is only eight MMAs), so descriptors are formed with one add from values kept in
+    // registers: low word = (shared address >> 4) + 2 j for the j-th 64-element K step.
+    if (lane == 0 && my_tiles > 0) {
       uint32_t s = 0, ph = 0;
       uint32_t group = 0;  // accumulation groups issued (FP4: one per tile; FP8: one per stage)
       bool ok = true;
       const uint32_t idesc_base =
           FP8 ? make_idesc_f8(BM, BN) : make_idesc_mxf4(BM, BN, p.sf_e8m0 != 0);
-      const bool with_sf = !(FP8 || p.sf_unit);
-      int mb, nb;
+      // high words of the two descriptor kinds (see make_desc_k128 / make_desc_sf)
+      const uint32_t k128_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+      const uint32_t sf_hi = (128u >> 4) | (1u << 14);
+      auto desc = [](uint32_t lo, uint32_t hi) -> uint64_t {
+        return (static_cast<uint64_t>(hi) << 32) | (lo & 0x3fffu);
+      };
+      const uint32_t ring_lo = ring_u32 >> 4, slot_lo = slot_bytes >> 4, aslot_lo = p.a_slot_bytes >> 4;
+      const uint32_t arena_lo = arena_u32 >> 4;
+      const uint32_t tile_lo = TILE_BYTES >> 4;
+      // idesc and scale-factor columns of the four K steps of a stage
+      uint32_t idesc_j[4], sfcol_j[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t sf_col, sf_id;
+        if (FP8 || p.sf_unit) { sf_col = 0; sf_id = 0; }
+        else if (VEC == 2) { sf_col = (j >> 1) * 4; sf_id = (j & 1) * 2; }
+        else { sf_col = j * 4; sf_id = 0; }
+        idesc_j[j] = idesc_with_sf_id(idesc_base, sf_id, sf_id);
+        sfcol_j[j] = sf_col;
+      }
+      const uint32_t tm_sfa = tmem_base + TM_SFA, tm_sfb = tmem_base + TM_SFB;
       if (!FP8 && p.sf_unit) {
         const uint64_t d = make_desc_sf(smem_u32(unit_sf));
-        tc_cp_32x128b_warpx4(tmem_base + TM_SFA, d);
-        tc_cp_32x128b_warpx4(tmem_base + TM_SFB, d);
+        tc_cp_32x128b_warpx4(tm_sfa, d);
+        tc_cp_32x128b_warpx4(tm_sfb, d);
       }
-      if (p.b_resident && walk.get(0, mb, nb)) {
+      if (resident) {
         if (!mbar_wait(&sm.b_full, 0, p.status, 5)) ok = false;
         tc_fence_after();
         if (ok && with_sf) {
           // B's scale factors stay in tensor memory for the whole kernel
           for (int ks = 0; ks < p.k_stages; ++ks)
             for (int a = 0; a < APS; ++a)
-              tc_cp_32x128b_warpx4(tmem_base + TM_SFB + (ks * APS + a) * 4,
-                                   make_desc_sf(smem_u32(stage_sfb(0, ks) + a * 512)));
+              tc_cp_32x128b_warpx4(tm_sfb + (ks * APS + a) * 4,
+                                   desc(arena_lo + ks * aslot_lo + tile_lo + a * 32, sf_hi));
         }
       }
-      for (int i = 0; ok && walk.get(i, mb, nb); ++i) {
+      for (int i = 0; i < my_tiles && ok; ++i) {
         for (int ks = 0; ks < p.k_stages; ++ks) {
-          const bool new_group = FP8 || ks == 0;
           const uint32_t acc = group & 1;
-          if (new_group) {
+          if (FP8 || ks == 0) {
             if (!mbar_wait(&sm.tmem_empty[acc], ((group >> 1) & 1) ^ 1, p.status, 2)) { ok = false; break; }
-            tc_fence_after();
+            tc_fence_after();  // orders the epilogue's tcgen05.ld of this buffer before the MMAs
+            trace_rec(p, 1, i, 0);
           }
           if (!mbar_wait(&sm.full[s], ph, p.status, 3)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t a_addr = smem_u32(slot_a(s));
-          const uint32_t b_addr = smem_u32(stage_b(s, ks));
+          trace_rec(p, 1, i, ks < 2 ? 1 + ks : 2);
+          const uint32_t a_lo = ring_lo + s * slot_lo;
+          const uint32_t b_lo = resident ? arena_lo + ks * aslot_lo : a_lo + aslot_lo;
           const uint32_t d_tmem = tmem_base + TM_ACC0 + acc * BN;
           if constexpr (FP8) {
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-              mma_f8(d_tmem, make_desc_k128(a_addr + j * 32), make_desc_k128(b_addr + j * 32),
-                     idesc_base, j != 0);
+              mma_f8(d_tmem, desc(a_lo + 2 * j, k128_hi), desc(b_lo + 2 * j, k128_hi), idesc_base, j != 0);
           } else {
-            uint32_t sfb_base = TM_SFB;
+            uint32_t sfb_t = tm_sfb;
             if (with_sf) {
 #pragma unroll
               for (int a = 0; a < APS; ++a)
-                tc_cp_32x128b_warpx4(tmem_base + TM_SFA + a * 4, make_desc_sf(smem_u32(slot_sfa(s) + a * 512)));
-              if (p.b_resident) {
-                sfb_base = TM_SFB + ks * APS * 4;
+                tc_cp_32x128b_warpx4(tm_sfa + a * 4, desc(a_lo + tile_lo + a * 32, sf_hi));
+              if (resident) {
+                sfb_t = tm_sfb + ks * APS * 4;
               } else {
 #pragma unroll
                 for (int a = 0; a < APS; ++a)
-                  tc_cp_32x128b_warpx4(tmem_base + TM_SFB + a * 4, make_desc_sf(smem_u32(stage_sfb(s, ks) + a * 512)));
+                  tc_cp_32x128b_warpx4(tm_sfb + a * 4, desc(b_lo + tile_lo + a * 32, sf_hi));
               }
             }
+            if (ks == 0) trace_rec(p, 1, i, 3);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              uint32_t sf_col, sf_id;
-              if (p.sf_unit) { sf_col = 0; sf_id = 0; }
-              else if constexpr (VEC == 2) { sf_col = (j >> 1) * 4; sf_id = (j & 1) * 2; }
-              else { sf_col = j * 4; sf_id = 0; }
-              mma_mxf4<VEC>(d_tmem, make_desc_k128(a_addr + j * 32), make_desc_k128(b_addr + j * 32),
-                            idesc_with_sf_id(idesc_base, sf_id, sf_id), tmem_base + TM_SFA + sf_col,
-                            tmem_base + sfb_base + sf_col, (ks | j) != 0);
+              if (p.dbg & 2) break;
+              mma_mxf4<VEC>(d_tmem, desc(a_lo + 2 * j, k128_hi), desc(b_lo + 2 * j, k128_hi), idesc_j[j],
+                            tm_sfa + sfcol_j[j], sfb_t + sfcol_j[j], (ks | j) != 0);
             }
           }
+          if (ks == 0) trace_rec(p, 1, i, 4);
           tc_commit(&sm.empty[s]);  // ring slot reusable once these MMAs have read it
+          if (ks == 0) trace_rec(p, 1, i, 5);
           if (FP8 || ks == p.k_stages - 1) {
             tc_commit(&sm.tmem_full[acc]);
             ++group;
+            trace_rec(p, 1, i, 6);
           }
           if (++s == static_cast<uint32_t>(nslots)) { s = 0; ph ^= 1; }
         }
@@ -499,6 +534,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     const int64_t n_out = GLU ? p.N / 2 : p.N;    // logical output columns
     const int out_tile_cols = GLU ? BN / 2 : BN;
     const bool has_work = !GLU || cc < 2;         // GLU: chunks 2, 3 are the gates of 0, 1
+    const bool tr = p.trace != nullptr && blockIdx.x == 0 && ew == 0 && lane == 0;
     uint32_t group = 0;
     bool ok = true;
     float g_ab = 1.0f, g_out = 1.0f;
@@ -508,10 +544,10 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     uint8_t* buf = sm.staging[ew];
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
 
-    int mb, nb;
+    int mb = mb0, nb = nb0;
     uint32_t res_phase = 0;
-    uint8_t* res_buf = buf + STAGING_BYTES / 2;  // second half of the staging buffer
-    for (int it = 0; ok && walk.get(it, mb, nb); ++it) {
+    uint8_t* res_buf = sm.staging[ew] + STAGING_BYTES / 2;  // second half of the staging buffer
+    for (int it = 0; it < my_tiles && ok; ++it, next_tile(mb, nb)) {
       const int64_t row = static_cast<int64_t>(mb) * BM + q * 32 + lane;
       const bool row_ok = row < p.M;
       const int64_t acc_col0 = static_cast<int64_t>(nb) * BN + cc * 32;             // accumulator / bias column
@@ -567,12 +603,15 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         if (!ok) break;
       } else {
         const uint32_t acc = group & 1;
+        if (tr) trace_rec(p, 2, it, 0);
         if (!mbar_wait(&sm.tmem_full[acc], (group >> 1) & 1, p.status, 4)) { ok = false; break; }
         tc_fence_after();
+        if (tr) trace_rec(p, 2, it, 1);
         if (has_work) {
           uint32_t r[32];
           tc_ld_32x32b_x32(lane_addr + TM_ACC0 + acc * BN + cc * 32, r);
           tc_wait_ld();
+          if (tr) trace_rec(p, 2, it, 2);
 #pragma unroll
           for (int i = 0; i < 32; ++i) z[i] = __uint_as_float(r[i]);
           if constexpr (GLU) {
@@ -613,7 +652,9 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         res_phase ^= 1;
         res_smem = res_buf;
       }
+      if (tr) trace_rec(p, 2, it, 3);
       ChunkOut<EPI>::apply(p, z, gate, row, acc_col0, acc_col0 + 64, out_col0, row_ok, res_smem, lane);
+      if (tr) trace_rec(p, 2, it, 4);
 
       if (p.out_dtype == VX_FP4) {
         const uint32_t sb = store_chunk_fp4(p, z, row, out_col0, g_out, row_ok && out_col0 < n_out);
@@ -633,9 +674,20 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                   static_cast<uint16_t>(sb);
           }
         }
+      } else if (p.dbg & 1) {
+        if (z[0] == 123.456f && row_ok) static_cast<float*>(p.out)[0] = z[1];  // keep z live
       } else if (p.tma_store) {
-        // stage 32 rows x 32 columns (swizzled like the tensor map), then one TMA store
-        if (lane == 0) tma_store_wait_read<0>();  // the previous tile's box has left the buffer
+        // stage 32 rows x 32 columns (swizzled like the tensor map), then one TMA store.
+        // bf16 boxes are 2 KB: without a residual block in the second half of the staging
+        // buffer the two halves alternate, so the store of tile i drains while tile i + 1 is
+        // converted and staged
+        const bool dbuf = p.out_dtype == VX_BF16 && !p.tma_residual;
+        if (dbuf) {
+          if (lane == 0) tma_store_wait_read<1>();
+          buf = sm.staging[ew] + (it & 1) * (STAGING_BYTES / 2);
+        } else {
+          if (lane == 0) tma_store_wait_read<0>();  // the previous tile's box has left the buffer
+        }
         __syncwarp();
         if (p.out_dtype == VX_BF16) {
           // 64-byte rows, 64-byte swizzle: 16-byte slot index ^= (row >> 1) & 3
@@ -657,10 +709,12 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         }
         fence_proxy_async_smem();
         __syncwarp();
+        if (tr) trace_rec(p, 2, it, 5);
         if (lane == 0 && box_ok) {
           tma_store_2d(&tmap_out, static_cast<int>(out_col0), mb * BM + q * 32, buf);
           tma_store_commit();
         }
+        if (tr) trace_rec(p, 2, it, 6);
       } else if (row_ok) {
         store_chunk_direct(p, z, row, out_col0, n_out);
       }
@@ -954,9 +1008,19 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
     p.tma_residual = 1;
   }
   const bool res = !(d->flags & VX_GEMM_STREAM_B);
+  p.dbg = (d->flags >> 8) & 0xff;
+  p.trace = g_trace_buffer;
   if (fp8) return dispatch_epi<KIND_FP8>(epi, ta, tb, to, tr, p, res, st);
   if (fmt == VX_FMT_ROWSCALE || fmt == VX_FMT_MX32) return dispatch_epi<KIND_FP4_VEC2>(epi, ta, tb, to, tr, p, res, st);
   return dispatch_epi<KIND_FP4_VEC4>(epi, ta, tb, to, tr, p, res, st);
+}
+
+int vx_set_trace_buffer(void* device_buffer, int64_t bytes) {
+  using namespace vx;
+  if (device_buffer && bytes < static_cast<int64_t>(3 * TRACE_TILES * TRACE_EVENTS * sizeof(unsigned long long)))
+    return fail(-1, "trace buffer needs %d bytes", (int)(3 * TRACE_TILES * TRACE_EVENTS * sizeof(unsigned long long)));
+  g_trace_buffer = static_cast<unsigned long long*>(device_buffer);
+  return 0;
 }
 
 int vx_mma_peak_probe(int kind, int n_tile, int iters, float* tflops_out) {

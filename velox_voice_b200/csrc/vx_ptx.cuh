@@ -44,14 +44,17 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One poll.  The suspend-time hint lets the hardware park the thread until the phase
+// completes (or the hint, in nanoseconds, runs out) instead of spinning: sixteen epilogue
+// warps polling in a tight loop take the issue slots the single MMA-issuing thread needs.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(20000u)
       : "memory");
   return ok != 0;
 }
@@ -60,8 +63,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 // status word layout: 0 = ok; else (code << 24) | (site << 16) | (blockIdx.x & 0xffff)
+// The wall clock (%globaltimer, slow to read) is consulted only after 64 failed polls (each
+// may park the thread for up to 20 us), so a wait that succeeds promptly never touches it.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int site) {
-  if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+  for (uint32_t spins = 0; spins < 64; ++spins)
+    if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (true) {

@@ -276,6 +276,7 @@ def bsgemm(
     out_natural: bool = False,
     direct_store: bool = False,
     stream_b: bool = False,
+    _dbg: int = 0,
 ):
     """``epilogue(A . B^T)``; A [M,K], B [N,K] quantized in the same format family.
 
@@ -316,7 +317,7 @@ def bsgemm(
         residual = _rows2d(residual, "residual")
         d.residual, d.residual_dtype, d.ldr = residual.data_ptr(), _dt(residual, "residual"), residual.stride(0)
         d.alpha = float(alpha)
-    d.flags = (GEMM_DIRECT_STORE if direct_store else 0) | (GEMM_STREAM_B if stream_b else 0)
+    d.flags = (GEMM_DIRECT_STORE if direct_store else 0) | (GEMM_STREAM_B if stream_b else 0) | (_dbg << 8)
     result = None
     if out_fmt is not None:
         ofmt = _fmt(out_fmt)
