@@ -134,6 +134,30 @@ typedef struct vx_gemm_desc {
 
 int vx_bsgemm(const vx_gemm_desc* desc, void* stream);
 
+/* Block-scaled FP4 GEMM for callers that cannot allocate device memory.  (No counterpart in
+ * the reference: its Python wrappers allocate through torch.)
+ *
+ * Same product as dgx_mxfp4_blkscale_gemm: out f32 [M,N] (dense, ld = N) from packed codes
+ * pack_a u8 [M,K/2], pack_b u8 [N,K/2] (dense) and UE8M0 scales in the reference's layout,
+ * scale_a u8 [K/16][M/2], scale_b u8 [K/16][N].  The tensor-core copy of the scales, which
+ * the regular route keeps in two caller-provided buffers, lives here in a fixed array inside
+ * the library: VX_NOALLOC_SF_MAX_BYTES per operand on every GPU that loads the library, held
+ * until the process exits.  Problems whose scale factors do not fit (vx_sf_bytes(fmt, rows, K) >
+ * the limit, i.e. roughly rows * K > 32 Mi) are rejected with a negative return code.
+ *
+ * Meant for hosts that gave all device memory to their own pool at start-up or run on a
+ * latency-critical thread: cudaMalloc would fail there or stall every stream.  The call itself
+ * never calls cudaMalloc / cudaFree or any allocating routine.
+ *
+ * The first call on each device looks up the array's device address (one-time set-up); make
+ * that first call before starting any stream capture.  All calls on a device share the
+ * array and overwrite it: two calls whose GPU work may overlap (different streams, or
+ * threads) race on it -- serialise them, e.g. issue them on one stream. */
+#define VX_NOALLOC_SF_MAX_BYTES (2 * 1024 * 1024)
+int vx_blkscale_gemm_noalloc(const void* pack_a, const void* pack_b, const void* scale_a,
+                             const void* scale_b, float* out, int64_t M, int64_t N, int64_t K,
+                             void* stream);
+
 /* Phase trace of the GEMM pipeline (the reference has a compile-time %globaltimer trace of its
  * Hopper QKV kernel, veloxvoice/kernels/csrc/hopper/block/wasp_producer.h:20-34).  While a
  * device buffer of 3 * 32 * 8 u64 is registered, CTA 0 of every vx_bsgemm launch stamps the SM

@@ -40,6 +40,7 @@ EXPORTS = (
     "vx_bsgemm",
     "vx_mma_peak_probe",
     "vx_set_trace_buffer",
+    "vx_blkscale_gemm_noalloc",
 )
 
 
@@ -122,6 +123,8 @@ def load(build_if_missing: bool = True) -> C.CDLL:
         lib.vx_sf_from_natural.argtypes = [i32, vp, i64, i64, vp, vp]
         lib.vx_bsgemm.restype = i32
         lib.vx_bsgemm.argtypes = [C.POINTER(GemmDesc), vp]
+        lib.vx_blkscale_gemm_noalloc.restype = i32
+        lib.vx_blkscale_gemm_noalloc.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, vp]
         lib.vx_set_trace_buffer.restype = i32
         lib.vx_set_trace_buffer.argtypes = [vp, i64]
         lib.vx_mma_peak_probe.restype = i32
