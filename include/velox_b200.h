@@ -129,6 +129,12 @@ typedef struct vx_gemm_desc {
   const float* out_amax;/* FP4 NV16 output: f32[1] static tensor amax */
 } vx_gemm_desc;
 
+/* VX_EPI_BIAS_GLU expects the rows of B (and the bias) interleaved per tile of vx_glu_tile(fmt)
+ * rows: tile/2 rows of the value half followed by the matching tile/2 rows of the gate half.
+ * (The reference's bf16 GLU kernel loads both halves' tiles per stage instead,
+ * veloxvoice/kernels/csrc/hopper/block/wasp_producer.h:47-72.) */
+int vx_glu_tile(int fmt);
+
 #define VX_GEMM_DIRECT_STORE 1 /* bypass the shared-memory staged TMA store */
 #define VX_GEMM_STREAM_B 2     /* never keep the B tile resident in shared memory */
 

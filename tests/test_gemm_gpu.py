@@ -216,11 +216,12 @@ def test_fused_epilogues(ops, epi_case, fmt, epi, direct, out_dtype):
 @pytest.mark.parametrize("fmt", [F.FMT_MX32, F.FMT_FP8_1X128])
 @pytest.mark.parametrize("direct", [False, True])
 def test_glu_epilogue(ops, epi_case, fmt, direct):
-    from velox_voice_b200.linear import glu_interleave_index
+    from velox_voice_b200.linear import glu_interleave_index, glu_tile
 
     M, N, K, x, w, bias, res = epi_case
-    idx = glu_interleave_index(N, "cuda")
-    assert np.array_equal(idx.cpu().numpy(), G.glu_interleave_rows(N))
+    tile = glu_tile(fmt)
+    idx = glu_interleave_index(N, "cuda", tile)
+    assert np.array_equal(idx.cpu().numpy(), G.glu_interleave_rows(N, tile))
     a = ops.quantize(x, fmt)
     b_plain = ops.quantize(w, fmt)
     b = ops.quantize(w[idx].contiguous(), fmt)

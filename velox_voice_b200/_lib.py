@@ -41,6 +41,7 @@ EXPORTS = (
     "vx_mma_peak_probe",
     "vx_set_trace_buffer",
     "vx_blkscale_gemm_noalloc",
+    "vx_glu_tile",
 )
 
 
@@ -125,6 +126,8 @@ def load(build_if_missing: bool = True) -> C.CDLL:
         lib.vx_bsgemm.argtypes = [C.POINTER(GemmDesc), vp]
         lib.vx_blkscale_gemm_noalloc.restype = i32
         lib.vx_blkscale_gemm_noalloc.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, vp]
+        lib.vx_glu_tile.restype = i32
+        lib.vx_glu_tile.argtypes = [i32]
         lib.vx_set_trace_buffer.restype = i32
         lib.vx_set_trace_buffer.argtypes = [vp, i64]
         lib.vx_mma_peak_probe.restype = i32

@@ -39,12 +39,10 @@ namespace vx {
 namespace {
 
 constexpr int BM = 128;            // rows of A per tile = TMEM lanes
-constexpr int BN = 128;            // rows of B per tile = accumulator columns
 constexpr int STAGE_ROW_BYTES = 128;  // K bytes per stage: 256 FP4 or 128 FP8 elements
 constexpr int TILE_BYTES = BM * STAGE_ROW_BYTES;  // 16 KB
-constexpr int SF_STAGE_MAX = 4 * 512;  // scale-factor atoms of one operand per stage
 constexpr int MAX_STAGES = 8;          // ring slots (the arena size decides how many are used)
-constexpr int ARENA_BYTES = 160 * 1024;
+constexpr int ARENA_BYTES = 156 * 1024;
 constexpr int RESIDENT_MAX_KSTAGES = 4;                  // B kept in shared memory up to 4 K stages
 constexpr int NUM_THREADS = 576;       // 2 + 16 warps
 constexpr int EPI_WARP0 = 2;
@@ -52,9 +50,11 @@ constexpr int STAGING_BYTES = 32 * 128;  // 32 rows x up to 128 bytes per epilog
 constexpr int FP8_MAX_KB = 16;           // K <= 2048 for the FP8 path
 
 // tensor-memory columns
-constexpr int TM_ACC0 = 0, TM_SFA = 256, TM_SFB = 272, TM_COLS = 512;  // SFB: up to 32 columns
+constexpr int TM_ACC0 = 0, TM_SFA = 256, TM_SFB = 320, TM_COLS = 512;  // SFA: 2 x 32, SFB: up to 128 columns
 
 enum Kind { KIND_FP4_VEC2 = 0, KIND_FP4_VEC4 = 1, KIND_FP8 = 2 };
+// rows of B per tile = accumulator columns
+__host__ __device__ constexpr int kind_bn(int kind) { return kind == KIND_FP8 ? 128 : 256; }
 
 struct GemmParams {
   int64_t M, N, K;
@@ -74,8 +74,10 @@ struct GemmParams {
   // epilogue
   // shared-memory plan
   int b_resident;         // 1: the CTA keeps its B tile (all K stages) in shared memory
-  int num_slots;          // ring slots in use
-  int a_slot_bytes;       // bytes of one operand tile + its scale-factor atoms in the arena
+  int num_slots;          // ring slots in use (a multiple of `group`)
+  int group;              // K stages per full / empty barrier (2 when a whole K = 512 tile is one wait)
+  int a_slot_bytes;       // bytes of one A tile + its scale-factor atoms in the arena
+  int b_slot_bytes;       // same for one B tile (BN rows)
   int tma_residual;       // 1: residual tiles are prefetched by TMA into the staging buffers
   int dbg;                // ablation bits (investigation only)
   unsigned long long* trace;  // phase trace buffer (CTA 0, first 32 tiles) or nullptr
@@ -102,6 +104,7 @@ struct GemmParams {
 struct __align__(1024) SmemLayout {
   uint8_t arena[ARENA_BYTES];
   uint8_t staging[16][STAGING_BYTES];
+  float bias_s[16][64];  // per epilogue warp: bias of its columns ([32..63]: second chunk / GLU gate)
   uint64_t full[MAX_STAGES];
   uint64_t empty[MAX_STAGES];
   uint64_t tmem_full[2];
@@ -129,29 +132,24 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 //   For GLU the caller passes value and gate chunks and `ncol0` in OUTPUT columns.
 template <int EPI>
 struct ChunkOut {
-  // Applies bias / activation / residual in place.  `bias_col0` indexes the bias vector
-  // (accumulator column order), `out_col0` the output / residual column.
+  // Applies bias / activation / residual in place.  `bias_s` / `gate_s`: 32 bias values of the
+  // chunk (and of its GLU gate chunk) in shared memory, or nullptr; `out_col0`: output column.
   static __device__ __forceinline__ void apply(const GemmParams& p, float (&z)[32], float (&gate)[32],
-                                               int64_t row, int64_t bias_col0, int64_t gate_col0,
+                                               int64_t row, const float* bias_s, const float* gate_s,
                                                int64_t out_col0, bool row_ok, const uint8_t* res_smem,
                                                int lane) {
     if constexpr (EPI != VX_EPI_NONE) {
-      if (p.bias) {
-        if (bias_col0 + 32 <= p.N) {
+      if (bias_s) {
+        // bias values cached in shared memory by this warp (all lanes read the same words)
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + bias_col0 + i));
-            z[i] += b.x; z[i + 1] += b.y; z[i + 2] += b.z; z[i + 3] += b.w;
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (bias_col0 + i < p.N) z[i] += __ldg(p.bias + bias_col0 + i);
+        for (int i = 0; i < 32; i += 4) {
+          const float4 b = *reinterpret_cast<const float4*>(bias_s + i);
+          z[i] += b.x; z[i + 1] += b.y; z[i + 2] += b.z; z[i + 3] += b.w;
         }
         if constexpr (EPI == VX_EPI_BIAS_GLU) {
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
-            const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + gate_col0 + i));
+            const float4 b = *reinterpret_cast<const float4*>(gate_s + i);
             gate[i] += b.x; gate[i + 1] += b.y; gate[i + 2] += b.z; gate[i + 3] += b.w;
           }
         }
@@ -309,8 +307,17 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   constexpr bool FP8 = (KIND == KIND_FP8);
   constexpr int VEC = (KIND == KIND_FP4_VEC4) ? 4 : 2;
-  constexpr int APS = (KIND == KIND_FP4_VEC4) ? 4 : 2;  // SF atoms per operand per stage
+  constexpr int APS = (KIND == KIND_FP4_VEC4) ? 4 : 2;  // SF atoms per 128 rows per stage
   constexpr bool GLU = (EPI == VX_EPI_BIAS_GLU);
+  // FP4: one 128 x 256 accumulator (a single N = 256 MMA does twice the work per issued
+  // instruction; the accumulator is drained into registers within ~200 cycles, so a second
+  // buffer would buy little).  FP8: 128 x 128, two buffers, one per 128-wide K block in flight.
+  constexpr bool WIDE = !FP8;
+  constexpr int BNT = kind_bn(KIND);         // accumulator columns = B rows per tile
+  constexpr int NRT = BNT / 128;             // 128-row scale-factor tiles of B per tile
+  constexpr int SFB_COLS = 4 * NRT;          // TMEM columns of one K atom of B scale factors
+  constexpr int NCH = (WIDE && !GLU) ? 2 : 1;  // 32-column chunks per epilogue warp
+  constexpr int GATE_OFF = BNT / 2;          // GLU: gate columns follow the value columns
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -321,32 +328,31 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   // This CTA's tiles.  B resident: fixed n-block, m-blocks mb0, mb0 + mstep, ...; streaming:
   // tiles t0, t0 + grid, ... with n fastest.  No division inside the loops.
   const int total_tiles = p.m_tiles * p.n_tiles;
-  int my_tiles, mb0, nb0, mstep;
+  int my_tiles, mb0, nb0;
   if (resident) {
     nb0 = blockIdx.x % p.n_tiles;
     mb0 = blockIdx.x / p.n_tiles;
-    mstep = gridDim.x / p.n_tiles;
+    const int mstep = gridDim.x / p.n_tiles;
     my_tiles = mb0 < p.m_tiles ? (p.m_tiles - mb0 + mstep - 1) / mstep : 0;
   } else {
     mb0 = blockIdx.x / p.n_tiles;
     nb0 = blockIdx.x - mb0 * p.n_tiles;
-    mstep = 0;
     my_tiles = static_cast<int>(blockIdx.x) < total_tiles ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
   }
-  const int step_m = resident ? mstep : static_cast<int>(gridDim.x) / p.n_tiles;
+  const int step_m = static_cast<int>(gridDim.x) / p.n_tiles;
   const int step_n = resident ? 0 : static_cast<int>(gridDim.x) % p.n_tiles;
-  // advance (mb, nb) to the CTA's next tile
   auto next_tile = [&](int& mb, int& nb) {
     mb += step_m;
     nb += step_n;
     if (nb >= p.n_tiles) { nb -= p.n_tiles; ++mb; }
   };
 
-  // arena addressing (shared-memory byte addresses)
-  const uint32_t slot_bytes = resident ? p.a_slot_bytes : 2 * p.a_slot_bytes;
+  // arena addressing: [resident B stages] then ring slots ([A | SFA] or [A | SFA | B | SFB])
+  const uint32_t a_slot = p.a_slot_bytes, b_slot = p.b_slot_bytes;
+  const uint32_t slot_bytes = resident ? a_slot : a_slot + b_slot;
+  const uint32_t ring_off = resident ? p.k_stages * b_slot : 0;
   const uint32_t arena_u32 = smem_u32(sm.arena);
-  const uint32_t ring_u32 = arena_u32 + (resident ? p.k_stages * p.a_slot_bytes : 0);
-  uint8_t* ring_ptr = sm.arena + (resident ? p.k_stages * p.a_slot_bytes : 0);
+  constexpr uint32_t B_TILE_BYTES = BNT * STAGE_ROW_BYTES;
 
   // ---- set-up
   if (threadIdx.x == 0) {
@@ -367,13 +373,18 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     if (p.tma_store) prefetch_tmap(&tmap_out);
     if (p.tma_residual) prefetch_tmap(&tmap_res);
   }
+  {
+    // Scale-factor tiles of B that lie beyond N are never loaded; they must read as zero
+    // (their B rows are zero-filled by TMA, and 0 x NaN-scale would poison the accumulator).
+    uint4* a4 = reinterpret_cast<uint4*>(sm.arena);
+    for (int i = threadIdx.x; i < ARENA_BYTES / 16; i += NUM_THREADS) a4[i] = make_uint4(0, 0, 0, 0);
+  }
   uint8_t* unit_sf = sm.staging[0];  // rowscale only: one atom of 0x7F, copied to TMEM before any tile
   if (!FP8 && p.sf_unit) {
-    // unit scale factors (UE8M0 0x7F = 1.0) for the per-row-scaled format
     uint32_t* u = reinterpret_cast<uint32_t*>(unit_sf);
     for (int i = threadIdx.x; i < 512 / 4; i += NUM_THREADS) u[i] = 0x7F7F7F7Fu;
-    fence_proxy_async_smem();
   }
+  fence_proxy_async_smem();
   if (warp == 1) {
     tmem_alloc(&sm.tmem_base, TM_COLS);
     tmem_relinquish();
@@ -382,43 +393,56 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = sm.tmem_base;
+  const int n_sf_tiles = static_cast<int>((p.N + 127) >> 7);  // 128-row SF tiles of B that exist
 
   if (warp == 0) {
     // =========================== TMA producer ===========================
     if (lane == 0 && my_tiles > 0) {
       uint32_t s = 0, ph = 0;
-      const uint32_t sf_bytes = with_sf ? static_cast<uint32_t>(APS * 512) : 0u;
+      const uint32_t sf_atom_bytes = with_sf ? static_cast<uint32_t>(APS * 512) : 0u;
       const int64_t sf_stage = APS * 512;
       bool ok = true;
-      if (resident) {
-        // the CTA's B tile: every K stage, once
-        mbar_expect_tx(&sm.b_full, p.k_stages * (TILE_BYTES + sf_bytes));
-        for (int ks = 0; ks < p.k_stages; ++ks) {
-          uint8_t* dst = sm.arena + ks * p.a_slot_bytes;
-          tma_load_2d(dst, &tmap_b, ks * STAGE_ROW_BYTES, nb0 * BN, &sm.b_full);
-          if (with_sf)
-            bulk_load(dst + TILE_BYTES, p.sfb + (static_cast<int64_t>(nb0) * p.sf_kg) * 512 + ks * sf_stage,
-                      APS * 512, &sm.b_full);
+      // B tile (+ its scale factors) of n-block nb, K stage ks -> dst; returns bytes in flight
+      auto load_b = [&](uint8_t* dst, int nb, int ks, uint64_t* bar) {
+        tma_load_2d(dst, &tmap_b, ks * STAGE_ROW_BYTES, nb * BNT, bar);
+        if (with_sf) {
+#pragma unroll
+          for (int rt = 0; rt < NRT; ++rt)
+            if (nb * NRT + rt < n_sf_tiles)
+              bulk_load(dst + B_TILE_BYTES + rt * APS * 512,
+                        p.sfb + (static_cast<int64_t>(nb * NRT + rt) * p.sf_kg) * 512 + ks * sf_stage, APS * 512, bar);
         }
+      };
+      auto b_tx = [&](int nb) -> uint32_t {
+        uint32_t t = B_TILE_BYTES;
+        if (with_sf) {
+#pragma unroll
+          for (int rt = 0; rt < NRT; ++rt)
+            if (nb * NRT + rt < n_sf_tiles) t += sf_atom_bytes;
+        }
+        return t;
+      };
+      if (resident) {
+        mbar_expect_tx(&sm.b_full, p.k_stages * b_tx(nb0));
+        for (int ks = 0; ks < p.k_stages; ++ks) load_b(sm.arena + ks * b_slot, nb0, ks, &sm.b_full);
       }
-      const uint32_t slot_tx = (resident ? 1u : 2u) * (TILE_BYTES + sf_bytes);
       int mb = mb0, nb = nb0;
+      const int G = p.group, k_groups = p.k_stages / G, ngs = nslots / G;
       for (int i = 0; i < my_tiles && ok; ++i) {
         const uint8_t* sfa_row = p.sfa + (static_cast<int64_t>(mb) * p.sf_kg) * 512;
-        const uint8_t* sfb_row = p.sfb + (static_cast<int64_t>(nb) * p.sf_kg) * 512;
-        for (int ks = 0; ks < p.k_stages; ++ks) {
+        const uint32_t slot_tx = TILE_BYTES + sf_atom_bytes + (resident ? 0u : b_tx(nb));
+        for (int kg = 0; kg < k_groups; ++kg) {
           if (!mbar_wait(&sm.empty[s], ph ^ 1, p.status, 1)) { ok = false; break; }
-          trace_rec(p, 0, i, ks < 4 ? ks : 3);
-          uint8_t* dst = ring_ptr + s * slot_bytes;
-          mbar_expect_tx(&sm.full[s], slot_tx);
-          tma_load_2d(dst, &tmap_a, ks * STAGE_ROW_BYTES, mb * BM, &sm.full[s]);
-          if (with_sf) bulk_load(dst + TILE_BYTES, sfa_row + ks * sf_stage, APS * 512, &sm.full[s]);
-          if (!resident) {
-            tma_load_2d(dst + p.a_slot_bytes, &tmap_b, ks * STAGE_ROW_BYTES, nb * BN, &sm.full[s]);
-            if (with_sf)
-              bulk_load(dst + p.a_slot_bytes + TILE_BYTES, sfb_row + ks * sf_stage, APS * 512, &sm.full[s]);
+          trace_rec(p, 0, i, kg < 4 ? kg : 3);
+          mbar_expect_tx(&sm.full[s], G * slot_tx);
+          for (int u = 0; u < G; ++u) {
+            const int ks = kg * G + u;
+            uint8_t* dst = sm.arena + ring_off + (s * G + u) * slot_bytes;
+            tma_load_2d(dst, &tmap_a, ks * STAGE_ROW_BYTES, mb * BM, &sm.full[s]);
+            if (with_sf) bulk_load(dst + TILE_BYTES, sfa_row + ks * sf_stage, APS * 512, &sm.full[s]);
+            if (!resident) load_b(dst + a_slot, nb, ks, &sm.full[s]);
           }
-          if (++s == static_cast<uint32_t>(nslots)) { s = 0; ph ^= 1; }
+          if (++s == static_cast<uint32_t>(ngs)) { s = 0; ph ^= 1; }
         }
         next_tile(mb, nb);
       }
@@ -434,92 +458,110 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       uint32_t group = 0;  // accumulation groups issued (FP4: one per tile; FP8: one per stage)
       bool ok = true;
       const uint32_t idesc_base =
-          FP8 ? make_idesc_f8(BM, BN) : make_idesc_mxf4(BM, BN, p.sf_e8m0 != 0);
+          FP8 ? make_idesc_f8(BM, BNT) : make_idesc_mxf4(BM, BNT, p.sf_e8m0 != 0);
       // high words of the two descriptor kinds (see make_desc_k128 / make_desc_sf)
       const uint32_t k128_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
       const uint32_t sf_hi = (128u >> 4) | (1u << 14);
       auto desc = [](uint32_t lo, uint32_t hi) -> uint64_t {
         return (static_cast<uint64_t>(hi) << 32) | (lo & 0x3fffu);
       };
-      const uint32_t ring_lo = ring_u32 >> 4, slot_lo = slot_bytes >> 4, aslot_lo = p.a_slot_bytes >> 4;
       const uint32_t arena_lo = arena_u32 >> 4;
-      const uint32_t tile_lo = TILE_BYTES >> 4;
+      const uint32_t ring_lo = (arena_u32 + ring_off) >> 4, slot_lo = slot_bytes >> 4;
+      const uint32_t aslot_lo = a_slot >> 4, bslot_lo = b_slot >> 4;
+      const uint32_t a_sf_lo = TILE_BYTES >> 4, b_sf_lo = B_TILE_BYTES >> 4;
       // idesc and scale-factor columns of the four K steps of a stage
-      uint32_t idesc_j[4], sfcol_j[4];
+      uint32_t idesc_j[4], sfa_col_j[4], sfb_col_j[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        uint32_t sf_col, sf_id;
-        if (FP8 || p.sf_unit) { sf_col = 0; sf_id = 0; }
-        else if (VEC == 2) { sf_col = (j >> 1) * 4; sf_id = (j & 1) * 2; }
-        else { sf_col = j * 4; sf_id = 0; }
+        uint32_t atom, sf_id;
+        if (FP8 || p.sf_unit) { atom = 0; sf_id = 0; }
+        else if (VEC == 2) { atom = j >> 1; sf_id = (j & 1) * 2; }
+        else { atom = j; sf_id = 0; }
         idesc_j[j] = idesc_with_sf_id(idesc_base, sf_id, sf_id);
-        sfcol_j[j] = sf_col;
+        sfa_col_j[j] = atom * 4;
+        sfb_col_j[j] = atom * SFB_COLS;
       }
       const uint32_t tm_sfa = tmem_base + TM_SFA, tm_sfb = tmem_base + TM_SFB;
       if (!FP8 && p.sf_unit) {
         const uint64_t d = make_desc_sf(smem_u32(unit_sf));
         tc_cp_32x128b_warpx4(tm_sfa, d);
-        tc_cp_32x128b_warpx4(tm_sfb, d);
+#pragma unroll
+        for (int rt = 0; rt < NRT; ++rt) tc_cp_32x128b_warpx4(tm_sfb + rt * 4, d);
       }
+      // B scale factors of one stage: shared (lo = B slot >> 4) -> TMEM columns at `col0`
+      auto cp_sfb = [&](uint32_t b_lo, uint32_t col0) {
+#pragma unroll
+        for (int a = 0; a < APS; ++a)
+#pragma unroll
+          for (int rt = 0; rt < NRT; ++rt)
+            tc_cp_32x128b_warpx4(col0 + a * SFB_COLS + rt * 4, desc(b_lo + b_sf_lo + (rt * APS + a) * 32, sf_hi));
+      };
       if (resident) {
         if (!mbar_wait(&sm.b_full, 0, p.status, 5)) ok = false;
         tc_fence_after();
-        if (ok && with_sf) {
-          // B's scale factors stay in tensor memory for the whole kernel
-          for (int ks = 0; ks < p.k_stages; ++ks)
-            for (int a = 0; a < APS; ++a)
-              tc_cp_32x128b_warpx4(tm_sfb + (ks * APS + a) * 4,
-                                   desc(arena_lo + ks * aslot_lo + tile_lo + a * 32, sf_hi));
-        }
+        if (ok && with_sf)  // B's scale factors stay in tensor memory for the whole kernel
+          for (int ks = 0; ks < p.k_stages; ++ks) cp_sfb(arena_lo + ks * bslot_lo, tm_sfb + ks * APS * SFB_COLS);
       }
+      const int G = p.group, k_groups = p.k_stages / G, ngs = nslots / G;
+      uint32_t sfsel = 0;  // which half of the scale-factor columns this group uses
       for (int i = 0; i < my_tiles && ok; ++i) {
-        for (int ks = 0; ks < p.k_stages; ++ks) {
-          const uint32_t acc = group & 1;
-          if (FP8 || ks == 0) {
-            if (!mbar_wait(&sm.tmem_empty[acc], ((group >> 1) & 1) ^ 1, p.status, 2)) { ok = false; break; }
+        for (int kg = 0; kg < k_groups; ++kg) {
+          const uint32_t acc = WIDE ? 0u : (group & 1);
+          if (FP8 || kg == 0) {
+            const uint32_t use = WIDE ? group : (group >> 1);
+            if (!mbar_wait_spin(&sm.tmem_empty[acc], (use & 1) ^ 1, p.status, 2)) { ok = false; break; }
             tc_fence_after();  // orders the epilogue's tcgen05.ld of this buffer before the MMAs
             trace_rec(p, 1, i, 0);
           }
-          if (!mbar_wait(&sm.full[s], ph, p.status, 3)) { ok = false; break; }
-          trace_rec(p, 1, i, ks < 2 ? 1 + ks : 2);
-          const uint32_t a_lo = ring_lo + s * slot_lo;
-          const uint32_t b_lo = resident ? arena_lo + ks * aslot_lo : a_lo + aslot_lo;
-          const uint32_t d_tmem = tmem_base + TM_ACC0 + acc * BN;
-          if constexpr (FP8) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              mma_f8(d_tmem, desc(a_lo + 2 * j, k128_hi), desc(b_lo + 2 * j, k128_hi), idesc_base, j != 0);
-          } else {
-            uint32_t sfb_t = tm_sfb;
+          if (!mbar_wait_spin(&sm.full[s], ph, p.status, 3)) { ok = false; break; }
+          trace_rec(p, 1, i, kg < 2 ? 1 + kg : 2);
+          const uint32_t d_tmem = tmem_base + TM_ACC0 + acc * 128;
+          const uint32_t a_lo0 = ring_lo + s * G * slot_lo;
+          // (Issuing the next tile's scale-factor copies ahead of this wait was tried: the
+          // tcgen05.commit that publishes the accumulator then fires ~1400 cycles later.)
+          const uint32_t sfa_buf = tm_sfa + sfsel * 32;
+          const uint32_t sfb_buf = tm_sfb + (resident ? 0u : sfsel * 64);
+          if constexpr (!FP8) {
             if (with_sf) {
-#pragma unroll
-              for (int a = 0; a < APS; ++a)
-                tc_cp_32x128b_warpx4(tm_sfa + a * 4, desc(a_lo + tile_lo + a * 32, sf_hi));
-              if (resident) {
-                sfb_t = tm_sfb + ks * APS * 4;
-              } else {
+              for (int u = 0; u < G; ++u) {
+                const uint32_t a_lo = a_lo0 + u * slot_lo;
 #pragma unroll
                 for (int a = 0; a < APS; ++a)
-                  tc_cp_32x128b_warpx4(tm_sfb + a * 4, desc(b_lo + tile_lo + a * 32, sf_hi));
+                  tc_cp_32x128b_warpx4(sfa_buf + (u * APS + a) * 4, desc(a_lo + a_sf_lo + a * 32, sf_hi));
+                if (!resident) cp_sfb(a_lo + aslot_lo, sfb_buf + u * APS * SFB_COLS);
               }
             }
-            if (ks == 0) trace_rec(p, 1, i, 3);
+            if (kg == 0) trace_rec(p, 1, i, 3);
+          }
+          for (int u = 0; u < G; ++u) {
+            const int ks = kg * G + u;
+            const uint32_t a_lo = a_lo0 + u * slot_lo;
+            const uint32_t b_lo = resident ? arena_lo + ks * bslot_lo : a_lo + aslot_lo;
+            if constexpr (FP8) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (p.dbg & 2) break;
-              mma_mxf4<VEC>(d_tmem, desc(a_lo + 2 * j, k128_hi), desc(b_lo + 2 * j, k128_hi), idesc_j[j],
-                            tm_sfa + sfcol_j[j], sfb_t + sfcol_j[j], (ks | j) != 0);
+              for (int j = 0; j < 4; ++j)
+                mma_f8(d_tmem, desc(a_lo + 2 * j, k128_hi), desc(b_lo + 2 * j, k128_hi), idesc_base, (u | j) != 0);
+            } else {
+              const uint32_t sfa_t = with_sf ? sfa_buf + u * APS * 4 : tm_sfa;
+              const uint32_t sfb_t = with_sf ? sfb_buf + (resident ? ks : u) * APS * SFB_COLS : tm_sfb;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (p.dbg & 2) break;
+                mma_mxf4<VEC>(d_tmem, desc(a_lo + 2 * j, k128_hi), desc(b_lo + 2 * j, k128_hi), idesc_j[j],
+                              sfa_t + sfa_col_j[j], sfb_t + sfb_col_j[j], (ks | j) != 0);
+              }
             }
           }
-          if (ks == 0) trace_rec(p, 1, i, 4);
-          tc_commit(&sm.empty[s]);  // ring slot reusable once these MMAs have read it
-          if (ks == 0) trace_rec(p, 1, i, 5);
-          if (FP8 || ks == p.k_stages - 1) {
+          if (kg == 0) trace_rec(p, 1, i, 4);
+          tc_commit(&sm.empty[s]);  // ring slots reusable once these MMAs have read them
+          if (kg == 0) trace_rec(p, 1, i, 5);
+          if (FP8 || kg == k_groups - 1) {
             tc_commit(&sm.tmem_full[acc]);
             ++group;
             trace_rec(p, 1, i, 6);
           }
-          if (++s == static_cast<uint32_t>(nslots)) { s = 0; ph ^= 1; }
+          sfsel ^= 1;
+          if (++s == static_cast<uint32_t>(ngs)) { s = 0; ph ^= 1; }
         }
       }
       if (!ok) sm.abort_flag = 1;
@@ -527,13 +569,14 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   } else {
     // =========================== epilogue ===========================
     // 16 warps; warp (q, cc) owns TMEM lanes [32 q, 32 q + 32) (the hardware ties a warp to
-    // the lane quadrant warp_id % 4) and accumulator columns [32 cc, 32 cc + 32).
+    // the lane quadrant warp_id % 4).  Columns: FP8 (128 wide) chunk cc; FP4 (256 wide) the two
+    // chunks [64 cc, 64 cc + 64); GLU pairs value chunk cc with its gate chunk.
     const int q = warp & 3;
     const int ew = warp - EPI_WARP0;
     const int cc = ew >> 2;
     const int64_t n_out = GLU ? p.N / 2 : p.N;    // logical output columns
-    const int out_tile_cols = GLU ? BN / 2 : BN;
-    const bool has_work = !GLU || cc < 2;         // GLU: chunks 2, 3 are the gates of 0, 1
+    constexpr int OUT_TILE_COLS = GLU ? BNT / 2 : BNT;
+    const bool has_work = !(GLU && !WIDE) || cc < 2;  // 128-wide GLU: chunks 2, 3 are the gates of 0, 1
     const bool tr = p.trace != nullptr && blockIdx.x == 0 && ew == 0 && lane == 0;
     uint32_t group = 0;
     bool ok = true;
@@ -541,38 +584,56 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     if (p.a_amax && p.b_amax) g_ab = nv16_global(__ldg(p.a_amax)) * nv16_global(__ldg(p.b_amax));
     if (p.out_amax) g_out = nv16_global(__ldg(p.out_amax));
     const int kb_count = FP8 ? p.k_stages : 0;
-    uint8_t* buf = sm.staging[ew];
+    uint8_t* const stage0 = sm.staging[ew];
+    uint8_t* const res_buf = stage0 + STAGING_BYTES / 2;  // residual block (second half)
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    const bool dbuf = p.out_dtype == VX_BF16 && !p.tma_residual;  // bf16 boxes alternate the two halves
+    uint32_t store_count = 0;
+    uint32_t res_phase = 0;
+    int bias_nb = -1;
+    const float* const bias_base = p.bias ? sm.bias_s[ew] : nullptr;
+
+    // residual block of (mb, tile column c0) -> res_buf (TMA, 32 rows x 32 bf16)
+    auto res_issue = [&](int mb_, int64_t out_col) {
+      if (lane == 0) {
+        mbar_expect_tx(&sm.res_full[ew], 32 * 64);
+        tma_load_2d(res_buf, &tmap_res, static_cast<int>(out_col), mb_ * BM + q * 32, &sm.res_full[ew]);
+      }
+    };
 
     int mb = mb0, nb = nb0;
-    uint32_t res_phase = 0;
-    uint8_t* res_buf = sm.staging[ew] + STAGING_BYTES / 2;  // second half of the staging buffer
-    for (int it = 0; it < my_tiles && ok; ++it, next_tile(mb, nb)) {
+    const int col_base = WIDE ? (GLU ? cc * 32 : cc * 64) : cc * 32;  // first accumulator column of this warp
+    bool res_inflight = false;
+    if constexpr (EPI == VX_EPI_BIAS_RESIDUAL) {
+      if (p.tma_residual && my_tiles > 0 && has_work) {
+        res_issue(mb, static_cast<int64_t>(nb) * OUT_TILE_COLS + col_base);
+        res_inflight = true;
+      }
+    }
+    for (int it = 0; it < my_tiles && ok; ++it) {
       const int64_t row = static_cast<int64_t>(mb) * BM + q * 32 + lane;
       const bool row_ok = row < p.M;
-      const int64_t acc_col0 = static_cast<int64_t>(nb) * BN + cc * 32;             // accumulator / bias column
-      const int64_t out_col0 = static_cast<int64_t>(nb) * out_tile_cols + cc * 32;  // output column
-      const bool box_ok = static_cast<int64_t>(mb) * BM + q * 32 < p.M && out_col0 < n_out;
-      bool res_pending = false;
-      if constexpr (EPI == VX_EPI_BIAS_RESIDUAL) {
-        // fetch this warp's 32 x 32 residual block now; it lands while the MMAs of the tile run
-        if (p.tma_residual && box_ok) {
-          if (lane == 0) {
-            tma_store_wait_read<0>();  // (the output box of the previous tile shares the staging buffer)
-            mbar_expect_tx(&sm.res_full[ew], 32 * 64);
-            tma_load_2d(res_buf, &tmap_res, static_cast<int>(out_col0), mb * BM + q * 32, &sm.res_full[ew]);
-          }
-          res_pending = true;
-        }
-      }
+      const bool rows_ok = static_cast<int64_t>(mb) * BM + q * 32 < p.M;
+      int mb_next = mb, nb_next = nb;
+      next_tile(mb_next, nb_next);
 
-      float z[32], gate[32];
+      if (p.bias && nb != bias_nb && EPI != VX_EPI_NONE) {
+        // (re)load this warp's bias values: lane i fetches the i-th column of each chunk
+        __syncwarp();
+        const int64_t c0 = static_cast<int64_t>(nb) * BNT + col_base + lane;
+        const int64_t c1 = GLU ? c0 + GATE_OFF : c0 + 32;
+        sm.bias_s[ew][lane] = c0 < p.N ? __ldg(p.bias + c0) : 0.0f;
+        sm.bias_s[ew][32 + lane] = c1 < p.N ? __ldg(p.bias + c1) : 0.0f;
+        __syncwarp();
+        bias_nb = nb;
+      }
+      float z[NCH][32], gate[32];
       if constexpr (FP8) {
         // promote each 128-wide K block: z += tmem * sa[row, kb] * sb[col, kb]
 #pragma unroll
-        for (int i = 0; i < 32; ++i) { z[i] = 0.0f; gate[i] = 0.0f; }
-        const int64_t ncol = acc_col0 + lane;   // lane <-> column for the scale fetch
-        const int64_t gcol = ncol + 64;
+        for (int i = 0; i < 32; ++i) { z[0][i] = 0.0f; gate[i] = 0.0f; }
+        const int64_t ncol = static_cast<int64_t>(nb) * BNT + col_base + lane;   // lane <-> column for the scale fetch
+        const int64_t gcol = ncol + GATE_OFF;
         for (int kb = 0; kb < kb_count; ++kb) {
           const uint32_t acc = group & 1;
           if (!mbar_wait(&sm.tmem_full[acc], (group >> 1) & 1, p.status, 4)) { ok = false; break; }
@@ -581,14 +642,14 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
           const float sbv = ncol < p.N ? __ldg(p.fb + ncol * kb_count + kb) : 0.0f;
           uint32_t r[32];
           if (has_work) {
-            tc_ld_32x32b_x32(lane_addr + TM_ACC0 + acc * BN + cc * 32, r);
+            tc_ld_32x32b_x32(lane_addr + TM_ACC0 + acc * 128 + col_base, r);
             tc_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i)
-              z[i] = fmaf(__uint_as_float(r[i]), sa * __shfl_sync(0xffffffffu, sbv, i), z[i]);
+              z[0][i] = fmaf(__uint_as_float(r[i]), sa * __shfl_sync(0xffffffffu, sbv, i), z[0][i]);
             if constexpr (GLU) {
               const float sbg = gcol < p.N ? __ldg(p.fb + gcol * kb_count + kb) : 0.0f;
-              tc_ld_32x32b_x32(lane_addr + TM_ACC0 + acc * BN + 64 + cc * 32, r);
+              tc_ld_32x32b_x32(lane_addr + TM_ACC0 + acc * 128 + GATE_OFF + col_base, r);
               tc_wait_ld();
 #pragma unroll
               for (int i = 0; i < 32; ++i)
@@ -602,122 +663,144 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         }
         if (!ok) break;
       } else {
-        const uint32_t acc = group & 1;
         if (tr) trace_rec(p, 2, it, 0);
-        if (!mbar_wait(&sm.tmem_full[acc], (group >> 1) & 1, p.status, 4)) { ok = false; break; }
+        // one polling lane per warp (512 polling threads would starve the MMA-issuing thread)
+        if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[0], group & 1, p.status, 4);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
         tc_fence_after();
         if (tr) trace_rec(p, 2, it, 1);
-        if (has_work) {
+        {
           uint32_t r[32];
-          tc_ld_32x32b_x32(lane_addr + TM_ACC0 + acc * BN + cc * 32, r);
-          tc_wait_ld();
-          if (tr) trace_rec(p, 2, it, 2);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) z[i] = __uint_as_float(r[i]);
+          for (int h = 0; h < NCH; ++h) {
+            tc_ld_32x32b_x32(lane_addr + TM_ACC0 + col_base + h * 32, r);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) z[h][i] = __uint_as_float(r[i]);
+          }
           if constexpr (GLU) {
-            tc_ld_32x32b_x32(lane_addr + TM_ACC0 + acc * BN + 64 + cc * 32, r);
+            tc_ld_32x32b_x32(lane_addr + TM_ACC0 + GATE_OFF + col_base, r);
             tc_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i) gate[i] = __uint_as_float(r[i]);
           }
         }
-        // accumulator chunk is in registers: hand the TMEM buffer back to the MMA warp
+        if (tr) trace_rec(p, 2, it, 2);
+        // the accumulator is in registers: hand tensor memory back to the MMA warp
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.tmem_empty[acc]);
+        if (lane == 0) mbar_arrive(&sm.tmem_empty[0]);
         ++group;
-        if (has_work) {
-          if (p.sf_unit) {
-            // reference order: raw * row_scale * col_scale
-            const float row_scale = row_ok ? ue8m0_to_float(__ldg(p.row_scale_u8 + row)) : 0.0f;
-            const int64_t ncol = acc_col0 + lane;
-            const float csv = ncol < p.N ? ue8m0_to_float(__ldg(p.col_scale_u8 + ncol)) : 0.0f;
+      }
+
+      if (has_work) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) z[i] = z[i] * row_scale * __shfl_sync(0xffffffffu, csv, i);
-          } else if (p.a_amax) {
+        for (int h = 0; h < NCH; ++h) {
+          const int64_t acc_col0 = static_cast<int64_t>(nb) * BNT + col_base + h * 32;       // accumulator / bias column
+          const int64_t out_col0 = static_cast<int64_t>(nb) * OUT_TILE_COLS + col_base + h * 32;  // output column
+          const bool box_ok = rows_ok && out_col0 < n_out;
+          if constexpr (!FP8) {
+            if (p.sf_unit) {
+              // reference order: raw * row_scale * col_scale
+              const float row_scale = row_ok ? ue8m0_to_float(__ldg(p.row_scale_u8 + row)) : 0.0f;
+              const int64_t ncol = acc_col0 + lane;
+              const float csv = ncol < p.N ? ue8m0_to_float(__ldg(p.col_scale_u8 + ncol)) : 0.0f;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) z[i] *= g_ab;
-            if constexpr (GLU) {
+              for (int i = 0; i < 32; ++i) z[h][i] = z[h][i] * row_scale * __shfl_sync(0xffffffffu, csv, i);
+            } else if (p.a_amax) {
 #pragma unroll
-              for (int i = 0; i < 32; ++i) gate[i] *= g_ab;
+              for (int i = 0; i < 32; ++i) z[h][i] *= g_ab;
+              if constexpr (GLU) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) gate[i] *= g_ab;
+              }
             }
           }
-        }
-      }
-      if (!has_work) continue;
+          const uint8_t* res_smem = nullptr;
+          if (res_inflight) {
+            if (!mbar_wait(&sm.res_full[ew], res_phase, p.status, 6)) { ok = false; break; }
+            res_phase ^= 1;
+            res_smem = res_buf;
+          }
+          if (tr && h == 0) trace_rec(p, 2, it, 3);
+          ChunkOut<EPI>::apply(p, z[h], gate, row, bias_base ? bias_base + h * 32 : nullptr, bias_base + 32, out_col0,
+                               row_ok, res_smem, lane);
+          if (tr && h == 0) trace_rec(p, 2, it, 4);
+          if constexpr (EPI == VX_EPI_BIAS_RESIDUAL) {
+            if (res_inflight) {
+              // the block has been consumed: fetch the next one (second chunk of this tile, or
+              // the first chunk of the next tile) into the same buffer
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (h + 1 < NCH) res_issue(mb, out_col0 + 32);
+              else if (it + 1 < my_tiles) res_issue(mb_next, static_cast<int64_t>(nb_next) * OUT_TILE_COLS + col_base);
+              else res_inflight = false;
+            }
+          }
 
-      const uint8_t* res_smem = nullptr;
-      if (res_pending) {
-        if (!mbar_wait(&sm.res_full[ew], res_phase, p.status, 6)) { ok = false; break; }
-        res_phase ^= 1;
-        res_smem = res_buf;
-      }
-      if (tr) trace_rec(p, 2, it, 3);
-      ChunkOut<EPI>::apply(p, z, gate, row, acc_col0, acc_col0 + 64, out_col0, row_ok, res_smem, lane);
-      if (tr) trace_rec(p, 2, it, 4);
-
-      if (p.out_dtype == VX_FP4) {
-        const uint32_t sb = store_chunk_fp4(p, z, row, out_col0, g_out, row_ok && out_col0 < n_out);
-        if (row_ok && out_col0 < n_out) {
-          // this chunk's scale byte(s) inside the row's SF word(s)
-          if (p.out_fmt == VX_FMT_MX32) {
-            const int64_t kg = nb;  // 128 columns = 4 blocks of 32 = one k-group
-            p.out_sf[((row >> 7) * p.out_sf_kg + kg) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + cc] =
-                static_cast<uint8_t>(sb);
-            if (p.out_scales) p.out_scales[row * (n_out >> 5) + (out_col0 >> 5)] = static_cast<uint8_t>(sb);
-          } else {
-            const int64_t kg = static_cast<int64_t>(nb) * 2 + (cc >> 1);  // 8 blocks of 16 = two k-groups
-            *reinterpret_cast<uint16_t*>(p.out_sf + ((row >> 7) * p.out_sf_kg + kg) * 512 + (row & 31) * 16 +
-                                         ((row >> 5) & 3) * 4 + (cc & 1) * 2) = static_cast<uint16_t>(sb);
-            if (p.out_scales)
-              *reinterpret_cast<uint16_t*>(p.out_scales + row * (n_out >> 4) + (out_col0 >> 4)) =
-                  static_cast<uint16_t>(sb);
+          if (p.out_dtype == VX_FP4) {
+            const uint32_t sb = store_chunk_fp4(p, z[h], row, out_col0, g_out, row_ok && out_col0 < n_out);
+            if (row_ok && out_col0 < n_out) {
+              // this chunk's scale byte(s) inside the row's SF word(s)
+              const int64_t sf_row = (row >> 7) * p.out_sf_kg * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4;
+              if (p.out_fmt == VX_FMT_MX32) {
+                p.out_sf[sf_row + (out_col0 >> 7) * 512 + ((out_col0 >> 5) & 3)] = static_cast<uint8_t>(sb);
+                if (p.out_scales) p.out_scales[row * (n_out >> 5) + (out_col0 >> 5)] = static_cast<uint8_t>(sb);
+              } else {
+                *reinterpret_cast<uint16_t*>(p.out_sf + sf_row + (out_col0 >> 6) * 512 + ((out_col0 >> 5) & 1) * 2) =
+                    static_cast<uint16_t>(sb);
+                if (p.out_scales)
+                  *reinterpret_cast<uint16_t*>(p.out_scales + row * (n_out >> 4) + (out_col0 >> 4)) =
+                      static_cast<uint16_t>(sb);
+              }
+            }
+          } else if (p.dbg & 1) {
+            if (z[h][0] == 123.456f && row_ok) static_cast<float*>(p.out)[0] = z[h][1];  // keep z live
+          } else if (p.tma_store) {
+            // stage 32 rows x 32 columns (swizzled like the tensor map), then one TMA store
+            uint8_t* buf = stage0;
+            if (dbuf) {
+              if (lane == 0) tma_store_wait_read<1>();  // the box staged two stores ago has left
+              buf = stage0 + (store_count & 1) * (STAGING_BYTES / 2);
+            } else {
+              if (lane == 0) tma_store_wait_read<0>();
+            }
+            ++store_count;
+            __syncwarp();
+            if (p.out_dtype == VX_BF16) {
+              // 64-byte rows, 64-byte swizzle: 16-byte slot index ^= (row >> 1) & 3
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint4 u;
+                u.x = pack_bf16x2(z[h][8 * v], z[h][8 * v + 1]);
+                u.y = pack_bf16x2(z[h][8 * v + 2], z[h][8 * v + 3]);
+                u.z = pack_bf16x2(z[h][8 * v + 4], z[h][8 * v + 5]);
+                u.w = pack_bf16x2(z[h][8 * v + 6], z[h][8 * v + 7]);
+                *reinterpret_cast<uint4*>(buf + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)) = u;
+              }
+            } else {
+              // 128-byte rows, 128-byte swizzle: slot index ^= row & 7
+#pragma unroll
+              for (int v = 0; v < 8; ++v)
+                *reinterpret_cast<float4*>(buf + lane * 128 + ((v ^ (lane & 7)) << 4)) =
+                    make_float4(z[h][4 * v], z[h][4 * v + 1], z[h][4 * v + 2], z[h][4 * v + 3]);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (tr && h == 0) trace_rec(p, 2, it, 5);
+            if (lane == 0 && box_ok) {
+              tma_store_2d(&tmap_out, static_cast<int>(out_col0), mb * BM + q * 32, buf);
+              tma_store_commit();
+            }
+            if (tr && h == 0) trace_rec(p, 2, it, 6);
+          } else if (row_ok) {
+            store_chunk_direct(p, z[h], row, out_col0, n_out);
           }
         }
-      } else if (p.dbg & 1) {
-        if (z[0] == 123.456f && row_ok) static_cast<float*>(p.out)[0] = z[1];  // keep z live
-      } else if (p.tma_store) {
-        // stage 32 rows x 32 columns (swizzled like the tensor map), then one TMA store.
-        // bf16 boxes are 2 KB: without a residual block in the second half of the staging
-        // buffer the two halves alternate, so the store of tile i drains while tile i + 1 is
-        // converted and staged
-        const bool dbuf = p.out_dtype == VX_BF16 && !p.tma_residual;
-        if (dbuf) {
-          if (lane == 0) tma_store_wait_read<1>();
-          buf = sm.staging[ew] + (it & 1) * (STAGING_BYTES / 2);
-        } else {
-          if (lane == 0) tma_store_wait_read<0>();  // the previous tile's box has left the buffer
-        }
-        __syncwarp();
-        if (p.out_dtype == VX_BF16) {
-          // 64-byte rows, 64-byte swizzle: 16-byte slot index ^= (row >> 1) & 3
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint4 u;
-            u.x = pack_bf16x2(z[8 * v], z[8 * v + 1]);
-            u.y = pack_bf16x2(z[8 * v + 2], z[8 * v + 3]);
-            u.z = pack_bf16x2(z[8 * v + 4], z[8 * v + 5]);
-            u.w = pack_bf16x2(z[8 * v + 6], z[8 * v + 7]);
-            *reinterpret_cast<uint4*>(buf + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)) = u;
-          }
-        } else {
-          // 128-byte rows, 128-byte swizzle: slot index ^= row & 7
-#pragma unroll
-          for (int v = 0; v < 8; ++v)
-            *reinterpret_cast<float4*>(buf + lane * 128 + ((v ^ (lane & 7)) << 4)) =
-                make_float4(z[4 * v], z[4 * v + 1], z[4 * v + 2], z[4 * v + 3]);
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (tr) trace_rec(p, 2, it, 5);
-        if (lane == 0 && box_ok) {
-          tma_store_2d(&tmap_out, static_cast<int>(out_col0), mb * BM + q * 32, buf);
-          tma_store_commit();
-        }
-        if (tr) trace_rec(p, 2, it, 6);
-      } else if (row_ok) {
-        store_chunk_direct(p, z, row, out_col0, n_out);
       }
+      mb = mb_next;
+      nb = nb_next;
     }
     if (p.tma_store && lane == 0) tma_store_wait_all<0>();
     if (!ok) sm.abort_flag = 1;
@@ -857,19 +940,32 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, 
     if (dev >= 0 && dev < 64) sm_cache[dev] = sms;
   }
   // shared-memory plan: keep B resident when all of its K stages fit beside a useful ring
+  constexpr int BNT = kind_bn(KIND);
+  constexpr int APS = KIND == KIND_FP4_VEC4 ? 4 : 2;
   const bool with_sf = KIND != KIND_FP8 && !p.sf_unit;
-  p.a_slot_bytes = TILE_BYTES + (with_sf ? SF_STAGE_MAX : 0);
+  p.a_slot_bytes = TILE_BYTES + (with_sf ? APS * 512 : 0);
+  p.b_slot_bytes = BNT * STAGE_ROW_BYTES + (with_sf ? (BNT / 128) * APS * 512 : 0);
+  // keep every slot 1024-byte aligned (128-byte swizzle atoms are 1 KB)
+  p.a_slot_bytes = (p.a_slot_bytes + 1023) & ~1023;
+  p.b_slot_bytes = (p.b_slot_bytes + 1023) & ~1023;
   const int tiles = p.m_tiles * p.n_tiles;
   int grid;
-  p.b_resident = allow_resident && p.k_stages <= RESIDENT_MAX_KSTAGES && p.n_tiles <= sms;
+  const int res_slots = (ARENA_BYTES - p.k_stages * p.b_slot_bytes) / p.a_slot_bytes;
+  p.b_resident = allow_resident && p.k_stages <= RESIDENT_MAX_KSTAGES && p.n_tiles <= sms && res_slots >= 2;
+  p.group = 1;
   if (p.b_resident) {
-    int slots = (ARENA_BYTES - p.k_stages * p.a_slot_bytes) / p.a_slot_bytes;
-    p.num_slots = slots > MAX_STAGES ? MAX_STAGES : slots;
+    p.num_slots = res_slots > MAX_STAGES ? MAX_STAGES : res_slots;
+    // a whole K <= 512 FP4 tile (two stages) behind one barrier pair: the MMA-issuing thread
+    // waits and commits once per tile instead of once per stage
+    if (KIND != KIND_FP8 && p.k_stages == 2 && p.num_slots >= 4) {
+      p.group = 2;
+      p.num_slots &= ~1;
+    }
     int groups = sms / p.n_tiles;
     if (groups > p.m_tiles) groups = p.m_tiles;
     grid = groups * p.n_tiles;
   } else {
-    int slots = ARENA_BYTES / (2 * p.a_slot_bytes);
+    const int slots = ARENA_BYTES / (p.a_slot_bytes + p.b_slot_bytes);
     p.num_slots = slots > MAX_STAGES ? MAX_STAGES : slots;
     grid = tiles < sms ? tiles : sms;
   }
@@ -925,7 +1021,10 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
   if (d->out_dtype != VX_F32 && d->out_dtype != VX_BF16 && d->out_dtype != VX_FP4)
     return fail(-1, "unknown out_dtype %d", d->out_dtype);
   if (d->bias && (reinterpret_cast<uintptr_t>(d->bias) & 15)) return fail(-1, "bias must be 16-byte aligned");
-  if (epi == VX_EPI_BIAS_GLU && (N % BN != 0)) return fail(-1, "GLU needs N %% 128 == 0 (interleaved halves)");
+  const int kind = fp8 ? KIND_FP8 : ((fmt == VX_FMT_ROWSCALE || fmt == VX_FMT_MX32) ? KIND_FP4_VEC2 : KIND_FP4_VEC4);
+  const int BN = kind_bn(kind);
+  if (epi == VX_EPI_BIAS_GLU && (N % BN != 0))
+    return fail(-1, "GLU needs N %% %d == 0 (value / gate halves interleaved per tile, see vx_glu_tile)", BN);
   if (epi == VX_EPI_BIAS_RESIDUAL) {
     if (!d->residual) return fail(-1, "residual must not be NULL");
     if (d->residual_dtype != VX_F32 && d->residual_dtype != VX_BF16) return fail(-1, "bad residual dtype");
@@ -963,7 +1062,7 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
     if (epi == VX_EPI_BIAS_GLU || epi == VX_EPI_BIAS_RESIDUAL) return fail(-1, "FP4 output supports NONE / BIAS / BIAS_SWISH");
     if (!d->out_scales_sf || !aligned16(d->out_scales_sf)) return fail(-1, "FP4 output needs out_scales_sf (16-byte aligned)");
     if (d->out_fmt == VX_FMT_NV16 && !d->out_amax) return fail(-1, "NV16 output needs out_amax");
-    if (N % BN != 0) return fail(-1, "FP4 output needs N %% 128 == 0");
+    if (N % 128 != 0) return fail(-1, "FP4 output needs N %% 128 == 0");
     if (!aligned16(d->out) || d->ldo % 16 != 0 || d->ldo < N / 2) return fail(-1, "FP4 output rows must be 16-byte aligned");
     p.out_fmt = d->out_fmt;
     p.out_sf = static_cast<uint8_t*>(d->out_scales_sf);
@@ -1014,6 +1113,8 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
   if (fmt == VX_FMT_ROWSCALE || fmt == VX_FMT_MX32) return dispatch_epi<KIND_FP4_VEC2>(epi, ta, tb, to, tr, p, res, st);
   return dispatch_epi<KIND_FP4_VEC4>(epi, ta, tb, to, tr, p, res, st);
 }
+
+int vx_glu_tile(int fmt) { return vx::kind_bn(fmt == VX_FMT_FP8_1X128 ? vx::KIND_FP8 : vx::KIND_FP4_VEC2); }
 
 int vx_set_trace_buffer(void* device_buffer, int64_t bytes) {
   using namespace vx;

@@ -82,6 +82,36 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
   }
 }
 
+// Same contract, plain polling without the suspend hint: for the one MMA-issuing thread, whose
+// reaction time is on the critical path of every tile.
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, int* status, int site) {
+  auto poll = [&]() -> bool {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+  };
+#pragma unroll 1
+  for (uint32_t spins = 0; spins < 100000; ++spins)
+    if (poll()) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (poll()) return true;
+    if ((++spins & 0x3ff) == 0) {
+      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+        if (status) atomicCAS(status, 0, (1 << 24) | ((site & 0xff) << 16) | (blockIdx.x & 0xffff));
+        return false;
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------ proxies / fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

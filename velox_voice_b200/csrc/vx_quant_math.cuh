@@ -17,13 +17,14 @@ __device__ __forceinline__ float amax8(const float (&v)[8]) {
 }
 
 // UE8M0 of a block maximum: biased exponent byte of 2^ceil(log2(max(amax/6, 1e-6))) and the
-// exact reciprocal 2^-e used to normalise.
+// exact reciprocal 2^-e used to normalise.  Division-free: the correctly rounded quotient
+// amax/6 is <= 2^e exactly when amax <= 6 * 2^e = 1.5 * 2^(e+2), so with amax = (1+m) 2^(E-127)
+// the byte is E - 2 (+1 when 1+m > 1.5), floored at 108 (= ceil(log2 1e-6) + 127).
 __device__ __forceinline__ void ue8m0_from_amax(float amax, uint32_t& byte, float& rcp) {
-  const float s = fmaxf(__fdiv_rn(amax, 6.0f), 1e-6f);
-  const uint32_t b = __float_as_uint(s);
-  const uint32_t ef = (b >> 23) + ((b & 0x7fffffu) ? 1u : 0u);
-  byte = ef > 255u ? 255u : ef;
-  rcp = ef <= 253u ? __uint_as_float((254u - ef) << 23) : 0.0f;
+  const uint32_t b = __float_as_uint(amax);
+  const int ef = max(static_cast<int>((b + 0x3FFFFFu) >> 23) - 2, 108);
+  byte = ef > 255 ? 255u : static_cast<uint32_t>(ef);
+  rcp = ef <= 253 ? __uint_as_float(static_cast<uint32_t>(254 - ef) << 23) : 0.0f;
 }
 
 // E2M1 encode of 8 normalised values (q = v * rcp) into one 32-bit word, low nibble first.
@@ -39,17 +40,33 @@ __device__ __forceinline__ void ue8m0_from_amax(float amax, uint32_t& byte, floa
 // and rep carries q's sign bit.  q is formed as (v * rcp) + (+0) with two separate roundings:
 // a product that is -0 or underflows to -0 becomes +0, so the sign bit equals (q < 0) exactly
 // (a fused multiply-add would keep the sign of the unrounded product).
-__device__ __forceinline__ float e2m1_rep(float v, float rcp) {
-  const float q = __fadd_rn(__fmul_rn(v, rcp), 0.0f);
-  const float a4 = fminf(fabsf(q), 4.0f);
-  const float n23 = __fmaf_ru(a4, 4.0f, 8388608.0f);                // 2^23 + ceil(4 a4)
-  const float rep = __fmaf_rn(n23, 0.2421875f, -2031616.0f);        // n * 31/128, exact
-  return __uint_as_float(__float_as_uint(rep) | (__float_as_uint(q) & 0x80000000u));
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+// Two values at a time: the two fused multiply-adds run as packed fp32 instructions (one issue
+// slot per pair).  The product, the "+0" and the clamp stay scalar: they must keep subnormal
+// results (a tiny negative value still encodes as -0, i.e. nibble 8, like the reference).
+__device__ __forceinline__ void e2m1_rep2(float v0, float v1, float rcp, float& r0, float& r1) {
+  const float q0 = __fadd_rn(__fmul_rn(v0, rcp), 0.0f);  // -0 -> +0
+  const float q1 = __fadd_rn(__fmul_rn(v1, rcp), 0.0f);
+  const uint64_t a2 = pack_f32x2(fminf(fabsf(q0), 4.0f), fminf(fabsf(q1), 4.0f));
+  uint64_t n2;  // 2^23 + ceil(4 a)
+  asm("fma.rp.f32x2 %0, %1, %2, %3;" : "=l"(n2) : "l"(a2), "l"(pack_f32x2(4.0f, 4.0f)),
+      "l"(pack_f32x2(8388608.0f, 8388608.0f)));
+  uint64_t p2;  // n * 31/128, exact
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(p2) : "l"(n2), "l"(pack_f32x2(0.2421875f, 0.2421875f)),
+      "l"(pack_f32x2(-2031616.0f, -2031616.0f)));
+  float p0, p1;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(p0), "=f"(p1) : "l"(p2));
+  r0 = __uint_as_float(__float_as_uint(p0) | (__float_as_uint(q0) & 0x80000000u));
+  r1 = __uint_as_float(__float_as_uint(p1) | (__float_as_uint(q1) & 0x80000000u));
 }
 __device__ __forceinline__ uint32_t e2m1_pack8(const float (&v)[8], float rcp) {
   float r[8];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) r[j] = e2m1_rep(v[j], rcp);
+  for (int j = 0; j < 8; j += 2) e2m1_rep2(v[j], v[j + 1], rcp, r[j], r[j + 1]);
   uint32_t w;
   asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
       "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"

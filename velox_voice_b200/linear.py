@@ -29,12 +29,20 @@ from .ops import (
 )
 
 
-def glu_interleave_index(n_out: int, device=None) -> torch.Tensor:
-    """Row order the GLU epilogue expects: per 128 rows, 64 value rows then their 64 gate rows."""
+def glu_tile(fmt) -> int:
+    """Rows per GLU interleave tile for a format (the GEMM's tile width)."""
+    from . import _lib
+
+    return int(_lib.load().vx_glu_tile(ops._fmt(fmt)))
+
+
+def glu_interleave_index(n_out: int, device=None, tile: int = 256) -> torch.Tensor:
+    """Row order the GLU epilogue expects: per `tile` rows, tile/2 value rows then their gate rows."""
     h = n_out // 2
-    if h % 64 != 0:
-        raise ValueError("GLU output width must be a multiple of 64")
-    a = torch.arange(h, device=device).view(-1, 64)
+    half = tile // 2
+    if h % half != 0:
+        raise ValueError(f"GLU output width must be a multiple of {half}")
+    a = torch.arange(h, device=device).view(-1, half)
     return torch.cat([a, a + h], dim=1).reshape(-1)
 
 
@@ -58,7 +66,7 @@ class PackedLinear:
         w = weight.detach()
         b = None if bias is None else bias.detach().float()
         if glu:
-            idx = glu_interleave_index(self.out_features, w.device)
+            idx = glu_interleave_index(self.out_features, w.device, glu_tile(fmt))
             w = w[idx]
             if b is not None:
                 b = b[idx]

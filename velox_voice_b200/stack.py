@@ -32,7 +32,7 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from . import ops
-from .linear import PackedLinear
+from .linear import PackedLinear, glu_tile
 from .ops import FMT_FP8_1X128, FMT_MX32, FMT_NV16
 
 
@@ -221,7 +221,8 @@ class ConformerLinearStack:
             rec[b + "ctx"] = float(ctx.abs().max())
             x = x + lin(b + "lo", ctx)
             z = lin(b + "pw1", ln(b + "ln_conv", x))
-            z = z.view(z.shape[0], -1, 2, 64)
+            half = glu_tile(self.fmt) // 2  # pw1's rows are stored interleaved per GEMM tile
+            z = z.view(z.shape[0], -1, 2, half)
             gl = (z[:, :, 0] * torch.sigmoid(z[:, :, 1])).reshape(z.shape[0], -1)
             rec[b + "glu"] = float(gl.abs().max())
             x = x + lin(b + "pw2", gl)
