@@ -252,6 +252,80 @@ def op_breakdown(stack, T, fmt_name, only=""):
     return cases
 
 
+def baseline_configs(dev, hbm_peak_gbs):
+    """BASELINE configs[0..2] as single (chains of) launches: us, algorithmic TFLOP/s and GB/s,
+    and the fraction of the roofline (slower of bytes at measured HBM peak and FLOPs at the
+    measured tensor-core peak of that operand type)."""
+    import torch
+
+    from velox_voice_b200 import ops
+
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    peak = {"fp4": ops.mma_peak_tflops("fp4", 256, 2048), "fp8": ops.mma_peak_tflops("fp8", 256, 2048)}
+
+    def timed(fn, n=7):
+        for _ in range(2):
+            fn()
+        ts = []
+        for _ in range(n):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    def entry(name, us, flops, nbytes, kind):
+        t_roof = max(nbytes / (hbm_peak_gbs * 1e3), flops / (peak[kind] * 1e6))  # us
+        return {"config": name, "us": round(us, 1), "TFLOPs": round(flops / us / 1e6, 1), "GBps": round(nbytes / us / 1e3, 1),
+                "roofline_us": round(t_roof, 1), "roofline_frac": round(t_roof / us, 3)}
+
+    out = []
+    torch.manual_seed(0)
+    # configs[0]: single MXFP4 linear, x [1024, 512] -> [1024, 2048] bf16 (quantize on the fly + GEMM)
+    x = torch.randn(1024, 512, device=dev).bfloat16()
+    w = ops.quantize(0.02 * torch.randn(2048, 512, device=dev), "mx32")
+    us = timed(lambda: ops.bsgemm(ops.quantize(x, "mx32", natural=False), w, out_dtype=torch.bfloat16))
+    out.append(entry("cfg1 mxfp4 linear 1024x2048x512 (quantize + GEMM)", us, 2 * 1024 * 2048 * 512,
+                     1024 * 512 * 2 + 2048 * 512 * (0.5 + 1 / 32) + 1024 * 2048 * 2, "fp4"))
+    # configs[1]: fused QKV, FP8 1x128, T = 90000 (activations already quantized; GEMM + bias -> bf16)
+    T = 90000
+    xa = torch.nn.functional.layer_norm(torch.randn(T, 512, device=dev), (512,)).bfloat16()
+    bound = (6.0 / (512 + 1536)) ** 0.5
+    wq = ops.quantize((torch.rand(1536, 512, device=dev) * 2 - 1) * bound, "fp8_1x128")
+    aq = ops.quantize(xa, "fp8_1x128")
+    bias = torch.zeros(1536, device=dev)
+    o = torch.empty(T, 1536, device=dev, dtype=torch.bfloat16)
+    us = timed(lambda: ops.bsgemm(aq, wq, epilogue=ops.EPI_BIAS, bias=bias, out=o))
+    out.append(entry("cfg2 fused QKV fp8_1x128 90000x1536x512 (GEMM + bias)", us, 2 * T * 1536 * 512,
+                     T * 512 * (1 + 4 / 128) + 1536 * 512 * (1 + 4 / 128) + T * 1536 * 2, "fp8"))
+    us = timed(lambda: ops.quantize(xa, "fp8_1x128"))
+    out.append(entry("cfg2 activation quantize fp8_1x128 [90000, 512]", us, 0, T * 512 * (2 + 1 + 4 / 128), "fp8"))
+    # configs[2]: macaron FFN, NVFP4: y = x + 0.5 * W2 swish(W1 LN(x)); 3 launches, FP4 intermediate
+    xf = torch.randn(T, 512, device=dev).bfloat16()
+    w1 = ops.quantize(0.02 * torch.randn(2048, 512, device=dev), "nv16")
+    w2 = ops.quantize(0.02 * torch.randn(512, 2048, device=dev), "nv16")
+    b1, b2 = torch.zeros(2048, device=dev), torch.zeros(512, device=dev)
+    g, be = torch.ones(512, device=dev), torch.zeros(512, device=dev)
+    am_x = torch.tensor([6.0], device=dev)
+    am_h = torch.tensor([8.0], device=dev)
+    y = torch.empty_like(xf)
+
+    def ffn():
+        q = ops.ln_quantize(xf, g, be, 1e-5, "nv16", amax_t=am_x)
+        h = ops.bsgemm(q, w1, epilogue=ops.EPI_BIAS_SWISH, bias=b1, out_fmt="nv16", out_amax=am_h)
+        ops.bsgemm(h, w2, epilogue=ops.EPI_BIAS_RESIDUAL, bias=b2, residual=xf, alpha=0.5, out=y)
+
+    us = timed(ffn)
+    nb = T * 512 * 2 + T * 512 * (0.5 + 1 / 16) * 2 + T * 2048 * (0.5 + 1 / 16) * 2 + T * 512 * 4
+    out.append(entry("cfg3 macaron FFN nv16 T=90000 (ln_quant + up/swish/FP4 + down/residual)", us, 2 * 2 * T * 512 * 2048, nb, "fp4"))
+    del flush
+    return out, peak
+
+
 # ----------------------------------------------------------------------------- our arm
 
 
@@ -379,6 +453,9 @@ def run_ours(a):
             roofline = {"kernel": top[0], "bound": "hbm", "achieved": round(ach, 1), "peak": hbm_peak, "unit": "GB/s",
                         "frac": round(ach / hbm_peak, 4), "traffic": traffic, "peak_source": peak_src,
                         "algorithmic_bytes_per_launch": int(top[3]), "us_per_launch": round(top[2], 1)}
+        cfgs, mma_peak = (None, None)
+        if not a.no_breakdown:
+            cfgs, mma_peak = baseline_configs(dev, hbm_peak)
         cpu_fps, cores, cpu_dt = cpu_stack_sample(a, a.cpu_frames)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": max(a.warmup, 3),
@@ -399,6 +476,8 @@ def run_ours(a):
             "clocks": clocks,
             "roofline": roofline,
             "breakdown": breakdown,
+            "baseline_configs": cfgs,
+            "mma_peak_tflops_measured": mma_peak,
             "cpu_baseline": {"value": cpu_fps, "unit": UNIT, "cores": cores, "kind": "port",
                              "sample": f"{a.cpu_frames} frames of the same stack on the host cores ({cpu_dt:.1f} s)"},
         }

@@ -24,9 +24,14 @@ int fail(int code, const char* fmt, ...) {
 }
 
 int* device_status_ptr() {
-  // Resolved per call: cudaGetSymbolAddress answers for the CURRENT device.
+  // cudaGetSymbolAddress answers for the CURRENT device; looked up once per device.
+  static int* cache[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = -1;
+  if (dev >= 0 && cache[dev]) return cache[dev];
   int* p = nullptr;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_device_status) != cudaSuccess) return nullptr;
+  if (dev >= 0) cache[dev] = p;
   return p;
 }
 

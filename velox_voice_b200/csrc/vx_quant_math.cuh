@@ -45,6 +45,20 @@ __device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
   asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
   return r;
 }
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+// packed fp32 pair arithmetic of sm_100 (round to nearest, subnormals kept)
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
 // Two values at a time: the two fused multiply-adds run as packed fp32 instructions (one issue
 // slot per pair).  The product, the "+0" and the clamp stay scalar: they must keep subnormal
 // results (a tiny negative value still encodes as -0, i.e. nibble 8, like the reference).
