@@ -110,3 +110,27 @@ def test_dense_linear_precision_modes():
         assert y3.shape == (2, 16, 64)
         ref = torch.nn.functional.linear(x, lin.weight, lin.bias)
         assert (y - ref).abs().max() / ref.abs().max() < 0.35  # FP4 with per-row scales
+
+
+def test_compiled_stack_host_calls_agree():
+    """Graph replay, the one-shot host call and the queued (copy/compute overlapped) host call
+    return the ids of the eager forward, batch by batch."""
+    from velox_voice_b200.stack import ConformerLinearStack, StackConfig, make_weights
+
+    cfg = StackConfig(blocks=2, fmt="mx32")
+    stack = ConformerLinearStack(cfg, make_weights(cfg, seed=2))
+    T = 640
+    comp = stack.compile(T, with_pos=False)
+    torch.manual_seed(2)
+    batches = [torch.randn(T, cfg.d_model).bfloat16().pin_memory() for _ in range(5)]
+    want = [stack.forward(b.cuda().clone()).argmax(dim=1).to(torch.int32).cpu() for b in batches]
+    for b, w in zip(batches, want):
+        assert torch.equal(comp.encode_ctc_host(b).clone(), w)
+    got = comp.encode_ctc_host_batches(batches)
+    assert len(got) == len(batches)
+    for g, w in zip(got, want):
+        assert torch.equal(g, w)
+    # second call re-uses the pooled output buffers and the staging buffers
+    got = comp.encode_ctc_host_batches(batches[::-1])
+    for g, w in zip(got, want[::-1]):
+        assert torch.equal(g, w)

@@ -27,7 +27,7 @@ moves work between GPUs as files and subprocesses (``tools/bench_wenet_multi_wor
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, Optional, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -255,6 +255,8 @@ class CompiledStack:
         self.pos = torch.zeros((frames, cfg.d_model), dtype=torch.bfloat16, device=dev) if with_pos else None
         self._x = torch.empty_like(self.x_in)
         self.ids_host = torch.empty((frames,), dtype=torch.int32).pin_memory()
+        self._stage = None
+        self._ids_pool: List[torch.Tensor] = []
         ops.reset_launch_count()
         self._body()  # warm-up: lazy module loading and one-time attribute calls happen here
         self.launches = ops.launch_count()
@@ -280,6 +282,45 @@ class CompiledStack:
         self.ids_host.copy_(self.ids, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         return self.ids_host
+
+    def encode_ctc_host_batches(self, batches: Sequence[torch.Tensor],
+                                out: Optional[List[torch.Tensor]] = None, after_each=None) -> List[torch.Tensor]:
+        """Throughput form of :meth:`encode_ctc_host` for a queue of utterance shards.
+
+        ``batches``: host bf16 [T, d] tensors (pinned for full copy speed); returns one pinned
+        host int32 [T] id tensor per batch (``out`` re-uses caller buffers).  The host->device
+        copy of batch i+1 runs on a copy stream into one of two staging buffers while the
+        stack of batch i runs, so per batch the cost is max(copy, compute) instead of their sum.
+        ``after_each(i)``, if given, is called after batch i has been enqueued (multi-GPU callers
+        enqueue their gather of ``self.ids`` there).  Results are complete when the call returns.
+        """
+        if self._stage is None:
+            self._stage = [torch.empty_like(self.x_in) for _ in range(2)]
+            self._h2d = torch.cuda.Stream(device=self.stack.device)
+            self._ev_in = [torch.cuda.Event() for _ in range(2)]
+            self._ev_free = [torch.cuda.Event() for _ in range(2)]
+        if out is None:
+            while len(self._ids_pool) < len(batches):
+                self._ids_pool.append(torch.empty((self.frames,), dtype=torch.int32).pin_memory())
+            out = self._ids_pool[: len(batches)]
+        main = torch.cuda.current_stream()
+        self._h2d.wait_stream(main)
+        for i, feats in enumerate(batches):
+            s = i & 1
+            with torch.cuda.stream(self._h2d):
+                if i >= 2:
+                    self._h2d.wait_event(self._ev_free[s])
+                self._stage[s].copy_(feats, non_blocking=True)
+                self._ev_in[s].record(self._h2d)
+            main.wait_event(self._ev_in[s])
+            self.x_in.copy_(self._stage[s])
+            self._ev_free[s].record(main)
+            self.graph.replay()
+            out[i].copy_(self.ids, non_blocking=True)
+            if after_each is not None:
+                after_each(i)
+        main.synchronize()
+        return list(out)
 
 
 # --------------------------------------------------------------------------------------
