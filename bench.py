@@ -46,6 +46,8 @@ def parse():
     ap.add_argument("--no-breakdown", action="store_true")
     ap.add_argument("--breakdown-only", action="store_true",
                     help="time the individual launches only (profiling aid); prints one JSON line")
+    ap.add_argument("--configs-only", action="store_true",
+                    help="time BASELINE configs[0..2] (single launches / the FFN chain) and exit")
     ap.add_argument("--ops", default="", help="with --breakdown-only: substring filter on the op name")
     return ap.parse_args()
 
@@ -371,6 +373,16 @@ def run_ours(a):
     pos = torch.randn(T, cfg.d_model, generator=g).bfloat16().to(dev)
     if a.fmt == "nv16":
         stack.calibrate(feats_host[:4096].to(dev), pos[:4096])
+    if a.configs_only:
+        peaks = {}
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                peaks = json.load(f)
+        except Exception:
+            pass
+        cfgs, mma_peak = baseline_configs(dev, float(peaks.get("hbm_gbs", 6650.0)))
+        print(json.dumps({"baseline_configs": cfgs, "mma_peak_tflops_measured": mma_peak}), flush=True)
+        return
     if a.breakdown_only:
         cases = op_breakdown(stack, T, a.fmt, a.ops)
         print(json.dumps({"breakdown": [{"op": n, "launches_per_step": c, "us": round(us, 1),

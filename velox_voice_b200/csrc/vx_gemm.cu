@@ -4,7 +4,8 @@
 //   FP4 operands (E2M1, two per byte):  tcgen05.mma kind::mxf4nvf4.block_scale, scale factors
 //       (UE8M0 per 32 / per 16, or E4M3 per 16) read by the MMA from tensor memory;
 //   FP8 operands (E4M3, fp32 scale per 1x128): tcgen05.mma kind::f8f6f4, one accumulation
-//       group per 128-wide K block, promoted into fp32 registers with sa[m,kb] * sb[n,kb].
+//       group per 128-wide K block, each into its own 128-column accumulator (four in flight),
+//       promoted into fp32 registers with sa[m,kb] * sb[n,kb].
 //
 // One persistent CTA per SM, 18 warps:
 //   warp 0      TMA producer: A / B tiles (128 rows x 128 bytes, 128-byte swizzle) and the
@@ -18,8 +19,9 @@
 //               store (clipped at the tensor edge by hardware) or direct vector stores;
 //               optional re-quantization of the result to FP4.  Sixteen warps (four per
 //               scheduler) hide the TMEM-load, shared-memory and MUFU latencies of each other.
-// Accumulators are double-buffered in tensor memory (2 x 128 columns), so the epilogue of
-// tile i overlaps the loads and MMAs of tile i + 1.
+// FP4: one 128 x 256 accumulator per tile, drained into registers right after the commit.
+// FP8: the four accumulators form a ring over the K blocks, released one by one, so the MMAs
+// of the next K blocks (and of the next tile) run while the epilogue promotes.
 //
 // Every mbarrier wait is bounded (vx_ptx.cuh); an expired wait sets the device status word
 // and the CTA drains and exits instead of hanging.
@@ -45,9 +47,14 @@ constexpr int MAX_STAGES = 8;          // ring slots (the arena size decides how
 constexpr int ARENA_BYTES = 156 * 1024;
 constexpr int RESIDENT_MAX_KSTAGES = 4;                  // B kept in shared memory up to 4 K stages
 constexpr int NUM_THREADS = 576;       // 2 + 16 warps
+// Registers are granted to a CTA in units of four warps: 18 warps count as 20, so the budget
+// is 65536 / 640 = 102 -> 96 registers per thread (112 does not launch).
+#define VX_GEMM_BOUNDS __launch_bounds__(NUM_THREADS, 1)
 constexpr int EPI_WARP0 = 2;
 constexpr int STAGING_BYTES = 32 * 128;  // 32 rows x up to 128 bytes per epilogue warp
 constexpr int FP8_MAX_KB = 16;           // K <= 2048 for the FP8 path
+constexpr int FP8_ACCS = 4;              // FP8 accumulators in tensor memory (128 columns each)
+constexpr int FP8_SB_BYTES_PER_KB = 16 * 32 * 4;  // epilogue tables of B scales: 16 warps x 32 columns per K block
 
 // tensor-memory columns
 constexpr int TM_ACC0 = 0, TM_SFA = 256, TM_SFB = 320, TM_COLS = 512;  // SFA: 2 x 32, SFB: up to 128 columns
@@ -107,8 +114,8 @@ struct __align__(1024) SmemLayout {
   float bias_s[16][64];  // per epilogue warp: bias of its columns ([32..63]: second chunk / GLU gate)
   uint64_t full[MAX_STAGES];
   uint64_t empty[MAX_STAGES];
-  uint64_t tmem_full[2];
-  uint64_t tmem_empty[2];
+  uint64_t tmem_full[FP8_ACCS];
+  uint64_t tmem_empty[FP8_ACCS];
   uint64_t b_full;
   uint64_t res_full[16];
   uint32_t tmem_base;
@@ -120,8 +127,22 @@ struct __align__(1024) SmemLayout {
 // roundings of the re-quantized activations often enough to move CTC argmaxes), and a Newton
 // reciprocal on the FMA pipe (one MUFU operation less, six instructions more: the FFN-up
 // epilogue is bound by instruction issue, not by the MUFU unit, and got 20 % slower).
-__device__ __forceinline__ float sigmoid_f(float z) { return __fdividef(1.0f, 1.0f + __expf(-z)); }
-__device__ __forceinline__ float silu_f(float z) { return __fdividef(z, 1.0f + __expf(-z)); }
+// ex2 / rcp with the .ftz qualifier are single MUFU instructions (the default forms wrap them
+// in range fix-ups for denormal inputs / results).  Results are the same here: a flushed
+// 2^x only ever feeds 1 + 2^x, and the reciprocal of a denominator above 2^126 belongs to
+// |z| > 87, whose product rounds to zero in bf16 / FP4 either way.
+__device__ __forceinline__ float ex2_ftz(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_ftz(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float sigmoid_f(float z) { return rcp_ftz(1.0f + ex2_ftz(-1.4426950408889634f * z)); }
+__device__ __forceinline__ float silu_f(float z) { return z * sigmoid_f(z); }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -300,7 +321,7 @@ unsigned long long* g_trace_buffer = nullptr;
 
 // ---------------------------------------------------------------------------------------
 template <int KIND, int EPI>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void VX_GEMM_BOUNDS
 bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
               const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_res,
               const GemmParams p) {
@@ -313,7 +334,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   constexpr bool GLU = (EPI == VX_EPI_BIAS_GLU);
   // FP4: one 128 x 256 accumulator (a single N = 256 MMA does twice the work per issued
   // instruction; the accumulator is drained into registers within ~200 cycles, so a second
-  // buffer would buy little).  FP8: 128 x 128, two buffers, one per 128-wide K block in flight.
+  // buffer would buy little).  FP8: 128 x 128, a ring of four, one per 128-wide K block in flight.
   constexpr bool WIDE = !FP8;
   constexpr int BNT = kind_bn(KIND);         // accumulator columns = B rows per tile
   constexpr int NRT = BNT / 128;             // 128-row scale-factor tiles of B per tile
@@ -362,7 +383,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       mbar_init(&sm.full[s], 1);
       mbar_init(&sm.empty[s], 1);
     }
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < FP8_ACCS; ++a) {
       mbar_init(&sm.tmem_full[a], 1);
       mbar_init(&sm.tmem_empty[a], 16);
     }
@@ -508,15 +529,16 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       uint32_t sfsel = 0;  // which half of the scale-factor columns this group uses
       for (int i = 0; i < my_tiles && ok; ++i) {
         for (int kg = 0; kg < k_groups; ++kg) {
-          const uint32_t acc = WIDE ? 0u : (group & 1);
+          const uint32_t acc = WIDE ? 0u : (group & (FP8_ACCS - 1));
           if (FP8 || kg == 0) {
-            const uint32_t use = WIDE ? group : (group >> 1);
+            const uint32_t use = WIDE ? group : (group / FP8_ACCS);
             if (!mbar_wait_spin(&sm.tmem_empty[acc], (use & 1) ^ 1, p.status, 2)) { ok = false; break; }
             tc_fence_after();  // orders the epilogue's tcgen05.ld of this buffer before the MMAs
-            trace_rec(p, 1, i, 0);
+            if (!FP8) trace_rec(p, 1, i, 0);
           }
           if (!mbar_wait_spin(&sm.full[s], ph, p.status, 3)) { ok = false; break; }
-          trace_rec(p, 1, i, kg < 2 ? 1 + kg : 2);
+          if (FP8) { if (kg < 4) trace_rec(p, 1, i, 2 * kg); }
+          else trace_rec(p, 1, i, kg < 2 ? 1 + kg : 2);
           const uint32_t d_tmem = tmem_base + TM_ACC0 + acc * 128;
           const uint32_t a_lo0 = ring_lo + s * G * slot_lo;
           // (Issuing the next tile's scale-factor copies ahead of this wait was tried: the
@@ -554,13 +576,14 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
               }
             }
           }
-          if (kg == 0) trace_rec(p, 1, i, 4);
+          if (!FP8 && kg == 0) trace_rec(p, 1, i, 4);
           tc_commit(&sm.empty[s]);  // ring slots reusable once these MMAs have read them
-          if (kg == 0) trace_rec(p, 1, i, 5);
+          if (!FP8 && kg == 0) trace_rec(p, 1, i, 5);
           if (FP8 || kg == k_groups - 1) {
             tc_commit(&sm.tmem_full[acc]);
             ++group;
-            trace_rec(p, 1, i, 6);
+            if (FP8) { if (kg < 4) trace_rec(p, 1, i, 2 * kg + 1); }
+            else trace_rec(p, 1, i, 6);
           }
           sfsel ^= 1;
           if (++s == static_cast<uint32_t>(ngs)) { s = 0; ph ^= 1; }
@@ -594,6 +617,12 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     uint32_t res_phase = 0;
     int bias_nb = -1;
     const float* const bias_base = p.bias ? sm.bias_s[ew] : nullptr;
+    // FP8: per-warp tables of B scales at the end of the arena, [chunk][quadrant][kb][32];
+    // a GLU warp also owns the table of its gate chunk (chunk cc + 2, whose warps are idle)
+    int sb_nb = -1;
+    float* const sb_all = reinterpret_cast<float*>(sm.arena + ARENA_BYTES - kb_count * FP8_SB_BYTES_PER_KB);
+    float* const sb_tab = sb_all + ((cc * 4 + q) * kb_count) * 32;
+    float* const sb_gate = sb_all + ((((cc + 2) & 3) * 4 + q) * kb_count) * 32;
 
     // residual block of (mb, tile column c0) -> res_buf (TMA, 32 rows x 32 bf16)
     auto res_issue = [&](int mb_, int64_t out_col) {
@@ -631,39 +660,84 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       }
       float z[NCH][32], gate[32];
       if constexpr (FP8) {
-        // promote each 128-wide K block: z += tmem * sa[row, kb] * sb[col, kb]
+        // B scales of this warp's columns, transposed into its private table [kb][32]
+        // (lane <-> column while loading; every lane reads whole rows of it afterwards)
+        if (nb != sb_nb) {
+          __syncwarp();
+          const int64_t ncol = static_cast<int64_t>(nb) * BNT + col_base + lane;
+          const float* src = p.fb + ncol * kb_count;
+          for (int kb = 0; kb < kb_count; ++kb) sb_tab[kb * 32 + lane] = ncol < p.N ? __ldg(src + kb) : 0.0f;
+          if constexpr (GLU) {
+            if (has_work) {
+              const int64_t gcol = ncol + GATE_OFF;
+              const float* gsrc = p.fb + gcol * kb_count;
+              for (int kb = 0; kb < kb_count; ++kb) sb_gate[kb * 32 + lane] = gcol < p.N ? __ldg(gsrc + kb) : 0.0f;
+            }
+          }
+          __syncwarp();
+          sb_nb = nb;
+        }
+        // promote each 128-wide K block: z += tmem * (sa[row, kb] * sb[col, kb]), two columns
+        // per packed fp32x2 instruction (same roundings as the scalar form)
+        uint64_t z2[16], g2[GLU ? 16 : 1];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) { z[0][i] = 0.0f; gate[i] = 0.0f; }
-        const int64_t ncol = static_cast<int64_t>(nb) * BNT + col_base + lane;   // lane <-> column for the scale fetch
-        const int64_t gcol = ncol + GATE_OFF;
+        for (int i = 0; i < 16; ++i) z2[i] = 0ull;
+        if constexpr (GLU) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) g2[i] = 0ull;
+        }
+        const float* sa_row = p.fa + row * kb_count;
+        float sa_next = row_ok ? __ldg(sa_row) : 0.0f;
         for (int kb = 0; kb < kb_count; ++kb) {
-          const uint32_t acc = group & 1;
-          if (!mbar_wait(&sm.tmem_full[acc], (group >> 1) & 1, p.status, 4)) { ok = false; break; }
+          const float sa = sa_next;
+          if (kb + 1 < kb_count && row_ok) sa_next = __ldg(sa_row + kb + 1);
+          const uint32_t acc = group & (FP8_ACCS - 1);
+          if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[acc], (group / FP8_ACCS) & 1, p.status, 4);
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) break;
           tc_fence_after();
-          const float sa = row_ok ? __ldg(p.fa + row * kb_count + kb) : 0.0f;
-          const float sbv = ncol < p.N ? __ldg(p.fb + ncol * kb_count + kb) : 0.0f;
+          if (tr && kb < 3) trace_rec(p, 2, it, 2 * kb);
+          const uint64_t sa2 = pack_f32x2(sa, sa);
+          // acc2[i] += r[2i, 2i+1] * (sa * table[2i, 2i+1])
+          auto promote = [&](uint64_t* acc2, const uint32_t (&r)[32], const float* table) {
+            const uint32_t taddr = smem_u32(table);
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+              uint64_t b0, b1;
+              asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(b0), "=l"(b1) : "r"(taddr + v * 16));
+              acc2[2 * v] = fma_f32x2(pack_f32x2(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1])),
+                                      mul_f32x2(sa2, b0), acc2[2 * v]);
+              acc2[2 * v + 1] = fma_f32x2(pack_f32x2(__uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3])),
+                                          mul_f32x2(sa2, b1), acc2[2 * v + 1]);
+            }
+          };
           uint32_t r[32];
+          if constexpr (GLU) {
+            if (has_work) {  // gate first, so that one register block serves both loads
+              tc_ld_32x32b_x32(lane_addr + TM_ACC0 + acc * 128 + GATE_OFF + col_base, r);
+              tc_wait_ld();
+              promote(g2, r, sb_gate + kb * 32);
+            }
+          }
           if (has_work) {
             tc_ld_32x32b_x32(lane_addr + TM_ACC0 + acc * 128 + col_base, r);
             tc_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              z[0][i] = fmaf(__uint_as_float(r[i]), sa * __shfl_sync(0xffffffffu, sbv, i), z[0][i]);
-            if constexpr (GLU) {
-              const float sbg = gcol < p.N ? __ldg(p.fb + gcol * kb_count + kb) : 0.0f;
-              tc_ld_32x32b_x32(lane_addr + TM_ACC0 + acc * 128 + GATE_OFF + col_base, r);
-              tc_wait_ld();
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                gate[i] = fmaf(__uint_as_float(r[i]), sa * __shfl_sync(0xffffffffu, sbg, i), gate[i]);
-            }
           }
+          // the K block is in registers: hand its accumulator back before the arithmetic
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&sm.tmem_empty[acc]);
           ++group;
+          if (has_work) promote(z2, r, sb_tab + kb * 32);
+          if (tr) trace_rec(p, 2, it, kb < 3 ? 2 * kb + 1 : 6);
         }
         if (!ok) break;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) unpack_f32x2(z2[i], z[0][2 * i], z[0][2 * i + 1]);
+        if constexpr (GLU) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) unpack_f32x2(g2[i], gate[2 * i], gate[2 * i + 1]);
+        }
       } else {
         if (tr) trace_rec(p, 2, it, 0);
         // one polling lane per warp (512 polling threads would starve the MMA-issuing thread)
@@ -725,10 +799,10 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             res_phase ^= 1;
             res_smem = res_buf;
           }
-          if (tr && h == 0) trace_rec(p, 2, it, 3);
+          if (tr && h == 0 && !FP8) trace_rec(p, 2, it, 3);
           ChunkOut<EPI>::apply(p, z[h], gate, row, bias_base ? bias_base + h * 32 : nullptr, bias_base + 32, out_col0,
                                row_ok, res_smem, lane);
-          if (tr && h == 0) trace_rec(p, 2, it, 4);
+          if (tr && h == 0 && !FP8) trace_rec(p, 2, it, 4);
           if constexpr (EPI == VX_EPI_BIAS_RESIDUAL) {
             if (res_inflight) {
               // the block has been consumed: fetch the next one (second chunk of this tile, or
@@ -790,12 +864,12 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             }
             fence_proxy_async_smem();
             __syncwarp();
-            if (tr && h == 0) trace_rec(p, 2, it, 5);
+            if (tr && h == 0 && !FP8) trace_rec(p, 2, it, 5);
             if (lane == 0 && box_ok) {
               tma_store_2d(&tmap_out, static_cast<int>(out_col0), mb * BM + q * 32, buf);
               tma_store_commit();
             }
-            if (tr && h == 0) trace_rec(p, 2, it, 6);
+            if (tr && h == 0) trace_rec(p, 2, it, FP8 ? 7 : 6);
           } else if (row_ok) {
             store_chunk_direct(p, z[h], row, out_col0, n_out);
           }
@@ -952,7 +1026,9 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, 
   p.b_slot_bytes = (p.b_slot_bytes + 1023) & ~1023;
   const int tiles = p.m_tiles * p.n_tiles;
   int grid;
-  const int res_slots = (ARENA_BYTES - p.k_stages * p.b_slot_bytes) / p.a_slot_bytes;
+  // FP8: the end of the arena holds the epilogue's B-scale tables
+  const int arena = ARENA_BYTES - (KIND == KIND_FP8 ? p.k_stages * FP8_SB_BYTES_PER_KB : 0);
+  const int res_slots = (arena - p.k_stages * p.b_slot_bytes) / p.a_slot_bytes;
   p.b_resident = allow_resident && p.k_stages <= RESIDENT_MAX_KSTAGES && p.n_tiles <= sms && res_slots >= 2;
   p.group = 1;
   if (p.b_resident) {
@@ -967,7 +1043,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, 
     if (groups > p.m_tiles) groups = p.m_tiles;
     grid = groups * p.n_tiles;
   } else {
-    const int slots = ARENA_BYTES / (p.a_slot_bytes + p.b_slot_bytes);
+    const int slots = arena / (p.a_slot_bytes + p.b_slot_bytes);
     p.num_slots = slots > MAX_STAGES ? MAX_STAGES : slots;
     grid = tiles < sms ? tiles : sms;
   }
