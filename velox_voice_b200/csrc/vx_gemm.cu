@@ -280,7 +280,7 @@ __device__ __forceinline__ uint32_t store_chunk_fp4(const GemmParams& p, const f
     for (int q = 0; q < 4; ++q) {
       const float v[8] = {z[8 * q], z[8 * q + 1], z[8 * q + 2], z[8 * q + 3],
                           z[8 * q + 4], z[8 * q + 5], z[8 * q + 6], z[8 * q + 7]};
-      w[q] = e2m1_pack8(v, rcp);
+      w[q] = e2m1_pack8<true>(v, rcp);
     }
     sbytes = byte;
   } else {
@@ -297,7 +297,7 @@ __device__ __forceinline__ uint32_t store_chunk_fp4(const GemmParams& p, const f
       for (int q = 0; q < 2; ++q) {
         const int b = 16 * h + 8 * q;
         const float v[8] = {z[b], z[b + 1], z[b + 2], z[b + 3], z[b + 4], z[b + 5], z[b + 6], z[b + 7]};
-        w[2 * h + q] = e2m1_pack8(v, rcp);
+        w[2 * h + q] = e2m1_pack8<false>(v, rcp);
       }
       sbytes |= byte << (8 * h);
     }

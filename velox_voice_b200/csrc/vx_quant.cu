@@ -45,6 +45,38 @@ struct QuantParams {
   int64_t ldy;
 };
 
+// Eight consecutive elements as loaded (not yet converted): lets a kernel issue the loads of
+// its next row before it works on the current one.
+// 64 registers per thread: four 256-thread blocks per SM (more blocks per SM spill and were slower)
+#define VX_QUANT_MIN_BLOCKS 4
+
+template <typename T> struct Raw8;
+template <> struct Raw8<__nv_bfloat16> {
+  uint4 u;
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) { u = __ldg(reinterpret_cast<const uint4*>(p)); }
+  __device__ __forceinline__ void zero() { u = make_uint4(0, 0, 0, 0); }
+  __device__ __forceinline__ void get(float (&v)[8]) const {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+};
+template <> struct Raw8<float> {
+  float4 a, b;
+  __device__ __forceinline__ void load(const float* p) {
+    a = __ldg(reinterpret_cast<const float4*>(p));
+    b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+  }
+  __device__ __forceinline__ void zero() { a = b = make_float4(0.f, 0.f, 0.f, 0.f); }
+  __device__ __forceinline__ void get(float (&v)[8]) const {
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+};
+
 __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
   const uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
   const uint32_t w[4] = {u.x, u.y, u.z, u.w};
@@ -88,7 +120,7 @@ __device__ __forceinline__ void quant_chunk(const QuantParams& p, int64_t row0, 
 
   if constexpr (FMT == VX_FMT_ROWSCALE) {
     if (active) {
-      *reinterpret_cast<uint32_t*>(p.codes + row0 * p.ldc + (k0 >> 1)) = e2m1_pack8(v[0], row_rcp);
+      *reinterpret_cast<uint32_t*>(p.codes + row0 * p.ldc + (k0 >> 1)) = e2m1_pack8<true>(v[0], row_rcp);
     }
   } else if constexpr (FMT == VX_FMT_FP8_1X128) {
 #pragma unroll
@@ -114,7 +146,7 @@ __device__ __forceinline__ void quant_chunk(const QuantParams& p, int64_t row0, 
 #pragma unroll
     for (int r = 0; r < RP; ++r) {
       if (active)
-        *reinterpret_cast<uint32_t*>(p.codes + (row0 + r) * p.ldc + (k0 >> 1)) = e2m1_pack8(v[r], rcp);
+        *reinterpret_cast<uint32_t*>(p.codes + (row0 + r) * p.ldc + (k0 >> 1)) = e2m1_pack8<FMT != VX_FMT_NV16>(v[r], rcp);
     }
     if (p.scales && active && (lane % LPB) == 0) {
       uint8_t* s = static_cast<uint8_t*>(p.scales);
@@ -139,7 +171,7 @@ __device__ __forceinline__ void quant_chunk(const QuantParams& p, int64_t row0, 
 
 // Streaming quantizer (no LayerNorm): any K % 8 == 0.
 template <typename T, int FMT>
-__global__ void __launch_bounds__(256) quant_kernel(const QuantParams p) {
+__global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) quant_kernel(const QuantParams p) {
   constexpr int RP = (FMT == VX_FMT_BLK16_A) ? 2 : 1;
   const int lane = threadIdx.x & 31;
   const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
@@ -149,8 +181,17 @@ __global__ void __launch_bounds__(256) quant_kernel(const QuantParams p) {
   float g = 1.0f;
   if constexpr (FMT == VX_FMT_NV16) g = nv16_global(__ldg(p.amax));
 
-  for (int64_t u = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-       u < nunits; u += warps) {
+  Raw8<T> raw[RP];
+  auto fetch = [&](int64_t u, int c) {
+    const int64_t k0 = static_cast<int64_t>(c) * 256 + lane * 8;
+#pragma unroll
+    for (int r = 0; r < RP; ++r) {
+      if (k0 < p.K) raw[r].load(x + (u * RP + r) * p.ldx + k0);
+      else raw[r].zero();
+    }
+  };
+  const int64_t u_first = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  for (int64_t u = u_first; u < nunits; u += warps) {
     const int64_t row0 = u * RP;
     float row_rcp = 0.0f;
     if constexpr (FMT == VX_FMT_ROWSCALE) {
@@ -168,17 +209,14 @@ __global__ void __launch_bounds__(256) quant_kernel(const QuantParams p) {
       ue8m0_from_amax(a, byte, row_rcp);
       if (p.scales && lane == 0) static_cast<uint8_t*>(p.scales)[row0] = static_cast<uint8_t>(byte);
     }
+    // chunk c + 1 (or chunk 0 of this warp's next unit) is loaded while chunk c is encoded
+    if (u == u_first || FMT == VX_FMT_ROWSCALE) fetch(u, 0);  // (ROWSCALE reads the row twice: no look-ahead)
     for (int c = 0; c < nchunks; ++c) {
-      const int64_t k0 = static_cast<int64_t>(c) * 256 + lane * 8;
       float v[RP][8];
 #pragma unroll
-      for (int r = 0; r < RP; ++r) {
-        if (k0 < p.K) load8(x + (row0 + r) * p.ldx + k0, v[r]);
-        else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) v[r][j] = 0.0f;
-        }
-      }
+      for (int r = 0; r < RP; ++r) raw[r].get(v[r]);
+      if (c + 1 < nchunks) fetch(u, c + 1);
+      else if (u + warps < nunits && FMT != VX_FMT_ROWSCALE) fetch(u + warps, 0);
       quant_chunk<FMT, RP>(p, row0, c, lane, v, row_rcp, g);
     }
   }
@@ -191,7 +229,7 @@ __global__ void __launch_bounds__(256) quant_kernel(const QuantParams p) {
 // correctly rounded, lane-sequential partial sums and a butterfly (xor 16, 8, 4, 2, 1) warp
 // reduction -- an order a CPU restatement can follow exactly.
 template <typename T, int FMT, int CH>
-__global__ void __launch_bounds__(256) ln_quant_kernel(const QuantParams p) {
+__global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) ln_quant_kernel(const QuantParams p) {
   constexpr int RP = (FMT == VX_FMT_BLK16_A) ? 2 : 1;
   const int lane = threadIdx.x & 31;
   const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
@@ -201,21 +239,33 @@ __global__ void __launch_bounds__(256) ln_quant_kernel(const QuantParams p) {
   float g = 1.0f;
   if constexpr (FMT == VX_FMT_NV16) g = nv16_global(__ldg(p.amax));
 
-  for (int64_t u = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-       u < nunits; u += warps) {
+  // the row(s) of unit u, as loaded; issued one iteration ahead of their use
+  Raw8<T> raw[CH][RP];
+  auto fetch = [&](int64_t u) {
+#pragma unroll
+    for (int r = 0; r < RP; ++r)
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        const int64_t k0 = static_cast<int64_t>(c) * 256 + lane * 8;
+        if (k0 < p.K) raw[c][r].load(x + (u * RP + r) * p.ldx + k0);
+        else raw[c][r].zero();
+      }
+  };
+  const int64_t u_first = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (u_first < nunits) fetch(u_first);
+  for (int64_t u = u_first; u < nunits; u += warps) {
     const int64_t row0 = u * RP;
     float v[CH][RP][8];
+#pragma unroll
+    for (int r = 0; r < RP; ++r)
+#pragma unroll
+      for (int c = 0; c < CH; ++c) raw[c][r].get(v[c][r]);
+    if (u + warps < nunits) fetch(u + warps);
 #pragma unroll
     for (int r = 0; r < RP; ++r) {
       float s = 0.0f, sq = 0.0f;
 #pragma unroll
       for (int c = 0; c < CH; ++c) {
-        const int64_t k0 = static_cast<int64_t>(c) * 256 + lane * 8;
-        if (k0 < p.K) load8(x + (row0 + r) * p.ldx + k0, v[c][r]);
-        else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) v[c][r][j] = 0.0f;
-        }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           s = __fadd_rn(s, v[c][r][j]);

@@ -32,14 +32,19 @@ __device__ __forceinline__ void ue8m0_from_amax(float amax, uint32_t& byte, floa
 // The reference rule -- magnitude code = number of thresholds {0.25, 0.75, 1.25, 1.75, 2.5,
 // 3.5} strictly exceeded, sign = (q < 0) -- is "round to nearest E2M1 value, ties toward zero,
 // capped at 4.0".  The hardware converter (cvt.rn.satfinite.e2m1x2.f32) rounds ties to even
-// and reaches 6.0, so it is fed a representative instead of q itself:
-//   n   = ceil(4 |q|) clamped to 16      (2^23 + x rounded toward +inf leaves ceil(x) in the
-//                                          low mantissa bits; all thresholds are multiples of 1/4)
-//   rep = n * 31/128                      strictly inside the interval that rounds, to nearest,
-//                                          to the reference's code for every n in 0..16
-// and rep carries q's sign bit.  q is formed as (v * rcp) + (+0) with two separate roundings:
-// a product that is -0 or underflows to -0 becomes +0, so the sign bit equals (q < 0) exactly
-// (a fused multiply-add would keep the sign of the unrounded product).
+// and reaches 6.0.  It is made to follow the reference by two cheap corrections:
+//   * the converter never sees a tie: q is replaced by q' = q when its last mantissa bit is
+//     set, else by the next fp32 value toward zero, which has it set (all six thresholds have
+//     that bit clear).  q <= t gives q' < t and q > t gives q' > t for every threshold t, so
+//     round-to-nearest of q' is the reference's code.  q' = (q * (1 - 2^-24)) | 1: the product
+//     rounds to the fp32 neighbour toward zero for every normal q (subnormal q stay put; they
+//     encode as zero either way).  For a power-of-two rcp the factor is folded into rcp
+//     (rcp * (1 - 2^-24) is exact), saving the second multiplication;
+//   * code 7 (6.0, reached for |q| > 5) is turned into code 6 on the packed word.
+// q is formed as (v * rcp) + (+0) with two separate roundings: a product that is -0 or
+// underflows to -0 becomes +0, so the sign bit equals (q < 0) exactly (a fused multiply-add
+// would keep the sign of the unrounded product); tiny negative q keep their sign and encode
+// as -0 (nibble 8), like the reference.
 __device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
   uint64_t r;
   asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
@@ -64,28 +69,17 @@ __device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
   asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
 }
-// Two values at a time: the two fused multiply-adds run as packed fp32 instructions (one issue
-// slot per pair).  The product, the "+0" and the clamp stay scalar: they must keep subnormal
-// results (a tiny negative value still encodes as -0, i.e. nibble 8, like the reference).
-__device__ __forceinline__ void e2m1_rep2(float v0, float v1, float rcp, float& r0, float& r1) {
-  const float q0 = __fadd_rn(__fmul_rn(v0, rcp), 0.0f);  // -0 -> +0
-  const float q1 = __fadd_rn(__fmul_rn(v1, rcp), 0.0f);
-  const uint64_t a2 = pack_f32x2(fminf(fabsf(q0), 4.0f), fminf(fabsf(q1), 4.0f));
-  uint64_t n2;  // 2^23 + ceil(4 a)
-  asm("fma.rp.f32x2 %0, %1, %2, %3;" : "=l"(n2) : "l"(a2), "l"(pack_f32x2(4.0f, 4.0f)),
-      "l"(pack_f32x2(8388608.0f, 8388608.0f)));
-  uint64_t p2;  // n * 31/128, exact
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(p2) : "l"(n2), "l"(pack_f32x2(0.2421875f, 0.2421875f)),
-      "l"(pack_f32x2(-2031616.0f, -2031616.0f)));
-  float p0, p1;
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(p0), "=f"(p1) : "l"(p2));
-  r0 = __uint_as_float(__float_as_uint(p0) | (__float_as_uint(q0) & 0x80000000u));
-  r1 = __uint_as_float(__float_as_uint(p1) | (__float_as_uint(q1) & 0x80000000u));
-}
+constexpr float kTowardZero = 0.99999994f;  // 1 - 2^-24
+template <bool POW2>
 __device__ __forceinline__ uint32_t e2m1_pack8(const float (&v)[8], float rcp) {
+  const float m = POW2 ? __fmul_rn(rcp, kTowardZero) : rcp;
   float r[8];
 #pragma unroll
-  for (int j = 0; j < 8; j += 2) e2m1_rep2(v[j], v[j + 1], rcp, r[j], r[j + 1]);
+  for (int j = 0; j < 8; ++j) {
+    float q = __fadd_rn(__fmul_rn(v[j], m), 0.0f);  // -0 -> +0
+    if (!POW2) q = __fmul_rn(q, kTowardZero);
+    r[j] = __uint_as_float(__float_as_uint(q) | 1u);
+  }
   uint32_t w;
   asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
       "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
@@ -95,7 +89,8 @@ __device__ __forceinline__ uint32_t e2m1_pack8(const float (&v)[8], float rcp) {
       "mov.b32 %0, {b0, b1, b2, b3};\n\t}"
       : "=r"(w)
       : "f"(r[0]), "f"(r[1]), "f"(r[2]), "f"(r[3]), "f"(r[4]), "f"(r[5]), "f"(r[6]), "f"(r[7]));
-  return w;
+  // nibbles with magnitude 7 -> 6: clear bit 0 where bits 0..2 are all set
+  return w ^ (w & (w >> 1) & (w >> 2) & 0x11111111u);
 }
 
 __device__ __forceinline__ float e4m3_to_float(uint32_t b) {
