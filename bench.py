@@ -233,11 +233,12 @@ def op_breakdown(stack, T, fmt_name, only=""):
         ts.sort()
         cases.append((name, count, ts[len(ts) // 2], nbytes, flops))
 
-    add("ln_quantize [T,512]", 4 * nb + 1, lambda: ops.ln_quantize(x, g, b, cfg.eps, fmt, amax_t=am),
+    add("ln_quantize [T,512]", 3 * nb + 1, lambda: ops.ln_quantize(x, g, b, cfg.eps, fmt, amax_t=am),
         T * d * 2 + qbytes(T, d), 0)
+    add("ln2_quantize [T,512] (norm_final + next LayerNorm + quantize)", nb,
+        lambda: ops.ln2_quantize(x, g, b, g, b, cfg.eps, fmt, y=x, amax_t=am), T * d * 4 + qbytes(T, d), 0)
     add("quantize [T,512]", 2 * nb + 1, lambda: ops.quantize(x, fmt, natural=fmt_name == "fp8_1x128", amax_t=am),
         T * d * 2 + qbytes(T, d), 0)
-    add("layernorm [T,512]", nb, lambda: ops.layernorm(x, g, b, cfg.eps, out=x), T * d * 4, 0)
     w1, w2 = stack.p["b0.ffm.w1"], stack.p["b0.ffm.w2"]
     if stack.fuse_ffn:
         hq = w1(xq, act="swish", out_fmt=fmt, out_amax=stack.amax.get("b0.ffm.h"))
@@ -260,7 +261,8 @@ def op_breakdown(stack, T, fmt_name, only=""):
     add("gemm lp 512->512", nb, lambda: stack.p["b0.lp"](xq), qbytes(T, d) + qbytes(d, d) + T * d * 2, 2 * T * d * d)
     add("gemm pw1 512->1024 GLU", nb, lambda: stack.p["b0.pw1"](xq), qbytes(T, d) + qbytes(2 * d, d) + T * d * 2,
         2 * T * d * 2 * d)
-    add("gemm ctc 512->5538 bias", 1, lambda: stack.p["ctc"](xq), qbytes(T, d) + qbytes(V, d) + T * V * 2, 2 * T * d * V)
+    add("gemm ctc 512->5538 bias + argmax (no logits written)", 1, lambda: stack.p["ctc"].argmax(xq),
+        qbytes(T, d) + qbytes(V, d) + T * 12, 2 * T * d * V)
     del flush
     return cases
 

@@ -47,7 +47,9 @@ enum vx_epilogue {
   VX_EPI_BIAS = 1,      /* out = acc + bias[n]                       */
   VX_EPI_BIAS_SWISH = 2,/* out = silu(acc + bias[n])                 */
   VX_EPI_BIAS_GLU = 3,  /* out[:, j] = (acc_a + b_a) * sigmoid(acc_b + b_b), GLU-interleaved weights */
-  VX_EPI_BIAS_RESIDUAL = 4 /* out = residual + alpha * (acc + bias[n]) */
+  VX_EPI_BIAS_RESIDUAL = 4, /* out = residual + alpha * (acc + bias[n]) */
+  VX_EPI_BIAS_ARGMAX = 5 /* no [M, N] output: per row the first column holding the maximum of
+                            bf16(acc + bias[n]); `out` = u64 keys [M], see vx_argmax_ids */
 };
 
 /* Scale factors in the layout the block-scaled tensor-core MMA consumes ("SF atoms"):
@@ -83,6 +85,18 @@ int vx_ln_quantize_pack(const void* x, int x_dtype, int64_t M, int64_t K, int64_
                         const float* gamma, const float* beta, float eps, int fmt, void* codes,
                         int64_t ldc, void* scales, void* scales_sf, const float* amax, void* y,
                         int y_dtype, int64_t ldy, void* stream);
+
+/* Two LayerNorms in a row, then the quantizer, in one pass over x:
+ *   y = LN(x; gamma1, beta1) stored (may alias x), codes = quantize(LN(y as stored; gamma2, beta2)).
+ * This is the end of one Conformer block (norm_final, torch_conformer.py:713) running into the
+ * first LayerNorm of the next block (:706) or into after_norm (:745): the reference runs two
+ * LayerNorm launches and a quantizer launch.  Same eps for both; y may be NULL (then the second
+ * LayerNorm reads the unrounded fp32 result of the first).  Other arguments as above. */
+int vx_ln2_quantize_pack(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx,
+                         const float* gamma1, const float* beta1, const float* gamma2,
+                         const float* beta2, float eps, int fmt, void* codes, int64_t ldc,
+                         void* scales, void* scales_sf, const float* amax, void* y, int y_dtype,
+                         int64_t ldy, void* stream);
 
 /* max |x| over a tensor into amax_out[0] (f32, overwritten).  No reference counterpart
  * (the reference has no per-tensor scale); needed by NV16. */
@@ -139,6 +153,14 @@ int vx_glu_tile(int fmt);
 #define VX_GEMM_STREAM_B 2     /* never keep the B tile resident in shared memory */
 
 int vx_bsgemm(const vx_gemm_desc* desc, void* stream);
+
+/* Greedy (argmax) head without materialising the logits: what the reference computes as
+ * ctc_lo(x).argmax(-1) on [T, vocab] logits (veloxvoice/models/wenet/torch_conformer.py:810-814).
+ * vx_bsgemm with VX_EPI_BIAS_ARGMAX clears and fills `out` = u64 [M]: key = (order-preserving
+ * bits of the bf16-rounded logit) << 32 | (0xFFFFFFFF - column), maximised over the columns, so
+ * equal bf16 logits resolve to the lowest column like torch.argmax.  vx_argmax_ids turns keys
+ * into ids i32 [M] and, when max_out != NULL, the winning logits f32 [M]. */
+int vx_argmax_ids(const void* keys, int64_t M, int32_t* ids, float* max_out, void* stream);
 
 /* Block-scaled FP4 GEMM for callers that cannot allocate device memory.  (No counterpart in
  * the reference: its Python wrappers allocate through torch.)

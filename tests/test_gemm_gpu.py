@@ -324,3 +324,32 @@ def test_argument_errors_raise(ops):
     with pytest.raises(VeloxError):
         ops.dgx_mxfp4_gemm(torch.zeros(128, 24, dtype=torch.uint8, device="cuda"), torch.zeros(128, 24, dtype=torch.uint8, device="cuda"),
                            torch.zeros(128, dtype=torch.uint8, device="cuda"), torch.zeros(128, dtype=torch.uint8, device="cuda"))
+
+
+@pytest.mark.parametrize("fmt", ["mx32", "nv16", "fp8_1x128", "rowscale"])
+@pytest.mark.parametrize("M,N,K", [(1000, 5538, 512), (130, 96, 256), (257, 700, 1024)])
+def test_argmax_epilogue_equals_argmax_of_the_bf16_logits(fmt, M, N, K):
+    """VX_EPI_BIAS_ARGMAX == bsgemm(bias, bf16).argmax(1), ties to the lowest column."""
+    from velox_voice_b200 import ops
+
+    torch.manual_seed(11)
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = torch.randn(N, K, device="cuda") * 0.05
+    w[N // 2] = w[3]           # duplicated vocabulary rows: exact ties in the logits
+    w[N - 1] = w[3]
+    bias = torch.randn(N, device="cuda") * 0.01
+    bias[N // 2] = bias[3]
+    bias[N - 1] = bias[3]
+    am = {}
+    if fmt == "nv16":
+        am = {"amax_t": ops.amax(x)}
+    a = ops.quantize(x, fmt, **am)
+    b = ops.quantize(w, fmt)
+    logits = ops.bsgemm(a, b, epilogue=ops.EPI_BIAS, bias=bias, out_dtype=torch.bfloat16)
+    want = logits.float().argmax(dim=1).to(torch.int32)
+    ids, vmax = ops.bsgemm_argmax(a, b, bias, return_max=True)
+    torch.cuda.synchronize()
+    assert torch.equal(ids, want)
+    assert torch.equal(vmax, logits.float().max(dim=1).values)
+    # rows whose maximum sits on the duplicated column must report the first copy
+    assert not bool(((ids == N // 2) | (ids == N - 1)).any())

@@ -222,3 +222,27 @@ def test_argument_errors_raise(ops):
         ops.quantize(torch.zeros(3, 64, device="cuda"), F.FMT_BLK16_A)  # odd row count
     with pytest.raises(TypeError):
         ops.quantize(torch.zeros(4, 64, device="cuda", dtype=torch.float16), F.FMT_MX32)
+
+
+@pytest.mark.parametrize("fmt", ["mx32", "nv16", "fp8_1x128", "rowscale"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_two_layernorms_fused_equal_the_two_launches(fmt, dtype):
+    """vx_ln2_quantize_pack == LayerNorm launch (stored y) followed by LayerNorm + quantize."""
+    from velox_voice_b200 import ops
+
+    torch.manual_seed(5)
+    M, K = 333, 512
+    x = (torch.randn(M, K, device="cuda") * 3 + 0.5).to(dtype)
+    g1, b1 = torch.rand(K, device="cuda") + 0.5, torch.randn(K, device="cuda") * 0.1
+    g2, b2 = torch.rand(K, device="cuda") + 0.5, torch.randn(K, device="cuda") * 0.1
+    am = torch.tensor([8.0], device="cuda") if fmt == "nv16" else None
+    y_ref = ops.layernorm(x.clone(), g1, b1, 1e-5)
+    q_ref = ops.ln_quantize(y_ref, g2, b2, 1e-5, fmt, natural=True, amax_t=am)
+    xin = x.clone()
+    q = ops.ln2_quantize(xin, g1, b1, g2, b2, 1e-5, fmt, y=xin, natural=True, amax_t=am)  # in place
+    torch.cuda.synchronize()
+    assert torch.equal(xin, y_ref)
+    assert torch.equal(q.codes, q_ref.codes)
+    assert torch.equal(q.scales, q_ref.scales)
+    if q.sf is not None:
+        assert torch.equal(q.sf, q_ref.sf)

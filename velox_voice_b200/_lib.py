@@ -23,7 +23,7 @@ FMT_BY_NAME = {
     "fp8_1x128": FMT_FP8_1X128,
 }
 DT_F32, DT_BF16, DT_FP4 = 0, 1, 2
-EPI_NONE, EPI_BIAS, EPI_BIAS_SWISH, EPI_BIAS_GLU, EPI_BIAS_RESIDUAL = range(5)
+EPI_NONE, EPI_BIAS, EPI_BIAS_SWISH, EPI_BIAS_GLU, EPI_BIAS_RESIDUAL, EPI_BIAS_ARGMAX = range(6)
 GEMM_DIRECT_STORE = 1
 GEMM_STREAM_B = 2
 
@@ -35,6 +35,7 @@ EXPORTS = (
     "vx_sf_bytes",
     "vx_quantize_pack",
     "vx_ln_quantize_pack",
+    "vx_ln2_quantize_pack",
     "vx_amax",
     "vx_sf_from_natural",
     "vx_bsgemm",
@@ -42,6 +43,7 @@ EXPORTS = (
     "vx_set_trace_buffer",
     "vx_blkscale_gemm_noalloc",
     "vx_glu_tile",
+    "vx_argmax_ids",
 )
 
 
@@ -116,6 +118,8 @@ def load(build_if_missing: bool = True) -> C.CDLL:
         lib.vx_sf_bytes.argtypes = [i32, i64, i64]
         lib.vx_quantize_pack.restype = i32
         lib.vx_quantize_pack.argtypes = [vp, i32, i64, i64, i64, i32, vp, i64, vp, vp, vp, vp]
+        lib.vx_ln2_quantize_pack.restype = i32
+        lib.vx_ln2_quantize_pack.argtypes = [vp, i32, i64, i64, i64, vp, vp, vp, vp, f32, i32, vp, i64, vp, vp, vp, vp, i32, i64, vp]
         lib.vx_ln_quantize_pack.restype = i32
         lib.vx_ln_quantize_pack.argtypes = [vp, i32, i64, i64, i64, vp, vp, f32, i32, vp, i64, vp, vp, vp, vp, i32, i64, vp]
         lib.vx_amax.restype = i32
@@ -128,6 +132,8 @@ def load(build_if_missing: bool = True) -> C.CDLL:
         lib.vx_blkscale_gemm_noalloc.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, vp]
         lib.vx_glu_tile.restype = i32
         lib.vx_glu_tile.argtypes = [i32]
+        lib.vx_argmax_ids.restype = i32
+        lib.vx_argmax_ids.argtypes = [vp, i64, vp, vp, vp]
         lib.vx_set_trace_buffer.restype = i32
         lib.vx_set_trace_buffer.argtypes = [vp, i64]
         lib.vx_mma_peak_probe.restype = i32

@@ -616,6 +616,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     uint32_t store_count = 0;
     uint32_t res_phase = 0;
     int bias_nb = -1;
+    uint32_t best_key = 0;  // ARGMAX: best (value, column) of this thread's row in the current tile
     const float* const bias_base = p.bias ? sm.bias_s[ew] : nullptr;
     // FP8: per-warp tables of B scales at the end of the arena, [chunk][quadrant][kb][32];
     // a GLU warp also owns the table of its gate chunk (chunk cc + 2, whose warps are idle)
@@ -815,7 +816,25 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             }
           }
 
-          if (p.out_dtype == VX_FP4) {
+          if constexpr (EPI == VX_EPI_BIAS_ARGMAX) {
+            // key: order-preserving bits of bf16(z) (high half) | 0xFFFF - tile column (low half)
+            const uint32_t cbase = 0xffffu - static_cast<uint32_t>(col_base + h * 32);
+            const int valid = p.N - acc_col0 >= 32 ? 32 : static_cast<int>(p.N - acc_col0);
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const uint32_t pk = pack_bf16x2(z[h][i], z[h][i + 1]);
+              const uint32_t x0 = pk << 16, x1 = pk & 0xffff0000u;
+              const uint32_t u0 = x0 ^ (static_cast<uint32_t>(static_cast<int32_t>(x0) >> 31) | 0x80000000u);
+              const uint32_t u1 = x1 ^ (static_cast<uint32_t>(static_cast<int32_t>(x1) >> 31) | 0x80000000u);
+              uint32_t k0 = (u0 & 0xffff0000u) | (cbase - i);
+              uint32_t k1 = (u1 & 0xffff0000u) | (cbase - i - 1);
+              if (valid < 32) {
+                if (i >= valid) k0 = 0;
+                if (i + 1 >= valid) k1 = 0;
+              }
+              best_key = max(best_key, max(k0, k1));
+            }
+          } else if (p.out_dtype == VX_FP4) {
             const uint32_t sb = store_chunk_fp4(p, z[h], row, out_col0, g_out, row_ok && out_col0 < n_out);
             if (row_ok && out_col0 < n_out) {
               // this chunk's scale byte(s) inside the row's SF word(s)
@@ -875,6 +894,15 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
           }
         }
       }
+      if constexpr (EPI == VX_EPI_BIAS_ARGMAX) {
+        if (has_work && row_ok && best_key != 0) {
+          const uint32_t gcol = static_cast<uint32_t>(nb) * BNT + (0xffffu - (best_key & 0xffffu));
+          const unsigned long long key =
+              (static_cast<unsigned long long>(best_key & 0xffff0000u) << 32) | (0xffffffffu - gcol);
+          atomicMax(static_cast<unsigned long long*>(p.out) + row, key);
+        }
+        best_key = 0;
+      }
       mb = mb_next;
       nb = nb_next;
     }
@@ -888,6 +916,19 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TM_COLS);
+  }
+}
+
+// keys of the ARGMAX epilogue -> column ids (and the winning bf16 logit as fp32)
+__global__ void argmax_ids_kernel(const unsigned long long* __restrict__ keys, int64_t M,
+                                  int32_t* __restrict__ ids, float* __restrict__ max_out) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= M) return;
+  const unsigned long long k = keys[i];
+  ids[i] = static_cast<int32_t>(0xffffffffu - static_cast<uint32_t>(k));
+  if (max_out) {
+    const uint32_t u = static_cast<uint32_t>(k >> 32);
+    max_out[i] = __uint_as_float((u & 0x80000000u) ? (u ^ 0x80000000u) : ~u & 0xffff0000u);
   }
 }
 
@@ -1061,6 +1102,7 @@ int dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, const CU
     case VX_EPI_BIAS_SWISH: return launch<KIND, VX_EPI_BIAS_SWISH>(ta, tb, to, tr, p, res, st);
     case VX_EPI_BIAS_GLU: return launch<KIND, VX_EPI_BIAS_GLU>(ta, tb, to, tr, p, res, st);
     case VX_EPI_BIAS_RESIDUAL: return launch<KIND, VX_EPI_BIAS_RESIDUAL>(ta, tb, to, tr, p, res, st);
+    case VX_EPI_BIAS_ARGMAX: return launch<KIND, VX_EPI_BIAS_ARGMAX>(ta, tb, to, tr, p, res, st);
     default: return fail(-1, "unknown epilogue %d", epi);
   }
 }
@@ -1095,7 +1137,10 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
   if (fmt_has_sf(fmt) && (!aligned16(d->a_scales) || !aligned16(d->b_scales)))
     return fail(-1, "SF atoms must be 16-byte aligned");
   const int epi = d->epilogue;
-  if (epi < VX_EPI_NONE || epi > VX_EPI_BIAS_RESIDUAL) return fail(-1, "unknown epilogue %d", epi);
+  if (epi < VX_EPI_NONE || epi > VX_EPI_BIAS_ARGMAX) return fail(-1, "unknown epilogue %d", epi);
+  const bool argmax = epi == VX_EPI_BIAS_ARGMAX;
+  if (argmax && (reinterpret_cast<uintptr_t>(d->out) & 7)) return fail(-1, "argmax keys must be 8-byte aligned");
+  if (argmax && N > 0xffffffffll) return fail(-1, "argmax needs N < 2^32");
   if (d->out_dtype != VX_F32 && d->out_dtype != VX_BF16 && d->out_dtype != VX_FP4)
     return fail(-1, "unknown out_dtype %d", d->out_dtype);
   if (d->bias && (reinterpret_cast<uintptr_t>(d->bias) & 15)) return fail(-1, "bias must be 16-byte aligned");
@@ -1135,7 +1180,9 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
   p.residual = d->residual; p.residual_dtype = d->residual_dtype; p.ldr = d->ldr; p.alpha = d->alpha;
   p.status = cached_status_ptr();
 
-  if (d->out_dtype == VX_FP4) {
+  if (argmax) {
+    p.out_dtype = VX_F32;
+  } else if (d->out_dtype == VX_FP4) {
     if (d->out_fmt != VX_FMT_MX32 && d->out_fmt != VX_FMT_NV16) return fail(-1, "FP4 output: out_fmt must be MX32 or NV16");
     if (epi == VX_EPI_BIAS_GLU || epi == VX_EPI_BIAS_RESIDUAL) return fail(-1, "FP4 output supports NONE / BIAS / BIAS_SWISH");
     if (!d->out_scales_sf || !aligned16(d->out_scales_sf)) return fail(-1, "FP4 output needs out_scales_sf (16-byte aligned)");
@@ -1153,7 +1200,8 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
   }
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (d->out_dtype == VX_FP4 && (M % BM != 0)) {
+  if (argmax) VX_CUDA_OK(cudaMemsetAsync(d->out, 0, static_cast<size_t>(M) * 8, st));
+  if (!argmax && d->out_dtype == VX_FP4 && (M % BM != 0)) {
     // SF rows of the last partial tile must read as zero
     VX_CUDA_OK(cudaMemsetAsync(p.out_sf, 0, static_cast<size_t>(vx_sf_bytes(d->out_fmt, M, N)), st));
   }
@@ -1165,7 +1213,7 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
   if (rc) return rc;
   const int oelt = d->out_dtype == VX_BF16 ? 2 : 4;
   p.tma_store = 0;
-  if (d->out_dtype != VX_FP4 && !(d->flags & VX_GEMM_DIRECT_STORE) && aligned16(d->out) &&
+  if (!argmax && d->out_dtype != VX_FP4 && !(d->flags & VX_GEMM_DIRECT_STORE) && aligned16(d->out) &&
       (d->ldo * oelt) % 16 == 0) {
     rc = make_tmap(&to, d->out_dtype == VX_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
                    oelt, d->out, M, n_out, d->ldo * oelt, 32, 32,
@@ -1190,6 +1238,18 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
   if (fp8) return dispatch_epi<KIND_FP8>(epi, ta, tb, to, tr, p, res, st);
   if (fmt == VX_FMT_ROWSCALE || fmt == VX_FMT_MX32) return dispatch_epi<KIND_FP4_VEC2>(epi, ta, tb, to, tr, p, res, st);
   return dispatch_epi<KIND_FP4_VEC4>(epi, ta, tb, to, tr, p, res, st);
+}
+
+int vx_argmax_ids(const void* keys, int64_t M, int32_t* ids, float* max_out, void* stream) {
+  using namespace vx;
+  if (M < 0) return fail(-1, "negative M");
+  if (M == 0) return 0;
+  if (!keys || !ids) return fail(-1, "keys and ids must not be NULL");
+  const int grid = static_cast<int>((M + 255) / 256);
+  argmax_ids_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const unsigned long long*>(keys), M, ids, max_out);
+  VX_CUDA_OK(cudaGetLastError());
+  return 0;
 }
 
 int vx_glu_tile(int fmt) { return vx::kind_bn(fmt == VX_FMT_FP8_1X128 ? vx::KIND_FP8 : vx::KIND_FP4_VEC2); }

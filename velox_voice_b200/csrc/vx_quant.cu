@@ -39,6 +39,8 @@ struct QuantParams {
   const float* amax;
   const float* gamma;
   const float* beta;
+  const float* gamma2;  // second LayerNorm applied to the stored y (nullptr: single LayerNorm)
+  const float* beta2;
   float eps;
   void* y;
   int y_bf16;
@@ -53,7 +55,8 @@ struct QuantParams {
 template <typename T> struct Raw8;
 template <> struct Raw8<__nv_bfloat16> {
   uint4 u;
-  __device__ __forceinline__ void load(const __nv_bfloat16* p) { u = __ldg(reinterpret_cast<const uint4*>(p)); }
+  // plain (coherent) loads: the LayerNorm kernels may store y over x while other rows are still read
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) { u = *reinterpret_cast<const uint4*>(p); }
   __device__ __forceinline__ void zero() { u = make_uint4(0, 0, 0, 0); }
   __device__ __forceinline__ void get(float (&v)[8]) const {
     const uint32_t w[4] = {u.x, u.y, u.z, u.w};
@@ -67,8 +70,8 @@ template <> struct Raw8<__nv_bfloat16> {
 template <> struct Raw8<float> {
   float4 a, b;
   __device__ __forceinline__ void load(const float* p) {
-    a = __ldg(reinterpret_cast<const float4*>(p));
-    b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+    a = *reinterpret_cast<const float4*>(p);
+    b = *(reinterpret_cast<const float4*>(p) + 1);
   }
   __device__ __forceinline__ void zero() { a = b = make_float4(0.f, 0.f, 0.f, 0.f); }
   __device__ __forceinline__ void get(float (&v)[8]) const {
@@ -236,6 +239,7 @@ __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) ln_quant_kernel(cons
   const int64_t nunits = p.M / RP;
   const T* x = static_cast<const T*>(p.x);
   const float k_f = static_cast<float>(p.K);
+  const int npass = p.gamma2 ? 2 : 1;
   float g = 1.0f;
   if constexpr (FMT == VX_FMT_NV16) g = nv16_global(__ldg(p.amax));
 
@@ -261,6 +265,11 @@ __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) ln_quant_kernel(cons
 #pragma unroll
       for (int c = 0; c < CH; ++c) raw[c][r].get(v[c][r]);
     if (u + warps < nunits) fetch(u + warps);
+    // one pass per LayerNorm: the second one (if any) normalises the rows as pass 0 stored them
+    const float* ga_p = p.gamma;
+    const float* be_p = p.beta;
+#pragma unroll 1
+    for (int pass = 0; pass < npass; ++pass) {
 #pragma unroll
     for (int r = 0; r < RP; ++r) {
       float s = 0.0f, sq = 0.0f;
@@ -285,13 +294,13 @@ __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) ln_quant_kernel(cons
         const int64_t k0 = static_cast<int64_t>(c) * 256 + lane * 8;
         if (k0 < p.K) {
           float ga[8], be[8];
-          load8(p.gamma + k0, ga);
-          load8(p.beta + k0, be);
+          load8(ga_p + k0, ga);
+          load8(be_p + k0, be);
 #pragma unroll
           for (int j = 0; j < 8; ++j)
             v[c][r][j] = __fadd_rn(
                 __fmul_rn(__fmul_rn(__fsub_rn(v[c][r][j], mean), rstd), ga[j]), be[j]);
-          if (p.y) {
+          if (p.y && pass == 0) {
             if (p.y_bf16) {
               uint4 u;
               u.x = pack2_bf16(v[c][r][0], v[c][r][1]);
@@ -299,6 +308,14 @@ __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) ln_quant_kernel(cons
               u.z = pack2_bf16(v[c][r][4], v[c][r][5]);
               u.w = pack2_bf16(v[c][r][6], v[c][r][7]);
               *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.y) + (row0 + r) * p.ldy + k0) = u;
+              if (npass > 1) {  // the next LayerNorm reads what was stored
+                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  v[c][r][2 * j] = __uint_as_float(w[j] << 16);
+                  v[c][r][2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+                }
+              }
             } else {
               float4* yp = reinterpret_cast<float4*>(static_cast<float*>(p.y) + (row0 + r) * p.ldy + k0);
               yp[0] = make_float4(v[c][r][0], v[c][r][1], v[c][r][2], v[c][r][3]);
@@ -307,6 +324,9 @@ __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) ln_quant_kernel(cons
           }
         }
       }
+    }
+      ga_p = p.gamma2;
+      be_p = p.beta2;
     }
     if (!p.codes) continue;  // plain LayerNorm
     float row_rcp = 0.0f;
@@ -404,7 +424,8 @@ int dispatch_fmt(int fmt, const QuantParams& p, bool ln, cudaStream_t st) {
 int quantize_common(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, int fmt,
                     void* codes, int64_t ldc, void* scales, void* scales_sf, const float* amax,
                     bool ln, const float* gamma, const float* beta, float eps, void* y,
-                    int y_dtype, int64_t ldy, void* stream) {
+                    int y_dtype, int64_t ldy, void* stream, const float* gamma2 = nullptr,
+                    const float* beta2 = nullptr) {
   if (!fmt_valid(fmt)) return fail(-1, "unknown format %d", fmt);
   if (x_dtype != VX_F32 && x_dtype != VX_BF16) return fail(-1, "x_dtype must be VX_F32 or VX_BF16");
   if (M < 0 || K < 0) return fail(-1, "negative shape");
@@ -437,6 +458,9 @@ int quantize_common(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ld
     if (y && y_dtype != VX_F32 && y_dtype != VX_BF16) return fail(-1, "y_dtype must be VX_F32 or VX_BF16");
     if (y && (!aligned16(y) || ldy < K || (ldy * (y_dtype == VX_BF16 ? 2 : 4)) % 16 != 0))
       return fail(-1, "y rows must be 16-byte aligned");
+    if ((gamma2 != nullptr) != (beta2 != nullptr)) return fail(-1, "gamma2 and beta2 go together");
+    if (gamma2 && (!aligned16(gamma2) || !aligned16(beta2))) return fail(-1, "gamma2/beta2 must be 16-byte aligned");
+    if (gamma2 && !codes) return fail(-1, "the second LayerNorm feeds the quantizer: codes must not be NULL");
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   QuantParams p{};
@@ -444,7 +468,7 @@ int quantize_common(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ld
   p.codes = static_cast<uint8_t*>(codes); p.ldc = ldc;
   p.scales = scales; p.sf = static_cast<uint8_t*>(scales_sf);
   p.sf_kg = sf_kgroups(fmt, K);
-  p.amax = amax; p.gamma = gamma; p.beta = beta; p.eps = eps; p.y = y; p.y_bf16 = (y_dtype == VX_BF16); p.ldy = ldy;
+  p.amax = amax; p.gamma = gamma; p.beta = beta; p.gamma2 = gamma2; p.beta2 = beta2; p.eps = eps; p.y = y; p.y_bf16 = (y_dtype == VX_BF16); p.ldy = ldy;
   if (scales_sf) {
     // rows / k-groups beyond the tensor must read as zero scale factors
     const int64_t nkb = K / blk;
@@ -480,6 +504,16 @@ int vx_ln_quantize_pack(const void* x, int x_dtype, int64_t M, int64_t K, int64_
                         int y_dtype, int64_t ldy, void* stream) {
   return vx::quantize_common(x, x_dtype, M, K, ldx, fmt, codes, ldc, scales, scales_sf, amax, true,
                              gamma, beta, eps, y, y_dtype, ldy, stream);
+}
+
+int vx_ln2_quantize_pack(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx,
+                         const float* gamma1, const float* beta1, const float* gamma2,
+                         const float* beta2, float eps, int fmt, void* codes, int64_t ldc,
+                         void* scales, void* scales_sf, const float* amax, void* y, int y_dtype,
+                         int64_t ldy, void* stream) {
+  if (!gamma2 || !beta2) return vx::fail(-1, "gamma2 and beta2 must not be NULL");
+  return vx::quantize_common(x, x_dtype, M, K, ldx, fmt, codes, ldc, scales, scales_sf, amax, true,
+                             gamma1, beta1, eps, y, y_dtype, ldy, stream, gamma2, beta2);
 }
 
 int vx_amax(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, float* amax_out,

@@ -28,6 +28,7 @@ from ._lib import (  # noqa: F401  (re-exported)
     DT_F32,
     DT_FP4,
     EPI_BIAS,
+    EPI_BIAS_ARGMAX,
     EPI_BIAS_GLU,
     EPI_BIAS_RESIDUAL,
     EPI_BIAS_SWISH,
@@ -228,6 +229,35 @@ def ln_quantize(
     return (q, y) if y is not None else q
 
 
+def ln2_quantize(x: torch.Tensor, gamma1, beta1, gamma2, beta2, eps: float, fmt, *, y: Optional[torch.Tensor] = None,
+                 natural: bool = False, sf: bool = True, amax_t: Optional[torch.Tensor] = None) -> Quantized:
+    """``y = LN1(x)`` stored into ``y`` (may be ``x`` itself) and ``quantize(LN2(y))`` returned, in
+    one pass: ``layernorm(x, g1, b1, out=y)`` followed by ``ln_quantize(y, g2, b2)``."""
+    fmt = _fmt(fmt)
+    _require_cuda(x, "x")
+    x = _rows2d(x, "x")
+    M, K = x.shape
+    if fmt == FMT_NV16 and amax_t is None:
+        raise ValueError("NV16 behind LayerNorm needs a calibrated tensor amax (amax_t)")
+    if fmt == FMT_ROWSCALE or fmt == FMT_FP8_1X128:
+        natural = True
+    g1, b1 = gamma1.float().contiguous(), beta1.float().contiguous()
+    g2, b2 = gamma2.float().contiguous(), beta2.float().contiguous()
+    codes, scales, sf_t = _alloc_outputs(fmt, M, K, x.device, natural, sf)
+    if y is not None:
+        y = _rows2d(y, "y")
+        if y.shape != x.shape:
+            raise ValueError("y must have the shape of x")
+    rc = _lib.load().vx_ln2_quantize_pack(
+        x.data_ptr(), _dt(x, "x"), M, K, x.stride(0), g1.data_ptr(), b1.data_ptr(), g2.data_ptr(), b2.data_ptr(),
+        float(eps), fmt, codes.data_ptr(), codes.stride(0), _ptr(scales), _ptr(sf_t), _ptr(amax_t),
+        _ptr(y), _dt(y, "y") if y is not None else 0, y.stride(0) if y is not None else K, _stream(),
+    )
+    _lib.check(rc, "vx_ln2_quantize_pack")
+    _count()
+    return Quantized(fmt, M, K, codes, scales, sf_t, amax_t)
+
+
 def layernorm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: float = 1e-5, out=None, out_dtype=None):
     """Row LayerNorm with fp32 statistics; output f32 or bf16."""
     _require_cuda(x, "x")
@@ -347,6 +377,50 @@ def bsgemm(
     _count()
     del keep
     return result
+
+
+def bsgemm_argmax(a: Quantized, b: Quantized, bias: Optional[torch.Tensor] = None, *,
+                  return_max: bool = False, keys: Optional[torch.Tensor] = None,
+                  ids: Optional[torch.Tensor] = None):
+    """Per row of ``A . B^T + bias``: the first column holding the maximum of the bf16-rounded
+    result -- ``bsgemm(..., out_dtype=bfloat16).argmax(1)`` without writing the [M, N] matrix
+    (the greedy CTC head).  Returns int32 ids [M] (and the winning values as float32 [M])."""
+    if a.fmt != b.fmt and not (a.fmt == FMT_BLK16_A and b.fmt == FMT_BLK16_B):
+        raise ValueError(f"operand formats differ ({a.fmt} vs {b.fmt})")
+    if a.k != b.k:
+        raise ValueError(f"K mismatch: {a.k} vs {b.k}")
+    M, N, K = a.rows, b.rows, a.k
+    dev = a.codes.device
+    if keys is None:
+        keys = torch.empty((M,), dtype=torch.int64, device=dev)
+    if ids is None:
+        ids = torch.empty((M,), dtype=torch.int32, device=dev)
+    if keys.dtype != torch.int64 or keys.numel() < M or ids.dtype != torch.int32 or ids.numel() < M:
+        raise ValueError("keys must be int64 [M] and ids int32 [M]")
+    d = _lib.GemmDesc()
+    d.struct_size = C.sizeof(_lib.GemmDesc)
+    d.fmt = a.fmt
+    d.M, d.N, d.K = M, N, K
+    d.a_codes, d.lda = a.codes.data_ptr(), a.codes.stride(0)
+    d.b_codes, d.ldb = b.codes.data_ptr(), b.codes.stride(0)
+    sa, sb = a.gemm_scales(), b.gemm_scales()
+    d.a_scales, d.b_scales = sa.data_ptr(), sb.data_ptr()
+    if a.fmt == FMT_NV16:
+        d.a_amax, d.b_amax = a.amax.data_ptr(), b.amax.data_ptr()
+    d.epilogue = EPI_BIAS_ARGMAX
+    if bias is not None:
+        if bias.dtype != torch.float32 or not bias.is_contiguous() or bias.numel() < N:
+            raise ValueError("bias must be a contiguous float32 vector with N entries")
+        d.bias = bias.data_ptr()
+    d.out_dtype, d.out, d.ldo = DT_F32, keys.data_ptr(), 1
+    lib = _lib.load()
+    _lib.check(lib.vx_bsgemm(C.byref(d), _stream()), "vx_bsgemm")
+    _count()
+    vmax = torch.empty((M,), dtype=torch.float32, device=dev) if return_max else None
+    _lib.check(lib.vx_argmax_ids(keys.data_ptr(), M, ids.data_ptr(), _ptr(vmax), _stream()), "vx_argmax_ids")
+    _count()
+    del sa, sb
+    return (ids, vmax) if return_max else ids
 
 
 def mma_peak_tflops(kind: str = "fp4", n_tile: int = 256, iters: int = 4096) -> float:

@@ -13,10 +13,14 @@ convolution and its norm/activation are NOT linear layers and are outside this l
 stack passes the value projection straight to ``lo`` and the GLU output straight to ``pw2``,
 so it measures and validates every linear of the encoder with the real operand shapes.
 
-Kernel sequence per block (14 launches; the reference issues >= 4 per linear):
-``ln_quant -> GEMM(bias, swish, FP4 out) -> GEMM(bias, 0.5 residual)`` for each FFN,
-``ln_quant -> GEMM(bias) [qkv] -> quant -> GEMM(bias, residual) [lo]``, ``GEMM [lp]``,
-``ln_quant -> GEMM(bias, GLU) -> quant -> GEMM(bias, residual)``, ``layernorm``.
+Kernel sequence per block (13 launches; the reference issues >= 4 per linear):
+``GEMM(bias, swish, FP4 out) -> GEMM(bias, 0.5 residual)`` for each FFN (the second one behind
+its ``ln_quant``), ``ln_quant -> GEMM(bias) [qkv] -> quant -> GEMM(bias, residual) [lo]``,
+``GEMM [lp]``, ``ln_quant -> GEMM(bias, GLU) -> quant -> GEMM(bias, residual)``, and one
+``ln2_quant`` kernel that applies norm_final, stores the residual stream and hands the next
+block's first FFN (or the CTC head, through after_norm) its quantized input.  The greedy head
+(:meth:`ConformerLinearStack.forward_ids`) takes the per-frame argmax inside the CTC GEMM's
+epilogue, so the [T, vocab] logits are never written.
 
 Multi-GPU: every operation is row-wise in the frames, so frames are cut into contiguous equal
 shards (:func:`shard_rows`), weights are replicated, and the only collective is the final
@@ -138,8 +142,9 @@ class ConformerLinearStack:
     def _q(self, key: str, x: torch.Tensor):
         return ops.quantize(x, self.fmt, natural=self.fmt == FMT_FP8_1X128, amax_t=self._amax(key, x))
 
-    def _ffn(self, b: str, ff: str, ln: str, x: torch.Tensor) -> torch.Tensor:
-        q = self._lnq(b + ln, x)
+    def _ffn(self, b: str, ff: str, ln: str, x: torch.Tensor, q=None) -> torch.Tensor:
+        if q is None:
+            q = self._lnq(b + ln, x)
         if self.fuse_ffn:
             h = self.p[b + ff + ".w1"](q, act="swish", out_fmt=self.fmt, out_amax=self._amax(b + ff + ".h", None))
         else:
@@ -147,16 +152,18 @@ class ConformerLinearStack:
         return self.p[b + ff + ".w2"](h, residual=x, alpha=0.5, out=x)
 
     # ---- forward
-    def forward(self, x: torch.Tensor, pos: Optional[torch.Tensor] = None, *, return_hidden: bool = False):
+    def forward(self, x: torch.Tensor, pos: Optional[torch.Tensor] = None, *, return_hidden: bool = False,
+                ids_only: bool = False, keys=None, ids=None):
         """x: bf16 [T, d_model] residual stream (overwritten in place); returns bf16 logits [T, vocab]."""
         cfg = self.cfg
         if x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != cfg.d_model:
             raise ValueError("x must be bf16 [T, d_model]")
         d = cfg.d_model
         pos_q = self._q("pos", pos) if pos is not None else None
+        q_in = None  # first LayerNorm of the block, already applied by the previous block's last kernel
         for i in range(cfg.blocks):
             b = f"b{i}."
-            x = self._ffn(b, "ffm", "ln_ffm", x)
+            x = self._ffn(b, "ffm", "ln_ffm", x, q_in)
             q = self._lnq(b + "ln_mha", x)
             qkv = self.p[b + "qkv"](q)
             if pos_q is not None:
@@ -167,11 +174,22 @@ class ConformerLinearStack:
             gl = self.p[b + "pw1"](q)
             x = self.p[b + "pw2"](self._q(b + "glu", gl), residual=x, alpha=1.0, out=x)
             x = self._ffn(b, "ff", "ln_ff", x)
+            # norm_final of this block + the LayerNorm that reads it next (first of the next block,
+            # or after_norm), one kernel: x <- LN_final(x), q_in <- quantize(LN_next(x))
+            nxt = f"b{i + 1}.ln_ffm" if i + 1 < cfg.blocks else "after"
             g, be = self.ln[b + "ln_final"]
-            x = ops.layernorm(x, g, be, cfg.eps, out=x)
-        q = self._lnq("after", x)
-        logits = self.p["ctc"](q)
+            g2, be2 = self.ln[nxt]
+            q_in = ops.ln2_quantize(x, g, be, g2, be2, cfg.eps, self.fmt, y=x, amax_t=self._amax(nxt, None))
+        if q_in is None:  # zero blocks
+            q_in = self._lnq("after", x)
+        if ids_only:
+            return self.p["ctc"].argmax(q_in, keys=keys, ids=ids)
+        logits = self.p["ctc"](q_in)
         return (logits, x) if return_hidden else logits
+
+    def forward_ids(self, x: torch.Tensor, pos: Optional[torch.Tensor] = None, *, keys=None, ids=None):
+        """Greedy CTC ids int32 [T] of ``forward(x, pos).argmax(1)`` without writing the logits."""
+        return self.forward(x, pos, ids_only=True, keys=keys, ids=ids)
 
     __call__ = forward
 
@@ -254,6 +272,8 @@ class CompiledStack:
         self.x_in = torch.zeros((frames, cfg.d_model), dtype=torch.bfloat16, device=dev)
         self.pos = torch.zeros((frames, cfg.d_model), dtype=torch.bfloat16, device=dev) if with_pos else None
         self._x = torch.empty_like(self.x_in)
+        self._keys = torch.empty((frames,), dtype=torch.int64, device=dev)
+        self._ids = torch.empty((frames,), dtype=torch.int32, device=dev)
         self.ids_host = torch.empty((frames,), dtype=torch.int32).pin_memory()
         self._stage = None
         self._ids_pool: List[torch.Tensor] = []
@@ -268,8 +288,7 @@ class CompiledStack:
 
     def _body(self):
         self._x.copy_(self.x_in)
-        self.logits = self.stack.forward(self._x, self.pos)
-        self.ids = self.logits.argmax(dim=1).to(torch.int32)
+        self.ids = self.stack.forward_ids(self._x, self.pos, keys=self._keys, ids=self._ids)
 
     def run(self):
         self.graph.replay()
