@@ -81,6 +81,8 @@ struct GemmParams {
   // epilogue
   // shared-memory plan
   int b_resident;         // 1: the CTA keeps its B tile (all K stages) in shared memory
+  int sfb_resident;       // 1: B streams, but its scale factors are copied to tensor memory once
+                          //    (the CTA owns one n-block, as with b_resident)
   int num_slots;          // ring slots in use (a multiple of `group`)
   int group;              // K stages per full / empty barrier (2 when a whole K = 512 tile is one wait)
   int a_slot_bytes;       // bytes of one A tile + its scale-factor atoms in the arena
@@ -117,6 +119,7 @@ struct __align__(1024) SmemLayout {
   uint64_t tmem_full[FP8_ACCS];
   uint64_t tmem_empty[FP8_ACCS];
   uint64_t b_full;
+  uint64_t sfb_done;   // sfb_resident: the scale-factor copies out of the borrowed ring slot are complete
   uint64_t res_full[16];
   uint32_t tmem_base;
   int abort_flag;
@@ -341,18 +344,24 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   constexpr int SFB_COLS = 4 * NRT;          // TMEM columns of one K atom of B scale factors
   constexpr int NCH = (WIDE && !GLU) ? 2 : 1;  // 32-column chunks per epilogue warp
   constexpr int GATE_OFF = BNT / 2;          // GLU: gate columns follow the value columns
+  // Swish (+ FP4 re-quantization) epilogues are bound by their own arithmetic, not by the
+  // MMA -> epilogue -> MMA hand-over: they read the second 32-column chunk only after the first
+  // is finished (half the live registers), which releases tensor memory later at no cost.
+  constexpr bool SEQ = (EPI == VX_EPI_BIAS_SWISH) && NCH == 2;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int nslots = p.num_slots;
   const bool resident = p.b_resident != 0;
   const bool with_sf = !(FP8 || p.sf_unit);
+  const bool sfb_res = p.sfb_resident != 0;   // implies !resident && with_sf
+  const bool owns_nb = resident || sfb_res;   // fixed n-block, B scale factors stay in TMEM
 
   // This CTA's tiles.  B resident: fixed n-block, m-blocks mb0, mb0 + mstep, ...; streaming:
   // tiles t0, t0 + grid, ... with n fastest.  No division inside the loops.
   const int total_tiles = p.m_tiles * p.n_tiles;
   int my_tiles, mb0, nb0;
-  if (resident) {
+  if (owns_nb) {
     nb0 = blockIdx.x % p.n_tiles;
     mb0 = blockIdx.x / p.n_tiles;
     const int mstep = gridDim.x / p.n_tiles;
@@ -363,7 +372,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     my_tiles = static_cast<int>(blockIdx.x) < total_tiles ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
   }
   const int step_m = static_cast<int>(gridDim.x) / p.n_tiles;
-  const int step_n = resident ? 0 : static_cast<int>(gridDim.x) % p.n_tiles;
+  const int step_n = owns_nb ? 0 : static_cast<int>(gridDim.x) % p.n_tiles;
   auto next_tile = [&](int& mb, int& nb) {
     mb += step_m;
     nb += step_n;
@@ -388,6 +397,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       mbar_init(&sm.tmem_empty[a], 16);
     }
     mbar_init(&sm.b_full, 1);
+    mbar_init(&sm.sfb_done, 1);
     for (int w = 0; w < 16; ++w) mbar_init(&sm.res_full[w], 1);
     sm.abort_flag = 0;
     mbar_fence_init();
@@ -428,7 +438,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       // B tile (+ its scale factors) of n-block nb, K stage ks -> dst; returns bytes in flight
       auto load_b = [&](uint8_t* dst, int nb, int ks, uint64_t* bar) {
         tma_load_2d(dst, &tmap_b, ks * STAGE_ROW_BYTES, nb * BNT, bar);
-        if (with_sf) {
+        if (with_sf && !sfb_res) {
 #pragma unroll
           for (int rt = 0; rt < NRT; ++rt)
             if (nb * NRT + rt < n_sf_tiles)
@@ -438,16 +448,31 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       };
       auto b_tx = [&](int nb) -> uint32_t {
         uint32_t t = B_TILE_BYTES;
-        if (with_sf) {
+        if (with_sf && !sfb_res) {
 #pragma unroll
           for (int rt = 0; rt < NRT; ++rt)
             if (nb * NRT + rt < n_sf_tiles) t += sf_atom_bytes;
         }
         return t;
       };
+      uint8_t* const sfb_stage = sm.arena + (nslots - 1) * slot_bytes + a_slot;
+      bool sfb_pending = sfb_res;
       if (resident) {
         mbar_expect_tx(&sm.b_full, p.k_stages * b_tx(nb0));
         for (int ks = 0; ks < p.k_stages; ++ks) load_b(sm.arena + ks * b_slot, nb0, ks, &sm.b_full);
+      } else if (sfb_res) {
+        // all scale factors of the n-block -> the B region of the last ring slot (zero-filled
+        // at set-up), [ks][rt][atom]; the ring takes that slot over once they are in TMEM
+        uint32_t tx = 0;
+        for (int rt = 0; rt < NRT; ++rt)
+          if (nb0 * NRT + rt < n_sf_tiles) tx += p.k_stages * sf_atom_bytes;
+        mbar_expect_tx(&sm.b_full, tx);
+        for (int ks = 0; ks < p.k_stages; ++ks)
+          for (int rt = 0; rt < NRT; ++rt)
+            if (nb0 * NRT + rt < n_sf_tiles)
+              bulk_load(sfb_stage + (ks * NRT + rt) * APS * 512,
+                        p.sfb + (static_cast<int64_t>(nb0 * NRT + rt) * p.sf_kg) * 512 + ks * sf_stage, APS * 512,
+                        &sm.b_full);
       }
       int mb = mb0, nb = nb0;
       const int G = p.group, k_groups = p.k_stages / G, ngs = nslots / G;
@@ -456,6 +481,10 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         const uint32_t slot_tx = TILE_BYTES + sf_atom_bytes + (resident ? 0u : b_tx(nb));
         for (int kg = 0; kg < k_groups; ++kg) {
           if (!mbar_wait(&sm.empty[s], ph ^ 1, p.status, 1)) { ok = false; break; }
+          if (sfb_pending && s == static_cast<uint32_t>(nslots - 1)) {
+            if (!mbar_wait(&sm.sfb_done, 0, p.status, 7)) { ok = false; break; }
+            sfb_pending = false;
+          }
           trace_rec(p, 0, i, kg < 4 ? kg : 3);
           mbar_expect_tx(&sm.full[s], G * slot_tx);
           for (int u = 0; u < G; ++u) {
@@ -473,10 +502,17 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     }
   } else if (warp == 1) {
     // =========================== MMA issuer ===========================
-    // One thread; every instruction it executes is on the critical path of a tile (K = 512
-    // is only eight MMAs), so descriptors are formed with one add from values kept in
-    // registers: low word = (shared address >> 4) + 2 j for the j-th 64-element K step.
-    if (lane == 0 && my_tiles > 0) {
+    // Every instruction here is on the critical path of a tile (K = 512 is only eight MMAs).
+    // The whole warp runs the loop with warp-uniform control flow and one elected lane issues
+    // the tcgen05 instructions: addresses and descriptors are then warp-uniform values (they
+    // can live in uniform registers, which is where the tensor-core instructions read them).
+    // Descriptors are formed with one add: low word = (shared address >> 4) + 2 j for the
+    // j-th 64-element K step.
+    if (my_tiles > 0) {
+      const bool leader = elect_one();
+      auto CP = [&](uint32_t taddr, uint64_t d) { if (leader) tc_cp_32x128b_warpx4(taddr, d); };
+      auto COMMIT = [&](uint64_t* bar) { if (leader) tc_commit(bar); };
+      auto TRACE = [&](int tile, int ev) { if (leader) trace_rec(p, 1, tile, ev); };
       uint32_t s = 0, ph = 0;
       uint32_t group = 0;  // accumulation groups issued (FP4: one per tile; FP8: one per stage)
       bool ok = true;
@@ -507,9 +543,9 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       const uint32_t tm_sfa = tmem_base + TM_SFA, tm_sfb = tmem_base + TM_SFB;
       if (!FP8 && p.sf_unit) {
         const uint64_t d = make_desc_sf(smem_u32(unit_sf));
-        tc_cp_32x128b_warpx4(tm_sfa, d);
+        CP(tm_sfa, d);
 #pragma unroll
-        for (int rt = 0; rt < NRT; ++rt) tc_cp_32x128b_warpx4(tm_sfb + rt * 4, d);
+        for (int rt = 0; rt < NRT; ++rt) CP(tm_sfb + rt * 4, d);
       }
       // B scale factors of one stage: shared (lo = B slot >> 4) -> TMEM columns at `col0`
       auto cp_sfb = [&](uint32_t b_lo, uint32_t col0) {
@@ -517,79 +553,127 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         for (int a = 0; a < APS; ++a)
 #pragma unroll
           for (int rt = 0; rt < NRT; ++rt)
-            tc_cp_32x128b_warpx4(col0 + a * SFB_COLS + rt * 4, desc(b_lo + b_sf_lo + (rt * APS + a) * 32, sf_hi));
+            CP(col0 + a * SFB_COLS + rt * 4, desc(b_lo + b_sf_lo + (rt * APS + a) * 32, sf_hi));
       };
       if (resident) {
         if (!mbar_wait(&sm.b_full, 0, p.status, 5)) ok = false;
         tc_fence_after();
         if (ok && with_sf)  // B's scale factors stay in tensor memory for the whole kernel
           for (int ks = 0; ks < p.k_stages; ++ks) cp_sfb(arena_lo + ks * bslot_lo, tm_sfb + ks * APS * SFB_COLS);
-      }
-      const int G = p.group, k_groups = p.k_stages / G, ngs = nslots / G;
-      uint32_t sfsel = 0;  // which half of the scale-factor columns this group uses
-      for (int i = 0; i < my_tiles && ok; ++i) {
-        for (int kg = 0; kg < k_groups; ++kg) {
-          const uint32_t acc = WIDE ? 0u : (group & (FP8_ACCS - 1));
-          if (FP8 || kg == 0) {
-            const uint32_t use = WIDE ? group : (group / FP8_ACCS);
-            if (!mbar_wait_spin(&sm.tmem_empty[acc], (use & 1) ^ 1, p.status, 2)) { ok = false; break; }
-            tc_fence_after();  // orders the epilogue's tcgen05.ld of this buffer before the MMAs
-            if (!FP8) trace_rec(p, 1, i, 0);
-          }
-          if (!mbar_wait_spin(&sm.full[s], ph, p.status, 3)) { ok = false; break; }
-          if (FP8) { if (kg < 4) trace_rec(p, 1, i, 2 * kg); }
-          else trace_rec(p, 1, i, kg < 2 ? 1 + kg : 2);
-          const uint32_t d_tmem = tmem_base + TM_ACC0 + acc * 128;
-          const uint32_t a_lo0 = ring_lo + s * G * slot_lo;
-          // (Issuing the next tile's scale-factor copies ahead of this wait was tried: the
-          // tcgen05.commit that publishes the accumulator then fires ~1400 cycles later.)
-          const uint32_t sfa_buf = tm_sfa + sfsel * 32;
-          const uint32_t sfb_buf = tm_sfb + (resident ? 0u : sfsel * 64);
-          if constexpr (!FP8) {
-            if (with_sf) {
-              for (int u = 0; u < G; ++u) {
-                const uint32_t a_lo = a_lo0 + u * slot_lo;
+      } else if (sfb_res) {
+        if (!mbar_wait(&sm.b_full, 0, p.status, 5)) ok = false;
+        tc_fence_after();
+        if (ok) {
+          const uint32_t st_lo = (arena_u32 + (nslots - 1) * slot_bytes + a_slot) >> 4;
+          for (int ks = 0; ks < p.k_stages; ++ks)
 #pragma unroll
-                for (int a = 0; a < APS; ++a)
-                  tc_cp_32x128b_warpx4(sfa_buf + (u * APS + a) * 4, desc(a_lo + a_sf_lo + a * 32, sf_hi));
-                if (!resident) cp_sfb(a_lo + aslot_lo, sfb_buf + u * APS * SFB_COLS);
-              }
-            }
-            if (kg == 0) trace_rec(p, 1, i, 3);
-          }
-          for (int u = 0; u < G; ++u) {
-            const int ks = kg * G + u;
-            const uint32_t a_lo = a_lo0 + u * slot_lo;
-            const uint32_t b_lo = resident ? arena_lo + ks * bslot_lo : a_lo + aslot_lo;
-            if constexpr (FP8) {
+            for (int a = 0; a < APS; ++a)
 #pragma unroll
-              for (int j = 0; j < 4; ++j)
-                mma_f8(d_tmem, desc(a_lo + 2 * j, k128_hi), desc(b_lo + 2 * j, k128_hi), idesc_base, (u | j) != 0);
-            } else {
-              const uint32_t sfa_t = with_sf ? sfa_buf + u * APS * 4 : tm_sfa;
-              const uint32_t sfb_t = with_sf ? sfb_buf + (resident ? ks : u) * APS * SFB_COLS : tm_sfb;
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                if (p.dbg & 2) break;
-                mma_mxf4<VEC>(d_tmem, desc(a_lo + 2 * j, k128_hi), desc(b_lo + 2 * j, k128_hi), idesc_j[j],
-                              sfa_t + sfa_col_j[j], sfb_t + sfb_col_j[j], (ks | j) != 0);
-              }
-            }
-          }
-          if (!FP8 && kg == 0) trace_rec(p, 1, i, 4);
-          tc_commit(&sm.empty[s]);  // ring slots reusable once these MMAs have read them
-          if (!FP8 && kg == 0) trace_rec(p, 1, i, 5);
-          if (FP8 || kg == k_groups - 1) {
-            tc_commit(&sm.tmem_full[acc]);
-            ++group;
-            if (FP8) { if (kg < 4) trace_rec(p, 1, i, 2 * kg + 1); }
-            else trace_rec(p, 1, i, 6);
-          }
-          sfsel ^= 1;
-          if (++s == static_cast<uint32_t>(ngs)) { s = 0; ph ^= 1; }
+              for (int rt = 0; rt < NRT; ++rt)
+                CP(tm_sfb + (ks * APS + a) * SFB_COLS + rt * 4,
+                                     desc(st_lo + ((ks * NRT + rt) * APS + a) * 32, sf_hi));
+          COMMIT(&sm.sfb_done);
         }
       }
-      if (!ok) sm.abort_flag = 1;
+      if constexpr (FP8) {
+        // Rounds of up to four 128-wide K blocks, block u of a round into accumulator u.  The
+        // accumulators are handed back in pairs (0,1) and (2,3) and published once per round,
+        // so this thread -- which shares its scheduler with four busy epilogue warps -- waits
+        // and commits a few times per tile instead of twice per K block.
+        const int G = p.group, ngs = nslots / G;
+        uint32_t use0 = 0, use1 = 0;  // rounds that used accumulator pair 0 / 1
+        int in_group = 0;
+        for (int i = 0; i < my_tiles && ok; ++i) {
+          for (int kb0 = 0; kb0 < p.k_stages && ok; kb0 += FP8_ACCS) {
+            const int nkb = p.k_stages - kb0 < FP8_ACCS ? p.k_stages - kb0 : FP8_ACCS;
+            for (int u = 0; u < nkb; ++u) {
+              if ((u & 1) == 0) {
+                const int pr = u >> 1;
+                const uint32_t use = pr ? use1 : use0;
+                if (!mbar_wait_spin(&sm.tmem_empty[pr], (use & 1) ^ 1, p.status, 2)) { ok = false; break; }
+                if (pr) ++use1; else ++use0;
+                tc_fence_after();  // orders the epilogue's tcgen05.ld of these buffers before the MMAs
+              }
+              if (in_group == 0) {
+                if (!mbar_wait_spin(&sm.full[s], ph, p.status, 3)) { ok = false; break; }
+                tc_fence_after();
+              }
+              if (kb0 == 0) TRACE(i, 2 * u);
+              const uint32_t a_lo = ring_lo + (s * G + in_group) * slot_lo;
+              const uint32_t b_lo = resident ? arena_lo + (kb0 + u) * bslot_lo : a_lo + aslot_lo;
+              const uint32_t d_tmem = tmem_base + TM_ACC0 + u * 128;
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                if (leader) mma_f8(d_tmem, desc(a_lo + 2 * j, k128_hi), desc(b_lo + 2 * j, k128_hi), idesc_base, j != 0);
+              if (++in_group == G) {
+                COMMIT(&sm.empty[s]);  // ring slots reusable once these MMAs have read them
+                in_group = 0;
+                if (++s == static_cast<uint32_t>(ngs)) { s = 0; ph ^= 1; }
+              }
+              if (kb0 == 0) TRACE(i, 2 * u + 1);
+            }
+            if (ok) COMMIT(&sm.tmem_full[0]);
+          }
+        }
+      } else {
+        const int G = p.group, k_groups = p.k_stages / G, ngs = nslots / G;
+        uint32_t sfsel = 0;  // which half of the scale-factor columns this group uses
+        for (int i = 0; i < my_tiles && ok; ++i) {
+          for (int kg = 0; kg < k_groups; ++kg) {
+            if (kg == 0) {
+              if (!mbar_wait_spin(&sm.tmem_empty[0], (group & 1) ^ 1, p.status, 2)) { ok = false; break; }
+              tc_fence_after();  // orders the epilogue's tcgen05.ld of this buffer before the MMAs
+              TRACE(i, 0);
+            }
+            if (!mbar_wait_spin(&sm.full[s], ph, p.status, 3)) { ok = false; break; }
+            TRACE(i, kg < 2 ? 1 + kg : 2);
+            const uint32_t d_tmem = tmem_base + TM_ACC0;
+            const uint32_t a_lo0 = ring_lo + s * G * slot_lo;
+            // (Issuing the next tile's scale-factor copies ahead of this wait was tried: the
+            // tcgen05.commit that publishes the accumulator then fires ~1400 cycles later.)
+            const uint32_t sfa_buf = tm_sfa + sfsel * 32;
+            const uint32_t sfb_buf = tm_sfb + (owns_nb ? 0u : sfsel * 64);
+            {
+              if (with_sf) {
+                for (int u = 0; u < G; ++u) {
+                  const uint32_t a_lo = a_lo0 + u * slot_lo;
+  #pragma unroll
+                  for (int a = 0; a < APS; ++a)
+                    CP(sfa_buf + (u * APS + a) * 4, desc(a_lo + a_sf_lo + a * 32, sf_hi));
+                  if (!owns_nb) cp_sfb(a_lo + aslot_lo, sfb_buf + u * APS * SFB_COLS);
+                }
+              }
+              if (kg == 0) TRACE(i, 3);
+            }
+            for (int u = 0; u < G; ++u) {
+              const int ks = kg * G + u;
+              const uint32_t a_lo = a_lo0 + u * slot_lo;
+              const uint32_t b_lo = resident ? arena_lo + ks * bslot_lo : a_lo + aslot_lo;
+              {
+                const uint32_t sfa_t = with_sf ? sfa_buf + u * APS * 4 : tm_sfa;
+                const uint32_t sfb_t = with_sf ? sfb_buf + (owns_nb ? ks : u) * APS * SFB_COLS : tm_sfb;
+  #pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  if (p.dbg & 2) break;
+                  if (leader) mma_mxf4<VEC>(d_tmem, desc(a_lo + 2 * j, k128_hi), desc(b_lo + 2 * j, k128_hi), idesc_j[j],
+                                sfa_t + sfa_col_j[j], sfb_t + sfb_col_j[j], (ks | j) != 0);
+                }
+              }
+            }
+            if (kg == 0) TRACE(i, 4);
+            COMMIT(&sm.empty[s]);  // ring slots reusable once these MMAs have read them
+            if (kg == 0) TRACE(i, 5);
+            if (kg == k_groups - 1) {
+              COMMIT(&sm.tmem_full[0]);
+              ++group;
+              TRACE(i, 6);
+            }
+            sfsel ^= 1;
+            if (++s == static_cast<uint32_t>(ngs)) { s = 0; ph ^= 1; }
+          }
+        }
+      }
+      if (!ok && leader) sm.abort_flag = 1;
     }
   } else {
     // =========================== epilogue ===========================
@@ -689,48 +773,56 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         }
         const float* sa_row = p.fa + row * kb_count;
         float sa_next = row_ok ? __ldg(sa_row) : 0.0f;
-        for (int kb = 0; kb < kb_count; ++kb) {
-          const float sa = sa_next;
-          if (kb + 1 < kb_count && row_ok) sa_next = __ldg(sa_row + kb + 1);
-          const uint32_t acc = group & (FP8_ACCS - 1);
-          if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[acc], (group / FP8_ACCS) & 1, p.status, 4);
+        for (int kb0 = 0; kb0 < kb_count && ok; kb0 += FP8_ACCS) {
+          // one round: up to four K blocks, block u in accumulator u, published together
+          const int nkb = kb_count - kb0 < FP8_ACCS ? kb_count - kb0 : FP8_ACCS;
+          if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[0], group & 1, p.status, 4);
           ok = __shfl_sync(0xffffffffu, ok, 0);
           if (!ok) break;
-          tc_fence_after();
-          if (tr && kb < 3) trace_rec(p, 2, it, 2 * kb);
-          const uint64_t sa2 = pack_f32x2(sa, sa);
-          // acc2[i] += r[2i, 2i+1] * (sa * table[2i, 2i+1])
-          auto promote = [&](uint64_t* acc2, const uint32_t (&r)[32], const float* table) {
-            const uint32_t taddr = smem_u32(table);
-#pragma unroll
-            for (int v = 0; v < 8; ++v) {
-              uint64_t b0, b1;
-              asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(b0), "=l"(b1) : "r"(taddr + v * 16));
-              acc2[2 * v] = fma_f32x2(pack_f32x2(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1])),
-                                      mul_f32x2(sa2, b0), acc2[2 * v]);
-              acc2[2 * v + 1] = fma_f32x2(pack_f32x2(__uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3])),
-                                          mul_f32x2(sa2, b1), acc2[2 * v + 1]);
-            }
-          };
-          uint32_t r[32];
-          if constexpr (GLU) {
-            if (has_work) {  // gate first, so that one register block serves both loads
-              tc_ld_32x32b_x32(lane_addr + TM_ACC0 + acc * 128 + GATE_OFF + col_base, r);
-              tc_wait_ld();
-              promote(g2, r, sb_gate + kb * 32);
-            }
-          }
-          if (has_work) {
-            tc_ld_32x32b_x32(lane_addr + TM_ACC0 + acc * 128 + col_base, r);
-            tc_wait_ld();
-          }
-          // the K block is in registers: hand its accumulator back before the arithmetic
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&sm.tmem_empty[acc]);
           ++group;
-          if (has_work) promote(z2, r, sb_tab + kb * 32);
-          if (tr) trace_rec(p, 2, it, kb < 3 ? 2 * kb + 1 : 6);
+          tc_fence_after();
+          if (tr && kb0 == 0) trace_rec(p, 2, it, 0);
+#pragma unroll 1
+          for (int u = 0; u < nkb; ++u) {
+            const int kb = kb0 + u;
+            const float sa = sa_next;
+            if (kb + 1 < kb_count && row_ok) sa_next = __ldg(sa_row + kb + 1);
+            const uint64_t sa2 = pack_f32x2(sa, sa);
+            // acc2[i] += r[2i, 2i+1] * (sa * table[2i, 2i+1])
+            auto promote = [&](uint64_t* acc2, const uint32_t (&r)[32], const float* table) {
+              const uint32_t taddr = smem_u32(table);
+#pragma unroll
+              for (int v = 0; v < 8; ++v) {
+                uint64_t b0, b1;
+                asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(b0), "=l"(b1) : "r"(taddr + v * 16));
+                acc2[2 * v] = fma_f32x2(pack_f32x2(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1])),
+                                        mul_f32x2(sa2, b0), acc2[2 * v]);
+                acc2[2 * v + 1] = fma_f32x2(pack_f32x2(__uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3])),
+                                            mul_f32x2(sa2, b1), acc2[2 * v + 1]);
+              }
+            };
+            const uint32_t acc_addr = lane_addr + TM_ACC0 + u * 128 + col_base;
+            uint32_t r[32];
+            if constexpr (GLU) {
+              if (has_work) {  // gate first, so that one register block serves both loads
+                tc_ld_32x32b_x32(acc_addr + GATE_OFF, r);
+                tc_wait_ld();
+                promote(g2, r, sb_gate + kb * 32);
+              }
+            }
+            if (has_work) {
+              tc_ld_32x32b_x32(acc_addr, r);
+              tc_wait_ld();
+            }
+            if ((u & 1) || u == nkb - 1) {
+              // both accumulators of the pair are in registers: hand the pair back
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&sm.tmem_empty[u >> 1]);
+            }
+            if (has_work) promote(z2, r, sb_tab + kb * 32);
+            if (tr && kb0 == 0) trace_rec(p, 2, it, 1 + u);
+          }
         }
         if (!ok) break;
 #pragma unroll
@@ -750,7 +842,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         {
           uint32_t r[32];
 #pragma unroll
-          for (int h = 0; h < NCH; ++h) {
+          for (int h = 0; h < (SEQ ? 1 : NCH); ++h) {
             tc_ld_32x32b_x32(lane_addr + TM_ACC0 + col_base + h * 32, r);
             tc_wait_ld();
 #pragma unroll
@@ -764,16 +856,32 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
           }
         }
         if (tr) trace_rec(p, 2, it, 2);
-        // the accumulator is in registers: hand tensor memory back to the MMA warp
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.tmem_empty[0]);
+        if constexpr (!SEQ) {
+          // the accumulator is in registers: hand tensor memory back to the MMA warp
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sm.tmem_empty[0]);
+        }
         ++group;
       }
 
       if (has_work) {
 #pragma unroll
         for (int h = 0; h < NCH; ++h) {
+          if constexpr (SEQ) {
+            // second chunk: read it now (its registers were free for the first chunk's
+            // arithmetic), then hand tensor memory back
+            if (h == 1) {
+              uint32_t r[32];
+              tc_ld_32x32b_x32(lane_addr + TM_ACC0 + col_base + 32, r);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) z[1][i] = __uint_as_float(r[i]);
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&sm.tmem_empty[0]);
+            }
+          }
           const int64_t acc_col0 = static_cast<int64_t>(nb) * BNT + col_base + h * 32;       // accumulator / bias column
           const int64_t out_col0 = static_cast<int64_t>(nb) * OUT_TILE_COLS + col_base + h * 32;  // output column
           const bool box_ok = rows_ok && out_col0 < n_out;
@@ -1072,11 +1180,24 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, 
   const int res_slots = (arena - p.k_stages * p.b_slot_bytes) / p.a_slot_bytes;
   p.b_resident = allow_resident && p.k_stages <= RESIDENT_MAX_KSTAGES && p.n_tiles <= sms && res_slots >= 2;
   p.group = 1;
+  p.sfb_resident = 0;
+  constexpr int SFB_STAGE_COLS = APS * (BNT / 128) * 4;  // TMEM columns of one stage of B scale factors
+  if (!p.b_resident && allow_resident && with_sf && p.n_tiles <= sms && p.k_stages * SFB_STAGE_COLS <= 128 &&
+      p.k_stages * (BNT / 128) * APS * 512 <= BNT * STAGE_ROW_BYTES) {
+    // B is too large to stay in shared memory, its scale factors are not: one copy into
+    // tensor memory per CTA instead of one per tile and stage
+    p.sfb_resident = 1;
+    p.b_slot_bytes = BNT * STAGE_ROW_BYTES;
+  }
   if (p.b_resident) {
     p.num_slots = res_slots > MAX_STAGES ? MAX_STAGES : res_slots;
     // a whole K <= 512 FP4 tile (two stages) behind one barrier pair: the MMA-issuing thread
     // waits and commits once per tile instead of once per stage
     if (KIND != KIND_FP8 && p.k_stages == 2 && p.num_slots >= 4) {
+      p.group = 2;
+      p.num_slots &= ~1;
+    }
+    if (KIND == KIND_FP8 && p.k_stages % 2 == 0 && p.num_slots >= 4) {  // one ring barrier per pair of K blocks
       p.group = 2;
       p.num_slots &= ~1;
     }
@@ -1086,7 +1207,16 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, 
   } else {
     const int slots = arena / (p.a_slot_bytes + p.b_slot_bytes);
     p.num_slots = slots > MAX_STAGES ? MAX_STAGES : slots;
+    if (KIND == KIND_FP8 && p.k_stages % 2 == 0 && p.num_slots >= 4) {
+      p.group = 2;
+      p.num_slots &= ~1;
+    }
     grid = tiles < sms ? tiles : sms;
+    if (p.sfb_resident) {
+      int groups = sms / p.n_tiles;
+      if (groups > p.m_tiles) groups = p.m_tiles;
+      grid = groups * p.n_tiles;
+    }
   }
   bsgemm_kernel<KIND, EPI><<<grid, NUM_THREADS, kSmemBytes, st>>>(ta, tb, to, tr, p);
   VX_CUDA_OK(cudaGetLastError());
