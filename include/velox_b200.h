@@ -151,6 +151,8 @@ int vx_glu_tile(int fmt);
 
 #define VX_GEMM_DIRECT_STORE 1 /* bypass the shared-memory staged TMA store */
 #define VX_GEMM_STREAM_B 2     /* never keep the B tile resident in shared memory */
+#define VX_GEMM_WIDE_TILES 4   /* FP4: force the 128 x 256 single-accumulator tile */
+#define VX_GEMM_NARROW_TILES 8 /* FP4: force the 128 x 128 double-accumulator tile (not for GLU) */
 
 int vx_bsgemm(const vx_gemm_desc* desc, void* stream);
 

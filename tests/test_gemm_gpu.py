@@ -353,3 +353,29 @@ def test_argmax_epilogue_equals_argmax_of_the_bf16_logits(fmt, M, N, K):
     assert torch.equal(vmax, logits.float().max(dim=1).values)
     # rows whose maximum sits on the duplicated column must report the first copy
     assert not bool(((ids == N // 2) | (ids == N - 1)).any())
+
+
+@pytest.mark.parametrize("fmt", [F.FMT_MX32, F.FMT_NV16, F.FMT_ROWSCALE])
+@pytest.mark.parametrize("M,N,K", [(300, 200, 512), (129, 5538, 512), (1024, 512, 2048), (257, 384, 256)])
+@pytest.mark.parametrize("epi", [G.EPI_NONE, G.EPI_BIAS, G.EPI_BIAS_SWISH, G.EPI_BIAS_RESIDUAL])
+def test_wide_and_narrow_tiles_give_the_same_bytes(ops, fmt, M, N, K, epi):
+    """The 128 x 256 single-accumulator and 128 x 128 double-accumulator FP4 kernels are two
+    schedules of the same arithmetic: outputs must be identical, and equal to the oracle."""
+    torch.manual_seed(21)
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = (0.05 * torch.randn(N, K, device="cuda")).bfloat16()
+    bias = torch.randn(N, device="cuda") if epi != G.EPI_NONE else None
+    res = torch.randn(M, N, device="cuda").bfloat16() if epi == G.EPI_BIAS_RESIDUAL else None
+    a, b = ops.quantize(x, fmt), ops.quantize(w, fmt)
+    outs = [ops.bsgemm(a, b, epilogue=epi, bias=bias, residual=res, alpha=0.5, out_dtype=torch.float32, tiles=t)
+            for t in ("wide", "narrow", None)]
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    ref = G.epilogue_ref(ref_from_q(fmt, a, b), epi, None if bias is None else bias.cpu().numpy(),
+                         None if res is None else res.float().cpu().numpy(), 0.5)
+    assert rel_err(outs[1].cpu().numpy(), ref) < REL_TOL
+    if fmt != F.FMT_ROWSCALE and N % 128 == 0 and epi in (G.EPI_NONE, G.EPI_BIAS, G.EPI_BIAS_SWISH):
+        am = torch.tensor([8.0], device="cuda") if fmt == F.FMT_NV16 else None
+        qs = [ops.bsgemm(a, b, epilogue=epi, bias=bias, out_fmt=fmt, out_amax=am, out_natural=True, tiles=t)
+              for t in ("wide", "narrow")]
+        assert torch.equal(qs[0].codes, qs[1].codes) and torch.equal(qs[0].sf, qs[1].sf)
+        assert torch.equal(qs[0].scales, qs[1].scales)

@@ -26,6 +26,8 @@ DT_F32, DT_BF16, DT_FP4 = 0, 1, 2
 EPI_NONE, EPI_BIAS, EPI_BIAS_SWISH, EPI_BIAS_GLU, EPI_BIAS_RESIDUAL, EPI_BIAS_ARGMAX = range(6)
 GEMM_DIRECT_STORE = 1
 GEMM_STREAM_B = 2
+GEMM_WIDE_TILES = 4
+GEMM_NARROW_TILES = 8
 
 EXPORTS = (
     "vx_abi_version",

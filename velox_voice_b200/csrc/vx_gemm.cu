@@ -59,9 +59,15 @@ constexpr int FP8_SB_BYTES_PER_KB = 16 * 32 * 4;  // epilogue tables of B scales
 // tensor-memory columns
 constexpr int TM_ACC0 = 0, TM_SFA = 256, TM_SFB = 320, TM_COLS = 512;  // SFA: 2 x 32, SFB: up to 128 columns
 
-enum Kind { KIND_FP4_VEC2 = 0, KIND_FP4_VEC4 = 1, KIND_FP8 = 2 };
+// FP4 kinds come in two tile shapes: 128 x 256 with one accumulator (fewest MMA instructions
+// and least operand traffic per output) and 128 x 128 with two accumulators (the epilogue of
+// tile i overlaps the MMAs of tile i + 1; best when K is short and B stays in shared memory).
+enum Kind { KIND_FP4_VEC2 = 0, KIND_FP4_VEC4 = 1, KIND_FP8 = 2, KIND_FP4_VEC2_N128 = 3, KIND_FP4_VEC4_N128 = 4 };
 // rows of B per tile = accumulator columns
-__host__ __device__ constexpr int kind_bn(int kind) { return kind == KIND_FP8 ? 128 : 256; }
+__host__ __device__ constexpr int kind_bn(int kind) {
+  return (kind == KIND_FP4_VEC2 || kind == KIND_FP4_VEC4) ? 256 : 128;
+}
+__host__ __device__ constexpr bool kind_vec4(int kind) { return kind == KIND_FP4_VEC4 || kind == KIND_FP4_VEC4_N128; }
 
 struct GemmParams {
   int64_t M, N, K;
@@ -332,13 +338,13 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   SmemLayout& sm = *reinterpret_cast<SmemLayout*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   constexpr bool FP8 = (KIND == KIND_FP8);
-  constexpr int VEC = (KIND == KIND_FP4_VEC4) ? 4 : 2;
-  constexpr int APS = (KIND == KIND_FP4_VEC4) ? 4 : 2;  // SF atoms per 128 rows per stage
+  constexpr int VEC = kind_vec4(KIND) ? 4 : 2;
+  constexpr int APS = kind_vec4(KIND) ? 4 : 2;  // SF atoms per 128 rows per stage
   constexpr bool GLU = (EPI == VX_EPI_BIAS_GLU);
   // FP4: one 128 x 256 accumulator (a single N = 256 MMA does twice the work per issued
   // instruction; the accumulator is drained into registers within ~200 cycles, so a second
   // buffer would buy little).  FP8: 128 x 128, a ring of four, one per 128-wide K block in flight.
-  constexpr bool WIDE = !FP8;
+  constexpr bool WIDE = kind_bn(KIND) == 256;
   constexpr int BNT = kind_bn(KIND);         // accumulator columns = B rows per tile
   constexpr int NRT = BNT / 128;             // 128-row scale-factor tiles of B per tile
   constexpr int SFB_COLS = 4 * NRT;          // TMEM columns of one K atom of B scale factors
@@ -620,14 +626,16 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         uint32_t sfsel = 0;  // which half of the scale-factor columns this group uses
         for (int i = 0; i < my_tiles && ok; ++i) {
           for (int kg = 0; kg < k_groups; ++kg) {
+            const uint32_t acc = WIDE ? 0u : (group & 1);
             if (kg == 0) {
-              if (!mbar_wait_spin(&sm.tmem_empty[0], (group & 1) ^ 1, p.status, 2)) { ok = false; break; }
+              const uint32_t use = WIDE ? group : (group >> 1);
+              if (!mbar_wait_spin(&sm.tmem_empty[acc], (use & 1) ^ 1, p.status, 2)) { ok = false; break; }
               tc_fence_after();  // orders the epilogue's tcgen05.ld of this buffer before the MMAs
               TRACE(i, 0);
             }
             if (!mbar_wait_spin(&sm.full[s], ph, p.status, 3)) { ok = false; break; }
             TRACE(i, kg < 2 ? 1 + kg : 2);
-            const uint32_t d_tmem = tmem_base + TM_ACC0;
+            const uint32_t d_tmem = tmem_base + TM_ACC0 + acc * 128;
             const uint32_t a_lo0 = ring_lo + s * G * slot_lo;
             // (Issuing the next tile's scale-factor copies ahead of this wait was tried: the
             // tcgen05.commit that publishes the accumulator then fires ~1400 cycles later.)
@@ -664,7 +672,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             COMMIT(&sm.empty[s]);  // ring slots reusable once these MMAs have read them
             if (kg == 0) TRACE(i, 5);
             if (kg == k_groups - 1) {
-              COMMIT(&sm.tmem_full[0]);
+              COMMIT(&sm.tmem_full[acc]);
               ++group;
               TRACE(i, 6);
             }
@@ -834,7 +842,9 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       } else {
         if (tr) trace_rec(p, 2, it, 0);
         // one polling lane per warp (512 polling threads would starve the MMA-issuing thread)
-        if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[0], group & 1, p.status, 4);
+        const uint32_t acc = WIDE ? 0u : (group & 1);
+        const uint32_t acc_addr = lane_addr + TM_ACC0 + acc * 128 + col_base;
+        if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[acc], (WIDE ? group : (group >> 1)) & 1, p.status, 4);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
         tc_fence_after();
@@ -843,13 +853,13 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
           uint32_t r[32];
 #pragma unroll
           for (int h = 0; h < (SEQ ? 1 : NCH); ++h) {
-            tc_ld_32x32b_x32(lane_addr + TM_ACC0 + col_base + h * 32, r);
+            tc_ld_32x32b_x32(acc_addr + h * 32, r);
             tc_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i) z[h][i] = __uint_as_float(r[i]);
           }
           if constexpr (GLU) {
-            tc_ld_32x32b_x32(lane_addr + TM_ACC0 + GATE_OFF + col_base, r);
+            tc_ld_32x32b_x32(acc_addr + GATE_OFF, r);
             tc_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i) gate[i] = __uint_as_float(r[i]);
@@ -860,7 +870,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
           // the accumulator is in registers: hand tensor memory back to the MMA warp
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&sm.tmem_empty[0]);
+          if (lane == 0) mbar_arrive(&sm.tmem_empty[acc]);
         }
         ++group;
       }
@@ -1166,7 +1176,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, 
   }
   // shared-memory plan: keep B resident when all of its K stages fit beside a useful ring
   constexpr int BNT = kind_bn(KIND);
-  constexpr int APS = KIND == KIND_FP4_VEC4 ? 4 : 2;
+  constexpr int APS = kind_vec4(KIND) ? 4 : 2;
   const bool with_sf = KIND != KIND_FP8 && !p.sf_unit;
   p.a_slot_bytes = TILE_BYTES + (with_sf ? APS * 512 : 0);
   p.b_slot_bytes = BNT * STAGE_ROW_BYTES + (with_sf ? (BNT / 128) * APS * 512 : 0);
@@ -1274,7 +1284,24 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
   if (d->out_dtype != VX_F32 && d->out_dtype != VX_BF16 && d->out_dtype != VX_FP4)
     return fail(-1, "unknown out_dtype %d", d->out_dtype);
   if (d->bias && (reinterpret_cast<uintptr_t>(d->bias) & 15)) return fail(-1, "bias must be 16-byte aligned");
-  const int kind = fp8 ? KIND_FP8 : ((fmt == VX_FMT_ROWSCALE || fmt == VX_FMT_MX32) ? KIND_FP4_VEC2 : KIND_FP4_VEC4);
+  const bool vec2 = fmt == VX_FMT_ROWSCALE || fmt == VX_FMT_MX32;
+  int kind = fp8 ? KIND_FP8 : (vec2 ? KIND_FP4_VEC2 : KIND_FP4_VEC4);
+  if (!fp8) {
+    // Two 128-wide accumulators overlap the epilogue of one tile with the MMAs of the next.
+    // Measured at M = 90000, K = 512: that wins for the residual epilogue (N = 512: 52 vs
+    // 57 us) and loses where the output is wide (N = 1536: 83 vs 78 us; N = 5538 argmax: 388 vs
+    // 327 us), because every 128-wide column block re-reads A.  It also wins whenever the
+    // wide tiling would leave SMs without a tile.  Swish (bound by its own epilogue
+    // arithmetic) and GLU (weights interleaved per 256 rows) stay on the wide tile, and so
+    // does a long K, where the wide tile halves the re-reads of A.
+    const int64_t stages = (K / 2 + STAGE_ROW_BYTES - 1) / STAGE_ROW_BYTES;
+    const int64_t wide_tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
+    bool narrow = stages <= 2 && epi != VX_EPI_BIAS_SWISH && epi != VX_EPI_BIAS_GLU &&
+                  (epi == VX_EPI_BIAS_RESIDUAL || wide_tiles < 148);
+    if (d->flags & VX_GEMM_WIDE_TILES) narrow = false;
+    if ((d->flags & VX_GEMM_NARROW_TILES) && epi != VX_EPI_BIAS_GLU) narrow = true;
+    if (narrow) kind = vec2 ? KIND_FP4_VEC2_N128 : KIND_FP4_VEC4_N128;
+  }
   const int BN = kind_bn(kind);
   if (epi == VX_EPI_BIAS_GLU && (N % BN != 0))
     return fail(-1, "GLU needs N %% %d == 0 (value / gate halves interleaved per tile, see vx_glu_tile)", BN);
@@ -1366,8 +1393,12 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
   p.dbg = (d->flags >> 8) & 0xff;
   p.trace = g_trace_buffer;
   if (fp8) return dispatch_epi<KIND_FP8>(epi, ta, tb, to, tr, p, res, st);
-  if (fmt == VX_FMT_ROWSCALE || fmt == VX_FMT_MX32) return dispatch_epi<KIND_FP4_VEC2>(epi, ta, tb, to, tr, p, res, st);
-  return dispatch_epi<KIND_FP4_VEC4>(epi, ta, tb, to, tr, p, res, st);
+  switch (kind) {
+    case KIND_FP4_VEC2: return dispatch_epi<KIND_FP4_VEC2>(epi, ta, tb, to, tr, p, res, st);
+    case KIND_FP4_VEC4: return dispatch_epi<KIND_FP4_VEC4>(epi, ta, tb, to, tr, p, res, st);
+    case KIND_FP4_VEC2_N128: return dispatch_epi<KIND_FP4_VEC2_N128>(epi, ta, tb, to, tr, p, res, st);
+    default: return dispatch_epi<KIND_FP4_VEC4_N128>(epi, ta, tb, to, tr, p, res, st);
+  }
 }
 
 int vx_argmax_ids(const void* keys, int64_t M, int32_t* ids, float* max_out, void* stream) {

@@ -41,7 +41,9 @@ from ._lib import (  # noqa: F401  (re-exported)
     FMT_NV16,
     FMT_ROWSCALE,
     GEMM_DIRECT_STORE,
+    GEMM_NARROW_TILES,
     GEMM_STREAM_B,
+    GEMM_WIDE_TILES,
 )
 
 _SF_FORMATS = (FMT_BLK16_A, FMT_BLK16_B, FMT_MX32, FMT_NV16)
@@ -306,6 +308,7 @@ def bsgemm(
     out_natural: bool = False,
     direct_store: bool = False,
     stream_b: bool = False,
+    tiles: Optional[str] = None,
     _dbg: int = 0,
 ):
     """``epilogue(A . B^T)``; A [M,K], B [N,K] quantized in the same format family.
@@ -313,6 +316,8 @@ def bsgemm(
     ``out_fmt`` (MX32 or NV16) re-quantizes the result in the epilogue and returns a
     :class:`Quantized` ready to be the A operand of the next GEMM; otherwise a tensor of
     ``out_dtype`` (float32 / bfloat16) [M, N] ([M, N/2] for the GLU epilogue) is returned.
+    ``tiles`` overrides the FP4 tile shape the library would pick ("wide" 128 x 256, one
+    accumulator; "narrow" 128 x 128, two accumulators); results do not depend on it.
     """
     fa, fb = a.fmt, b.fmt
     if fa == FMT_BLK16_A:
@@ -347,7 +352,10 @@ def bsgemm(
         residual = _rows2d(residual, "residual")
         d.residual, d.residual_dtype, d.ldr = residual.data_ptr(), _dt(residual, "residual"), residual.stride(0)
         d.alpha = float(alpha)
-    d.flags = (GEMM_DIRECT_STORE if direct_store else 0) | (GEMM_STREAM_B if stream_b else 0) | (_dbg << 8)
+    if tiles not in (None, "wide", "narrow"):
+        raise ValueError("tiles must be None, 'wide' or 'narrow'")
+    d.flags = ((GEMM_DIRECT_STORE if direct_store else 0) | (GEMM_STREAM_B if stream_b else 0)
+               | (GEMM_WIDE_TILES if tiles == "wide" else 0) | (GEMM_NARROW_TILES if tiles == "narrow" else 0) | (_dbg << 8))
     result = None
     if out_fmt is not None:
         ofmt = _fmt(out_fmt)
