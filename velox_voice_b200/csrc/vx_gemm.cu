@@ -162,7 +162,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 // Epilogue of one 32-column chunk held in registers by one thread (one output row).
 //   z[i]  accumulator value of logical column `ncol0 + i` (after scales)
 //   For GLU the caller passes value and gate chunks and `ncol0` in OUTPUT columns.
-template <int EPI>
+template <int EPI, bool RES_TMA>
 struct ChunkOut {
   // Applies bias / activation / residual in place.  `bias_s` / `gate_s`: 32 bias values of the
   // chunk (and of its GLU gate chunk) in shared memory, or nullptr; `out_col0`: output column.
@@ -194,7 +194,7 @@ struct ChunkOut {
 #pragma unroll
       for (int i = 0; i < 32; ++i) z[i] *= sigmoid_f(gate[i]);
     } else if constexpr (EPI == VX_EPI_BIAS_RESIDUAL) {
-      if (res_smem) {
+      if (RES_TMA || res_smem) {
         // bf16 block staged by TMA: 64-byte rows, 16-byte slots swizzled by (row >> 1) & 3
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
@@ -273,12 +273,12 @@ __device__ __forceinline__ void store_chunk_direct(const GemmParams& p, const fl
 // Re-quantize one 32-column chunk of an output row to E2M1 (MX32: one UE8M0 scale; NV16: two
 // E4M3 scales) -- the same arithmetic as the stand-alone quantizer.  Returns the scale bytes
 // (1 or 2, little end first) for the caller to assemble into SF words.
-__device__ __forceinline__ uint32_t store_chunk_fp4(const GemmParams& p, const float (&z)[32],
+__device__ __forceinline__ uint32_t store_chunk_fp4(const GemmParams& p, const int out_fmt, const float (&z)[32],
                                                     int64_t row, int64_t col0, float g_out,
                                                     bool row_ok) {
   uint32_t w[4];
   uint32_t sbytes;
-  if (p.out_fmt == VX_FMT_MX32) {
+  if (out_fmt == VX_FMT_MX32) {
     float a = fabsf(z[0]);
 #pragma unroll
     for (int i = 1; i < 32; ++i) a = fmaxf(a, fabsf(z[i]));
@@ -329,7 +329,12 @@ __device__ __forceinline__ void trace_rec(const GemmParams& p, int role, int til
 unsigned long long* g_trace_buffer = nullptr;
 
 // ---------------------------------------------------------------------------------------
-template <int KIND, int EPI>
+// OUT fixes the output route at compile time, which prunes the other routes from the kernel:
+//   0  chosen at run time (fp32 / bf16 / FP4, TMA or direct stores, per-row-scaled format);
+//   1  bf16 through staged TMA stores, residual (if any) prefetched by TMA;
+//   2  FP4 re-quantized in the operands' own block format (MX32 for the 32-block kinds, NV16
+//      for the 16-block kinds).
+template <int KIND, int EPI, int OUT>
 __global__ void VX_GEMM_BOUNDS
 bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
               const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_res,
@@ -355,11 +360,18 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   // is finished (half the live registers), which releases tensor memory later at no cost.
   constexpr bool SEQ = (EPI == VX_EPI_BIAS_SWISH) && NCH == 2;
 
+  const int out_dtype = OUT == 1 ? static_cast<int>(VX_BF16) : (OUT == 2 ? static_cast<int>(VX_FP4) : p.out_dtype);
+  const bool tma_store = OUT == 1 ? true : (OUT == 2 ? false : p.tma_store != 0);
+  const bool tma_residual = OUT == 1 ? EPI == VX_EPI_BIAS_RESIDUAL : (OUT == 2 ? false : p.tma_residual != 0);
+  const bool sf_unit = OUT != 0 ? false : p.sf_unit != 0;
+  const int out_fmt = OUT == 2 ? static_cast<int>(kind_vec4(KIND) ? VX_FMT_NV16 : VX_FMT_MX32) : p.out_fmt;
+  const int dbg = OUT == 0 ? p.dbg : 0;
+
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int nslots = p.num_slots;
   const bool resident = p.b_resident != 0;
-  const bool with_sf = !(FP8 || p.sf_unit);
+  const bool with_sf = !(FP8 || sf_unit);
   const bool sfb_res = p.sfb_resident != 0;   // implies !resident && with_sf
   const bool owns_nb = resident || sfb_res;   // fixed n-block, B scale factors stay in TMEM
 
@@ -409,8 +421,8 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     mbar_fence_init();
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
-    if (p.tma_store) prefetch_tmap(&tmap_out);
-    if (p.tma_residual) prefetch_tmap(&tmap_res);
+    if (tma_store) prefetch_tmap(&tmap_out);
+    if (tma_residual) prefetch_tmap(&tmap_res);
   }
   {
     // Scale-factor tiles of B that lie beyond N are never loaded; they must read as zero
@@ -419,7 +431,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     for (int i = threadIdx.x; i < ARENA_BYTES / 16; i += NUM_THREADS) a4[i] = make_uint4(0, 0, 0, 0);
   }
   uint8_t* unit_sf = sm.staging[0];  // rowscale only: one atom of 0x7F, copied to TMEM before any tile
-  if (!FP8 && p.sf_unit) {
+  if (!FP8 && sf_unit) {
     uint32_t* u = reinterpret_cast<uint32_t*>(unit_sf);
     for (int i = threadIdx.x; i < 512 / 4; i += NUM_THREADS) u[i] = 0x7F7F7F7Fu;
   }
@@ -539,7 +551,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         uint32_t atom, sf_id;
-        if (FP8 || p.sf_unit) { atom = 0; sf_id = 0; }
+        if (FP8 || sf_unit) { atom = 0; sf_id = 0; }
         else if (VEC == 2) { atom = j >> 1; sf_id = (j & 1) * 2; }
         else { atom = j; sf_id = 0; }
         idesc_j[j] = idesc_with_sf_id(idesc_base, sf_id, sf_id);
@@ -547,7 +559,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         sfb_col_j[j] = atom * SFB_COLS;
       }
       const uint32_t tm_sfa = tmem_base + TM_SFA, tm_sfb = tmem_base + TM_SFB;
-      if (!FP8 && p.sf_unit) {
+      if (!FP8 && sf_unit) {
         const uint64_t d = make_desc_sf(smem_u32(unit_sf));
         CP(tm_sfa, d);
 #pragma unroll
@@ -662,7 +674,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                 const uint32_t sfb_t = with_sf ? sfb_buf + (owns_nb ? ks : u) * APS * SFB_COLS : tm_sfb;
   #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                  if (p.dbg & 2) break;
+                  if (dbg & 2) break;
                   if (leader) mma_mxf4<VEC>(d_tmem, desc(a_lo + 2 * j, k128_hi), desc(b_lo + 2 * j, k128_hi), idesc_j[j],
                                 sfa_t + sfa_col_j[j], sfb_t + sfb_col_j[j], (ks | j) != 0);
                 }
@@ -704,7 +716,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     uint8_t* const stage0 = sm.staging[ew];
     uint8_t* const res_buf = stage0 + STAGING_BYTES / 2;  // residual block (second half)
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-    const bool dbuf = p.out_dtype == VX_BF16 && !p.tma_residual;  // bf16 boxes alternate the two halves
+    const bool dbuf = out_dtype == VX_BF16 && !tma_residual;  // bf16 boxes alternate the two halves
     uint32_t store_count = 0;
     uint32_t res_phase = 0;
     int bias_nb = -1;
@@ -729,7 +741,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     const int col_base = WIDE ? (GLU ? cc * 32 : cc * 64) : cc * 32;  // first accumulator column of this warp
     bool res_inflight = false;
     if constexpr (EPI == VX_EPI_BIAS_RESIDUAL) {
-      if (p.tma_residual && my_tiles > 0 && has_work) {
+      if (tma_residual && my_tiles > 0 && has_work) {
         res_issue(mb, static_cast<int64_t>(nb) * OUT_TILE_COLS + col_base);
         res_inflight = true;
       }
@@ -896,14 +908,14 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
           const int64_t out_col0 = static_cast<int64_t>(nb) * OUT_TILE_COLS + col_base + h * 32;  // output column
           const bool box_ok = rows_ok && out_col0 < n_out;
           if constexpr (!FP8) {
-            if (p.sf_unit) {
+            if (sf_unit) {
               // reference order: raw * row_scale * col_scale
               const float row_scale = row_ok ? ue8m0_to_float(__ldg(p.row_scale_u8 + row)) : 0.0f;
               const int64_t ncol = acc_col0 + lane;
               const float csv = ncol < p.N ? ue8m0_to_float(__ldg(p.col_scale_u8 + ncol)) : 0.0f;
 #pragma unroll
               for (int i = 0; i < 32; ++i) z[h][i] = z[h][i] * row_scale * __shfl_sync(0xffffffffu, csv, i);
-            } else if (p.a_amax) {
+            } else if (kind_vec4(KIND) && p.a_amax) {
 #pragma unroll
               for (int i = 0; i < 32; ++i) z[h][i] *= g_ab;
               if constexpr (GLU) {
@@ -919,7 +931,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             res_smem = res_buf;
           }
           if (tr && h == 0 && !FP8) trace_rec(p, 2, it, 3);
-          ChunkOut<EPI>::apply(p, z[h], gate, row, bias_base ? bias_base + h * 32 : nullptr, bias_base + 32, out_col0,
+          ChunkOut<EPI, OUT == 1>::apply(p, z[h], gate, row, bias_base ? bias_base + h * 32 : nullptr, bias_base + 32, out_col0,
                                row_ok, res_smem, lane);
           if (tr && h == 0 && !FP8) trace_rec(p, 2, it, 4);
           if constexpr (EPI == VX_EPI_BIAS_RESIDUAL) {
@@ -952,12 +964,12 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
               }
               best_key = max(best_key, max(k0, k1));
             }
-          } else if (p.out_dtype == VX_FP4) {
-            const uint32_t sb = store_chunk_fp4(p, z[h], row, out_col0, g_out, row_ok && out_col0 < n_out);
+          } else if (out_dtype == VX_FP4) {
+            const uint32_t sb = store_chunk_fp4(p, out_fmt, z[h], row, out_col0, g_out, row_ok && out_col0 < n_out);
             if (row_ok && out_col0 < n_out) {
               // this chunk's scale byte(s) inside the row's SF word(s)
               const int64_t sf_row = (row >> 7) * p.out_sf_kg * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4;
-              if (p.out_fmt == VX_FMT_MX32) {
+              if (out_fmt == VX_FMT_MX32) {
                 p.out_sf[sf_row + (out_col0 >> 7) * 512 + ((out_col0 >> 5) & 3)] = static_cast<uint8_t>(sb);
                 if (p.out_scales) p.out_scales[row * (n_out >> 5) + (out_col0 >> 5)] = static_cast<uint8_t>(sb);
               } else {
@@ -968,9 +980,9 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                       static_cast<uint16_t>(sb);
               }
             }
-          } else if (p.dbg & 1) {
+          } else if (dbg & 1) {
             if (z[h][0] == 123.456f && row_ok) static_cast<float*>(p.out)[0] = z[h][1];  // keep z live
-          } else if (p.tma_store) {
+          } else if (tma_store) {
             // stage 32 rows x 32 columns (swizzled like the tensor map), then one TMA store
             uint8_t* buf = stage0;
             if (dbuf) {
@@ -981,7 +993,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             }
             ++store_count;
             __syncwarp();
-            if (p.out_dtype == VX_BF16) {
+            if (out_dtype == VX_BF16) {
               // 64-byte rows, 64-byte swizzle: 16-byte slot index ^= (row >> 1) & 3
 #pragma unroll
               for (int v = 0; v < 4; ++v) {
@@ -1024,7 +1036,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       mb = mb_next;
       nb = nb_next;
     }
-    if (p.tma_store && lane == 0) tma_store_wait_all<0>();
+    if (tma_store && lane == 0) tma_store_wait_all<0>();
     if (!ok) sm.abort_flag = 1;
   }
 
@@ -1156,13 +1168,13 @@ int* cached_status_ptr() {
 
 constexpr size_t kSmemBytes = sizeof(SmemLayout) + 1024;
 
-template <int KIND, int EPI>
+template <int KIND, int EPI, int OUT>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const CUtensorMap& tr,
            GemmParams& p, bool allow_resident, cudaStream_t st) {
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(bsgemm_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    attr_err = cudaFuncSetAttribute(bsgemm_kernel<KIND, EPI, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     static_cast<int>(kSmemBytes));
   });
   if (attr_err != cudaSuccess) return fail(static_cast<int>(attr_err), "cudaFuncSetAttribute: %s", cudaGetErrorString(attr_err));
@@ -1228,21 +1240,34 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, 
       grid = groups * p.n_tiles;
     }
   }
-  bsgemm_kernel<KIND, EPI><<<grid, NUM_THREADS, kSmemBytes, st>>>(ta, tb, to, tr, p);
+  bsgemm_kernel<KIND, EPI, OUT><<<grid, NUM_THREADS, kSmemBytes, st>>>(ta, tb, to, tr, p);
   VX_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
+template <int KIND, int EPI>
+int dispatch_out(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to,
+                 const CUtensorMap& tr, GemmParams& p, bool res, cudaStream_t st) {
+  constexpr bool fp4_out_ok = KIND != KIND_FP8 && (EPI == VX_EPI_NONE || EPI == VX_EPI_BIAS || EPI == VX_EPI_BIAS_SWISH);
+  if constexpr (EPI != VX_EPI_BIAS_ARGMAX) {
+    if (out == 1) return launch<KIND, EPI, 1>(ta, tb, to, tr, p, res, st);
+    if constexpr (fp4_out_ok) {
+      if (out == 2) return launch<KIND, EPI, 2>(ta, tb, to, tr, p, res, st);
+    }
+  }
+  return launch<KIND, EPI, 0>(ta, tb, to, tr, p, res, st);
+}
+
 template <int KIND>
-int dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to,
+int dispatch_epi(int epi, int out, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to,
                  const CUtensorMap& tr, GemmParams& p, bool res, cudaStream_t st) {
   switch (epi) {
-    case VX_EPI_NONE: return launch<KIND, VX_EPI_NONE>(ta, tb, to, tr, p, res, st);
-    case VX_EPI_BIAS: return launch<KIND, VX_EPI_BIAS>(ta, tb, to, tr, p, res, st);
-    case VX_EPI_BIAS_SWISH: return launch<KIND, VX_EPI_BIAS_SWISH>(ta, tb, to, tr, p, res, st);
-    case VX_EPI_BIAS_GLU: return launch<KIND, VX_EPI_BIAS_GLU>(ta, tb, to, tr, p, res, st);
-    case VX_EPI_BIAS_RESIDUAL: return launch<KIND, VX_EPI_BIAS_RESIDUAL>(ta, tb, to, tr, p, res, st);
-    case VX_EPI_BIAS_ARGMAX: return launch<KIND, VX_EPI_BIAS_ARGMAX>(ta, tb, to, tr, p, res, st);
+    case VX_EPI_NONE: return dispatch_out<KIND, VX_EPI_NONE>(out, ta, tb, to, tr, p, res, st);
+    case VX_EPI_BIAS: return dispatch_out<KIND, VX_EPI_BIAS>(out, ta, tb, to, tr, p, res, st);
+    case VX_EPI_BIAS_SWISH: return dispatch_out<KIND, VX_EPI_BIAS_SWISH>(out, ta, tb, to, tr, p, res, st);
+    case VX_EPI_BIAS_GLU: return dispatch_out<KIND, VX_EPI_BIAS_GLU>(out, ta, tb, to, tr, p, res, st);
+    case VX_EPI_BIAS_RESIDUAL: return dispatch_out<KIND, VX_EPI_BIAS_RESIDUAL>(out, ta, tb, to, tr, p, res, st);
+    case VX_EPI_BIAS_ARGMAX: return dispatch_out<KIND, VX_EPI_BIAS_ARGMAX>(out, ta, tb, to, tr, p, res, st);
     default: return fail(-1, "unknown epilogue %d", epi);
   }
 }
@@ -1392,12 +1417,20 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
   const bool res = !(d->flags & VX_GEMM_STREAM_B);
   p.dbg = (d->flags >> 8) & 0xff;
   p.trace = g_trace_buffer;
-  if (fp8) return dispatch_epi<KIND_FP8>(epi, ta, tb, to, tr, p, res, st);
+  // compile-time output route (see bsgemm_kernel): 1 and 2 cover the encoder's launches
+  int out_route = 0;
+  if (!p.dbg && !p.sf_unit) {
+    if (d->out_dtype == VX_BF16 && p.tma_store && (epi != VX_EPI_BIAS_RESIDUAL || p.tma_residual) && !argmax)
+      out_route = 1;
+    else if (d->out_dtype == VX_FP4 && !argmax && d->out_fmt == (vec2 ? VX_FMT_MX32 : VX_FMT_NV16))
+      out_route = 2;
+  }
   switch (kind) {
-    case KIND_FP4_VEC2: return dispatch_epi<KIND_FP4_VEC2>(epi, ta, tb, to, tr, p, res, st);
-    case KIND_FP4_VEC4: return dispatch_epi<KIND_FP4_VEC4>(epi, ta, tb, to, tr, p, res, st);
-    case KIND_FP4_VEC2_N128: return dispatch_epi<KIND_FP4_VEC2_N128>(epi, ta, tb, to, tr, p, res, st);
-    default: return dispatch_epi<KIND_FP4_VEC4_N128>(epi, ta, tb, to, tr, p, res, st);
+    case KIND_FP8: return dispatch_epi<KIND_FP8>(epi, out_route, ta, tb, to, tr, p, res, st);
+    case KIND_FP4_VEC2: return dispatch_epi<KIND_FP4_VEC2>(epi, out_route, ta, tb, to, tr, p, res, st);
+    case KIND_FP4_VEC4: return dispatch_epi<KIND_FP4_VEC4>(epi, out_route, ta, tb, to, tr, p, res, st);
+    case KIND_FP4_VEC2_N128: return dispatch_epi<KIND_FP4_VEC2_N128>(epi, out_route, ta, tb, to, tr, p, res, st);
+    default: return dispatch_epi<KIND_FP4_VEC4_N128>(epi, out_route, ta, tb, to, tr, p, res, st);
   }
 }
 
