@@ -366,6 +366,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   const bool sf_unit = OUT != 0 ? false : p.sf_unit != 0;
   const int out_fmt = OUT == 2 ? static_cast<int>(kind_vec4(KIND) ? VX_FMT_NV16 : VX_FMT_MX32) : p.out_fmt;
   const int dbg = OUT == 0 ? p.dbg : 0;
+  const bool tr_on = p.trace != nullptr && blockIdx.x == 0;  // phase trace requested (CTA 0 only)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -503,7 +504,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             if (!mbar_wait(&sm.sfb_done, 0, p.status, 7)) { ok = false; break; }
             sfb_pending = false;
           }
-          trace_rec(p, 0, i, kg < 4 ? kg : 3);
+          if (tr_on) trace_rec(p, 0, i, kg < 4 ? kg : 3);
           mbar_expect_tx(&sm.full[s], G * slot_tx);
           for (int u = 0; u < G; ++u) {
             const int ks = kg * G + u;
@@ -530,7 +531,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       const bool leader = elect_one();
       auto CP = [&](uint32_t taddr, uint64_t d) { if (leader) tc_cp_32x128b_warpx4(taddr, d); };
       auto COMMIT = [&](uint64_t* bar) { if (leader) tc_commit(bar); };
-      auto TRACE = [&](int tile, int ev) { if (leader) trace_rec(p, 1, tile, ev); };
+      auto TRACE = [&](int tile, int ev) { if (tr_on && leader) trace_rec(p, 1, tile, ev); };
       uint32_t s = 0, ph = 0;
       uint32_t group = 0;  // accumulation groups issued (FP4: one per tile; FP8: one per stage)
       bool ok = true;
@@ -706,7 +707,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     const int64_t n_out = GLU ? p.N / 2 : p.N;    // logical output columns
     constexpr int OUT_TILE_COLS = GLU ? BNT / 2 : BNT;
     const bool has_work = !(GLU && !WIDE) || cc < 2;  // 128-wide GLU: chunks 2, 3 are the gates of 0, 1
-    const bool tr = p.trace != nullptr && blockIdx.x == 0 && ew == 0 && lane == 0;
+    const bool tr = tr_on && ew == 0 && lane == 0;
     uint32_t group = 0;
     bool ok = true;
     float g_ab = 1.0f, g_out = 1.0f;

@@ -63,12 +63,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 // status word layout: 0 = ok; else (code << 24) | (site << 16) | (blockIdx.x & 0xffff)
-// The wall clock (%globaltimer, slow to read) is consulted only after 64 failed polls (each
-// may park the thread for up to 20 us), so a wait that succeeds promptly never touches it.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int site) {
-#pragma unroll 1
-  for (uint32_t spins = 0; spins < 64; ++spins)
-    if (mbar_try_wait(bar, parity)) return true;
+// Slow path of a wait (kept inline: an out-of-line call was measured slower in most kernels): polls against the
+// wall clock (%globaltimer, slow to read) and gives up after kWaitLimitNs.
+__device__ __forceinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int* status, int site) {
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (true) {
@@ -82,10 +79,20 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
   }
 }
 
-// Same contract, plain polling without the suspend hint: for the one MMA-issuing thread, whose
-// reaction time is on the critical path of every tile.
+// Parked wait: each poll may suspend the thread for up to 20 us, so a wait that succeeds
+// within 64 polls never reads the clock.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int site) {
+#pragma unroll 1
+  for (uint32_t spins = 0; spins < 64; ++spins)
+    if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, status, site);
+}
+
+// Same contract, plain polling without the suspend hint: for the MMA-issuing warp and the
+// epilogue's polling lane, whose reaction time is on the critical path of every tile.
 __device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, int* status, int site) {
-  auto poll = [&]() -> bool {
+#pragma unroll 1
+  for (uint32_t spins = 0; spins < 100000; ++spins) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -94,22 +101,9 @@ __device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, i
         : "=r"(ok)
         : "r"(smem_u32(bar)), "r"(parity)
         : "memory");
-    return ok != 0;
-  };
-#pragma unroll 1
-  for (uint32_t spins = 0; spins < 100000; ++spins)
-    if (poll()) return true;
-  const uint64_t t0 = globaltimer_ns();
-  uint32_t spins = 0;
-  while (true) {
-    if (poll()) return true;
-    if ((++spins & 0x3ff) == 0) {
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
-        if (status) atomicCAS(status, 0, (1 << 24) | ((site & 0xff) << 16) | (blockIdx.x & 0xffff));
-        return false;
-      }
-    }
+    if (ok) return true;
   }
+  return mbar_wait_slow(bar, parity, status, site);
 }
 
 // ------------------------------------------------------------------ proxies / fences
