@@ -107,23 +107,27 @@ __device__ __forceinline__ float warp_max(float a) {
   return a;
 }
 
-__device__ __forceinline__ int64_t sf_offset(int64_t row, int64_t kgroup, int64_t sf_kg) {
+template <typename I>
+__device__ __forceinline__ I sf_offset(I row, I kgroup, I sf_kg) {
   return ((row >> 7) * sf_kg + kgroup) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4;
 }
 
 // Quantize one 256-element chunk of RP rows held in registers and store codes + scales.
 // `row_rcp` / `row_byte` are used by ROWSCALE only (the row maximum is known beforehand).
-template <int FMT, int RP>
-__device__ __forceinline__ void quant_chunk(const QuantParams& p, int64_t row0, int c, int lane,
+// I: index type -- 32-bit when every element / byte offset of the call fits (most tensors; half
+// the integer instructions of the 64-bit form), else 64-bit.
+template <int FMT, int RP, typename I>
+__device__ __forceinline__ void quant_chunk(const QuantParams& p, I row0, int c, int lane,
                                             float (&v)[RP][8], float row_rcp, float g) {
-  const int64_t k0 = static_cast<int64_t>(c) * 256 + lane * 8;
-  const bool active = k0 < p.K;
+  const I K = static_cast<I>(p.K), M = static_cast<I>(p.M), ldc = static_cast<I>(p.ldc);
+  const I k0 = static_cast<I>(c) * 256 + lane * 8;
+  const bool active = k0 < K;
   float a = amax8(v[0]);
   if constexpr (RP == 2) a = fmaxf(a, amax8(v[1]));
 
   if constexpr (FMT == VX_FMT_ROWSCALE) {
     if (active) {
-      *reinterpret_cast<uint32_t*>(p.codes + row0 * p.ldc + (k0 >> 1)) = e2m1_pack8<true>(v[0], row_rcp);
+      *reinterpret_cast<uint32_t*>(p.codes + row0 * ldc + (k0 >> 1)) = e2m1_pack8<true>(v[0], row_rcp);
     }
   } else if constexpr (FMT == VX_FMT_FP8_1X128) {
 #pragma unroll
@@ -131,9 +135,9 @@ __device__ __forceinline__ void quant_chunk(const QuantParams& p, int64_t row0, 
     float scale, rcp;
     fp8_block(a, scale, rcp);
     if (active) {
-      *reinterpret_cast<uint2*>(p.codes + row0 * p.ldc + k0) = fp8_pack8(v[0], rcp);
+      *reinterpret_cast<uint2*>(p.codes + row0 * ldc + k0) = fp8_pack8(v[0], rcp);
       if (p.scales && (lane & 15) == 0)
-        static_cast<float*>(p.scales)[row0 * (p.K >> 7) + (k0 >> 7)] = scale;
+        static_cast<float*>(p.scales)[row0 * (K >> 7) + (k0 >> 7)] = scale;
     }
   } else {
     constexpr int BLK = (FMT == VX_FMT_MX32) ? 32 : 16;
@@ -145,17 +149,17 @@ __device__ __forceinline__ void quant_chunk(const QuantParams& p, int64_t row0, 
     if constexpr (FMT == VX_FMT_NV16) nv16_block(a, g, byte, rcp);
     else ue8m0_from_amax(a, byte, rcp);
     if (!active) byte = 0;
-    const int64_t kb = k0 / BLK;  // block index along K
+    const I kb = k0 / BLK;  // block index along K
 #pragma unroll
     for (int r = 0; r < RP; ++r) {
       if (active)
-        *reinterpret_cast<uint32_t*>(p.codes + (row0 + r) * p.ldc + (k0 >> 1)) = e2m1_pack8<FMT != VX_FMT_NV16>(v[r], rcp);
+        *reinterpret_cast<uint32_t*>(p.codes + (row0 + r) * ldc + (k0 >> 1)) = e2m1_pack8<FMT != VX_FMT_NV16>(v[r], rcp);
     }
     if (p.scales && active && (lane % LPB) == 0) {
       uint8_t* s = static_cast<uint8_t*>(p.scales);
-      if constexpr (FMT == VX_FMT_BLK16_A) s[kb * (p.M >> 1) + (row0 >> 1)] = byte;
-      else if constexpr (FMT == VX_FMT_BLK16_B) s[kb * p.M + row0] = byte;
-      else s[row0 * (p.K / BLK) + kb] = byte;
+      if constexpr (FMT == VX_FMT_BLK16_A) s[kb * (M >> 1) + (row0 >> 1)] = byte;
+      else if constexpr (FMT == VX_FMT_BLK16_B) s[kb * M + row0] = byte;
+      else s[row0 * (K / BLK) + kb] = byte;
     }
     if (p.sf) {
       // assemble the 4 scale bytes of one k-group into a word held by every lane of the group
@@ -163,47 +167,47 @@ __device__ __forceinline__ void quant_chunk(const QuantParams& p, int64_t row0, 
 #pragma unroll
       for (int o = LPB; o < 4 * LPB; o <<= 1) w |= __shfl_xor_sync(0xffffffffu, w, o);
       if (active && (lane % (4 * LPB)) == 0) {
-        const int64_t kg = kb >> 2;
+        const I kg = kb >> 2;
 #pragma unroll
         for (int r = 0; r < RP; ++r)
-          *reinterpret_cast<uint32_t*>(p.sf + sf_offset(row0 + r, kg, p.sf_kg)) = w;
+          *reinterpret_cast<uint32_t*>(p.sf + sf_offset<I>(row0 + r, kg, static_cast<I>(p.sf_kg))) = w;
       }
     }
   }
 }
 
 // Streaming quantizer (no LayerNorm): any K % 8 == 0.
-template <typename T, int FMT>
+template <typename T, int FMT, typename I>
 __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) quant_kernel(const QuantParams p) {
   constexpr int RP = (FMT == VX_FMT_BLK16_A) ? 2 : 1;
   const int lane = threadIdx.x & 31;
-  const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
-  const int64_t nunits = p.M / RP;
-  const int nchunks = static_cast<int>((p.K + 255) >> 8);
+  const I warps = static_cast<I>(gridDim.x) * (blockDim.x >> 5);
+  const I nunits = static_cast<I>(p.M) / RP;
+  const int nchunks = static_cast<int>((static_cast<I>(p.K) + 255) >> 8);
   const T* x = static_cast<const T*>(p.x);
   float g = 1.0f;
   if constexpr (FMT == VX_FMT_NV16) g = nv16_global(__ldg(p.amax));
 
   Raw8<T> raw[RP];
-  auto fetch = [&](int64_t u, int c) {
-    const int64_t k0 = static_cast<int64_t>(c) * 256 + lane * 8;
+  auto fetch = [&](I u, int c) {
+    const I k0 = static_cast<I>(c) * 256 + lane * 8;
 #pragma unroll
     for (int r = 0; r < RP; ++r) {
-      if (k0 < p.K) raw[r].load(x + (u * RP + r) * p.ldx + k0);
+      if (k0 < static_cast<I>(p.K)) raw[r].load(x + (u * RP + r) * static_cast<I>(p.ldx) + k0);
       else raw[r].zero();
     }
   };
-  const int64_t u_first = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  for (int64_t u = u_first; u < nunits; u += warps) {
-    const int64_t row0 = u * RP;
+  const I u_first = static_cast<I>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  for (I u = u_first; u < nunits; u += warps) {
+    const I row0 = u * RP;
     float row_rcp = 0.0f;
     if constexpr (FMT == VX_FMT_ROWSCALE) {
       float a = 0.0f;
       for (int c = 0; c < nchunks; ++c) {
-        const int64_t k0 = static_cast<int64_t>(c) * 256 + lane * 8;
-        if (k0 < p.K) {
+        const I k0 = static_cast<I>(c) * 256 + lane * 8;
+        if (k0 < static_cast<I>(p.K)) {
           float t[8];
-          load8(x + row0 * p.ldx + k0, t);
+          load8(x + row0 * static_cast<I>(p.ldx) + k0, t);
           a = fmaxf(a, amax8(t));
         }
       }
@@ -220,7 +224,7 @@ __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) quant_kernel(const Q
       for (int r = 0; r < RP; ++r) raw[r].get(v[r]);
       if (c + 1 < nchunks) fetch(u, c + 1);
       else if (u + warps < nunits && FMT != VX_FMT_ROWSCALE) fetch(u + warps, 0);
-      quant_chunk<FMT, RP>(p, row0, c, lane, v, row_rcp, g);
+      quant_chunk<FMT, RP, I>(p, row0, c, lane, v, row_rcp, g);
     }
   }
 }
@@ -231,12 +235,12 @@ __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) quant_kernel(const Q
 // with every operation individually rounded (no FMA contraction), rstd = 1 / sqrt(var + eps)
 // correctly rounded, lane-sequential partial sums and a butterfly (xor 16, 8, 4, 2, 1) warp
 // reduction -- an order a CPU restatement can follow exactly.
-template <typename T, int FMT, int CH>
+template <typename T, int FMT, int CH, typename I>
 __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) ln_quant_kernel(const QuantParams p) {
   constexpr int RP = (FMT == VX_FMT_BLK16_A) ? 2 : 1;
   const int lane = threadIdx.x & 31;
-  const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
-  const int64_t nunits = p.M / RP;
+  const I warps = static_cast<I>(gridDim.x) * (blockDim.x >> 5);
+  const I nunits = static_cast<I>(p.M) / RP;
   const T* x = static_cast<const T*>(p.x);
   const float k_f = static_cast<float>(p.K);
   const int npass = p.gamma2 ? 2 : 1;
@@ -245,20 +249,20 @@ __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) ln_quant_kernel(cons
 
   // the row(s) of unit u, as loaded; issued one iteration ahead of their use
   Raw8<T> raw[CH][RP];
-  auto fetch = [&](int64_t u) {
+  auto fetch = [&](I u) {
 #pragma unroll
     for (int r = 0; r < RP; ++r)
 #pragma unroll
       for (int c = 0; c < CH; ++c) {
-        const int64_t k0 = static_cast<int64_t>(c) * 256 + lane * 8;
-        if (k0 < p.K) raw[c][r].load(x + (u * RP + r) * p.ldx + k0);
+        const I k0 = static_cast<I>(c) * 256 + lane * 8;
+        if (k0 < static_cast<I>(p.K)) raw[c][r].load(x + (u * RP + r) * static_cast<I>(p.ldx) + k0);
         else raw[c][r].zero();
       }
   };
-  const int64_t u_first = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const I u_first = static_cast<I>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (u_first < nunits) fetch(u_first);
-  for (int64_t u = u_first; u < nunits; u += warps) {
-    const int64_t row0 = u * RP;
+  for (I u = u_first; u < nunits; u += warps) {
+    const I row0 = u * RP;
     float v[CH][RP][8];
 #pragma unroll
     for (int r = 0; r < RP; ++r)
@@ -291,8 +295,8 @@ __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) ln_quant_kernel(cons
       const float rstd = __frcp_rn(__fsqrt_rn(__fadd_rn(var, p.eps)));
 #pragma unroll
       for (int c = 0; c < CH; ++c) {
-        const int64_t k0 = static_cast<int64_t>(c) * 256 + lane * 8;
-        if (k0 < p.K) {
+        const I k0 = static_cast<I>(c) * 256 + lane * 8;
+        if (k0 < static_cast<I>(p.K)) {
           float ga[8], be[8];
           load8(ga_p + k0, ga);
           load8(be_p + k0, be);
@@ -307,7 +311,7 @@ __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) ln_quant_kernel(cons
               u.y = pack2_bf16(v[c][r][2], v[c][r][3]);
               u.z = pack2_bf16(v[c][r][4], v[c][r][5]);
               u.w = pack2_bf16(v[c][r][6], v[c][r][7]);
-              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.y) + (row0 + r) * p.ldy + k0) = u;
+              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.y) + (row0 + r) * static_cast<I>(p.ldy) + k0) = u;
               if (npass > 1) {  // the next LayerNorm reads what was stored
                 const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
@@ -317,7 +321,7 @@ __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) ln_quant_kernel(cons
                 }
               }
             } else {
-              float4* yp = reinterpret_cast<float4*>(static_cast<float*>(p.y) + (row0 + r) * p.ldy + k0);
+              float4* yp = reinterpret_cast<float4*>(static_cast<float*>(p.y) + (row0 + r) * static_cast<I>(p.ldy) + k0);
               yp[0] = make_float4(v[c][r][0], v[c][r][1], v[c][r][2], v[c][r][3]);
               yp[1] = make_float4(v[c][r][4], v[c][r][5], v[c][r][6], v[c][r][7]);
             }
@@ -340,7 +344,7 @@ __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) ln_quant_kernel(cons
       if (p.scales && lane == 0) static_cast<uint8_t*>(p.scales)[row0] = static_cast<uint8_t>(byte);
     }
 #pragma unroll
-    for (int c = 0; c < CH; ++c) quant_chunk<FMT, RP>(p, row0, c, lane, v[c], row_rcp, g);
+    for (int c = 0; c < CH; ++c) quant_chunk<FMT, RP, I>(p, row0, c, lane, v[c], row_rcp, g);
   }
 }
 
@@ -391,19 +395,32 @@ int grid_for_rows(int64_t units) {
   return static_cast<int>(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
 }
 
-template <typename T, int FMT>
-void launch_quant(const QuantParams& p, bool ln, cudaStream_t st) {
+template <typename T, int FMT, typename I>
+void launch_quant_idx(const QuantParams& p, bool ln, cudaStream_t st) {
   constexpr int RP = (FMT == VX_FMT_BLK16_A) ? 2 : 1;
   const int grid = grid_for_rows(p.M / RP);
   if (!ln) {
-    quant_kernel<T, FMT><<<grid, 256, 0, st>>>(p);
+    quant_kernel<T, FMT, I><<<grid, 256, 0, st>>>(p);
   } else if (p.K <= 512) {
-    ln_quant_kernel<T, FMT, 2><<<grid, 256, 0, st>>>(p);
+    ln_quant_kernel<T, FMT, 2, I><<<grid, 256, 0, st>>>(p);
   } else if (p.K <= 1024) {
-    ln_quant_kernel<T, FMT, 4><<<grid, 256, 0, st>>>(p);
+    ln_quant_kernel<T, FMT, 4, I><<<grid, 256, 0, st>>>(p);
   } else {
-    ln_quant_kernel<T, FMT, 8><<<grid, 256, 0, st>>>(p);
+    ln_quant_kernel<T, FMT, 8, I><<<grid, 256, 0, st>>>(p);
   }
+}
+
+template <typename T, int FMT>
+void launch_quant(const QuantParams& p, bool ln, cudaStream_t st) {
+  // 32-bit indices when every offset the kernels form stays below 2^31 (rows padded to 128 for
+  // the scale-factor atoms; strides in elements, y possibly fp32)
+  int64_t ld = p.K;
+  if (p.ldx > ld) ld = p.ldx;
+  if (p.ldy > ld) ld = p.ldy;
+  if (p.ldc > ld && p.codes) ld = p.ldc;
+  const bool small = (p.M + 128) * ld < (1ll << 31) && (p.M + 128) * (p.sf_kg * 4 + 1) < (1ll << 31);
+  if (small) launch_quant_idx<T, FMT, int32_t>(p, ln, st);
+  else launch_quant_idx<T, FMT, int64_t>(p, ln, st);
 }
 
 template <typename T>
