@@ -176,13 +176,16 @@ struct ChunkOut {
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
           const float4 b = *reinterpret_cast<const float4*>(bias_s + i);
-          z[i] += b.x; z[i + 1] += b.y; z[i + 2] += b.z; z[i + 3] += b.w;
+          // (explicit roundings: every schedule of a kernel must produce the same bits)
+          z[i] = __fadd_rn(z[i], b.x); z[i + 1] = __fadd_rn(z[i + 1], b.y);
+          z[i + 2] = __fadd_rn(z[i + 2], b.z); z[i + 3] = __fadd_rn(z[i + 3], b.w);
         }
         if constexpr (EPI == VX_EPI_BIAS_GLU) {
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
             const float4 b = *reinterpret_cast<const float4*>(gate_s + i);
-            gate[i] += b.x; gate[i + 1] += b.y; gate[i + 2] += b.z; gate[i + 3] += b.w;
+            gate[i] = __fadd_rn(gate[i], b.x); gate[i + 1] = __fadd_rn(gate[i + 1], b.y);
+            gate[i + 2] = __fadd_rn(gate[i + 2], b.z); gate[i + 3] = __fadd_rn(gate[i + 3], b.w);
           }
         }
       }
@@ -359,6 +362,10 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   // MMA -> epilogue -> MMA hand-over: they read the second 32-column chunk only after the first
   // is finished (half the live registers), which releases tensor memory later at no cost.
   constexpr bool SEQ = (EPI == VX_EPI_BIAS_SWISH) && NCH == 2;
+  // Swish with NV16 output on the wide tile: software-pipelined epilogue (see PIPE below).
+  // Measured at T = 90000: NV16 FFN chain 343 -> 331 us with it; the MX32 FFN-up kernel got
+  // slower (154 -> 165 us), so the 32-block kinds keep the plain chunk-after-chunk order.
+  constexpr bool PIPE = SEQ && OUT == 2 && kind_vec4(KIND);
 
   const int out_dtype = OUT == 1 ? static_cast<int>(VX_BF16) : (OUT == 2 ? static_cast<int>(VX_FP4) : p.out_dtype);
   const bool tma_store = OUT == 1 ? true : (OUT == 2 ? false : p.tma_store != 0);
@@ -747,6 +754,52 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         res_inflight = true;
       }
     }
+    // PIPE: the chunk whose Swish is done and whose E2M1 encode is still pending, with where it goes
+    float za[PIPE ? 32 : 1], zb[PIPE ? 32 : 1];
+    float pend_rcp0 = 0.0f, pend_rcp1 = 0.0f;
+    uint32_t pend_sb = 0;
+    bool pend_ok = false;
+    uint8_t* pend_codes = nullptr;
+    int64_t pend_sf = 0, pend_nat = 0;
+    // Block scale(s) of a finished chunk: MX32 one UE8M0 byte, NV16 two E4M3 bytes.
+    auto chunk_scales = [&](const float (&zc)[32], float& rcp0, float& rcp1) -> uint32_t {
+      if (out_fmt == VX_FMT_MX32) {
+        float a = fabsf(zc[0]);
+#pragma unroll
+        for (int i = 1; i < 32; ++i) a = fmaxf(a, fabsf(zc[i]));
+        uint32_t byte;
+        ue8m0_from_amax(a, byte, rcp0);
+        rcp1 = rcp0;
+        return byte;
+      } else {
+        uint32_t sb2 = 0;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          float a = fabsf(zc[16 * hh]);
+#pragma unroll
+          for (int i = 1; i < 16; ++i) a = fmaxf(a, fabsf(zc[16 * hh + i]));
+          uint32_t byte;
+          float rcp;
+          nv16_block(a, g_out, byte, rcp);
+          if (hh == 0) rcp0 = rcp; else rcp1 = rcp;
+          sb2 |= byte << (8 * hh);
+        }
+        return sb2;
+      }
+    };
+    // Codes + scale byte(s) of the pending chunk to memory.
+    auto pend_store = [&](const uint32_t (&w)[4]) {
+      if (pend_ok) {
+        *reinterpret_cast<uint4*>(pend_codes) = make_uint4(w[0], w[1], w[2], w[3]);
+        if (out_fmt == VX_FMT_MX32) {
+          p.out_sf[pend_sf] = static_cast<uint8_t>(pend_sb);
+          if (p.out_scales) p.out_scales[pend_nat] = static_cast<uint8_t>(pend_sb);
+        } else {
+          *reinterpret_cast<uint16_t*>(p.out_sf + pend_sf) = static_cast<uint16_t>(pend_sb);
+          if (p.out_scales) *reinterpret_cast<uint16_t*>(p.out_scales + pend_nat) = static_cast<uint16_t>(pend_sb);
+        }
+      }
+    };
     for (int it = 0; it < my_tiles && ok; ++it) {
       const int64_t row = static_cast<int64_t>(mb) * BM + q * 32 + lane;
       const bool row_ok = row < p.M;
@@ -763,6 +816,74 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         sm.bias_s[ew][32 + lane] = c1 < p.N ? __ldg(p.bias + c1) : 0.0f;
         __syncwarp();
         bias_nb = nb;
+      }
+      if constexpr (PIPE) {
+        // Software-pipelined epilogue.  Swish is bound by the special-function unit (ex2 + rcp
+        // per value, a quarter of the FMA rate), the E2M1 re-quantization by the FMA / ALU
+        // pipes; run one after the other, each leaves the other's pipe idle.  Here the Swish of
+        // the chunk just read from tensor memory is interleaved, instruction by instruction, with
+        // the encode of the previous chunk (whose block scale needed all of its 32 values first).
+        if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[0], group & 1, p.status, 4);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        tc_fence_after();
+        ++group;
+        const uint32_t acc_addr = lane_addr + TM_ACC0 + col_base;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          float (&zn)[32] = h == 0 ? za : zb;  // chunk read now
+          float (&zo)[32] = h == 0 ? zb : za;  // pending chunk: previous tile's second / this tile's first
+          {
+            uint32_t r[32];
+            tc_ld_32x32b_x32(acc_addr + h * 32, r);
+            tc_wait_ld();
+            if (h == 1) {  // both chunks are out of tensor memory
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&sm.tmem_empty[0]);
+            }
+            const float gs = (kind_vec4(KIND) && p.a_amax) ? g_ab : 1.0f;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (bias_base) b = *reinterpret_cast<const float4*>(bias_base + h * 32 + i);
+              const float bb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float t = __uint_as_float(r[i + j]);
+                if (kind_vec4(KIND) && p.a_amax) t = __fmul_rn(t, gs);
+                zn[i + j] = bias_base ? __fadd_rn(t, bb[j]) : t;
+              }
+            }
+          }
+          uint32_t w[4];
+#pragma unroll
+          for (int g8 = 0; g8 < 4; ++g8) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) zn[8 * g8 + j] = silu_f(zn[8 * g8 + j]);
+            const float v[8] = {zo[8 * g8], zo[8 * g8 + 1], zo[8 * g8 + 2], zo[8 * g8 + 3],
+                                zo[8 * g8 + 4], zo[8 * g8 + 5], zo[8 * g8 + 6], zo[8 * g8 + 7]};
+            if (kind_vec4(KIND)) w[g8] = e2m1_pack8<false>(v, g8 < 2 ? pend_rcp0 : pend_rcp1);
+            else w[g8] = e2m1_pack8<true>(v, pend_rcp0);
+          }
+          pend_store(w);
+          // the chunk just finished becomes the pending one
+          const int64_t out_col0 = static_cast<int64_t>(nb) * BNT + col_base + h * 32;
+          pend_sb = chunk_scales(zn, pend_rcp0, pend_rcp1);
+          pend_ok = row_ok && out_col0 < p.N;
+          pend_codes = static_cast<uint8_t*>(p.out) + row * p.ldo + (out_col0 >> 1);
+          const int64_t sf_row = (row >> 7) * p.out_sf_kg * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4;
+          if (out_fmt == VX_FMT_MX32) {
+            pend_sf = sf_row + (out_col0 >> 7) * 512 + ((out_col0 >> 5) & 3);
+            pend_nat = row * (p.N >> 5) + (out_col0 >> 5);
+          } else {
+            pend_sf = sf_row + (out_col0 >> 6) * 512 + ((out_col0 >> 5) & 1) * 2;
+            pend_nat = row * (p.N >> 4) + (out_col0 >> 4);
+          }
+        }
+        mb = mb_next;
+        nb = nb_next;
+        continue;
       }
       float z[NCH][32], gate[32];
       if constexpr (FP8) {
@@ -918,10 +1039,10 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
               for (int i = 0; i < 32; ++i) z[h][i] = z[h][i] * row_scale * __shfl_sync(0xffffffffu, csv, i);
             } else if (kind_vec4(KIND) && p.a_amax) {
 #pragma unroll
-              for (int i = 0; i < 32; ++i) z[h][i] *= g_ab;
+              for (int i = 0; i < 32; ++i) z[h][i] = __fmul_rn(z[h][i], g_ab);
               if constexpr (GLU) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) gate[i] *= g_ab;
+                for (int i = 0; i < 32; ++i) gate[i] = __fmul_rn(gate[i], g_ab);
               }
             }
           }
@@ -1036,6 +1157,19 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       }
       mb = mb_next;
       nb = nb_next;
+    }
+    if constexpr (PIPE) {
+      if (my_tiles > 0 && ok) {  // encode the last pending chunk (the second of the last tile)
+        uint32_t w[4];
+#pragma unroll
+        for (int g8 = 0; g8 < 4; ++g8) {
+          const float v[8] = {zb[8 * g8], zb[8 * g8 + 1], zb[8 * g8 + 2], zb[8 * g8 + 3],
+                              zb[8 * g8 + 4], zb[8 * g8 + 5], zb[8 * g8 + 6], zb[8 * g8 + 7]};
+          if (kind_vec4(KIND)) w[g8] = e2m1_pack8<false>(v, g8 < 2 ? pend_rcp0 : pend_rcp1);
+          else w[g8] = e2m1_pack8<true>(v, pend_rcp0);
+        }
+        pend_store(w);
+      }
     }
     if (tma_store && lane == 0) tma_store_wait_all<0>();
     if (!ok) sm.abort_flag = 1;
