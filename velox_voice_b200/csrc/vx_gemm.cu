@@ -758,7 +758,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     float za[PIPE ? 32 : 1], zb[PIPE ? 32 : 1];
     float pend_rcp0 = 0.0f, pend_rcp1 = 0.0f;
     uint32_t pend_sb = 0;
-    bool pend_ok = false;
+    bool pend_ok = false, pend_col_ok = false;
     uint8_t* pend_codes = nullptr;
     int64_t pend_sf = 0, pend_nat = 0;
     // Block scale(s) of a finished chunk: MX32 one UE8M0 byte, NV16 two E4M3 bytes.
@@ -789,14 +789,15 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     };
     // Codes + scale byte(s) of the pending chunk to memory.
     auto pend_store = [&](const uint32_t (&w)[4]) {
-      if (pend_ok) {
-        *reinterpret_cast<uint4*>(pend_codes) = make_uint4(w[0], w[1], w[2], w[3]);
+      if (pend_ok) *reinterpret_cast<uint4*>(pend_codes) = make_uint4(w[0], w[1], w[2], w[3]);
+      if (pend_col_ok) {  // rows of the last tile beyond M get zero scale factors
+        const uint32_t sbw = pend_ok ? pend_sb : 0u;
         if (out_fmt == VX_FMT_MX32) {
-          p.out_sf[pend_sf] = static_cast<uint8_t>(pend_sb);
-          if (p.out_scales) p.out_scales[pend_nat] = static_cast<uint8_t>(pend_sb);
+          p.out_sf[pend_sf] = static_cast<uint8_t>(sbw);
+          if (p.out_scales && pend_ok) p.out_scales[pend_nat] = static_cast<uint8_t>(sbw);
         } else {
-          *reinterpret_cast<uint16_t*>(p.out_sf + pend_sf) = static_cast<uint16_t>(pend_sb);
-          if (p.out_scales) *reinterpret_cast<uint16_t*>(p.out_scales + pend_nat) = static_cast<uint16_t>(pend_sb);
+          *reinterpret_cast<uint16_t*>(p.out_sf + pend_sf) = static_cast<uint16_t>(sbw);
+          if (p.out_scales && pend_ok) *reinterpret_cast<uint16_t*>(p.out_scales + pend_nat) = static_cast<uint16_t>(sbw);
         }
       }
     };
@@ -870,7 +871,8 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
           // the chunk just finished becomes the pending one
           const int64_t out_col0 = static_cast<int64_t>(nb) * BNT + col_base + h * 32;
           pend_sb = chunk_scales(zn, pend_rcp0, pend_rcp1);
-          pend_ok = row_ok && out_col0 < p.N;
+          pend_col_ok = out_col0 < p.N;
+          pend_ok = row_ok && pend_col_ok;
           pend_codes = static_cast<uint8_t*>(p.out) + row * p.ldo + (out_col0 >> 1);
           const int64_t sf_row = (row >> 7) * p.out_sf_kg * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4;
           if (out_fmt == VX_FMT_MX32) {
@@ -1088,18 +1090,20 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             }
           } else if (out_dtype == VX_FP4) {
             const uint32_t sb = store_chunk_fp4(p, out_fmt, z[h], row, out_col0, g_out, row_ok && out_col0 < n_out);
-            if (row_ok && out_col0 < n_out) {
-              // this chunk's scale byte(s) inside the row's SF word(s)
+            if (out_col0 < n_out) {
+              // this chunk's scale byte(s) inside the row's SF word(s); rows of the last tile
+              // beyond M get zero scale factors (the SF atoms cover whole 128-row tiles)
+              const uint32_t sbw = row_ok ? sb : 0u;
               const int64_t sf_row = (row >> 7) * p.out_sf_kg * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4;
               if (out_fmt == VX_FMT_MX32) {
-                p.out_sf[sf_row + (out_col0 >> 7) * 512 + ((out_col0 >> 5) & 3)] = static_cast<uint8_t>(sb);
-                if (p.out_scales) p.out_scales[row * (n_out >> 5) + (out_col0 >> 5)] = static_cast<uint8_t>(sb);
+                p.out_sf[sf_row + (out_col0 >> 7) * 512 + ((out_col0 >> 5) & 3)] = static_cast<uint8_t>(sbw);
+                if (p.out_scales && row_ok) p.out_scales[row * (n_out >> 5) + (out_col0 >> 5)] = static_cast<uint8_t>(sbw);
               } else {
                 *reinterpret_cast<uint16_t*>(p.out_sf + sf_row + (out_col0 >> 6) * 512 + ((out_col0 >> 5) & 1) * 2) =
-                    static_cast<uint16_t>(sb);
-                if (p.out_scales)
+                    static_cast<uint16_t>(sbw);
+                if (p.out_scales && row_ok)
                   *reinterpret_cast<uint16_t*>(p.out_scales + row * (n_out >> 4) + (out_col0 >> 4)) =
-                      static_cast<uint16_t>(sb);
+                      static_cast<uint16_t>(sbw);
               }
             }
           } else if (dbg & 1) {
@@ -1518,8 +1522,8 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (argmax) VX_CUDA_OK(cudaMemsetAsync(d->out, 0, static_cast<size_t>(M) * 8, st));
-  if (!argmax && d->out_dtype == VX_FP4 && (M % BM != 0)) {
-    // SF rows of the last partial tile must read as zero
+  if (!argmax && d->out_dtype == VX_FP4 && p.out_sf_kg * (d->out_fmt == VX_FMT_MX32 ? 128 : 64) != N) {
+    // k-groups beyond N must read as zero (rows of the last tile beyond M: written as zero by the epilogue)
     VX_CUDA_OK(cudaMemsetAsync(p.out_sf, 0, static_cast<size_t>(vx_sf_bytes(d->out_fmt, M, N)), st));
   }
 

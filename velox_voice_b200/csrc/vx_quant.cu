@@ -176,6 +176,19 @@ __device__ __forceinline__ void quant_chunk(const QuantParams& p, I row0, int c,
   }
 }
 
+// Scale-factor atoms cover rows in tiles of 128: the rows between M and the next multiple of
+// 128 must read as zero scale factors (the GEMM multiplies their zero-filled operand rows by
+// them).  Every k-group word of those rows is cleared here, by the kernel that fills the rest.
+template <typename I>
+__device__ __forceinline__ void zero_pad_rows(const QuantParams& p, I gwarp, I warps, int lane) {
+  const I M = static_cast<I>(p.M), sf_kg = static_cast<I>(p.sf_kg);
+  if (!p.sf || (M & 127) == 0) return;
+  const I m_pad = (M + 127) & ~static_cast<I>(127);
+  for (I r = M + gwarp; r < m_pad; r += warps)
+    for (I kg = lane; kg < sf_kg; kg += 32)
+      *reinterpret_cast<uint32_t*>(p.sf + sf_offset<I>(r, kg, sf_kg)) = 0u;
+}
+
 // Streaming quantizer (no LayerNorm): any K % 8 == 0.
 template <typename T, int FMT, typename I>
 __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) quant_kernel(const QuantParams p) {
@@ -227,6 +240,7 @@ __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) quant_kernel(const Q
       quant_chunk<FMT, RP, I>(p, row0, c, lane, v, row_rcp, g);
     }
   }
+  zero_pad_rows<I>(p, u_first, warps, lane);
 }
 
 // LayerNorm + quantize, row resident in registers (CH chunks of 256 elements, K <= 256 CH).
@@ -346,6 +360,7 @@ __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) ln_quant_kernel(cons
 #pragma unroll
     for (int c = 0; c < CH; ++c) quant_chunk<FMT, RP, I>(p, row0, c, lane, v[c], row_rcp, g);
   }
+  zero_pad_rows<I>(p, u_first, warps, lane);
 }
 
 template <typename T>
@@ -487,9 +502,9 @@ int quantize_common(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ld
   p.sf_kg = sf_kgroups(fmt, K);
   p.amax = amax; p.gamma = gamma; p.beta = beta; p.gamma2 = gamma2; p.beta2 = beta2; p.eps = eps; p.y = y; p.y_bf16 = (y_dtype == VX_BF16); p.ldy = ldy;
   if (scales_sf) {
-    // rows / k-groups beyond the tensor must read as zero scale factors
+    // k-groups beyond K must read as zero scale factors (rows beyond M: cleared by the kernel)
     const int64_t nkb = K / blk;
-    if ((M & 127) != 0 || p.sf_kg * 4 != nkb)
+    if (p.sf_kg * 4 != nkb)
       VX_CUDA_OK(cudaMemsetAsync(scales_sf, 0, static_cast<size_t>(vx_sf_bytes(fmt, M, K)), st));
   }
   return x_dtype == VX_BF16 ? dispatch_fmt<__nv_bfloat16>(fmt, p, ln, st)

@@ -302,6 +302,13 @@ class CompiledStack:
         torch.cuda.current_stream().synchronize()
         return self.ids_host
 
+    def reserve_host_ids(self, n: int) -> None:
+        """Pinned host id buffers for ``n`` queued batches (pinning is slow and synchronises the
+        device: call this once, outside any latency-sensitive region)."""
+        if len(self._ids_pool) < n:
+            block = torch.empty((n - len(self._ids_pool), self.frames), dtype=torch.int32).pin_memory()
+            self._ids_pool.extend(block.unbind(0))
+
     def encode_ctc_host_batches(self, batches: Sequence[torch.Tensor],
                                 out: Optional[List[torch.Tensor]] = None, after_each=None) -> List[torch.Tensor]:
         """Throughput form of :meth:`encode_ctc_host` for a queue of utterance shards.
@@ -319,8 +326,7 @@ class CompiledStack:
             self._ev_in = [torch.cuda.Event() for _ in range(2)]
             self._ev_free = [torch.cuda.Event() for _ in range(2)]
         if out is None:
-            while len(self._ids_pool) < len(batches):
-                self._ids_pool.append(torch.empty((self.frames,), dtype=torch.int32).pin_memory())
+            self.reserve_host_ids(len(batches))
             out = self._ids_pool[: len(batches)]
         main = torch.cuda.current_stream()
         self._h2d.wait_stream(main)
