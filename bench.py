@@ -3,7 +3,7 @@
 
 A step = one pass of the MXFP4 encoder linear stack (12 Conformer blocks' linears + CTC head,
 greedy argmax) over T encoder frames per GPU (default 90000 = one hour of 16 kHz audio,
-BASELINE configs[3]/[4]); synthetic ~N(0,1) bf16 features, random-init weights (seed 0).
+benchmark configs[3]/[4]); synthetic ~N(0,1) bf16 features, random-init weights (seed 0).
 Frames are independent, so N GPUs each take their own T frames with replicated weights (weak
 scaling); the only collective is the gather of the per-frame CTC ids.
 
@@ -47,7 +47,7 @@ def parse():
     ap.add_argument("--breakdown-only", action="store_true",
                     help="time the individual launches only (profiling aid); prints one JSON line")
     ap.add_argument("--configs-only", action="store_true",
-                    help="time BASELINE configs[0..2] (single launches / the FFN chain) and exit")
+                    help="time benchmark configs[0..2] (single launches / the FFN chain) and exit")
     ap.add_argument("--ops", default="", help="with --breakdown-only: substring filter on the op name")
     return ap.parse_args()
 
@@ -270,7 +270,7 @@ def op_breakdown(stack, T, fmt_name, only=""):
 
 
 def baseline_configs(dev, hbm_peak_gbs):
-    """BASELINE configs[0..2] as single (chains of) launches: us, algorithmic TFLOP/s and GB/s,
+    """benchmark configs[0..2] as single (chains of) launches: us, algorithmic TFLOP/s and GB/s,
     and the fraction of the roofline (slower of bytes at measured HBM peak and FLOPs at the
     measured tensor-core peak of that operand type)."""
     import torch

@@ -176,7 +176,7 @@ def test_block_formats_f32_out(ops, fmt, M, N, K, direct):
 
 
 def test_cfg1_single_mxfp4_linear(ops):
-    """BASELINE configs[0]: x bf16 [1024, 512] ~ N(0,1), W [2048, 512] ~ N(0, 0.02), seed 0, bf16 out."""
+    """benchmark configs[0]: x bf16 [1024, 512] ~ N(0,1), W [2048, 512] ~ N(0, 0.02), seed 0, bf16 out."""
     torch.manual_seed(0)
     x = torch.randn(1024, 512).bfloat16().cuda()
     w = (0.02 * torch.randn(2048, 512)).cuda()
@@ -279,7 +279,7 @@ def test_requantized_output_is_the_quantizer_of_the_f32_output(ops, epi_case, ou
         assert rel_err(y.cpu().numpy(), ref) < 1e-5
 
 
-# ------------------------------------------------------------------ BASELINE sizes
+# ------------------------------------------------------------------ benchmark sizes
 
 
 @pytest.mark.parametrize("fmt,N,K,epi", [(F.FMT_FP8_1X128, 1536, 512, G.EPI_BIAS), (F.FMT_NV16, 2048, 512, G.EPI_BIAS_SWISH),

@@ -207,7 +207,7 @@ def test_layernorm_only_and_bf16_output(ops):
 
 @pytest.mark.parametrize("fmt", [F.FMT_MX32, F.FMT_FP8_1X128, F.FMT_NV16])
 def test_full_size_activation_shape(ops, fmt):
-    # BASELINE shapes: T = 90000 frames x d_model 512; oracle compared on every row
+    # benchmark shapes: T = 90000 frames x d_model 512; oracle compared on every row
     torch.manual_seed(0)
     x = torch.randn(90000, 512, device="cuda").bfloat16()
     _check(ops, x, fmt)

@@ -1,4 +1,4 @@
-"""The encoder linear stack on the GPU against the CPU oracle stack (BASELINE configs[3]/[4])."""
+"""The encoder linear stack on the GPU against the CPU oracle stack (benchmark configs[3]/[4])."""
 
 import numpy as np
 import pytest
