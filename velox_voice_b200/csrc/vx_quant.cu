@@ -116,12 +116,15 @@ __device__ __forceinline__ I sf_offset(I row, I kgroup, I sf_kg) {
 // `row_rcp` / `row_byte` are used by ROWSCALE only (the row maximum is known beforehand).
 // I: index type -- 32-bit when every element / byte offset of the call fits (most tensors; half
 // the integer instructions of the 64-bit form), else 64-bit.
-template <int FMT, int RP, typename I>
+// FAST: the common call shape, fixed at compile time -- K a whole number of 256-element chunks
+// (a power of two behind LayerNorm), scale factors wanted as SF atoms only -- drops the
+// per-chunk bounds predicates, the natural-layout stores and their tests from the inner loop.
+template <int FMT, int RP, typename I, bool FAST>
 __device__ __forceinline__ void quant_chunk(const QuantParams& p, I row0, int c, int lane,
                                             float (&v)[RP][8], float row_rcp, float g) {
   const I K = static_cast<I>(p.K), M = static_cast<I>(p.M), ldc = static_cast<I>(p.ldc);
   const I k0 = static_cast<I>(c) * 256 + lane * 8;
-  const bool active = k0 < K;
+  const bool active = FAST || k0 < K;
   float a = amax8(v[0]);
   if constexpr (RP == 2) a = fmaxf(a, amax8(v[1]));
 
@@ -155,13 +158,13 @@ __device__ __forceinline__ void quant_chunk(const QuantParams& p, I row0, int c,
       if (active)
         *reinterpret_cast<uint32_t*>(p.codes + (row0 + r) * ldc + (k0 >> 1)) = e2m1_pack8<FMT != VX_FMT_NV16>(v[r], rcp);
     }
-    if (p.scales && active && (lane % LPB) == 0) {
+    if (!FAST && p.scales && active && (lane % LPB) == 0) {
       uint8_t* s = static_cast<uint8_t*>(p.scales);
       if constexpr (FMT == VX_FMT_BLK16_A) s[kb * (M >> 1) + (row0 >> 1)] = byte;
       else if constexpr (FMT == VX_FMT_BLK16_B) s[kb * M + row0] = byte;
       else s[row0 * (K / BLK) + kb] = byte;
     }
-    if (p.sf) {
+    if (FAST || p.sf) {
       // assemble the 4 scale bytes of one k-group into a word held by every lane of the group
       uint32_t w = byte << (8 * ((lane / LPB) & 3));
 #pragma unroll
@@ -190,7 +193,7 @@ __device__ __forceinline__ void zero_pad_rows(const QuantParams& p, I gwarp, I w
 }
 
 // Streaming quantizer (no LayerNorm): any K % 8 == 0.
-template <typename T, int FMT, typename I>
+template <typename T, int FMT, typename I, bool FAST>
 __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) quant_kernel(const QuantParams p) {
   constexpr int RP = (FMT == VX_FMT_BLK16_A) ? 2 : 1;
   const int lane = threadIdx.x & 31;
@@ -206,7 +209,7 @@ __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) quant_kernel(const Q
     const I k0 = static_cast<I>(c) * 256 + lane * 8;
 #pragma unroll
     for (int r = 0; r < RP; ++r) {
-      if (k0 < static_cast<I>(p.K)) raw[r].load(x + (u * RP + r) * static_cast<I>(p.ldx) + k0);
+      if (FAST || k0 < static_cast<I>(p.K)) raw[r].load(x + (u * RP + r) * static_cast<I>(p.ldx) + k0);
       else raw[r].zero();
     }
   };
@@ -218,7 +221,7 @@ __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) quant_kernel(const Q
       float a = 0.0f;
       for (int c = 0; c < nchunks; ++c) {
         const I k0 = static_cast<I>(c) * 256 + lane * 8;
-        if (k0 < static_cast<I>(p.K)) {
+        if (FAST || k0 < static_cast<I>(p.K)) {
           float t[8];
           load8(x + row0 * static_cast<I>(p.ldx) + k0, t);
           a = fmaxf(a, amax8(t));
@@ -237,7 +240,7 @@ __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) quant_kernel(const Q
       for (int r = 0; r < RP; ++r) raw[r].get(v[r]);
       if (c + 1 < nchunks) fetch(u, c + 1);
       else if (u + warps < nunits && FMT != VX_FMT_ROWSCALE) fetch(u + warps, 0);
-      quant_chunk<FMT, RP, I>(p, row0, c, lane, v, row_rcp, g);
+      quant_chunk<FMT, RP, I, FAST>(p, row0, c, lane, v, row_rcp, g);
     }
   }
   zero_pad_rows<I>(p, u_first, warps, lane);
@@ -249,7 +252,7 @@ __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) quant_kernel(const Q
 // with every operation individually rounded (no FMA contraction), rstd = 1 / sqrt(var + eps)
 // correctly rounded, lane-sequential partial sums and a butterfly (xor 16, 8, 4, 2, 1) warp
 // reduction -- an order a CPU restatement can follow exactly.
-template <typename T, int FMT, int CH, typename I>
+template <typename T, int FMT, int CH, typename I, bool FAST>
 __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) ln_quant_kernel(const QuantParams p) {
   constexpr int RP = (FMT == VX_FMT_BLK16_A) ? 2 : 1;
   const int lane = threadIdx.x & 31;
@@ -269,7 +272,7 @@ __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) ln_quant_kernel(cons
 #pragma unroll
       for (int c = 0; c < CH; ++c) {
         const I k0 = static_cast<I>(c) * 256 + lane * 8;
-        if (k0 < static_cast<I>(p.K)) raw[c][r].load(x + (u * RP + r) * static_cast<I>(p.ldx) + k0);
+        if (FAST || k0 < static_cast<I>(p.K)) raw[c][r].load(x + (u * RP + r) * static_cast<I>(p.ldx) + k0);
         else raw[c][r].zero();
       }
   };
@@ -304,13 +307,15 @@ __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) ln_quant_kernel(cons
         s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, o));
         sq = __fadd_rn(sq, __shfl_xor_sync(0xffffffffu, sq, o));
       }
-      const float mean = __fdiv_rn(s, k_f);
-      const float var = fmaxf(__fsub_rn(__fdiv_rn(sq, k_f), __fmul_rn(mean, mean)), 0.0f);
+      // FAST: K is a power of two, so multiplying by 1/K gives the same correctly rounded quotient
+      const float mean = FAST ? __fmul_rn(s, 1.0f / (CH * 256)) : __fdiv_rn(s, k_f);
+      const float ex2 = FAST ? __fmul_rn(sq, 1.0f / (CH * 256)) : __fdiv_rn(sq, k_f);
+      const float var = fmaxf(__fsub_rn(ex2, __fmul_rn(mean, mean)), 0.0f);
       const float rstd = __frcp_rn(__fsqrt_rn(__fadd_rn(var, p.eps)));
 #pragma unroll
       for (int c = 0; c < CH; ++c) {
         const I k0 = static_cast<I>(c) * 256 + lane * 8;
-        if (k0 < static_cast<I>(p.K)) {
+        if (FAST || k0 < static_cast<I>(p.K)) {
           float ga[8], be[8];
           load8(ga_p + k0, ga);
           load8(be_p + k0, be);
@@ -346,7 +351,7 @@ __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) ln_quant_kernel(cons
       ga_p = p.gamma2;
       be_p = p.beta2;
     }
-    if (!p.codes) continue;  // plain LayerNorm
+    if (!FAST && !p.codes) continue;  // plain LayerNorm
     float row_rcp = 0.0f;
     if constexpr (FMT == VX_FMT_ROWSCALE) {
       float a = 0.0f;
@@ -358,7 +363,7 @@ __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) ln_quant_kernel(cons
       if (p.scales && lane == 0) static_cast<uint8_t*>(p.scales)[row0] = static_cast<uint8_t>(byte);
     }
 #pragma unroll
-    for (int c = 0; c < CH; ++c) quant_chunk<FMT, RP, I>(p, row0, c, lane, v[c], row_rcp, g);
+    for (int c = 0; c < CH; ++c) quant_chunk<FMT, RP, I, FAST>(p, row0, c, lane, v[c], row_rcp, g);
   }
   zero_pad_rows<I>(p, u_first, warps, lane);
 }
@@ -410,18 +415,18 @@ int grid_for_rows(int64_t units) {
   return static_cast<int>(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
 }
 
-template <typename T, int FMT, typename I>
+template <typename T, int FMT, typename I, bool FAST>
 void launch_quant_idx(const QuantParams& p, bool ln, cudaStream_t st) {
   constexpr int RP = (FMT == VX_FMT_BLK16_A) ? 2 : 1;
   const int grid = grid_for_rows(p.M / RP);
   if (!ln) {
-    quant_kernel<T, FMT, I><<<grid, 256, 0, st>>>(p);
+    quant_kernel<T, FMT, I, FAST><<<grid, 256, 0, st>>>(p);
   } else if (p.K <= 512) {
-    ln_quant_kernel<T, FMT, 2, I><<<grid, 256, 0, st>>>(p);
+    ln_quant_kernel<T, FMT, 2, I, FAST><<<grid, 256, 0, st>>>(p);
   } else if (p.K <= 1024) {
-    ln_quant_kernel<T, FMT, 4, I><<<grid, 256, 0, st>>>(p);
+    ln_quant_kernel<T, FMT, 4, I, FAST><<<grid, 256, 0, st>>>(p);
   } else {
-    ln_quant_kernel<T, FMT, 8, I><<<grid, 256, 0, st>>>(p);
+    ln_quant_kernel<T, FMT, 8, I, FAST><<<grid, 256, 0, st>>>(p);
   }
 }
 
@@ -434,8 +439,16 @@ void launch_quant(const QuantParams& p, bool ln, cudaStream_t st) {
   if (p.ldy > ld) ld = p.ldy;
   if (p.ldc > ld && p.codes) ld = p.ldc;
   const bool small = (p.M + 128) * ld < (1ll << 31) && (p.M + 128) * (p.sf_kg * 4 + 1) < (1ll << 31);
-  if (small) launch_quant_idx<T, FMT, int32_t>(p, ln, st);
-  else launch_quant_idx<T, FMT, int64_t>(p, ln, st);
+  // FAST (see quant_chunk): SF-atom formats, whole chunks, no natural-layout scales; behind
+  // LayerNorm K must also fill its register chunks exactly (512, 1024 or 2048)
+  constexpr bool sf_fmt = FMT == VX_FMT_MX32 || FMT == VX_FMT_NV16 || FMT == VX_FMT_BLK16_A || FMT == VX_FMT_BLK16_B;
+  const bool fast = sf_fmt && small && p.codes && p.sf && !p.scales && p.K % 256 == 0 &&
+                    (!ln || p.K == 512 || p.K == 1024 || p.K == 2048);
+  if constexpr (sf_fmt) {
+    if (fast) return launch_quant_idx<T, FMT, int32_t, true>(p, ln, st);
+  }
+  if (small) launch_quant_idx<T, FMT, int32_t, false>(p, ln, st);
+  else launch_quant_idx<T, FMT, int64_t, false>(p, ln, st);
 }
 
 template <typename T>
