@@ -9,19 +9,21 @@
 //
 // One persistent CTA per SM, 18 warps:
 //   warp 0      TMA producer: A / B tiles (128 rows x 128 bytes, 128-byte swizzle) and the
-//               scale-factor atoms of the stage into a 4-deep shared-memory ring;
-//   warp 1      owns tensor memory; one elected thread copies scale factors shared -> tensor
-//               memory (tcgen05.cp) and issues the MMAs; tcgen05.commit releases ring slots
-//               and publishes finished accumulators;
-//   warps 2..17 epilogue: each warp reads a 32-lane x 32-column block of the 128 x 128 fp32
-//               accumulator (tcgen05.ld, one row per thread), applies scales / bias / Swish /
-//               GLU / residual, then either a swizzled shared-memory staging buffer + TMA
-//               store (clipped at the tensor edge by hardware) or direct vector stores;
-//               optional re-quantization of the result to FP4.  Sixteen warps (four per
-//               scheduler) hide the TMEM-load, shared-memory and MUFU latencies of each other.
-// FP4: one 128 x 256 accumulator per tile, drained into registers right after the commit.
-// FP8: the four accumulators form a ring over the K blocks, released one by one, so the MMAs
-// of the next K blocks (and of the next tile) run while the epilogue promotes.
+//               scale-factor atoms of the stage into a shared-memory ring (B, or only B's
+//               scale factors, stay resident when they fit);
+//   warp 1      owns tensor memory; runs warp-uniformly, one elected lane copies scale
+//               factors shared -> tensor memory (tcgen05.cp) and issues the MMAs;
+//               tcgen05.commit releases ring slots and publishes finished accumulators;
+//   warps 2..17 epilogue: each warp reads 32-lane x 32-column blocks of the fp32 accumulator
+//               (tcgen05.ld, one row per thread), applies scales / bias / Swish / GLU /
+//               residual / per-row argmax, then either a swizzled shared-memory staging
+//               buffer + TMA store (clipped at the tensor edge by hardware) or direct vector
+//               stores; optional re-quantization of the result to FP4.  Sixteen warps (four
+//               per scheduler) hide the TMEM-load, shared-memory and MUFU latencies of each other.
+// FP4: a 128 x 256 tile with one accumulator, drained into registers right after the commit,
+// or a 128 x 128 tile with two accumulators (epilogue of tile i under the MMAs of tile i + 1).
+// FP8: rounds of four K blocks into four accumulators, published per round and handed back in
+// pairs, so the MMAs of the next round run while the epilogue promotes.
 //
 // Every mbarrier wait is bounded (vx_ptx.cuh); an expired wait sets the device status word
 // and the CTA drains and exits instead of hanging.
@@ -367,9 +369,9 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   constexpr int VEC = kind_vec4(KIND) ? 4 : 2;
   constexpr int APS = kind_vec4(KIND) ? 4 : 2;  // SF atoms per 128 rows per stage
   constexpr bool GLU = (EPI == VX_EPI_BIAS_GLU);
-  // FP4: one 128 x 256 accumulator (a single N = 256 MMA does twice the work per issued
-  // instruction; the accumulator is drained into registers within ~200 cycles, so a second
-  // buffer would buy little).  FP8: 128 x 128, a ring of four, one per 128-wide K block in flight.
+  // FP4 wide: one 128 x 256 accumulator (a single N = 256 MMA does twice the work per issued
+  // instruction).  FP4 narrow: two 128 x 128 accumulators.  FP8: 128 x 128, four accumulators,
+  // one per 128-wide K block of a round.
   constexpr bool WIDE = kind_bn(KIND) == 256;
   constexpr int BNT = kind_bn(KIND);         // accumulator columns = B rows per tile
   constexpr int NRT = BNT / 128;             // 128-row scale-factor tiles of B per tile
