@@ -53,6 +53,7 @@ constexpr int NUM_THREADS = 576;       // 2 + 16 warps
 // is 65536 / 640 = 102 -> 96 registers per thread (112 does not launch).
 #define VX_GEMM_BOUNDS __launch_bounds__(NUM_THREADS, 1)
 
+
 constexpr int EPI_WARP0 = 2;
 constexpr int STAGING_BYTES = 32 * 128;  // 32 rows x up to 128 bytes per epilogue warp
 constexpr int FP8_MAX_KB = 16;           // K <= 2048 for the FP8 path
@@ -927,15 +928,9 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
           __syncwarp();
           sb_nb = nb;
         }
-        // promote each 128-wide K block: z += tmem * (sa[row, kb] * sb[col, kb]), two columns
-        // per packed fp32x2 instruction (same roundings as the scalar form)
-        uint64_t z2[16], g2[GLU ? 16 : 1];
+        // promote each 128-wide K block: z += tmem * (sa[row, kb] * sb[col, kb])
 #pragma unroll
-        for (int i = 0; i < 16; ++i) z2[i] = 0ull;
-        if constexpr (GLU) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) g2[i] = 0ull;
-        }
+        for (int i = 0; i < 32; ++i) { z[0][i] = 0.0f; gate[i] = 0.0f; }
         const float* sa_row = p.fa + row * kb_count;
         float sa_next = row_ok ? __ldg(sa_row) : 0.0f;
         for (int kb0 = 0; kb0 < kb_count && ok; kb0 += FP8_ACCS) {
@@ -953,17 +948,24 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             const float sa = sa_next;
             if (kb + 1 < kb_count && row_ok) sa_next = __ldg(sa_row + kb + 1);
             const uint64_t sa2 = pack_f32x2(sa, sa);
-            // acc2[i] += r[2i, 2i+1] * (sa * table[2i, 2i+1])
-            auto promote = [&](uint64_t* acc2, const uint32_t (&r)[32], const float* table) {
+            // acc[i] += r[i] * (sa * table[i]).  The scale products are a packed fp32x2
+            // multiply (both operands come as pairs: sb from shared memory, sa duplicated); the
+            // accumulation is scalar, because the accumulator values arrive from tensor memory
+            // in single registers and pairing them costs more moves than the packed form saves
+            // (measured: all-packed 208 us, all-scalar 232 us, this 194 us on the QKV shape).
+            auto promote = [&](float (&acc)[32], const uint32_t (&r)[32], const float* table) {
               const uint32_t taddr = smem_u32(table);
 #pragma unroll
               for (int v = 0; v < 8; ++v) {
                 uint64_t b0, b1;
                 asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(b0), "=l"(b1) : "r"(taddr + v * 16));
-                acc2[2 * v] = fma_f32x2(pack_f32x2(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1])),
-                                        mul_f32x2(sa2, b0), acc2[2 * v]);
-                acc2[2 * v + 1] = fma_f32x2(pack_f32x2(__uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3])),
-                                            mul_f32x2(sa2, b1), acc2[2 * v + 1]);
+                float s0, s1, s2, s3;
+                unpack_f32x2(mul_f32x2(sa2, b0), s0, s1);
+                unpack_f32x2(mul_f32x2(sa2, b1), s2, s3);
+                acc[4 * v] = fmaf(__uint_as_float(r[4 * v]), s0, acc[4 * v]);
+                acc[4 * v + 1] = fmaf(__uint_as_float(r[4 * v + 1]), s1, acc[4 * v + 1]);
+                acc[4 * v + 2] = fmaf(__uint_as_float(r[4 * v + 2]), s2, acc[4 * v + 2]);
+                acc[4 * v + 3] = fmaf(__uint_as_float(r[4 * v + 3]), s3, acc[4 * v + 3]);
               }
             };
             const uint32_t acc_addr = lane_addr + TM_ACC0 + u * 128 + col_base;
@@ -972,7 +974,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
               if (has_work) {  // gate first, so that one register block serves both loads
                 tc_ld_32x32b_x32(acc_addr + GATE_OFF, r);
                 tc_wait_ld();
-                promote(g2, r, sb_gate + kb * 32);
+                promote(gate, r, sb_gate + kb * 32);
               }
             }
             if (has_work) {
@@ -985,17 +987,11 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
               __syncwarp();
               if (lane == 0) mbar_arrive(&sm.tmem_empty[u >> 1]);
             }
-            if (has_work) promote(z2, r, sb_tab + kb * 32);
+            if (has_work) promote(z[0], r, sb_tab + kb * 32);
             if (tr && kb0 == 0) trace_rec(p, 2, it, 1 + u);
           }
         }
         if (!ok) break;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) unpack_f32x2(z2[i], z[0][2 * i], z[0][2 * i + 1]);
-        if constexpr (GLU) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) unpack_f32x2(g2[i], gate[2 * i], gate[2 * i + 1]);
-        }
       } else {
         if (tr) trace_rec(p, 2, it, 0);
         // one polling lane per warp (512 polling threads would starve the MMA-issuing thread)
