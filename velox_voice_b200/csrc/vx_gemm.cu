@@ -135,7 +135,7 @@ struct __align__(1024) SmemLayout {
   int abort_flag;
 };
 
-// sigmoid via ex2.approx + rcp.approx (relative error ~1e-6).  Alternatives measured and
+// sigmoid(g) = 1 / (1 + 2^(-g log2 e)) via ex2.approx + rcp.approx (relative error ~1e-6).  Alternatives measured and
 // rejected: tanh.approx (one MUFU operation, but its 2^-11 error flips FP4 codes / bf16
 // roundings of the re-quantized activations often enough to move CTC argmaxes), and a Newton
 // reciprocal on the FMA pipe (one MUFU operation less, six instructions more: 20 % slower).
@@ -153,18 +153,20 @@ __device__ __forceinline__ float rcp_ftz(float x) {
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ float sigmoid_f(float z) { return rcp_ftz(1.0f + ex2_ftz(-1.4426950408889634f * z)); }
 // Four Swish values with one reciprocal (the special-function unit is the busiest pipe of the
 // Swish epilogues): with d_i = 1 + 2^(-z_i log2 e), 1/d_0 = d_1 (d_2 d_3) / (d_0 d_1 d_2 d_3) and so
 // on -- 1.25 MUFU operations per value instead of 2, nine extra multiplications per four values
 // (measured 152 -> 144 us on the FFN-up kernel).  The exponent is capped at 2^30 so the product
 // of four cannot overflow; a sigmoid below 2^-30 only occurs for z < -20.8, where z * sigmoid(z)
 // is below 1e-7 in magnitude either way.
-__device__ __forceinline__ void silu4_f(float& z0, float& z1, float& z2, float& z3) {
-  const float d0 = 1.0f + ex2_ftz(fminf(-1.4426950408889634f * z0, 30.0f));
-  const float d1 = 1.0f + ex2_ftz(fminf(-1.4426950408889634f * z1, 30.0f));
-  const float d2 = 1.0f + ex2_ftz(fminf(-1.4426950408889634f * z2, 30.0f));
-  const float d3 = 1.0f + ex2_ftz(fminf(-1.4426950408889634f * z3, 30.0f));
+__device__ __forceinline__ float sigmoid_f(float z) { return rcp_ftz(1.0f + ex2_ftz(-1.4426950408889634f * z)); }
+// z_i *= sigmoid(g_i) for four values
+__device__ __forceinline__ void mul_sigmoid4(float& z0, float& z1, float& z2, float& z3,
+                                             float g0, float g1, float g2, float g3) {
+  const float d0 = 1.0f + ex2_ftz(fminf(-1.4426950408889634f * g0, 30.0f));
+  const float d1 = 1.0f + ex2_ftz(fminf(-1.4426950408889634f * g1, 30.0f));
+  const float d2 = 1.0f + ex2_ftz(fminf(-1.4426950408889634f * g2, 30.0f));
+  const float d3 = 1.0f + ex2_ftz(fminf(-1.4426950408889634f * g3, 30.0f));
   const float p01 = __fmul_rn(d0, d1), p23 = __fmul_rn(d2, d3);
   const float r = rcp_ftz(__fmul_rn(p01, p23));
   const float r01 = __fmul_rn(r, p23), r23 = __fmul_rn(r, p01);
@@ -172,6 +174,9 @@ __device__ __forceinline__ void silu4_f(float& z0, float& z1, float& z2, float& 
   z1 = __fmul_rn(z1, __fmul_rn(r01, d0));
   z2 = __fmul_rn(z2, __fmul_rn(r23, d3));
   z3 = __fmul_rn(z3, __fmul_rn(r23, d2));
+}
+__device__ __forceinline__ void silu4_f(float& z0, float& z1, float& z2, float& z3) {
+  mul_sigmoid4(z0, z1, z2, z3, z0, z1, z2, z3);
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
@@ -216,6 +221,8 @@ struct ChunkOut {
       for (int i = 0; i < 32; i += 4) silu4_f(z[i], z[i + 1], z[i + 2], z[i + 3]);
     } else if constexpr (EPI == VX_EPI_BIAS_GLU) {
 #pragma unroll
+      // (one reciprocal per value here: the shared-reciprocal form's extra roundings flip enough
+      // bf16 roundings of the GLU output to move the 12-block stack away from the CPU oracle)
       for (int i = 0; i < 32; ++i) z[i] *= sigmoid_f(gate[i]);
     } else if constexpr (EPI == VX_EPI_BIAS_RESIDUAL) {
       if (RES_TMA || res_smem) {
