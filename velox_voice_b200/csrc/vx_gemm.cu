@@ -320,7 +320,7 @@ __device__ __forceinline__ uint32_t store_chunk_fp4(const GemmParams& p, const i
     for (int q = 0; q < 4; ++q) {
       const float v[8] = {z[8 * q], z[8 * q + 1], z[8 * q + 2], z[8 * q + 3],
                           z[8 * q + 4], z[8 * q + 5], z[8 * q + 6], z[8 * q + 7]};
-      w[q] = e2m1_pack8<true>(v, rcp);
+      w[q] = e2m1_pack8<true, false>(v, rcp);
     }
     sbytes = byte;
   } else {
@@ -337,7 +337,7 @@ __device__ __forceinline__ uint32_t store_chunk_fp4(const GemmParams& p, const i
       for (int q = 0; q < 2; ++q) {
         const int b = 16 * h + 8 * q;
         const float v[8] = {z[b], z[b + 1], z[b + 2], z[b + 3], z[b + 4], z[b + 5], z[b + 6], z[b + 7]};
-        w[2 * h + q] = e2m1_pack8<false>(v, rcp);
+        w[2 * h + q] = e2m1_pack8<false, false>(v, rcp);
       }
       sbytes |= byte << (8 * h);
     }
@@ -893,8 +893,8 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
               silu4_f(zn[8 * g8 + j], zn[8 * g8 + j + 1], zn[8 * g8 + j + 2], zn[8 * g8 + j + 3]);
             const float v[8] = {zo[8 * g8], zo[8 * g8 + 1], zo[8 * g8 + 2], zo[8 * g8 + 3],
                                 zo[8 * g8 + 4], zo[8 * g8 + 5], zo[8 * g8 + 6], zo[8 * g8 + 7]};
-            if (kind_vec4(KIND)) w[g8] = e2m1_pack8<false>(v, g8 < 2 ? pend_rcp0 : pend_rcp1);
-            else w[g8] = e2m1_pack8<true>(v, pend_rcp0);
+            if (kind_vec4(KIND)) w[g8] = e2m1_pack8<false, false>(v, g8 < 2 ? pend_rcp0 : pend_rcp1);
+            else w[g8] = e2m1_pack8<true, false>(v, pend_rcp0);
           }
           pend_store(w);
           // the chunk just finished becomes the pending one
@@ -1193,8 +1193,8 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         for (int g8 = 0; g8 < 4; ++g8) {
           const float v[8] = {zb[8 * g8], zb[8 * g8 + 1], zb[8 * g8 + 2], zb[8 * g8 + 3],
                               zb[8 * g8 + 4], zb[8 * g8 + 5], zb[8 * g8 + 6], zb[8 * g8 + 7]};
-          if (kind_vec4(KIND)) w[g8] = e2m1_pack8<false>(v, g8 < 2 ? pend_rcp0 : pend_rcp1);
-          else w[g8] = e2m1_pack8<true>(v, pend_rcp0);
+          if (kind_vec4(KIND)) w[g8] = e2m1_pack8<false, false>(v, g8 < 2 ? pend_rcp0 : pend_rcp1);
+          else w[g8] = e2m1_pack8<true, false>(v, pend_rcp0);
         }
         pend_store(w);
       }

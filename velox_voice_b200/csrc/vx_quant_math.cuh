@@ -70,13 +70,17 @@ __device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
   return r;
 }
 constexpr float kTowardZero = 0.99999994f;  // 1 - 2^-24
-template <bool POW2>
+// CANON_ZERO = false skips the "+ (+0)": a product that is (or underflows to) -0 then encodes as
+// nibble 8 (-0) where the reference writes 0 -- the same value.  The GEMM epilogue uses it (its
+// inputs are -0 only for an exactly -0 pre-activation); the quantizers keep the reference's bytes.
+template <bool POW2, bool CANON_ZERO = true>
 __device__ __forceinline__ uint32_t e2m1_pack8(const float (&v)[8], float rcp) {
   const float m = POW2 ? __fmul_rn(rcp, kTowardZero) : rcp;
   float r[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    float q = __fadd_rn(__fmul_rn(v[j], m), 0.0f);  // -0 -> +0
+    float q = __fmul_rn(v[j], m);
+    if (CANON_ZERO) q = __fadd_rn(q, 0.0f);  // -0 -> +0
     if (!POW2) q = __fmul_rn(q, kTowardZero);
     r[j] = __uint_as_float(__float_as_uint(q) | 1u);
   }
