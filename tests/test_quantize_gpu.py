@@ -246,3 +246,40 @@ def test_two_layernorms_fused_equal_the_two_launches(fmt, dtype):
     assert torch.equal(q.scales, q_ref.scales)
     if q.sf is not None:
         assert torch.equal(q.sf, q_ref.sf)
+
+
+@pytest.mark.parametrize("fmt", ["mx32", "nv16"])
+def test_sf_rows_beyond_m_read_as_zero_on_recycled_memory(fmt):
+    """The SF atoms cover rows in tiles of 128; the rows between M and the next multiple of 128
+    must be zero whatever the buffer held before (the kernels clear them, no memset launch)."""
+    from velox_voice_b200 import ops
+
+    def poison(nbytes):
+        t = torch.full((nbytes,), 0xFF, dtype=torch.uint8, device="cuda")
+        torch.cuda.synchronize()
+        del t  # the caching allocator hands these bytes to the next torch.empty of that size
+
+    torch.manual_seed(3)
+    M, K, N = 300, 512, 256
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    g, b = torch.ones(K, device="cuda"), torch.zeros(K, device="cuda")
+    am = torch.tensor([8.0], device="cuda") if fmt == "nv16" else None
+    lib_sf = lambda rows, k: ((rows + 127) // 128) * int(ops._lib.load().vx_sf_kgroups(ops._fmt(fmt), k)) * 512
+
+    def check(q, rows):
+        sf = q.sf.view((rows + 127) // 128, -1, 32, 4, 4)  # [tile, kg, r % 32, (r / 32) % 4, kb % 4]
+        r = torch.arange(128, device="cuda")
+        pad = (r + 128 * ((rows - 1) // 128)) >= rows
+        last = sf[-1]  # [kg, 32, 4, 4]
+        by_row = last.permute(2, 1, 0, 3).reshape(128, -1)  # row = (r/32 % 4) * 32 + r % 32
+        assert int(by_row[pad].max()) == 0, "scale factors of rows beyond M are not zero"
+        assert int(by_row[~pad].max()) > 0
+
+    poison(lib_sf(M, K))
+    check(ops.quantize(x, fmt, natural=False, amax_t=am), M)
+    poison(lib_sf(M, K))
+    check(ops.ln_quantize(x, g, b, 1e-5, fmt, amax_t=am), M)
+    w = ops.quantize(0.05 * torch.randn(N, K, device="cuda"), fmt)
+    a = ops.quantize(x, fmt, amax_t=am)
+    poison(lib_sf(M, N))
+    check(ops.bsgemm(a, w, epilogue=ops.EPI_BIAS_SWISH, bias=torch.zeros(N, device="cuda"), out_fmt=fmt, out_amax=am), M)
