@@ -130,7 +130,7 @@ struct __align__(1024) SmemLayout {
   uint64_t tmem_empty[FP8_ACCS];
   uint64_t b_full;
   uint64_t sfb_done;   // sfb_resident: the scale-factor copies out of the borrowed ring slot are complete
-  uint64_t res_full[16];
+  uint64_t res_full[2][16];  // residual block landed, per buffer and epilogue warp
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -452,7 +452,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     }
     mbar_init(&sm.b_full, 1);
     mbar_init(&sm.sfb_done, 1);
-    for (int w = 0; w < 16; ++w) mbar_init(&sm.res_full[w], 1);
+    for (int w = 0; w < 16; ++w) { mbar_init(&sm.res_full[0][w], 1); mbar_init(&sm.res_full[1][w], 1); }
     sm.abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&tmap_a);
@@ -750,11 +750,13 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     if (p.out_amax) g_out = nv16_global(__ldg(p.out_amax));
     const int kb_count = FP8 ? p.k_stages : 0;
     uint8_t* const stage0 = sm.staging[ew];
-    uint8_t* const res_buf = stage0 + STAGING_BYTES / 2;  // residual block (second half)
+    // TMA residual: the two halves of the staging buffer alternate per 32-column chunk.  The
+    // residual block of chunk c lands in half c & 1, the result is formed in place and stored
+    // from there, while the block of chunk c + 1 is already in flight into the other half.
+    uint32_t res_chunk = 0;  // chunks consumed so far
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     const bool dbuf = out_dtype == VX_BF16 && !tma_residual;  // bf16 boxes alternate the two halves
     uint32_t store_count = 0;
-    uint32_t res_phase = 0;
     int bias_nb = -1;
     uint32_t best_key = 0;  // ARGMAX: best (value, column) of this thread's row in the current tile
     const float* const bias_base = p.bias ? sm.bias_s[ew] : nullptr;
@@ -765,11 +767,12 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     float* const sb_tab = sb_all + ((cc * 4 + q) * kb_count) * 32;
     float* const sb_gate = sb_all + ((((cc + 2) & 3) * 4 + q) * kb_count) * 32;
 
-    // residual block of (mb, tile column c0) -> res_buf (TMA, 32 rows x 32 bf16)
-    auto res_issue = [&](int mb_, int64_t out_col) {
+    // residual block of (mb, tile column c0) -> staging half `c & 1` (TMA, 32 rows x 32 bf16)
+    auto res_issue = [&](uint32_t c, int mb_, int64_t out_col) {
       if (lane == 0) {
-        mbar_expect_tx(&sm.res_full[ew], 32 * 64);
-        tma_load_2d(res_buf, &tmap_res, static_cast<int>(out_col), mb_ * BM + q * 32, &sm.res_full[ew]);
+        mbar_expect_tx(&sm.res_full[c & 1][ew], 32 * 64);
+        tma_load_2d(stage0 + (c & 1) * (STAGING_BYTES / 2), &tmap_res, static_cast<int>(out_col), mb_ * BM + q * 32,
+                    &sm.res_full[c & 1][ew]);
       }
     };
 
@@ -778,7 +781,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     bool res_inflight = false;
     if constexpr (EPI == VX_EPI_BIAS_RESIDUAL) {
       if (tma_residual && my_tiles > 0 && has_work) {
-        res_issue(mb, static_cast<int64_t>(nb) * OUT_TILE_COLS + col_base);
+        res_issue(0, mb, static_cast<int64_t>(nb) * OUT_TILE_COLS + col_base);
         res_inflight = true;
       }
     }
@@ -1073,26 +1076,26 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             }
           }
           const uint8_t* res_smem = nullptr;
-          if (res_inflight) {
-            if (!mbar_wait(&sm.res_full[ew], res_phase, p.status, 6)) { ok = false; break; }
-            res_phase ^= 1;
-            res_smem = res_buf;
+          uint8_t* const res_half = stage0 + (res_chunk & 1) * (STAGING_BYTES / 2);
+          if constexpr (EPI == VX_EPI_BIAS_RESIDUAL) {
+            if (res_inflight) {
+              // first send for the next block (second chunk of this tile, or the first chunk of
+              // the next tile): its half was last read by the store of the previous chunk
+              const bool more = h + 1 < NCH || it + 1 < my_tiles;
+              if (more) {
+                if (lane == 0) tma_store_wait_read<0>();
+                __syncwarp();
+                if (h + 1 < NCH) res_issue(res_chunk + 1, mb, out_col0 + 32);
+                else res_issue(res_chunk + 1, mb_next, static_cast<int64_t>(nb_next) * OUT_TILE_COLS + col_base);
+              }
+              if (!mbar_wait(&sm.res_full[res_chunk & 1][ew], (res_chunk >> 1) & 1, p.status, 6)) { ok = false; break; }
+              res_smem = res_half;
+            }
           }
           if (tr && h == 0 && !FP8) trace_rec(p, 2, it, 3);
           ChunkOut<EPI, OUT == 1>::apply(p, z[h], gate, row, bias_base ? bias_base + h * 32 : nullptr, bias_base + 32, out_col0,
                                row_ok, res_smem, lane);
           if (tr && h == 0 && !FP8) trace_rec(p, 2, it, 4);
-          if constexpr (EPI == VX_EPI_BIAS_RESIDUAL) {
-            if (res_inflight) {
-              // the block has been consumed: fetch the next one (second chunk of this tile, or
-              // the first chunk of the next tile) into the same buffer
-              fence_proxy_async_smem();
-              __syncwarp();
-              if (h + 1 < NCH) res_issue(mb, out_col0 + 32);
-              else if (it + 1 < my_tiles) res_issue(mb_next, static_cast<int64_t>(nb_next) * OUT_TILE_COLS + col_base);
-              else res_inflight = false;
-            }
-          }
 
           if constexpr (EPI == VX_EPI_BIAS_ARGMAX) {
             // key: order-preserving bits of bf16(z) (high half) | 0xFFFF - tile column (low half)
@@ -1135,7 +1138,10 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
           } else if (tma_store) {
             // stage 32 rows x 32 columns (swizzled like the tensor map), then one TMA store
             uint8_t* buf = stage0;
-            if (dbuf) {
+            if (res_smem) {
+              buf = res_half;  // in place over the residual block (same box layout); its previous
+                               // store was waited for before that block was requested
+            } else if (dbuf) {
               if (lane == 0) tma_store_wait_read<1>();  // the box staged two stores ago has left
               buf = stage0 + (store_count & 1) * (STAGING_BYTES / 2);
             } else {
@@ -1172,6 +1178,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
           } else if (row_ok) {
             store_chunk_direct(p, z[h], row, out_col0, n_out);
           }
+          if (EPI == VX_EPI_BIAS_RESIDUAL && res_inflight) ++res_chunk;
         }
       }
       if constexpr (EPI == VX_EPI_BIAS_ARGMAX) {
