@@ -164,6 +164,18 @@ int vx_bsgemm(const vx_gemm_desc* desc, void* stream);
  * into ids i32 [M] and, when max_out != NULL, the winning logits f32 [M]. */
 int vx_argmax_ids(const void* keys, int64_t M, int32_t* ids, float* max_out, void* stream);
 
+/* Attention fold pack in one pass: replaces velox_qkv_pack
+ * (veloxvoice/kernels/csrc/velox_qkv_pack.cu:34-97; Python wrapper qkv_pack in
+ * veloxvoice/kernels/ops/cuda_ops.py:554-581), i.e. the torch fold chain of
+ * veloxvoice/models/wenet/torch_conformer.py:488-510.
+ *   qkv bf16 [T, 3d] (q | k | v per token, row stride ld_qkv elements), p0 bf16 [T, d] (lp(pos_emb)),
+ *   pos_u / pos_v bf16 [heads, head_dim], scale f32;
+ *   q2 = bf16(bf16(q + u) * scale) | bf16(bf16(q + v) * scale),  k2 = k | p0,  v2 = v | 0,
+ *   each bf16 [heads, T, 2 head_dim] contiguous.  d = heads * head_dim, head_dim % 8 == 0. */
+int vx_qkv_pack(const void* qkv, int64_t ld_qkv, const void* p0, int64_t ld_p0, const void* pos_u,
+                const void* pos_v, float scale, int64_t T, int heads, int head_dim, void* q2, void* k2,
+                void* v2, void* stream);
+
 /* Block-scaled FP4 GEMM for callers that cannot allocate device memory.  (No counterpart in
  * the reference: its Python wrappers allocate through torch.)
  *

@@ -124,3 +124,32 @@ def layernorm_ref(x, gamma, beta, eps: float = 1e-5) -> np.ndarray:
     y = (y * rstd[:, None]).astype(np.float32)
     y = (y * g).astype(np.float32)
     return (y + b).astype(np.float32)
+
+
+def qkv_pack_ref(qkv, p0, pos_u, pos_v, scale: float, heads: int):
+    """The attention fold chain behind the fused QKV projection, in bf16 like the model runs it.
+
+    ``veloxvoice/models/wenet/torch_conformer.py:488-510`` (torch ops) and its single-pass
+    kernel ``veloxvoice/kernels/csrc/velox_qkv_pack.cu:34-97``:
+
+        q2 = cat([q + pos_u, q + pos_v], -1) * scale     k2 = cat([k, p0], -1)     v2 = cat([v, 0], -1)
+
+    with q | k | v the thirds of ``qkv`` [T, 3d] split into ``heads`` heads; every elementwise
+    result is rounded to bf16 (the sum, then the product).  Inputs are arrays of bf16-valued
+    numbers; returns three float32 arrays [heads, T, 2 dk] of bf16-valued numbers.
+    """
+    qkv = np.asarray(qkv, dtype=np.float32)
+    T, d3 = qkv.shape
+    d = d3 // 3
+    dk = d // heads
+    u = np.asarray(pos_u, dtype=np.float32).reshape(heads, 1, dk)
+    v = np.asarray(pos_v, dtype=np.float32).reshape(heads, 1, dk)
+    split = lambda a: a.reshape(T, heads, dk).transpose(1, 0, 2)  # [h, T, dk]
+    q, k, vv = split(qkv[:, :d]), split(qkv[:, d:2 * d]), split(qkv[:, 2 * d:])
+    s = F32(scale)
+    qa = to_bf16((to_bf16(q + u) * s).astype(np.float32))
+    qb = to_bf16((to_bf16(q + v) * s).astype(np.float32))
+    q2 = np.concatenate([qa, qb], axis=-1)
+    k2 = np.concatenate([k, split(np.asarray(p0, dtype=np.float32))], axis=-1)
+    v2 = np.concatenate([vv, np.zeros_like(vv)], axis=-1)
+    return q2, k2, v2

@@ -46,6 +46,7 @@ EXPORTS = (
     "vx_blkscale_gemm_noalloc",
     "vx_glu_tile",
     "vx_argmax_ids",
+    "vx_qkv_pack",
 )
 
 
@@ -134,6 +135,8 @@ def load(build_if_missing: bool = True) -> C.CDLL:
         lib.vx_blkscale_gemm_noalloc.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, vp]
         lib.vx_glu_tile.restype = i32
         lib.vx_glu_tile.argtypes = [i32]
+        lib.vx_qkv_pack.restype = i32
+        lib.vx_qkv_pack.argtypes = [vp, i64, vp, i64, vp, vp, f32, i64, i32, i32, vp, vp, vp, vp]
         lib.vx_argmax_ids.restype = i32
         lib.vx_argmax_ids.argtypes = [vp, i64, vp, vp, vp]
         lib.vx_set_trace_buffer.restype = i32

@@ -8,7 +8,8 @@
   ``veloxvoice/kernels/ops/triton_ops.py:132``);
 * ``veloxvoice.kernels.ops.cuda_ops`` / ``veloxvoice.kernels.ops``: ``dgx_mxfp4_gemm``,
   ``dgx_mxfp4_blkscale_gemm``, ``mxfp4_gemm``, ``nvfp4_linear``, ``_dequantize_to_bf16`` are
-  replaced (the reference's build of them raises off sm_121a, ``cuda_ops.py:591-597``);
+  replaced (the reference's build of them raises off sm_121a, ``cuda_ops.py:591-597``), and
+  ``qkv_pack`` (``cuda_ops.py:554-581``) runs on this library's kernel;
 * ``veloxvoice.models.wenet.mxfp4_linear`` -> provides ``_pad16``, which
   ``DenseLinear._prequantize_weight`` imports (``torch_conformer.py:222-226``) from a module
   the reference tree does not contain;
@@ -32,7 +33,8 @@ _OPS_PKG = "veloxvoice.kernels.ops"
 _MXFP4_LINEAR = "veloxvoice.models.wenet.mxfp4_linear"
 _NVFP4_LINEAR = "veloxvoice.models.wenet.nvfp4_linear"
 
-GEMM_NAMES = ("dgx_mxfp4_gemm", "dgx_mxfp4_blkscale_gemm", "mxfp4_gemm", "nvfp4_linear", "_dequantize_to_bf16")
+GEMM_NAMES = ("dgx_mxfp4_gemm", "dgx_mxfp4_blkscale_gemm", "mxfp4_gemm", "nvfp4_linear", "_dequantize_to_bf16",
+              "qkv_pack")
 QUANT_NAMES = ("per_row_col_quantize", "triton_quantize_w", "mxfp4_block_quantize", "mxfp4_dequant")
 
 

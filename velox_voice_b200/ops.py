@@ -431,6 +431,31 @@ def bsgemm_argmax(a: Quantized, b: Quantized, bias: Optional[torch.Tensor] = Non
     return (ids, vmax) if return_max else ids
 
 
+def qkv_pack(qkv: torch.Tensor, p0: torch.Tensor, pos_u: torch.Tensor, pos_v: torch.Tensor, scale: float):
+    """Single-pass attention fold pack, signature of the reference's ``qkv_pack``
+    (``veloxvoice/kernels/ops/cuda_ops.py:554-581``): qkv bf16 [T, 3d], p0 bf16 [T, d],
+    pos_u / pos_v [h, dk] -> (q2, k2, v2) bf16 [h, T, 2 dk] each."""
+    _require_cuda(qkv, "qkv")
+    if qkv.dtype != torch.bfloat16 or p0.dtype != torch.bfloat16:
+        raise ValueError("qkv and p0 must be bfloat16")
+    T, d3 = qkv.shape
+    d = d3 // 3
+    h = pos_u.shape[0]
+    dk = d // h
+    if d * 3 != d3 or h * dk != d or p0.shape != (T, d):
+        raise ValueError("shapes: qkv [T, 3 h dk], p0 [T, h dk], pos_u / pos_v [h, dk]")
+    qkv, p0 = _rows2d(qkv, "qkv"), _rows2d(p0, "p0")
+    u = pos_u.to(torch.bfloat16).contiguous()
+    v = pos_v.to(torch.bfloat16).contiguous()
+    packed = torch.empty((3, h, T, 2 * dk), dtype=torch.bfloat16, device=qkv.device)
+    rc = _lib.load().vx_qkv_pack(qkv.data_ptr(), qkv.stride(0), p0.data_ptr(), p0.stride(0), u.data_ptr(), v.data_ptr(),
+                                 float(scale), T, h, dk, packed[0].data_ptr(), packed[1].data_ptr(), packed[2].data_ptr(),
+                                 _stream())
+    _lib.check(rc, "vx_qkv_pack")
+    _count()
+    return packed[0], packed[1], packed[2]
+
+
 def mma_peak_tflops(kind: str = "fp4", n_tile: int = 256, iters: int = 4096) -> float:
     """Measured tensor-core rate of back-to-back MMAs without memory traffic (dense TFLOP/s)."""
     out = C.c_float(0.0)
