@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define VX_ABI_VERSION 1
+#define VX_ABI_VERSION 2
 
 /* Quantization formats.  values / scale / natural scale layout
  *  ROWSCALE   E2M1, one UE8M0 per row                      u8 [R]
@@ -48,8 +48,12 @@ enum vx_epilogue {
   VX_EPI_BIAS_SWISH = 2,/* out = silu(acc + bias[n])                 */
   VX_EPI_BIAS_GLU = 3,  /* out[:, j] = (acc_a + b_a) * sigmoid(acc_b + b_b), GLU-interleaved weights */
   VX_EPI_BIAS_RESIDUAL = 4, /* out = residual + alpha * (acc + bias[n]) */
-  VX_EPI_BIAS_ARGMAX = 5 /* no [M, N] output: per row the first column holding the maximum of
+  VX_EPI_BIAS_ARGMAX = 5, /* no [M, N] output: per row the first column holding the maximum of
                             bf16(acc + bias[n]); `out` = u64 keys [M], see vx_argmax_ids */
+  VX_EPI_BIAS_QKVPACK = 6 /* fused QKV projection written as the attention fold pack (vx_qkv_pack):
+                            N = 3 * heads * head_dim, `out` = bf16 [3 * heads, M, 2 * head_dim]
+                            (q2 | k2 | v2); the second half of k2 is left for the positional
+                            projection, see VX_GEMM_OUT_HEADS */
 };
 
 /* Scale factors in the layout the block-scaled tensor-core MMA consumes ("SF atoms"):
@@ -141,6 +145,12 @@ typedef struct vx_gemm_desc {
   void* out_scales_sf;  /* FP4 output: SF atoms of the output rows */
   void* out_scales;     /* FP4 output: natural layout, may be NULL */
   const float* out_amax;/* FP4 NV16 output: f32[1] static tensor amax */
+  int32_t heads;        /* BIAS_QKVPACK / VX_GEMM_OUT_HEADS: number of attention heads */
+  int32_t head_dim;     /*   columns per head (multiple of 32) */
+  const void* pos_u;    /* BIAS_QKVPACK: bf16 [heads, head_dim] positional biases */
+  const void* pos_v;
+  float qk_scale;       /* BIAS_QKVPACK: scale applied to q + bias */
+  int32_t head_col_off; /* VX_GEMM_OUT_HEADS: first column inside the head row (0 or head_dim) */
 } vx_gemm_desc;
 
 /* VX_EPI_BIAS_GLU expects the rows of B (and the bias) interleaved per tile of vx_glu_tile(fmt)
@@ -153,6 +163,10 @@ int vx_glu_tile(int fmt);
 #define VX_GEMM_STREAM_B 2     /* never keep the B tile resident in shared memory */
 #define VX_GEMM_WIDE_TILES 4   /* FP4: force the 128 x 256 single-accumulator tile */
 #define VX_GEMM_NARROW_TILES 8 /* FP4: force the 128 x 128 double-accumulator tile (not for GLU) */
+#define VX_GEMM_OUT_HEADS 16   /* bf16 output written head-major: `out` = [heads, M, ldo], column n goes to
+                                  out[n / head_dim][m][head_col_off + n % head_dim]; N = heads * head_dim.
+                                  With head_col_off = head_dim and out = the k2 third of a BIAS_QKVPACK
+                                  buffer this is where lp(pos_emb) belongs (torch_conformer.py:472,507) */
 
 int vx_bsgemm(const vx_gemm_desc* desc, void* stream);
 

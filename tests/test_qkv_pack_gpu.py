@@ -40,3 +40,36 @@ def test_qkv_pack_takes_a_strided_qkv():
     b = ops.qkv_pack(qkv.cuda(), p0.cuda(), u.cuda(), v.cuda(), scale)
     for x, y in zip(a, b):
         assert torch.equal(x, y)
+
+
+@pytest.mark.parametrize("fmt", ["mx32", "nv16", "fp8_1x128"])
+@pytest.mark.parametrize("T", [300, 1000])
+def test_fused_qkv_projection_writes_the_fold_pack(fmt, T):
+    """QKV GEMM with the pack epilogue + the positional projection written head-major ==
+    qkv_pack of the same two GEMMs' ordinary bf16 outputs, bit for bit."""
+    from velox_voice_b200 import ops
+
+    torch.manual_seed(4)
+    h, dk, K = 8, 64, 512
+    d = h * dk
+    x = torch.randn(T, K, device="cuda").bfloat16()
+    pos = torch.randn(T, K, device="cuda").bfloat16()
+    wqkv = 0.05 * torch.randn(3 * d, K, device="cuda")
+    wlp = 0.05 * torch.randn(d, K, device="cuda")
+    bias = 0.1 * torch.randn(3 * d, device="cuda")
+    u, v = torch.randn(h, dk, device="cuda").bfloat16(), torch.randn(h, dk, device="cuda").bfloat16()
+    am = {"amax_t": torch.tensor([6.0], device="cuda")} if fmt == "nv16" else {}
+    a, ap = ops.quantize(x, fmt, **am), ops.quantize(pos, fmt, **am)
+    wq, wl = ops.quantize(wqkv, fmt), ops.quantize(wlp, fmt)
+    scale = dk ** -0.5
+
+    qkv = ops.bsgemm(a, wq, epilogue=ops.EPI_BIAS, bias=bias, out_dtype=torch.bfloat16)
+    p0 = ops.bsgemm(ap, wl, out_dtype=torch.bfloat16)
+    want = ops.qkv_pack(qkv, p0, u, v, scale)
+
+    packed = torch.full((3, h, T, 2 * dk), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.bsgemm_qkv_pack(a, wq, bias, u, v, scale, packed=packed)
+    ops.bsgemm_heads(ap, wl, None, packed[1], col_off=dk)
+    torch.cuda.synchronize()
+    for i, name in enumerate(("q2", "k2", "v2")):
+        assert torch.equal(packed[i], want[i]), name

@@ -23,11 +23,13 @@ FMT_BY_NAME = {
     "fp8_1x128": FMT_FP8_1X128,
 }
 DT_F32, DT_BF16, DT_FP4 = 0, 1, 2
-EPI_NONE, EPI_BIAS, EPI_BIAS_SWISH, EPI_BIAS_GLU, EPI_BIAS_RESIDUAL, EPI_BIAS_ARGMAX = range(6)
+ABI_VERSION = 2  # VX_ABI_VERSION of include/velox_b200.h
+EPI_NONE, EPI_BIAS, EPI_BIAS_SWISH, EPI_BIAS_GLU, EPI_BIAS_RESIDUAL, EPI_BIAS_ARGMAX, EPI_BIAS_QKVPACK = range(7)
 GEMM_DIRECT_STORE = 1
 GEMM_STREAM_B = 2
 GEMM_WIDE_TILES = 4
 GEMM_NARROW_TILES = 8
+GEMM_OUT_HEADS = 16
 
 EXPORTS = (
     "vx_abi_version",
@@ -81,6 +83,12 @@ class GemmDesc(C.Structure):
         ("out_scales_sf", C.c_void_p),
         ("out_scales", C.c_void_p),
         ("out_amax", C.c_void_p),
+        ("heads", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("pos_u", C.c_void_p),
+        ("pos_v", C.c_void_p),
+        ("qk_scale", C.c_float),
+        ("head_col_off", C.c_int32),
     ]
 
 
@@ -143,7 +151,7 @@ def load(build_if_missing: bool = True) -> C.CDLL:
         lib.vx_set_trace_buffer.argtypes = [vp, i64]
         lib.vx_mma_peak_probe.restype = i32
         lib.vx_mma_peak_probe.argtypes = [i32, i32, i32, C.POINTER(C.c_float)]
-        if lib.vx_abi_version() != 1:
+        if lib.vx_abi_version() != ABI_VERSION:
             raise RuntimeError("libvelox_b200.so: ABI version mismatch")
         _lib = lib
         return lib

@@ -114,6 +114,11 @@ struct GemmParams {
   uint8_t* out_scales;
   int64_t out_sf_kg;
   const float* out_amax;
+  // head-major bf16 output (attention fold pack)
+  int heads, head_dim, head_col_off;
+  const __nv_bfloat16* pos_u;
+  const __nv_bfloat16* pos_v;
+  float qk_scale;
   int* status;
 };
 
@@ -1097,7 +1102,71 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                                row_ok, res_smem, lane);
           if (tr && h == 0 && !FP8) trace_rec(p, 2, it, 4);
 
-          if constexpr (EPI == VX_EPI_BIAS_ARGMAX) {
+          if constexpr (EPI == VX_EPI_BIAS_QKVPACK) {
+            // Attention fold pack: this 32-column chunk lies inside one head of q, k or v.
+            //   q: two boxes, bf16(bf16(q + u) * scale) and bf16(bf16(q + v) * scale) side by side;
+            //   k: one box (the other half of the head row belongs to the positional projection);
+            //   v: one box and a box of zeros.
+            const int dk = p.head_dim;
+            const int d_model = p.heads * dk;
+            const int part = static_cast<int>(out_col0) / d_model;
+            const int within = static_cast<int>(out_col0) - part * d_model;
+            const int hh = within / dk, j0 = within - hh * dk;
+            auto rnd = [](float x) { return __bfloat162float(__float2bfloat16_rn(x)); };
+            auto stage_bf16 = [&](uint8_t* buf, const float (&v)[32]) {
+#pragma unroll
+              for (int v4 = 0; v4 < 4; ++v4) {
+                uint4 u;
+                u.x = pack_bf16x2(v[8 * v4], v[8 * v4 + 1]);
+                u.y = pack_bf16x2(v[8 * v4 + 2], v[8 * v4 + 3]);
+                u.z = pack_bf16x2(v[8 * v4 + 4], v[8 * v4 + 5]);
+                u.w = pack_bf16x2(v[8 * v4 + 6], v[8 * v4 + 7]);
+                *reinterpret_cast<uint4*>(buf + lane * 64 + ((v4 ^ ((lane >> 1) & 3)) << 4)) = u;
+              }
+            };
+            // bias vector (32 bf16, the same for every lane) -> fp32
+            auto load_bias32 = [&](const __nv_bfloat16* src, float (&b)[32]) {
+#pragma unroll
+              for (int v4 = 0; v4 < 4; ++v4) {
+                const uint4 w = __ldg(reinterpret_cast<const uint4*>(src) + v4);
+                const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  b[8 * v4 + 2 * j] = __uint_as_float(ww[j] << 16);
+                  b[8 * v4 + 2 * j + 1] = __uint_as_float(ww[j] & 0xffff0000u);
+                }
+              }
+            };
+            if (lane == 0) tma_store_wait_read<0>();
+            __syncwarp();
+            uint8_t* const buf_a = stage0;
+            uint8_t* const buf_b = stage0 + STAGING_BYTES / 2;
+            if (part == 0) {
+              float b[32], o[32];
+              load_bias32(p.pos_u + within, b);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __fmul_rn(rnd(__fadd_rn(rnd(z[h][i]), b[i])), p.qk_scale);
+              stage_bf16(buf_a, o);
+              load_bias32(p.pos_v + within, b);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __fmul_rn(rnd(__fadd_rn(rnd(z[h][i]), b[i])), p.qk_scale);
+              stage_bf16(buf_b, o);
+            } else {
+              stage_bf16(buf_a, z[h]);
+              if (part == 2) {
+#pragma unroll
+                for (int v4 = 0; v4 < 4; ++v4) *reinterpret_cast<uint4*>(buf_b + lane * 64 + (v4 << 4)) = make_uint4(0, 0, 0, 0);
+              }
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0 && box_ok) {
+              const int zc = part * p.heads + hh;
+              tma_store_3d(&tmap_out, j0, mb * BM + q * 32, zc, buf_a);
+              if (part != 1) tma_store_3d(&tmap_out, dk + j0, mb * BM + q * 32, zc, buf_b);
+              tma_store_commit();
+            }
+          } else if constexpr (EPI == VX_EPI_BIAS_ARGMAX) {
             // key: order-preserving bits of bf16(z) (high half) | 0xFFFF - tile column (low half)
             const uint32_t cbase = 0xffffu - static_cast<uint32_t>(col_base + h * 32);
             const int valid = p.N - acc_col0 >= 32 ? 32 : static_cast<int>(p.N - acc_col0);
@@ -1171,7 +1240,13 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             __syncwarp();
             if (tr && h == 0 && !FP8) trace_rec(p, 2, it, 5);
             if (lane == 0 && box_ok) {
-              tma_store_2d(&tmap_out, static_cast<int>(out_col0), mb * BM + q * 32, buf);
+              if (p.heads > 0) {  // head-major: [head][row][head_col_off + column inside the head]
+                const int hh = static_cast<int>(out_col0) / p.head_dim;
+                tma_store_3d(&tmap_out, p.head_col_off + static_cast<int>(out_col0) - hh * p.head_dim, mb * BM + q * 32,
+                             hh, buf);
+              } else {
+                tma_store_2d(&tmap_out, static_cast<int>(out_col0), mb * BM + q * 32, buf);
+              }
               tma_store_commit();
             }
             if (tr && h == 0) trace_rec(p, 2, it, FP8 ? 7 : 6);
@@ -1328,6 +1403,22 @@ int make_tmap(CUtensorMap* m, CUtensorMapDataType dt, int elt, const void* ptr, 
   return 0;
 }
 
+// 3-D bf16 tensor [z][rows][cols] (cols contiguous, row pitch `cols` elements): boxes of
+// 32 columns x 32 rows x 1, 64-byte swizzle -- the head-major output of the attention fold pack.
+int make_tmap_heads(CUtensorMap* m, const void* ptr, int64_t zdim, int64_t rows, int64_t cols) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return fail(-2, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(zdim)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(cols * 2), static_cast<cuuint64_t>(rows * cols * 2)};
+  const cuuint32_t box[3] = {32, 32, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(-3, "cuTensorMapEncodeTiled (3-D) failed (%d)", static_cast<int>(r));
+  return 0;
+}
+
 int* cached_status_ptr() {
   static int* cache[64] = {};
   int dev = 0;
@@ -1438,6 +1529,7 @@ int dispatch_epi(int epi, int out, const CUtensorMap& ta, const CUtensorMap& tb,
     case VX_EPI_BIAS_GLU: return dispatch_out<KIND, VX_EPI_BIAS_GLU>(out, ta, tb, to, tr, p, res, st);
     case VX_EPI_BIAS_RESIDUAL: return dispatch_out<KIND, VX_EPI_BIAS_RESIDUAL>(out, ta, tb, to, tr, p, res, st);
     case VX_EPI_BIAS_ARGMAX: return dispatch_out<KIND, VX_EPI_BIAS_ARGMAX>(out, ta, tb, to, tr, p, res, st);
+    case VX_EPI_BIAS_QKVPACK: return launch<KIND, VX_EPI_BIAS_QKVPACK, 1>(ta, tb, to, tr, p, res, st);
     default: return fail(-1, "unknown epilogue %d", epi);
   }
 }
@@ -1472,8 +1564,27 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
   if (fmt_has_sf(fmt) && (!aligned16(d->a_scales) || !aligned16(d->b_scales)))
     return fail(-1, "SF atoms must be 16-byte aligned");
   const int epi = d->epilogue;
-  if (epi < VX_EPI_NONE || epi > VX_EPI_BIAS_ARGMAX) return fail(-1, "unknown epilogue %d", epi);
+  if (epi < VX_EPI_NONE || epi > VX_EPI_BIAS_QKVPACK) return fail(-1, "unknown epilogue %d", epi);
   const bool argmax = epi == VX_EPI_BIAS_ARGMAX;
+  const bool qkvpack = epi == VX_EPI_BIAS_QKVPACK;
+  const bool out_heads = (d->flags & VX_GEMM_OUT_HEADS) != 0;
+  if (qkvpack || out_heads) {
+    if (d->heads <= 0 || d->head_dim <= 0 || d->head_dim % 32 != 0)
+      return fail(-1, "head-major output needs heads > 0 and head_dim %% 32 == 0");
+    if (d->out_dtype != VX_BF16 || !aligned16(d->out)) return fail(-1, "head-major output is bf16, 16-byte aligned");
+    if (d->flags & VX_GEMM_DIRECT_STORE) return fail(-1, "head-major output goes through TMA stores only");
+    if (qkvpack) {
+      if (N != 3ll * d->heads * d->head_dim) return fail(-1, "BIAS_QKVPACK needs N = 3 * heads * head_dim");
+      if (!d->pos_u || !d->pos_v || !aligned16(d->pos_u) || !aligned16(d->pos_v))
+        return fail(-1, "BIAS_QKVPACK needs pos_u / pos_v (bf16, 16-byte aligned)");
+      if (out_heads) return fail(-1, "VX_GEMM_OUT_HEADS does not combine with BIAS_QKVPACK");
+    } else {
+      if (epi != VX_EPI_NONE && epi != VX_EPI_BIAS) return fail(-1, "VX_GEMM_OUT_HEADS supports NONE / BIAS");
+      if (N != static_cast<int64_t>(d->heads) * d->head_dim) return fail(-1, "VX_GEMM_OUT_HEADS needs N = heads * head_dim");
+      if (d->head_col_off < 0 || d->head_col_off % 8 != 0 || d->ldo % 8 != 0 || d->ldo < d->head_col_off + d->head_dim)
+        return fail(-1, "VX_GEMM_OUT_HEADS: head_col_off / ldo must be multiples of 8 and ldo >= head_col_off + head_dim");
+    }
+  }
   if (argmax && (reinterpret_cast<uintptr_t>(d->out) & 7)) return fail(-1, "argmax keys must be 8-byte aligned");
   if (argmax && N > 0xffffffffll) return fail(-1, "argmax needs N < 2^32");
   if (d->out_dtype != VX_F32 && d->out_dtype != VX_BF16 && d->out_dtype != VX_FP4)
@@ -1532,7 +1643,14 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
   p.residual = d->residual; p.residual_dtype = d->residual_dtype; p.ldr = d->ldr; p.alpha = d->alpha;
   p.status = cached_status_ptr();
 
-  if (argmax) {
+  if (qkvpack || out_heads) {
+    p.heads = d->heads;
+    p.head_dim = d->head_dim;
+    p.head_col_off = qkvpack ? 0 : d->head_col_off;
+    p.pos_u = static_cast<const __nv_bfloat16*>(d->pos_u);
+    p.pos_v = static_cast<const __nv_bfloat16*>(d->pos_v);
+    p.qk_scale = d->qk_scale;
+  } else if (argmax) {
     p.out_dtype = VX_F32;
   } else if (d->out_dtype == VX_FP4) {
     if (d->out_fmt != VX_FMT_MX32 && d->out_fmt != VX_FMT_NV16) return fail(-1, "FP4 output: out_fmt must be MX32 or NV16");
@@ -1565,7 +1683,12 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
   if (rc) return rc;
   const int oelt = d->out_dtype == VX_BF16 ? 2 : 4;
   p.tma_store = 0;
-  if (!argmax && d->out_dtype != VX_FP4 && !(d->flags & VX_GEMM_DIRECT_STORE) && aligned16(d->out) &&
+  if (qkvpack || out_heads) {
+    rc = qkvpack ? make_tmap_heads(&to, d->out, 3ll * d->heads, M, 2ll * d->head_dim)
+                 : make_tmap_heads(&to, d->out, d->heads, M, d->ldo);
+    if (rc) return rc;
+    p.tma_store = 1;
+  } else if (!argmax && d->out_dtype != VX_FP4 && !(d->flags & VX_GEMM_DIRECT_STORE) && aligned16(d->out) &&
       (d->ldo * oelt) % 16 == 0) {
     rc = make_tmap(&to, d->out_dtype == VX_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
                    oelt, d->out, M, n_out, d->ldo * oelt, 32, 32,

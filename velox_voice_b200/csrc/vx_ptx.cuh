@@ -135,6 +135,14 @@ __device__ __forceinline__ void tma_store_2d(const void* tmap, int x, int y, con
       "r"(x), "r"(y), "r"(smem_u32(smem_src))
       : "memory");
 }
+// 3-D tiled store shared -> global (x innermost).
+__device__ __forceinline__ void tma_store_3d(const void* tmap, int x, int y, int z, const void* smem_src) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(
+          reinterpret_cast<uint64_t>(tmap)),
+      "r"(x), "r"(y), "r"(z), "r"(smem_u32(smem_src))
+      : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }

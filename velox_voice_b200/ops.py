@@ -30,6 +30,7 @@ from ._lib import (  # noqa: F401  (re-exported)
     EPI_BIAS,
     EPI_BIAS_ARGMAX,
     EPI_BIAS_GLU,
+    EPI_BIAS_QKVPACK,
     EPI_BIAS_RESIDUAL,
     EPI_BIAS_SWISH,
     EPI_NONE,
@@ -42,6 +43,7 @@ from ._lib import (  # noqa: F401  (re-exported)
     FMT_ROWSCALE,
     GEMM_DIRECT_STORE,
     GEMM_NARROW_TILES,
+    GEMM_OUT_HEADS,
     GEMM_STREAM_B,
     GEMM_WIDE_TILES,
 )
@@ -454,6 +456,76 @@ def qkv_pack(qkv: torch.Tensor, p0: torch.Tensor, pos_u: torch.Tensor, pos_v: to
     _lib.check(rc, "vx_qkv_pack")
     _count()
     return packed[0], packed[1], packed[2]
+
+
+def bsgemm_qkv_pack(a: Quantized, w_qkv: Quantized, bias: Optional[torch.Tensor], pos_u: torch.Tensor,
+                    pos_v: torch.Tensor, scale: float, *, packed: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Fused QKV projection written straight into the attention fold pack (``qkv_pack`` of the
+    bf16 projection, without the [T, 3d] intermediate).  Returns bf16 [3, h, T, 2 dk]:
+    ``packed[0]`` = q2, ``packed[1]`` = k2 (second half of every head row NOT written: it belongs
+    to ``bsgemm_heads(pos, lp, out=packed[1], col_off=dk)``), ``packed[2]`` = v2."""
+    h, dk = pos_u.shape
+    M, N, K = a.rows, w_qkv.rows, a.k
+    if N != 3 * h * dk or a.k != w_qkv.k or a.fmt != w_qkv.fmt:
+        raise ValueError("w_qkv must be [3 h dk, K] in the format of the activations")
+    dev = a.codes.device
+    if packed is None:
+        packed = torch.empty((3, h, M, 2 * dk), dtype=torch.bfloat16, device=dev)
+    if packed.shape != (3, h, M, 2 * dk) or packed.dtype != torch.bfloat16 or not packed.is_contiguous():
+        raise ValueError("packed must be a contiguous bf16 [3, h, M, 2 dk] tensor")
+    u = pos_u.to(torch.bfloat16).contiguous()
+    v = pos_v.to(torch.bfloat16).contiguous()
+    d = _lib.GemmDesc()
+    d.struct_size = C.sizeof(_lib.GemmDesc)
+    d.fmt = a.fmt
+    d.M, d.N, d.K = M, N, K
+    d.a_codes, d.lda = a.codes.data_ptr(), a.codes.stride(0)
+    d.b_codes, d.ldb = w_qkv.codes.data_ptr(), w_qkv.codes.stride(0)
+    sa, sb = a.gemm_scales(), w_qkv.gemm_scales()
+    d.a_scales, d.b_scales = sa.data_ptr(), sb.data_ptr()
+    if a.fmt == FMT_NV16:
+        d.a_amax, d.b_amax = a.amax.data_ptr(), w_qkv.amax.data_ptr()
+    d.epilogue = EPI_BIAS_QKVPACK
+    if bias is not None:
+        d.bias = bias.data_ptr()
+    d.out_dtype, d.out, d.ldo = DT_BF16, packed.data_ptr(), 2 * dk
+    d.heads, d.head_dim = h, dk
+    d.pos_u, d.pos_v, d.qk_scale = u.data_ptr(), v.data_ptr(), float(scale)
+    _lib.check(_lib.load().vx_bsgemm(C.byref(d), _stream()), "vx_bsgemm")
+    _count()
+    del sa, sb, u, v
+    return packed
+
+
+def bsgemm_heads(a: Quantized, w: Quantized, bias: Optional[torch.Tensor], out: torch.Tensor, *, col_off: int = 0):
+    """``A . W^T (+ bias)`` written head-major: ``out`` bf16 [h, M, width], result column n goes to
+    ``out[n // dk, m, col_off + n % dk]`` with dk = N / h.  With ``out = packed[1]`` and
+    ``col_off = dk`` this puts lp(pos_emb) where the attention fold pack wants it."""
+    h, M, width = out.shape
+    N = w.rows
+    dk = N // h
+    if M != a.rows or h * dk != N or out.dtype != torch.bfloat16 or not out.is_contiguous():
+        raise ValueError("out must be a contiguous bf16 [h, M, width] tensor with N = h * dk")
+    d = _lib.GemmDesc()
+    d.struct_size = C.sizeof(_lib.GemmDesc)
+    d.fmt = a.fmt
+    d.M, d.N, d.K = M, N, a.k
+    d.a_codes, d.lda = a.codes.data_ptr(), a.codes.stride(0)
+    d.b_codes, d.ldb = w.codes.data_ptr(), w.codes.stride(0)
+    sa, sb = a.gemm_scales(), w.gemm_scales()
+    d.a_scales, d.b_scales = sa.data_ptr(), sb.data_ptr()
+    if a.fmt == FMT_NV16:
+        d.a_amax, d.b_amax = a.amax.data_ptr(), w.amax.data_ptr()
+    d.epilogue = EPI_BIAS if bias is not None else EPI_NONE
+    if bias is not None:
+        d.bias = bias.data_ptr()
+    d.out_dtype, d.out, d.ldo = DT_BF16, out.data_ptr(), width
+    d.heads, d.head_dim, d.head_col_off = h, dk, col_off
+    d.flags = GEMM_OUT_HEADS
+    _lib.check(_lib.load().vx_bsgemm(C.byref(d), _stream()), "vx_bsgemm")
+    _count()
+    del sa, sb
+    return out
 
 
 def mma_peak_tflops(kind: str = "fp4", n_tile: int = 256, iters: int = 4096) -> float:
