@@ -2,10 +2,11 @@
 """Benchmark of the quantized-linear path: encoder frames per second of the full linear stack.
 
 A step = one pass of the MXFP4 encoder linear stack (12 Conformer blocks' linears + CTC head,
-greedy argmax) over T encoder frames per GPU (default 90000 = one hour of 16 kHz audio,
-benchmark configs[3]/[4]); synthetic ~N(0,1) bf16 features, random-init weights (seed 0).
-Frames are independent, so N GPUs each take their own T frames with replicated weights (weak
-scaling); the only collective is the gather of the per-frame CTC ids.
+greedy argmax) over ONE HOUR of synthetic 16 kHz audio (89,999 encoder frames: seeded PCM ->
+80-bin Kaldi fbank -> fixed seeded stand-in for the subsampling front, velox_voice_b200/synth.py),
+random-init weights (seed 0).  With N GPUs the hour is cut into N equal frame shards (strong
+scaling), weights replicated; the only collective is the gather of the per-frame CTC ids (a
+second leg gathers the bf16 logits instead, a third gives the weak-scaling number).
 
     python bench.py --gpus 1 --steps 10 --warmup 3
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
@@ -39,22 +40,29 @@ def parse():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--frames", type=int, default=90000, help="encoder frames per GPU")
+    ap.add_argument("--frames", type=int, default=0,
+                    help="encoder frames of the whole job (default: the synthetic hour, 89,999)")
     ap.add_argument("--fmt", default="mx32", choices=["mx32", "nv16", "fp8_1x128"])
     ap.add_argument("--blocks", type=int, default=12)
-    ap.add_argument("--cpu-frames", type=int, default=1024, help="frames of the CPU baseline sample")
-    ap.add_argument("--no-breakdown", action="store_true")
-    ap.add_argument("--breakdown-only", action="store_true",
-                    help="time the individual launches only (profiling aid); prints one JSON line")
-    ap.add_argument("--configs-only", action="store_true",
-                    help="time benchmark configs[0..2] (single launches / the FFN chain) and exit")
-    ap.add_argument("--ops", default="", help="with --breakdown-only: substring filter on the op name")
+    ap.add_argument("--cpu-frames", type=int, default=4096, help="frames per step of the CPU arms' sample")
+    ap.add_argument("--no-breakdown", action="store_true", help="skip the per-launch timings (no roofline object)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the logits-gather and weak-scaling legs")
+    ap.add_argument("--traffic-bytes", type=float, default=None,
+                    help="dram bytes (read + write) of one launch of the dominant kernel from an ncu capture of THIS build")
     return ap.parse_args()
 
 
+def total_frames(a) -> int:
+    from velox_voice_b200 import synth
+
+    return a.frames if a.frames > 0 else synth.total_encoder_frames()
+
+
 def workload_name(a) -> str:
-    return (f"cfg4/cfg5 encoder linear stack, {a.fmt}, {a.blocks} blocks + CTC 512->5538, "
-            f"T={a.frames} frames per GPU (1-hour audio), attention/depthwise conv left out")
+    return (f"cfg5: one hour of synthetic 16 kHz audio (seed 1) -> 80-bin Kaldi fbank -> fixed seeded 4x80->512 "
+            f"stand-in for the subsampling front -> cfg4 encoder linear stack, {a.fmt}, {a.blocks} blocks + CTC 512->5538 "
+            f"greedy ids; T={total_frames(a)} encoder frames in total, cut into equal frame shards over the GPUs; "
+            f"attention / depthwise conv left out")
 
 
 # ----------------------------------------------------------------------------- clocks
@@ -118,9 +126,42 @@ class ClockSampler:
 _CPU_STACKS = {}
 
 
-def cpu_stack_sample(a, frames: int, repeats: int = 1):
-    """The path's CPU restatement (oracle: quantize -> dequantize -> fp32 matmul per linear)
-    on `frames` frames with every host thread torch can use.  Returns (frames/s, threads)."""
+def cpu_reference_sample(a, frames: int):
+    """The reference's CPU path of the stack on `frames` frames with every host thread torch can
+    use: its own DenseLinear / WenetConformerFF classes in their fp32 lane (F.linear) when the
+    copy of the reference package is present in oracle/_ref, else this repository's fp32
+    restatement of the same lane.  Returns (frames/s, threads, seconds, kind)."""
+    import numpy as np
+    import torch
+
+    from oracle import ref_stack
+    from oracle.stack import cpu_linear_stack_fp32
+    from velox_voice_b200.stack import StackConfig, make_weights
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    cfg = StackConfig(blocks=a.blocks, fmt=a.fmt)
+    key = ("fp32", a.blocks)
+    st = _CPU_STACKS.get(key)
+    if st is None:
+        w = {k: v.numpy() for k, v in make_weights(cfg, seed=0).items()}
+        if ref_stack.available():
+            rs = ref_stack.ReferenceCpuStack(w, cfg.blocks)
+            st = (rs.forward, "reference")
+        else:
+            st = ((lambda x: cpu_linear_stack_fp32(w, x, cfg.blocks)), "port")
+        _CPU_STACKS[key] = st
+    fn, kind = st
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(frames, cfg.d_model, generator=g).bfloat16().float().numpy()
+    t0 = time.perf_counter()
+    fn(x)
+    dt = time.perf_counter() - t0
+    return frames / dt, torch.get_num_threads(), dt, kind
+
+
+def cpu_quantized_port_sample(a, frames: int):
+    """The quantized path's CPU restatement (oracle: quantize -> dequantize -> fp32 matmul per
+    linear) on `frames` frames.  Returns (frames/s, threads, seconds)."""
     import numpy as np
     import torch
 
@@ -130,20 +171,18 @@ def cpu_stack_sample(a, frames: int, repeats: int = 1):
 
     torch.set_num_threads(os.cpu_count() or 1)
     cfg = StackConfig(blocks=a.blocks, fmt=a.fmt)
-    key = (a.blocks, a.fmt)
+    key = ("q", a.blocks, a.fmt)
     st = _CPU_STACKS.get(key)
     if st is None:
         w = {k: v.numpy() for k, v in make_weights(cfg, seed=0).items()}
-        # nv16: per-call (dynamic) tensor amax on the CPU
         st = OracleStack(w, F.FMT_NAMES[a.fmt], cfg.blocks, amax={} if a.fmt == "nv16" else None)
         st.forward(np.zeros((8, cfg.d_model), np.float32))  # quantize the weights once, untimed
         _CPU_STACKS[key] = st
     g = torch.Generator().manual_seed(1)
     x = torch.randn(frames, cfg.d_model, generator=g).bfloat16().float().numpy()
     t0 = time.perf_counter()
-    for _ in range(repeats):
-        st.forward(x)
-    dt = (time.perf_counter() - t0) / repeats
+    st.forward(x)
+    dt = time.perf_counter() - t0
     return frames / dt, torch.get_num_threads(), dt
 
 
@@ -152,195 +191,29 @@ def run_reference(a):
     if rank != 0:
         return
     per_step = []
-    fps, threads, _ = cpu_stack_sample(a, a.cpu_frames)  # warm-up (weights quantized, pages touched)
-    for _ in range(max(a.warmup - 1, 0)):
-        cpu_stack_sample(a, 64)
+    for _ in range(max(a.warmup, 1)):
+        _, threads, _, kind = cpu_reference_sample(a, min(a.cpu_frames, 512))
     t0 = time.perf_counter()
     for _ in range(a.steps):
-        f, threads, dt = cpu_stack_sample(a, a.cpu_frames)
+        _, threads, dt, kind = cpu_reference_sample(a, a.cpu_frames)
         per_step.append(dt)
     wall = time.perf_counter() - t0
     dt = sum(per_step) / len(per_step)
     value = a.cpu_frames / dt
+    what = ("the reference's own DenseLinear / WenetConformerFF classes, fp32 lane (F.linear)" if kind == "reference"
+            else "fp32 F.linear restatement of the reference's CPU lane")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps,
-        "warmup": a.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "warmup": a.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload_name(a), "sample": f"{a.cpu_frames} frames per step on the host cores"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": f"{a.cpu_frames} frames of the same stack per step (weights pre-quantized), "
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind,
+                         "sample": f"{a.cpu_frames} frames of the same stack per step through {what}, "
                                    f"{a.steps} steps, wall {wall:.1f} s"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
-
-
-# ----------------------------------------------------------------------------- per-op breakdown
-
-# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch at T = 90000, mx32, from the
-# `ncu --set full` captures summarised under profiles/ (ncu_bsgemm_*_T90000.md,
-# ncu_ln_quant_mx32_T90000.md, ncu_quant_mx32_T90000.md).  Writes still held in the 126 MB L2 when the kernel ends are
-# not in the counter, so traffic can be below the algorithmic bytes.
-NCU_DRAM_BYTES = {
-    "gemm ffn-up 512->2048 swish, FP4 out": 25505536 + 38924032,
-    "ln_quantize [T,512]": 92183552 + 7837696,
-    "quantize [T,512]": 92173568 + 8598272,
-    "gemm qkv 512->1536 bias": 25019392 + 222124544,
-    "gemm ffn-down 2048->512 +0.5 residual": 191464192 + 52525568,
-    "gemm ctc 512->5538 bias + argmax (no logits written)": 26791680 + 0,
-}
-
-
-def op_breakdown(stack, T, fmt_name, only=""):
-    """Times every distinct launch of one block (+ CTC) alone, L2 flushed before each timed
-    launch, and returns [(name, count_per_step, us, algorithmic_bytes, flops)]."""
-    import torch
-
-    from velox_voice_b200 import ops
-
-    cfg = stack.cfg
-    dev = stack.device
-    d, f, V = cfg.d_model, cfg.ffn, cfg.vocab
-    nb = cfg.blocks
-    fmt = stack.fmt
-    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
-    x = torch.randn(T, d, device=dev).bfloat16()
-    g, b = stack.ln["b0.ln_ffm"]
-    sfb = 1 / 32 if fmt_name == "mx32" else (1 / 16 if fmt_name == "nv16" else 4 / 128)
-    ebytes = 1.0 if fmt_name == "fp8_1x128" else 0.5
-
-    def qbytes(rows, k):
-        return rows * k * (ebytes + sfb)
-
-    am = stack.amax.get("b0.ln_ffm")
-    xq = ops.ln_quantize(x, g, b, cfg.eps, fmt, amax_t=am)
-    res = torch.randn(T, d, device=dev).bfloat16()
-    cases = []
-
-    def add(name, count, fn, nbytes, flops):
-        if only and only not in name:
-            return
-        for _ in range(2):
-            fn()
-        ts = []
-        for _ in range(5):
-            flush.zero_()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            fn()
-            e1.record()
-            torch.cuda.synchronize()
-            ts.append(e0.elapsed_time(e1) * 1e3)
-        ts.sort()
-        cases.append((name, count, ts[len(ts) // 2], nbytes, flops))
-
-    add("ln_quantize [T,512]", 3 * nb + 1, lambda: ops.ln_quantize(x, g, b, cfg.eps, fmt, amax_t=am),
-        T * d * 2 + qbytes(T, d), 0)
-    add("ln2_quantize [T,512] (norm_final + next LayerNorm + quantize)", nb,
-        lambda: ops.ln2_quantize(x, g, b, g, b, cfg.eps, fmt, y=x, amax_t=am), T * d * 4 + qbytes(T, d), 0)
-    add("quantize [T,512]", 2 * nb + 1, lambda: ops.quantize(x, fmt, natural=fmt_name == "fp8_1x128", amax_t=am),
-        T * d * 2 + qbytes(T, d), 0)
-    w1, w2 = stack.p["b0.ffm.w1"], stack.p["b0.ffm.w2"]
-    if stack.fuse_ffn:
-        hq = w1(xq, act="swish", out_fmt=fmt, out_amax=stack.amax.get("b0.ffm.h"))
-        add("gemm ffn-up 512->2048 swish, FP4 out", 2 * nb,
-            lambda: w1(xq, act="swish", out_fmt=fmt, out_amax=stack.amax.get("b0.ffm.h")),
-            qbytes(T, d) + qbytes(f, d) + qbytes(T, f), 2 * T * d * f)
-    else:
-        h = w1(xq, act="swish")
-        hq = ops.quantize(h, fmt, natural=fmt_name == "fp8_1x128")
-        add("gemm ffn-up 512->2048 swish, bf16 out", 2 * nb, lambda: w1(xq, act="swish"),
-            qbytes(T, d) + qbytes(f, d) + T * f * 2, 2 * T * d * f)
-        add("quantize [T,2048]", 2 * nb, lambda: ops.quantize(h, fmt, natural=fmt_name == "fp8_1x128"),
-            T * f * 2 + qbytes(T, f), 0)
-    add("gemm ffn-down 2048->512 +0.5 residual", 2 * nb, lambda: w2(hq, residual=res, alpha=0.5, out=res),
-        qbytes(T, f) + qbytes(d, f) + T * d * 4, 2 * T * d * f)
-    add("gemm qkv 512->1536 bias", nb, lambda: stack.p["b0.qkv"](xq), qbytes(T, d) + qbytes(3 * d, d) + T * 3 * d * 2,
-        2 * T * d * 3 * d)
-    add("gemm lo/pw2 512->512 +residual", 2 * nb, lambda: stack.p["b0.lo"](xq, residual=res, alpha=1.0, out=res),
-        qbytes(T, d) + qbytes(d, d) + T * d * 4, 2 * T * d * d)
-    add("gemm lp 512->512", nb, lambda: stack.p["b0.lp"](xq), qbytes(T, d) + qbytes(d, d) + T * d * 2, 2 * T * d * d)
-    add("gemm pw1 512->1024 GLU", nb, lambda: stack.p["b0.pw1"](xq), qbytes(T, d) + qbytes(2 * d, d) + T * d * 2,
-        2 * T * d * 2 * d)
-    add("gemm ctc 512->5538 bias + argmax (no logits written)", 1, lambda: stack.p["ctc"].argmax(xq),
-        qbytes(T, d) + qbytes(V, d) + T * 12, 2 * T * d * V)
-    del flush
-    return cases
-
-
-def baseline_configs(dev, hbm_peak_gbs):
-    """benchmark configs[0..2] as single (chains of) launches: us, algorithmic TFLOP/s and GB/s,
-    and the fraction of the roofline (slower of bytes at measured HBM peak and FLOPs at the
-    measured tensor-core peak of that operand type)."""
-    import torch
-
-    from velox_voice_b200 import ops
-
-    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
-    peak = {"fp4": ops.mma_peak_tflops("fp4", 256, 2048), "fp8": ops.mma_peak_tflops("fp8", 256, 2048)}
-
-    def timed(fn, n=7):
-        for _ in range(2):
-            fn()
-        ts = []
-        for _ in range(n):
-            flush.zero_()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            fn()
-            e1.record()
-            torch.cuda.synchronize()
-            ts.append(e0.elapsed_time(e1) * 1e3)
-        ts.sort()
-        return ts[len(ts) // 2]
-
-    def entry(name, us, flops, nbytes, kind):
-        t_roof = max(nbytes / (hbm_peak_gbs * 1e3), flops / (peak[kind] * 1e6))  # us
-        return {"config": name, "us": round(us, 1), "TFLOPs": round(flops / us / 1e6, 1), "GBps": round(nbytes / us / 1e3, 1),
-                "roofline_us": round(t_roof, 1), "roofline_frac": round(t_roof / us, 3)}
-
-    out = []
-    torch.manual_seed(0)
-    # configs[0]: single MXFP4 linear, x [1024, 512] -> [1024, 2048] bf16 (quantize on the fly + GEMM)
-    x = torch.randn(1024, 512, device=dev).bfloat16()
-    w = ops.quantize(0.02 * torch.randn(2048, 512, device=dev), "mx32")
-    us = timed(lambda: ops.bsgemm(ops.quantize(x, "mx32", natural=False), w, out_dtype=torch.bfloat16))
-    out.append(entry("cfg1 mxfp4 linear 1024x2048x512 (quantize + GEMM)", us, 2 * 1024 * 2048 * 512,
-                     1024 * 512 * 2 + 2048 * 512 * (0.5 + 1 / 32) + 1024 * 2048 * 2, "fp4"))
-    # configs[1]: fused QKV, FP8 1x128, T = 90000 (activations already quantized; GEMM + bias -> bf16)
-    T = 90000
-    xa = torch.nn.functional.layer_norm(torch.randn(T, 512, device=dev), (512,)).bfloat16()
-    bound = (6.0 / (512 + 1536)) ** 0.5
-    wq = ops.quantize((torch.rand(1536, 512, device=dev) * 2 - 1) * bound, "fp8_1x128")
-    aq = ops.quantize(xa, "fp8_1x128")
-    bias = torch.zeros(1536, device=dev)
-    o = torch.empty(T, 1536, device=dev, dtype=torch.bfloat16)
-    us = timed(lambda: ops.bsgemm(aq, wq, epilogue=ops.EPI_BIAS, bias=bias, out=o))
-    out.append(entry("cfg2 fused QKV fp8_1x128 90000x1536x512 (GEMM + bias)", us, 2 * T * 1536 * 512,
-                     T * 512 * (1 + 4 / 128) + 1536 * 512 * (1 + 4 / 128) + T * 1536 * 2, "fp8"))
-    us = timed(lambda: ops.quantize(xa, "fp8_1x128"))
-    out.append(entry("cfg2 activation quantize fp8_1x128 [90000, 512]", us, 0, T * 512 * (2 + 1 + 4 / 128), "fp8"))
-    # configs[2]: macaron FFN, NVFP4: y = x + 0.5 * W2 swish(W1 LN(x)); 3 launches, FP4 intermediate
-    xf = torch.randn(T, 512, device=dev).bfloat16()
-    w1 = ops.quantize(0.02 * torch.randn(2048, 512, device=dev), "nv16")
-    w2 = ops.quantize(0.02 * torch.randn(512, 2048, device=dev), "nv16")
-    b1, b2 = torch.zeros(2048, device=dev), torch.zeros(512, device=dev)
-    g, be = torch.ones(512, device=dev), torch.zeros(512, device=dev)
-    am_x = torch.tensor([6.0], device=dev)
-    am_h = torch.tensor([8.0], device=dev)
-    y = torch.empty_like(xf)
-
-    def ffn():
-        q = ops.ln_quantize(xf, g, be, 1e-5, "nv16", amax_t=am_x)
-        h = ops.bsgemm(q, w1, epilogue=ops.EPI_BIAS_SWISH, bias=b1, out_fmt="nv16", out_amax=am_h)
-        ops.bsgemm(h, w2, epilogue=ops.EPI_BIAS_RESIDUAL, bias=b2, residual=xf, alpha=0.5, out=y)
-
-    us = timed(ffn)
-    nb = T * 512 * 2 + T * 512 * (0.5 + 1 / 16) * 2 + T * 2048 * (0.5 + 1 / 16) * 2 + T * 512 * 4
-    out.append(entry("cfg3 macaron FFN nv16 T=90000 (ln_quant + up/swish/FP4 + down/residual)", us, 2 * 2 * T * 512 * 2048, nb, "fp4"))
-    del flush
-    return out, peak
 
 
 # ----------------------------------------------------------------------------- our arm
@@ -366,39 +239,29 @@ def run_ours(a):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
-    from velox_voice_b200 import _lib, ops
-    from velox_voice_b200.stack import ConformerLinearStack, StackConfig, make_weights
+    from velox_voice_b200 import _lib, opbench, synth
+    from velox_voice_b200.stack import ConformerLinearStack, StackConfig, make_weights, shard_capacity, shard_rows
 
-    T = a.frames
+    T = total_frames(a)                       # the whole job
+    s0, s1 = shard_rows(T, world, rank)       # this rank's frames
+    cap = shard_capacity(T, world)            # rows of every rank's slot in the gathers
+    Tl = s1 - s0
     cfg = StackConfig(blocks=a.blocks, fmt=a.fmt)
     stack = ConformerLinearStack(cfg, make_weights(cfg, seed=0), device=dev)
-    g = torch.Generator().manual_seed(1 + rank)
-    feats_host = torch.randn(T, cfg.d_model, generator=g).bfloat16().pin_memory()
-    pos = torch.randn(T, cfg.d_model, generator=g).bfloat16().to(dev)
+    feats, _ = synth.encoder_features(s0, s1, device=dev)
+    feats_host = torch.zeros((cap, cfg.d_model), dtype=torch.bfloat16).pin_memory()
+    feats_host[:Tl].copy_(feats)
+    del feats
+    g = torch.Generator().manual_seed(1000 + rank)
+    pos = torch.randn(cap, cfg.d_model, generator=g).bfloat16().to(dev)
     if a.fmt == "nv16":
         stack.calibrate(feats_host[:4096].to(dev), pos[:4096])
-    if a.configs_only:
-        peaks = {}
-        try:
-            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-                peaks = json.load(f)
-        except Exception:
-            pass
-        cfgs, mma_peak = baseline_configs(dev, float(peaks.get("hbm_gbs", 6650.0)))
-        print(json.dumps({"baseline_configs": cfgs, "mma_peak_tflops_measured": mma_peak}), flush=True)
-        return
-    if a.breakdown_only:
-        cases = op_breakdown(stack, T, a.fmt, a.ops)
-        print(json.dumps({"breakdown": [{"op": n, "launches_per_step": c, "us": round(us, 1),
-                                         "GBps": round(nb / us / 1e3, 1), "TFLOPs": round(fl / us / 1e6, 1)}
-                                        for n, c, us, nb, fl in cases]}), flush=True)
-        return
-    comp = stack.compile(T)
+    comp = stack.compile(cap)
     comp.pos.copy_(pos)
     comp.x_in.copy_(feats_host)
-    ids_all = torch.empty((world * T,), dtype=torch.int32, device=dev)
+    ids_all = torch.empty((world * cap,), dtype=torch.int32, device=dev)
 
-    def gather():
+    def gather_ids():
         if world > 1:
             dist.all_gather_into_tensor(ids_all, comp.ids)
 
@@ -414,39 +277,48 @@ def run_ours(a):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    # ---- device-resident timing: inputs already in HBM
-    for _ in range(max(a.warmup, 3)):
+    def timed(step_fn, steps, warmup):
+        """K steps bracketed by barrier + synchronize, CUDA events, max over ranks -> ms."""
+        for _ in range(warmup):
+            step_fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step_fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1))
+
+    # ---- device-resident timing: this rank's shard already in HBM; ids gathered every step
+    def step_ids():
         comp.run()
-        gather()
+        gather_ids()
+
+    for _ in range(max(a.warmup, 3)):
+        step_ids()
     barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(a.steps):
-        comp.run()
-        gather()
-    e1.record()
-    torch.cuda.synchronize(dev)
-    barrier()
-    ms = max_over_ranks(e0.elapsed_time(e1))
+    ms = timed(step_ids, a.steps, 0)
     clocks = sampler.stop() if rank == 0 else None
     status = _lib.device_status()
     ms_per_step = ms / a.steps
-    value = world * T * a.steps / (ms * 1e-3)
+    value = T * a.steps / (ms * 1e-3)
 
     # ---- end to end through the public call: pinned host features in, host ids out
     for _ in range(2):
         comp.encode_ctc_host(feats_host)
     barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
     e0.record()
     for _ in range(a.steps):
         comp.encode_ctc_host(feats_host)
-        gather()
+        gather_ids()
     e1.record()
     torch.cuda.synchronize(dev)
     seq_ms = max_over_ranks(max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3))
@@ -457,65 +329,156 @@ def run_ours(a):
     barrier()
     t0 = time.perf_counter()
     e0.record()
-    comp.encode_ctc_host_batches(queue, after_each=lambda i: gather())
+    comp.encode_ctc_host_batches(queue, after_each=lambda i: gather_ids())
     e1.record()
     torch.cuda.synchronize(dev)
     e2e_ms = max_over_ranks(max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3))
-    e2e_value = world * T * a.steps / (e2e_ms * 1e-3)
-    e2e_seq_value = world * T * a.steps / (seq_ms * 1e-3)
+    e2e_value = T * a.steps / (e2e_ms * 1e-3)
+    e2e_seq_value = T * a.steps / (seq_ms * 1e-3)
+
+    # ---- the same job with the bf16 CTC logits gathered instead of the ids, and (N > 1) the
+    #      weak-scaling number: every GPU takes a whole hour of its own
+    extras = {}
+    if not a.no_extras:
+        ldv = (cfg.vocab + 7) // 8 * 8
+        logits = [torch.empty((cap, ldv), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        full = [torch.empty((world * cap, ldv), dtype=torch.bfloat16, device=dev) for _ in range(2)] if world > 1 else None
+        comm = torch.cuda.Stream(device=dev)
+        ev_done = [torch.cuda.Event() for _ in range(2)]
+        ev_free = [torch.cuda.Event() for _ in range(2)]
+        for e in ev_free:
+            e.record()
+        state = {"i": 0}
+        xw = torch.empty_like(comp.x_in)
+
+        def logits_pass(buf):
+            xw.copy_(comp.x_in)
+            stack.forward(xw, comp.pos, out_logits=buf[:, : cfg.vocab])
+
+        def step_logits_serial():
+            logits_pass(logits[0])
+            if world > 1:
+                dist.all_gather_into_tensor(full[0], logits[0])
+
+        def step_logits_overlapped():
+            # the gather of step i runs on a side stream under the stack of step i + 1
+            k = state["i"] & 1
+            state["i"] += 1
+            main = torch.cuda.current_stream()
+            main.wait_event(ev_free[k])
+            logits_pass(logits[k])
+            ev_done[k].record(main)
+            if world > 1:
+                with torch.cuda.stream(comm):
+                    comm.wait_event(ev_done[k])
+                    dist.all_gather_into_tensor(full[k], logits[k])
+                    ev_free[k].record(comm)
+
+        def drain():
+            torch.cuda.current_stream().wait_stream(comm)
+
+        k_extra = max(2, min(a.steps, 5))
+        ms_ser = timed(step_logits_serial, k_extra, 2)
+        extras["logits_gather_serial"] = {"value": T * k_extra / (ms_ser * 1e-3), "ms_per_step": ms_ser / k_extra}
+
+        def steps_overlapped():
+            step_logits_overlapped()
+
+        for _ in range(2):
+            steps_overlapped()
+        drain()
+        barrier()
+        e0.record()
+        for _ in range(k_extra):
+            steps_overlapped()
+        drain()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        barrier()
+        ms_ovl = max_over_ranks(e0.elapsed_time(e1))
+        extras["logits_gather_overlapped"] = {"value": T * k_extra / (ms_ovl * 1e-3), "ms_per_step": ms_ovl / k_extra}
+        extras["logits_bytes_gathered_per_step"] = world * cap * ldv * 2
+        extras["note"] = ("eager launches (no CUDA graph); bf16 logits [T, 5538] written and, for N > 1, all-gathered "
+                          "(NCCL all_gather_into_tensor of equal row slots); overlapped = gather of step i under the stack of step i+1")
+        del logits, full
+        if world > 1:
+            comp_w = stack.compile(T)
+            gw = torch.Generator().manual_seed(7 + rank)
+            comp_w.x_in.copy_(torch.randn(T, cfg.d_model, generator=gw).bfloat16())
+            comp_w.pos.copy_(torch.randn(T, cfg.d_model, generator=gw).bfloat16())
+            ids_w = torch.empty((world * T,), dtype=torch.int32, device=dev)
+
+            def step_weak():
+                comp_w.run()
+                dist.all_gather_into_tensor(ids_w, comp_w.ids)
+
+            ms_w = timed(step_weak, k_extra, 2)
+            extras["weak_scaling"] = {"value": world * T * k_extra / (ms_w * 1e-3), "ms_per_step": ms_w / k_extra,
+                                      "frames_per_gpu": T, "note": "every GPU takes T frames of its own (randn features), ids gathered"}
+            del comp_w, ids_w
 
     line = None
     if rank == 0:
         flops_per_frame = cfg.flops_per_frame()
-        peaks = {}
-        try:
-            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-                peaks = json.load(f)
-        except Exception:
-            pass
-        hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
-        peak_src = "measured (MEASURED_PEAKS.json)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
-        roofline, breakdown = None, None
+        hbm_peak, peak_src = opbench.measured_hbm_peak(ROOT)
+        roofline, breakdown, cfgs, mma_peak = None, None, None, None
         if not a.no_breakdown:
-            cases = op_breakdown(stack, T, a.fmt)
+            cases = opbench.op_breakdown(stack, cap, a.fmt)
             total_us = sum(c * us for _, c, us, _, _ in cases)
             breakdown = [{"op": n, "launches_per_step": c, "us": round(us, 1), "share": round(c * us / total_us, 3),
                           "GBps": round(nb / us / 1e3, 1), "TFLOPs": round(fl / us / 1e6, 1)} for n, c, us, nb, fl in cases]
             top = max(cases, key=lambda t: t[1] * t[2])
-            traffic = NCU_DRAM_BYTES.get(top[0]) if (T == 90000 and a.fmt == "mx32") else None
-            ach = top[3] / top[2] / 1e3
-            roofline = {"kernel": top[0], "bound": "hbm", "achieved": round(ach, 1), "peak": hbm_peak, "unit": "GB/s",
-                        "frac": round(ach / hbm_peak, 4), "traffic": traffic, "peak_source": peak_src,
-                        "algorithmic_bytes_per_launch": int(top[3]), "us_per_launch": round(top[2], 1)}
-        cfgs, mma_peak = (None, None)
-        if not a.no_breakdown:
-            cfgs, mma_peak = baseline_configs(dev, hbm_peak)
-            # the same launch against the tensor-core roofline (FP4 peak measured by the
-            # library's own back-to-back-MMA probe): whichever bound gives the longer time binds
             kind = "fp8" if a.fmt == "fp8_1x128" else "fp4"
-            tf = top[4] / top[2] / 1e6
-            roofline["tensor"] = {"achieved": round(tf, 1), "peak": round(mma_peak[kind], 1), "unit": "TFLOP/s",
-                                  "frac": round(tf / mma_peak[kind], 4),
-                                  "peak_source": "vx_mma_peak_probe (measured, dense)"}
+            from velox_voice_b200 import ops
+
+            mma_peak = {"fp4": ops.mma_peak_tflops("fp4", 256, 2048), "fp8": ops.mma_peak_tflops("fp8", 256, 2048)}
+            # the dominant launch against both roofs; the one that gives the longer time binds
+            gbs, tfs = top[3] / top[2] / 1e3, top[4] / top[2] / 1e6
             t_hbm, t_tc = top[3] / (hbm_peak * 1e3), top[4] / (mma_peak[kind] * 1e6)
-            roofline["binding"] = "tensor" if t_tc > t_hbm else "hbm"
-            roofline["roofline_us"] = round(max(t_hbm, t_tc), 1)
-            roofline["frac_of_binding_roofline"] = round(max(t_hbm, t_tc) / top[2], 4)
-        cpu_fps, cores, cpu_dt = cpu_stack_sample(a, a.cpu_frames)
+            tensor_bound = t_tc > t_hbm
+            roofline = {
+                "kernel": top[0], "bound": "tensor" if tensor_bound else "hbm",
+                "achieved": round(tfs if tensor_bound else gbs, 1),
+                "peak": round(mma_peak[kind], 1) if tensor_bound else hbm_peak,
+                "unit": "TFLOP/s" if tensor_bound else "GB/s",
+                "frac": round((tfs / mma_peak[kind]) if tensor_bound else (gbs / hbm_peak), 4),
+                "traffic": a.traffic_bytes,
+                "peak_source": ("vx_mma_peak_probe in this run (measured, dense, back-to-back MMAs)" if tensor_bound else peak_src),
+                "us_per_launch": round(top[2], 1), "roofline_us": round(max(t_hbm, t_tc), 1),
+                "algorithmic_bytes_per_launch": int(top[3]), "algorithmic_flops_per_launch": int(top[4]),
+                "hbm": {"achieved": round(gbs, 1), "peak": hbm_peak, "unit": "GB/s", "frac": round(gbs / hbm_peak, 4), "peak_source": peak_src},
+                "tensor": {"achieved": round(tfs, 1), "peak": round(mma_peak[kind], 1), "unit": "TFLOP/s",
+                           "frac": round(tfs / mma_peak[kind], 4)},
+                "rows_per_launch": cap,
+            }
+            if world == 1:
+                cfgs, _ = opbench.baseline_configs(dev, hbm_peak)
+        cpu_base = None
+        if world == 1:
+            cpu_fps, cores, cpu_dt, kind_cpu = cpu_reference_sample(a, a.cpu_frames)
+            q_fps, _, q_dt = cpu_quantized_port_sample(a, min(a.cpu_frames, 1024))
+            cpu_base = {"value": cpu_fps, "unit": UNIT, "cores": cores, "kind": kind_cpu,
+                        "sample": f"{a.cpu_frames} frames of the same stack on the host cores ({cpu_dt:.1f} s), fp32 F.linear lane "
+                                  + ("through the reference's own DenseLinear / WenetConformerFF classes" if kind_cpu == "reference"
+                                     else "(restatement: the reference package copy is absent)"),
+                        "quantized_port": {"value": q_fps, "unit": UNIT, "kind": "port",
+                                           "sample": f"{min(a.cpu_frames, 1024)} frames through the CPU oracle "
+                                                     f"(quantize -> dequantize -> fp32 matmul), {q_dt:.1f} s"}}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": max(a.warmup, 3),
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": {"mx32": "fp4 (e2m1, ue8m0 per 32) x fp4 -> f32", "nv16": "fp4 (e2m1, e4m3 per 16) -> f32",
                       "fp8_1x128": "fp8 (e4m3, f32 per 1x128) -> f32"}[a.fmt],
             "data": "synthetic",
-            "config": {"workload": workload_name(a), "frames_per_gpu": T, "format": a.fmt, "blocks": a.blocks,
-                       "l2": "working set per launch > L2 (126 MB) at T=90000; per-op timings flush L2",
-                       "parallelism": f"frame shards x{world}, weights replicated, ids all-gather"},
+            "config": {"workload": workload_name(a), "total_frames": T, "frames_per_gpu": cap, "format": a.fmt, "blocks": a.blocks,
+                       "l2": ("working set per launch > L2 (126 MB) at one GPU; per-launch timings flush L2 (512 MB write) "
+                              "before every timed launch"),
+                       "parallelism": f"{world} equal frame shards of one {T}-frame job, weights replicated, ids all-gather"},
             "tflops": value * flops_per_frame / 1e12,
             "flops_per_frame": flops_per_frame,
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": T * cfg.d_model * 2, "d2h_bytes_per_step": T * 4,
-                    "ms_per_step": e2e_ms / a.steps, "call": "CompiledStack.encode_ctc_host_batches (K shards queued, "
-                    "copy of shard i+1 overlaps the stack of shard i)",
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": cap * cfg.d_model * 2, "d2h_bytes_per_step": cap * 4,
+                    "ms_per_step": e2e_ms / a.steps, "call": "CompiledStack.encode_ctc_host_batches (K jobs queued, "
+                    "copy of job i+1 overlaps the stack of job i); bytes are per GPU",
                     "sequential_value": e2e_seq_value, "sequential_call": "CompiledStack.encode_ctc_host per step"},
             "gpu_launches": comp.launches * a.steps,
             "gpu_launches_per_step": comp.launches,
@@ -525,9 +488,9 @@ def run_ours(a):
             "breakdown": breakdown,
             "baseline_configs": cfgs,
             "mma_peak_tflops_measured": mma_peak,
-            "cpu_baseline": {"value": cpu_fps, "unit": UNIT, "cores": cores, "kind": "port",
-                             "sample": f"{a.cpu_frames} frames of the same stack on the host cores ({cpu_dt:.1f} s)"},
+            "cpu_baseline": cpu_base,
         }
+        line.update(extras)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

@@ -227,6 +227,18 @@ int vx_set_trace_buffer(void* device_buffer, int64_t bytes);
  * kind 0 = FP4 block-scaled (kind::mxf4nvf4), 1 = FP8 (kind::f8f6f4).  Host pointer out. */
 int vx_mma_peak_probe(int kind, int n_tile, int iters, float* tflops_out);
 
+/* Self-test of the bounded device-side waits (the reference's waits spin without a limit,
+ * veloxvoice/kernels/csrc/dgx/arch/tma/tma_lite.h:82-91): launches one small kernel whose only
+ * mbarrier is never arrived at, with a wait limit of `limit_ns` nanoseconds (at most 1e8).  The
+ * wait gives up, vx_device_status then reports (1 << 24) | (site << 16) | 0 once, and the GPU
+ * context stays usable.  Nothing faults, traps or hangs. */
+int vx_wait_selftest(int64_t limit_ns, int site, void* stream);
+
+/* Counters of the tensor-map cache (host pointers, either may be NULL): vx_bsgemm encodes a
+ * CUtensorMap per operand / output once per distinct (pointer, extents, pitch, box) and re-uses
+ * it afterwards; the reference encodes on every call (dgx_mxfp4_gemm.cu:61-109). */
+int vx_tmap_cache_stats(int64_t* hits, int64_t* misses);
+
 /* Device-side status word of the last kernels (0 = OK; nonzero = a bounded wait expired:
  * (code<<24)|(site<<16)|block).  Synchronises the device.  Host pointer out. */
 int vx_device_status(int* status_out);

@@ -49,6 +49,8 @@ EXPORTS = (
     "vx_glu_tile",
     "vx_argmax_ids",
     "vx_qkv_pack",
+    "vx_wait_selftest",
+    "vx_tmap_cache_stats",
 )
 
 
@@ -149,6 +151,10 @@ def load(build_if_missing: bool = True) -> C.CDLL:
         lib.vx_argmax_ids.argtypes = [vp, i64, vp, vp, vp]
         lib.vx_set_trace_buffer.restype = i32
         lib.vx_set_trace_buffer.argtypes = [vp, i64]
+        lib.vx_wait_selftest.restype = i32
+        lib.vx_wait_selftest.argtypes = [i64, i32, vp]
+        lib.vx_tmap_cache_stats.restype = i32
+        lib.vx_tmap_cache_stats.argtypes = [C.POINTER(i64), C.POINTER(i64)]
         lib.vx_mma_peak_probe.restype = i32
         lib.vx_mma_peak_probe.argtypes = [i32, i32, i32, C.POINTER(C.c_float)]
         if lib.vx_abi_version() != ABI_VERSION:

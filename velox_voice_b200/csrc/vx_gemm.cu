@@ -33,6 +33,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "vx_common.cuh"
@@ -98,7 +99,6 @@ struct GemmParams {
   int a_slot_bytes;       // bytes of one A tile + its scale-factor atoms in the arena
   int b_slot_bytes;       // same for one B tile (BN rows)
   int tma_residual;       // 1: residual tiles are prefetched by TMA into the staging buffers
-  int dbg;                // ablation bits (investigation only)
   unsigned long long* trace;  // phase trace buffer (CTA 0, first 32 tiles) or nullptr
   int out_dtype;          // vx_dtype
   int tma_store;
@@ -405,11 +405,11 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   const bool tma_residual = OUT == 1 ? EPI == VX_EPI_BIAS_RESIDUAL : (OUT == 2 ? false : p.tma_residual != 0);
   const bool sf_unit = OUT != 0 ? false : p.sf_unit != 0;
   const int out_fmt = OUT == 2 ? static_cast<int>(kind_vec4(KIND) ? VX_FMT_NV16 : VX_FMT_MX32) : p.out_fmt;
-  const int dbg = OUT == 0 ? p.dbg : 0;
   const bool tr_on = p.trace != nullptr && blockIdx.x == 0;  // phase trace requested (CTA 0 only)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  volatile int* const abortp = &sm.abort_flag;  // raised by the first role whose bounded wait expires
   const int nslots = p.num_slots;
   const bool resident = p.b_resident != 0;
   const bool with_sf = !(FP8 || sf_unit);
@@ -539,9 +539,9 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         const uint8_t* sfa_row = p.sfa + (static_cast<int64_t>(mb) * p.sf_kg) * 512;
         const uint32_t slot_tx = TILE_BYTES + sf_atom_bytes + (resident ? 0u : b_tx(nb));
         for (int kg = 0; kg < k_groups; ++kg) {
-          if (!mbar_wait(&sm.empty[s], ph ^ 1, p.status, 1)) { ok = false; break; }
+          if (!mbar_wait(&sm.empty[s], ph ^ 1, p.status, 1, abortp)) { ok = false; break; }
           if (sfb_pending && s == static_cast<uint32_t>(nslots - 1)) {
-            if (!mbar_wait(&sm.sfb_done, 0, p.status, 7)) { ok = false; break; }
+            if (!mbar_wait(&sm.sfb_done, 0, p.status, 7, abortp)) { ok = false; break; }
             sfb_pending = false;
           }
           if (tr_on) trace_rec(p, 0, i, kg < 4 ? kg : 3);
@@ -615,12 +615,12 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             CP(col0 + a * SFB_COLS + rt * 4, desc(b_lo + b_sf_lo + (rt * APS + a) * 32, sf_hi));
       };
       if (resident) {
-        if (!mbar_wait(&sm.b_full, 0, p.status, 5)) ok = false;
+        if (!mbar_wait(&sm.b_full, 0, p.status, 5, abortp)) ok = false;
         tc_fence_after();
         if (ok && with_sf)  // B's scale factors stay in tensor memory for the whole kernel
           for (int ks = 0; ks < p.k_stages; ++ks) cp_sfb(arena_lo + ks * bslot_lo, tm_sfb + ks * APS * SFB_COLS);
       } else if (sfb_res) {
-        if (!mbar_wait(&sm.b_full, 0, p.status, 5)) ok = false;
+        if (!mbar_wait(&sm.b_full, 0, p.status, 5, abortp)) ok = false;
         tc_fence_after();
         if (ok) {
           const uint32_t st_lo = (arena_u32 + (nslots - 1) * slot_bytes + a_slot) >> 4;
@@ -649,12 +649,12 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
               if ((u & 1) == 0) {
                 const int pr = u >> 1;
                 const uint32_t use = pr ? use1 : use0;
-                if (!mbar_wait_spin(&sm.tmem_empty[pr], (use & 1) ^ 1, p.status, 2)) { ok = false; break; }
+                if (!mbar_wait_spin(&sm.tmem_empty[pr], (use & 1) ^ 1, p.status, 2, abortp)) { ok = false; break; }
                 if (pr) ++use1; else ++use0;
                 tc_fence_after();  // orders the epilogue's tcgen05.ld of these buffers before the MMAs
               }
               if (in_group == 0) {
-                if (!mbar_wait_spin(&sm.full[s], ph, p.status, 3)) { ok = false; break; }
+                if (!mbar_wait_spin(&sm.full[s], ph, p.status, 3, abortp)) { ok = false; break; }
                 tc_fence_after();
               }
               if (kb0 == 0) TRACE(i, 2 * u);
@@ -682,11 +682,11 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             const uint32_t acc = WIDE ? 0u : (group & 1);
             if (kg == 0) {
               const uint32_t use = WIDE ? group : (group >> 1);
-              if (!mbar_wait_spin(&sm.tmem_empty[acc], (use & 1) ^ 1, p.status, 2)) { ok = false; break; }
+              if (!mbar_wait_spin(&sm.tmem_empty[acc], (use & 1) ^ 1, p.status, 2, abortp)) { ok = false; break; }
               tc_fence_after();  // orders the epilogue's tcgen05.ld of this buffer before the MMAs
               TRACE(i, 0);
             }
-            if (!mbar_wait_spin(&sm.full[s], ph, p.status, 3)) { ok = false; break; }
+            if (!mbar_wait_spin(&sm.full[s], ph, p.status, 3, abortp)) { ok = false; break; }
             TRACE(i, kg < 2 ? 1 + kg : 2);
             const uint32_t d_tmem = tmem_base + TM_ACC0 + acc * 128;
             const uint32_t a_lo0 = ring_lo + s * G * slot_lo;
@@ -715,7 +715,6 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                 const uint32_t sfb_t = with_sf ? sfb_buf + (owns_nb ? ks : u) * APS * SFB_COLS : tm_sfb;
   #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                  if (dbg & 2) break;
                   if (leader) mma_mxf4<VEC>(d_tmem, desc(a_lo + 2 * j, k128_hi), desc(b_lo + 2 * j, k128_hi), idesc_j[j],
                                 sfa_t + sfa_col_j[j], sfb_t + sfb_col_j[j], (ks | j) != 0);
                 }
@@ -860,7 +859,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         // pipes; run one after the other, each leaves the other's pipe idle.  Here the Swish of
         // the chunk just read from tensor memory is interleaved, instruction by instruction, with
         // the encode of the previous chunk (whose block scale needed all of its 32 values first).
-        if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[0], group & 1, p.status, 4);
+        if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[0], group & 1, p.status, 4, abortp);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
         tc_fence_after();
@@ -951,7 +950,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         for (int kb0 = 0; kb0 < kb_count && ok; kb0 += FP8_ACCS) {
           // one round: up to four K blocks, block u in accumulator u, published together
           const int nkb = kb_count - kb0 < FP8_ACCS ? kb_count - kb0 : FP8_ACCS;
-          if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[0], group & 1, p.status, 4);
+          if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[0], group & 1, p.status, 4, abortp);
           ok = __shfl_sync(0xffffffffu, ok, 0);
           if (!ok) break;
           ++group;
@@ -1012,7 +1011,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         // one polling lane per warp (512 polling threads would starve the MMA-issuing thread)
         const uint32_t acc = WIDE ? 0u : (group & 1);
         const uint32_t acc_addr = lane_addr + TM_ACC0 + acc * 128 + col_base;
-        if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[acc], (WIDE ? group : (group >> 1)) & 1, p.status, 4);
+        if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[acc], (WIDE ? group : (group >> 1)) & 1, p.status, 4, abortp);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
         tc_fence_after();
@@ -1093,7 +1092,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                 if (h + 1 < NCH) res_issue(res_chunk + 1, mb, out_col0 + 32);
                 else res_issue(res_chunk + 1, mb_next, static_cast<int64_t>(nb_next) * OUT_TILE_COLS + col_base);
               }
-              if (!mbar_wait(&sm.res_full[res_chunk & 1][ew], (res_chunk >> 1) & 1, p.status, 6)) { ok = false; break; }
+              if (!mbar_wait(&sm.res_full[res_chunk & 1][ew], (res_chunk >> 1) & 1, p.status, 6, abortp)) { ok = false; break; }
               res_smem = res_half;
             }
           }
@@ -1202,8 +1201,6 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                       static_cast<uint16_t>(sbw);
               }
             }
-          } else if (dbg & 1) {
-            if (z[h][0] == 123.456f && row_ok) static_cast<float*>(p.out)[0] = z[h][1];  // keep z live
           } else if (tma_store) {
             // stage 32 rows x 32 columns (swizzled like the tensor map), then one TMA store
             uint8_t* buf = stage0;
@@ -1365,6 +1362,26 @@ __global__ void __launch_bounds__(128, 1) mma_probe_kernel(int iters, int* statu
 }
 
 // ---------------------------------------------------------------------------------------
+// Self-test of the bounded wait: one thread waits on an mbarrier that nothing ever arrives at,
+// with a caller-chosen limit.  The wait runs out, the status word is set, the kernel returns and
+// the context stays usable -- the same path a lost arrival takes in the GEMM, in milliseconds
+// instead of the production limit.  No tensor memory and no copy is in flight here.
+__global__ void wait_selftest_kernel(unsigned long long limit_ns, int site, int* status) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+    abort_flag = 0;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_wait_slow(&bar, 0, status, site, &abort_flag, limit_ns);
+  __syncthreads();
+  // a second role of the same CTA sees the raised flag and leaves without writing a status of its own
+  if (threadIdx.x == 32) mbar_wait_slow(&bar, 0, status, site + 1, &abort_flag, limit_ns);
+}
+
+// ---------------------------------------------------------------------------------------
 // Host side
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                    const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -1384,11 +1401,66 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+// Encoded tensor maps, cached by everything that goes into the encoding (base pointer, extents,
+// pitch, box, element type, swizzle, rank).  A map is a pure function of those values -- it holds
+// no reference to the allocation -- so an entry stays valid when the memory is freed and the
+// address is handed out again.  The reference re-encodes its maps on every call
+// (veloxvoice/kernels/csrc/dgx/dgx_mxfp4_gemm.cu:61-109); a steady-state caller (same buffers every
+// step) pays the driver call once here.  Direct-mapped, one mutex: a lookup is a hash, a lock and a
+// 48-byte compare.
+struct TmapKey {
+  const void* ptr;
+  int64_t d0, d1, d2, pitch;
+  int32_t box0, box1, dt, swizzle;
+  bool operator==(const TmapKey& o) const {
+    return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && d2 == o.d2 && pitch == o.pitch && box0 == o.box0 &&
+           box1 == o.box1 && dt == o.dt && swizzle == o.swizzle;
+  }
+};
+constexpr int kTmapCacheSlots = 1024;
+struct TmapSlot { TmapKey key; CUtensorMap map; bool used; };
+TmapSlot g_tmap_cache[kTmapCacheSlots];
+std::mutex g_tmap_mutex;
+std::atomic<uint64_t> g_tmap_hits{0}, g_tmap_misses{0};
+
+inline uint32_t tmap_hash(const TmapKey& k) {
+  uint64_t h = reinterpret_cast<uintptr_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
+  h ^= static_cast<uint64_t>(k.d0) * 0xC2B2AE3D27D4EB4Full + static_cast<uint64_t>(k.d1) * 0x165667B19E3779F9ull;
+  h ^= static_cast<uint64_t>(k.d2) * 0x27D4EB2F165667C5ull + static_cast<uint64_t>(k.pitch) * 0x85EBCA77C2B2AE63ull;
+  h ^= (static_cast<uint64_t>(k.box0) << 40) ^ (static_cast<uint64_t>(k.box1) << 24) ^ (static_cast<uint64_t>(k.dt) << 8) ^
+       static_cast<uint64_t>(k.swizzle);
+  h ^= h >> 29;
+  h *= 0xBF58476D1CE4E5B9ull;
+  h ^= h >> 32;
+  return static_cast<uint32_t>(h) & (kTmapCacheSlots - 1);
+}
+bool tmap_lookup(const TmapKey& k, CUtensorMap* out) {
+  TmapSlot& s = g_tmap_cache[tmap_hash(k)];
+  std::lock_guard<std::mutex> lock(g_tmap_mutex);
+  if (s.used && s.key == k) {
+    *out = s.map;
+    g_tmap_hits.fetch_add(1, std::memory_order_relaxed);
+    return true;
+  }
+  return false;
+}
+void tmap_insert(const TmapKey& k, const CUtensorMap& m) {
+  TmapSlot& s = g_tmap_cache[tmap_hash(k)];
+  std::lock_guard<std::mutex> lock(g_tmap_mutex);
+  s.key = k;
+  s.map = m;
+  s.used = true;
+  g_tmap_misses.fetch_add(1, std::memory_order_relaxed);
+}
+
 // 2-D row-major tensor [rows, cols] of `elt`-byte elements, row pitch `pitch_bytes`; box =
 // box_cols x box_rows; the inner extent in bytes equals the swizzle span (128 or 64).
 int make_tmap(CUtensorMap* m, CUtensorMapDataType dt, int elt, const void* ptr, int64_t rows,
               int64_t cols, int64_t pitch_bytes, int box_cols, int box_rows,
               CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+  const TmapKey key{ptr, cols, rows, 0, pitch_bytes, box_cols, box_rows, static_cast<int32_t>(dt),
+                    static_cast<int32_t>(swizzle)};
+  if (tmap_lookup(key, m)) return 0;
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return fail(-2, "cuTensorMapEncodeTiled is not available from the driver");
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
@@ -1400,12 +1472,16 @@ int make_tmap(CUtensorMap* m, CUtensorMapDataType dt, int elt, const void* ptr, 
                         CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(-3, "cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
+  tmap_insert(key, *m);
   return 0;
 }
 
 // 3-D bf16 tensor [z][rows][cols] (cols contiguous, row pitch `cols` elements): boxes of
 // 32 columns x 32 rows x 1, 64-byte swizzle -- the head-major output of the attention fold pack.
 int make_tmap_heads(CUtensorMap* m, const void* ptr, int64_t zdim, int64_t rows, int64_t cols) {
+  const TmapKey key{ptr, cols, rows, zdim, cols * 2, 32, 32, static_cast<int32_t>(CU_TENSOR_MAP_DATA_TYPE_BFLOAT16),
+                    static_cast<int32_t>(CU_TENSOR_MAP_SWIZZLE_64B)};
+  if (tmap_lookup(key, m)) return 0;
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return fail(-2, "cuTensorMapEncodeTiled is not available from the driver");
   const cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(zdim)};
@@ -1416,6 +1492,7 @@ int make_tmap_heads(CUtensorMap* m, const void* ptr, int64_t zdim, int64_t rows,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(-3, "cuTensorMapEncodeTiled (3-D) failed (%d)", static_cast<int>(r));
+  tmap_insert(key, *m);
   return 0;
 }
 
@@ -1432,15 +1509,18 @@ constexpr size_t kSmemBytes = sizeof(SmemLayout) + 1024;
 template <int KIND, int EPI, int OUT>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const CUtensorMap& tr,
            GemmParams& p, bool allow_resident, cudaStream_t st) {
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(bsgemm_kernel<KIND, EPI, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(kSmemBytes));
-  });
-  if (attr_err != cudaSuccess) return fail(static_cast<int>(attr_err), "cudaFuncSetAttribute: %s", cudaGetErrorString(attr_err));
   int dev = 0, sms = 0;
   VX_CUDA_OK(cudaGetDevice(&dev));
+  // The dynamic shared-memory opt-in belongs to the (function, device) pair: once per device
+  // and template instance (a process may drive several GPUs).
+  static std::atomic<uint64_t> attr_done{0};
+  const bool dev_cached = dev >= 0 && dev < 64;
+  if (!dev_cached || !(attr_done.load(std::memory_order_acquire) & (1ull << dev))) {
+    const cudaError_t e = cudaFuncSetAttribute(bsgemm_kernel<KIND, EPI, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               static_cast<int>(kSmemBytes));
+    if (e != cudaSuccess) return fail(static_cast<int>(e), "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    if (dev_cached) attr_done.fetch_or(1ull << dev, std::memory_order_release);
+  }
   static int sm_cache[64] = {};
   if (dev >= 0 && dev < 64 && sm_cache[dev]) sms = sm_cache[dev];
   else {
@@ -1568,6 +1648,11 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
   const bool argmax = epi == VX_EPI_BIAS_ARGMAX;
   const bool qkvpack = epi == VX_EPI_BIAS_QKVPACK;
   const bool out_heads = (d->flags & VX_GEMM_OUT_HEADS) != 0;
+  constexpr int32_t kKnownFlags = VX_GEMM_DIRECT_STORE | VX_GEMM_STREAM_B | VX_GEMM_WIDE_TILES | VX_GEMM_NARROW_TILES |
+                                  VX_GEMM_OUT_HEADS;
+  if (d->flags & ~kKnownFlags) return fail(-1, "unknown bits in flags (0x%x)", d->flags & ~kKnownFlags);
+  if (qkvpack && fmt == VX_FMT_ROWSCALE)
+    return fail(-1, "BIAS_QKVPACK is not available for the per-row-scaled format (use a block-scaled format or FP8)");
   if (qkvpack || out_heads) {
     if (d->heads <= 0 || d->head_dim <= 0 || d->head_dim % 32 != 0)
       return fail(-1, "head-major output needs heads > 0 and head_dim %% 32 == 0");
@@ -1708,11 +1793,10 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
     p.tma_residual = 1;
   }
   const bool res = !(d->flags & VX_GEMM_STREAM_B);
-  p.dbg = (d->flags >> 8) & 0xff;
   p.trace = g_trace_buffer;
   // compile-time output route (see bsgemm_kernel): 1 and 2 cover the encoder's launches
   int out_route = 0;
-  if (!p.dbg && !p.sf_unit) {
+  if (!p.sf_unit) {
     if (d->out_dtype == VX_BF16 && p.tma_store && (epi != VX_EPI_BIAS_RESIDUAL || p.tma_residual) && !argmax)
       out_route = 1;
     else if (d->out_dtype == VX_FP4 && !argmax && d->out_fmt == (vec2 ? VX_FMT_MX32 : VX_FMT_NV16))
@@ -1736,6 +1820,24 @@ int vx_argmax_ids(const void* keys, int64_t M, int32_t* ids, float* max_out, voi
   argmax_ids_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const unsigned long long*>(keys), M, ids, max_out);
   VX_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+int vx_wait_selftest(int64_t limit_ns, int site, void* stream) {
+  using namespace vx;
+  if (limit_ns <= 0 || limit_ns > 100000000ll) return fail(-1, "limit_ns must be in (0, 1e8] (at most 100 ms)");
+  if (site < 0 || site > 254) return fail(-1, "site must be in [0, 254]");
+  int* status = cached_status_ptr();
+  if (!status) return fail(-2, "device status word unavailable");
+  wait_selftest_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<unsigned long long>(limit_ns), site, status);
+  VX_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+int vx_tmap_cache_stats(int64_t* hits, int64_t* misses) {
+  using namespace vx;
+  if (hits) *hits = static_cast<int64_t>(g_tmap_hits.load());
+  if (misses) *misses = static_cast<int64_t>(g_tmap_misses.load());
   return 0;
 }
 

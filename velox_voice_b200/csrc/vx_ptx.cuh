@@ -64,15 +64,20 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 // status word layout: 0 = ok; else (code << 24) | (site << 16) | (blockIdx.x & 0xffff)
 // Slow path of a wait (kept inline: an out-of-line call was measured slower in most kernels): polls against the
-// wall clock (%globaltimer, slow to read) and gives up after kWaitLimitNs.
-__device__ __forceinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int* status, int site) {
+// wall clock (%globaltimer, slow to read) and gives up after `limit_ns`.  `abort` (optional) is a
+// flag in shared memory that the first role of a CTA to give up raises: the other roles of that
+// CTA then leave their own waits at once instead of running out their own limits one after another.
+__device__ __forceinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int* status, int site,
+                                               volatile int* abort = nullptr, uint64_t limit_ns = kWaitLimitNs) {
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 0x3ff) == 0) {
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+    if ((++spins & 0x3f) == 0) {
+      if (abort && *abort) return false;
+      if (globaltimer_ns() - t0 > limit_ns) {
         if (status) atomicCAS(status, 0, (1 << 24) | ((site & 0xff) << 16) | (blockIdx.x & 0xffff));
+        if (abort) *abort = 1;
         return false;
       }
     }
@@ -81,16 +86,18 @@ __device__ __forceinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, i
 
 // Parked wait: each poll may suspend the thread for up to 20 us, so a wait that succeeds
 // within 64 polls never reads the clock.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int site) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int site,
+                                          volatile int* abort = nullptr) {
 #pragma unroll 1
   for (uint32_t spins = 0; spins < 64; ++spins)
     if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait_slow(bar, parity, status, site);
+  return mbar_wait_slow(bar, parity, status, site, abort);
 }
 
 // Same contract, plain polling without the suspend hint: for the MMA-issuing warp and the
 // epilogue's polling lane, whose reaction time is on the critical path of every tile.
-__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, int* status, int site) {
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, int* status, int site,
+                                               volatile int* abort = nullptr) {
 #pragma unroll 1
   for (uint32_t spins = 0; spins < 100000; ++spins) {
     uint32_t ok;
@@ -103,7 +110,7 @@ __device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, i
         : "memory");
     if (ok) return true;
   }
-  return mbar_wait_slow(bar, parity, status, site);
+  return mbar_wait_slow(bar, parity, status, site, abort);
 }
 
 // ------------------------------------------------------------------ proxies / fences

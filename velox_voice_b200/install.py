@@ -13,7 +13,12 @@
 * ``veloxvoice.models.wenet.mxfp4_linear`` -> provides ``_pad16``, which
   ``DenseLinear._prequantize_weight`` imports (``torch_conformer.py:222-226``) from a module
   the reference tree does not contain;
-* ``veloxvoice.models.wenet.nvfp4_linear``: ``quantize_w``, ``Nvfp4Linear``, ``nvfp4_gemm``.
+* ``veloxvoice.models.wenet.nvfp4_linear``: ``quantize_w``, ``Nvfp4Linear``, ``nvfp4_gemm``,
+  ``quantize_and_gemm`` and the pure-torch helpers ``_encode_codes``, ``pack_codes``,
+  ``decode_codes``, ``ue8m0_from_scale``, ``ue8m0_to_float``, ``CODE_LUT``;
+* the bf16 operator names ``fused_qkv``, ``fused_qkv_wgmma``, ``pwlin_glu`` (the reference's
+  builds of the last two are sm_90a sources, ``cuda_ops.py:363-401,480-539``) run quantize + one
+  GEMM with the bias (+ GLU) in its epilogue and keep the ``Tensor | None`` convention.
 
 After that ``Velox.load(..., kernel_precision="mxfp4")`` / ``transcribe_pcm`` run their FP4
 lane on a B200 without any change to the reference's files.
@@ -34,7 +39,9 @@ _MXFP4_LINEAR = "veloxvoice.models.wenet.mxfp4_linear"
 _NVFP4_LINEAR = "veloxvoice.models.wenet.nvfp4_linear"
 
 GEMM_NAMES = ("dgx_mxfp4_gemm", "dgx_mxfp4_blkscale_gemm", "mxfp4_gemm", "nvfp4_linear", "_dequantize_to_bf16",
-              "qkv_pack")
+              "qkv_pack", "fused_qkv", "fused_qkv_wgmma", "pwlin_glu")
+# names of veloxvoice.kernels.ops (the package re-exports these; the reference's own tests import them from there)
+OPS_PKG_NAMES = tuple(n for n in GEMM_NAMES if n != "_dequantize_to_bf16")
 QUANT_NAMES = ("per_row_col_quantize", "triton_quantize_w", "mxfp4_block_quantize", "mxfp4_dequant")
 
 
@@ -64,6 +71,12 @@ def make_nvfp4_linear_module() -> types.ModuleType:
     m.BLOCK = 16
     m.CODE_LUT = _lazy_lut()
     m.quantize_w = ops.quantize_w
+    m._encode_codes = ops._encode_codes
+    m.pack_codes = ops.pack_codes
+    m.decode_codes = ops.decode_codes
+    m.ue8m0_from_scale = ops.ue8m0_from_scale
+    m.ue8m0_to_float = ops.ue8m0_to_float
+    m.quantize_and_gemm = ops.quantize_and_gemm
     m.Nvfp4Linear = linear.Nvfp4Linear
     m.nvfp4_gemm = linear.nvfp4_gemm
     m.dgx_mxfp4_gemm = ops.dgx_mxfp4_gemm
@@ -90,7 +103,7 @@ def install(patch_modules: bool = True) -> dict:
                 mod = importlib.import_module(name)
             except ImportError:
                 continue  # no veloxvoice on this machine: the replacement modules still stand
-            for n in GEMM_NAMES:
+            for n in (GEMM_NAMES if name == _CUDA_OPS else OPS_PKG_NAMES):
                 setattr(mod, n, getattr(ops, n))
             if name == _OPS_PKG:
                 for n in QUANT_NAMES:

@@ -138,10 +138,10 @@ class DenseLinear(nn.Linear):
             x2 = x.reshape(-1, orig_shape[-1])
             if self._wq is None:
                 self._prequantize_weight(precision)
-            xq, xs = ops.per_row_col_quantize(x2 if x2.dtype in (torch.float32, torch.bfloat16) else x2.float())
-            out = ops.dgx_mxfp4_gemm(xq, self._wq, xs, self._ws)
-            if self.bias is not None:
-                out = out + self.bias
+            if x2.dtype not in (torch.float32, torch.bfloat16):
+                x2 = x2.float()
+            # quantize + one GEMM with the scales and the bias in its epilogue (fp32 out)
+            out = ops.rowscale_linear(x2, self._wq, self._ws, None if self.bias is None else self.bias.detach())
             return out.view(*orig_shape[:-1], self.out_features)
         return torch.nn.functional.linear(x, self.weight, self.bias)
 
@@ -166,17 +166,11 @@ class Nvfp4Linear(nn.Module):
     def forward(self, x):
         orig_shape = x.shape
         x = x.reshape(-1, self.in_features)
-        out = ops.nvfp4_linear(x, self.weight_q, self.weight_s, w_bf16=self.weight_bf16)
-        if self.bias is not None:
-            out = out + self.bias
+        out = ops.rowscale_linear(x, self.weight_q, self.weight_s, self.bias)
         return out.view(*orig_shape[:-1], self.out_features)
 
 
 def nvfp4_gemm(x, w, b=None):
     """x [M, K] @ w [N, K]^T with both sides quantized online (``nvfp4_linear.py:161-168``)."""
-    xq, xs = ops.quantize_w(x)
     wq, ws = ops.quantize_w(w)
-    out = ops.dgx_mxfp4_gemm(xq, wq, xs, ws)
-    if b is not None:
-        out = out + b
-    return out
+    return ops.rowscale_linear(x, wq, ws, b)

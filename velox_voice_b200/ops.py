@@ -295,6 +295,52 @@ def sf_from_natural(fmt, scales: torch.Tensor, rows: int, k: int) -> torch.Tenso
     return out
 
 
+def _check_vector(t: Optional[torch.Tensor], name: str, n: int, dev, dtype=torch.float32) -> None:
+    if t is None:
+        return
+    _require_cuda(t, name)
+    if t.device != dev:
+        raise ValueError(f"{name} is on {t.device}, the operands are on {dev}")
+    if t.dtype != dtype or not t.is_contiguous() or t.numel() < n:
+        raise ValueError(f"{name} must be a contiguous {dtype} tensor with at least {n} entries")
+
+
+def _gemm_desc(a: Quantized, b: Quantized, bias: Optional[torch.Tensor]):
+    """Checks the operands of a GEMM (formats, K, device, bias) and returns a ``vx_gemm_desc``
+    with the operand side filled in, plus the tensors that must outlive the launch."""
+    if not isinstance(a, Quantized) or not isinstance(b, Quantized):
+        raise TypeError("operands must be Quantized (see quantize / ln_quantize)")
+    fa, fb = a.fmt, b.fmt
+    if fa == FMT_BLK16_A:
+        if fb != FMT_BLK16_B:
+            raise ValueError("BLK16: A must be quantized in mode 'A' and B in mode 'B'")
+    elif fa != fb:
+        raise ValueError(f"operand formats differ ({fa} vs {fb})")
+    if a.k != b.k:
+        raise ValueError(f"K mismatch: {a.k} vs {b.k}")
+    _require_cuda(a.codes, "A codes")
+    _require_cuda(b.codes, "B codes")
+    dev = a.codes.device
+    if b.codes.device != dev:
+        raise ValueError(f"operands on different devices ({dev} vs {b.codes.device})")
+    _check_vector(bias, "bias", b.rows, dev)
+    d = _lib.GemmDesc()
+    d.struct_size = C.sizeof(_lib.GemmDesc)
+    d.fmt = fa
+    d.M, d.N, d.K = a.rows, b.rows, a.k
+    d.a_codes, d.lda = a.codes.data_ptr(), a.codes.stride(0)
+    d.b_codes, d.ldb = b.codes.data_ptr(), b.codes.stride(0)
+    sa, sb = a.gemm_scales(), b.gemm_scales()
+    d.a_scales, d.b_scales = sa.data_ptr(), sb.data_ptr()
+    if fa == FMT_NV16:
+        if a.amax is None or b.amax is None:
+            raise ValueError("NV16 operands carry their tensor amax")
+        d.a_amax, d.b_amax = a.amax.data_ptr(), b.amax.data_ptr()
+    if bias is not None:
+        d.bias = bias.data_ptr()
+    return d, (sa, sb)
+
+
 def bsgemm(
     a: Quantized,
     b: Quantized,
@@ -311,7 +357,6 @@ def bsgemm(
     direct_store: bool = False,
     stream_b: bool = False,
     tiles: Optional[str] = None,
-    _dbg: int = 0,
 ):
     """``epilogue(A . B^T)``; A [M,K], B [N,K] quantized in the same format family.
 
@@ -321,43 +366,24 @@ def bsgemm(
     ``tiles`` overrides the FP4 tile shape the library would pick ("wide" 128 x 256, one
     accumulator; "narrow" 128 x 128, two accumulators); results do not depend on it.
     """
-    fa, fb = a.fmt, b.fmt
-    if fa == FMT_BLK16_A:
-        if fb != FMT_BLK16_B:
-            raise ValueError("BLK16: A must be quantized in mode 'A' and B in mode 'B'")
-    elif fa != fb:
-        raise ValueError(f"operand formats differ ({fa} vs {fb})")
-    if a.k != b.k:
-        raise ValueError(f"K mismatch: {a.k} vs {b.k}")
+    d, keep = _gemm_desc(a, b, bias)
     M, N, K = a.rows, b.rows, a.k
     dev = a.codes.device
     n_out = N // 2 if epilogue == EPI_BIAS_GLU else N
-    d = _lib.GemmDesc()
-    d.struct_size = C.sizeof(_lib.GemmDesc)
-    d.fmt = fa
-    d.M, d.N, d.K = M, N, K
-    d.a_codes, d.lda = a.codes.data_ptr(), a.codes.stride(0)
-    d.b_codes, d.ldb = b.codes.data_ptr(), b.codes.stride(0)
-    sa, sb = a.gemm_scales(), b.gemm_scales()
-    d.a_scales, d.b_scales = sa.data_ptr(), sb.data_ptr()
-    if fa == FMT_NV16:
-        d.a_amax, d.b_amax = a.amax.data_ptr(), b.amax.data_ptr()
     d.epilogue = epilogue
-    keep = [sa, sb]
-    if bias is not None:
-        if bias.dtype != torch.float32 or not bias.is_contiguous() or bias.numel() < N:
-            raise ValueError("bias must be a contiguous float32 vector with N entries")
-        d.bias = bias.data_ptr()
     if epilogue == EPI_BIAS_RESIDUAL:
         if residual is None:
             raise ValueError("EPI_BIAS_RESIDUAL needs `residual`")
+        _require_cuda(residual, "residual")
         residual = _rows2d(residual, "residual")
+        if residual.shape[0] != M or residual.shape[1] != N or residual.device != dev:
+            raise ValueError(f"residual must be [{M}, {N}] on {dev}")
         d.residual, d.residual_dtype, d.ldr = residual.data_ptr(), _dt(residual, "residual"), residual.stride(0)
         d.alpha = float(alpha)
     if tiles not in (None, "wide", "narrow"):
         raise ValueError("tiles must be None, 'wide' or 'narrow'")
     d.flags = ((GEMM_DIRECT_STORE if direct_store else 0) | (GEMM_STREAM_B if stream_b else 0)
-               | (GEMM_WIDE_TILES if tiles == "wide" else 0) | (GEMM_NARROW_TILES if tiles == "narrow" else 0) | (_dbg << 8))
+               | (GEMM_WIDE_TILES if tiles == "wide" else 0) | (GEMM_NARROW_TILES if tiles == "narrow" else 0))
     result = None
     if out_fmt is not None:
         ofmt = _fmt(out_fmt)
@@ -369,6 +395,7 @@ def bsgemm(
         if ofmt == FMT_NV16:
             if out_amax is None:
                 raise ValueError("NV16 output needs a calibrated tensor amax (out_amax)")
+            _check_vector(out_amax, "out_amax", 1, dev)
             d.out_amax = out_amax.data_ptr()
         result = Quantized(ofmt, M, n_out, codes, scales, sf_t, out_amax)
     else:
@@ -379,8 +406,9 @@ def bsgemm(
                 out = torch.empty((M, ld), dtype=out_dtype, device=dev)[:, :n_out]
             else:
                 out = torch.empty((M, n_out), dtype=out_dtype, device=dev)
-        if out.dim() != 2 or out.shape[0] != M or out.shape[1] != n_out or out.stride(1) != 1:
-            raise ValueError(f"out must be [{M}, {n_out}] with unit column stride")
+        _require_cuda(out, "out")
+        if out.dim() != 2 or out.shape[0] != M or out.shape[1] != n_out or out.stride(1) != 1 or out.device != dev:
+            raise ValueError(f"out must be [{M}, {n_out}] with unit column stride on {dev}")
         d.out_dtype, d.out, d.ldo = _dt(out, "out"), out.data_ptr(), out.stride(0)
         result = out
     _lib.check(_lib.load().vx_bsgemm(C.byref(d), _stream()), "vx_bsgemm")
@@ -395,33 +423,16 @@ def bsgemm_argmax(a: Quantized, b: Quantized, bias: Optional[torch.Tensor] = Non
     """Per row of ``A . B^T + bias``: the first column holding the maximum of the bf16-rounded
     result -- ``bsgemm(..., out_dtype=bfloat16).argmax(1)`` without writing the [M, N] matrix
     (the greedy CTC head).  Returns int32 ids [M] (and the winning values as float32 [M])."""
-    if a.fmt != b.fmt and not (a.fmt == FMT_BLK16_A and b.fmt == FMT_BLK16_B):
-        raise ValueError(f"operand formats differ ({a.fmt} vs {b.fmt})")
-    if a.k != b.k:
-        raise ValueError(f"K mismatch: {a.k} vs {b.k}")
+    d, keep = _gemm_desc(a, b, bias)
     M, N, K = a.rows, b.rows, a.k
     dev = a.codes.device
     if keys is None:
         keys = torch.empty((M,), dtype=torch.int64, device=dev)
     if ids is None:
         ids = torch.empty((M,), dtype=torch.int32, device=dev)
-    if keys.dtype != torch.int64 or keys.numel() < M or ids.dtype != torch.int32 or ids.numel() < M:
-        raise ValueError("keys must be int64 [M] and ids int32 [M]")
-    d = _lib.GemmDesc()
-    d.struct_size = C.sizeof(_lib.GemmDesc)
-    d.fmt = a.fmt
-    d.M, d.N, d.K = M, N, K
-    d.a_codes, d.lda = a.codes.data_ptr(), a.codes.stride(0)
-    d.b_codes, d.ldb = b.codes.data_ptr(), b.codes.stride(0)
-    sa, sb = a.gemm_scales(), b.gemm_scales()
-    d.a_scales, d.b_scales = sa.data_ptr(), sb.data_ptr()
-    if a.fmt == FMT_NV16:
-        d.a_amax, d.b_amax = a.amax.data_ptr(), b.amax.data_ptr()
+    _check_vector(keys, "keys", M, dev, torch.int64)
+    _check_vector(ids, "ids", M, dev, torch.int32)
     d.epilogue = EPI_BIAS_ARGMAX
-    if bias is not None:
-        if bias.dtype != torch.float32 or not bias.is_contiguous() or bias.numel() < N:
-            raise ValueError("bias must be a contiguous float32 vector with N entries")
-        d.bias = bias.data_ptr()
     d.out_dtype, d.out, d.ldo = DT_F32, keys.data_ptr(), 1
     lib = _lib.load()
     _lib.check(lib.vx_bsgemm(C.byref(d), _stream()), "vx_bsgemm")
@@ -429,7 +440,7 @@ def bsgemm_argmax(a: Quantized, b: Quantized, bias: Optional[torch.Tensor] = Non
     vmax = torch.empty((M,), dtype=torch.float32, device=dev) if return_max else None
     _lib.check(lib.vx_argmax_ids(keys.data_ptr(), M, ids.data_ptr(), _ptr(vmax), _stream()), "vx_argmax_ids")
     _count()
-    del sa, sb
+    del keep
     return (ids, vmax) if return_max else ids
 
 
@@ -437,7 +448,10 @@ def qkv_pack(qkv: torch.Tensor, p0: torch.Tensor, pos_u: torch.Tensor, pos_v: to
     """Single-pass attention fold pack, signature of the reference's ``qkv_pack``
     (``veloxvoice/kernels/ops/cuda_ops.py:554-581``): qkv bf16 [T, 3d], p0 bf16 [T, d],
     pos_u / pos_v [h, dk] -> (q2, k2, v2) bf16 [h, T, 2 dk] each."""
-    _require_cuda(qkv, "qkv")
+    for t, n in ((qkv, "qkv"), (p0, "p0"), (pos_u, "pos_u"), (pos_v, "pos_v")):
+        _require_cuda(t, n)
+        if t.device != qkv.device:
+            raise ValueError(f"{n} is on {t.device}, qkv on {qkv.device}")
     if qkv.dtype != torch.bfloat16 or p0.dtype != torch.bfloat16:
         raise ValueError("qkv and p0 must be bfloat16")
     T, d3 = qkv.shape
@@ -464,36 +478,33 @@ def bsgemm_qkv_pack(a: Quantized, w_qkv: Quantized, bias: Optional[torch.Tensor]
     bf16 projection, without the [T, 3d] intermediate).  Returns bf16 [3, h, T, 2 dk]:
     ``packed[0]`` = q2, ``packed[1]`` = k2 (second half of every head row NOT written: it belongs
     to ``bsgemm_heads(pos, lp, out=packed[1], col_off=dk)``), ``packed[2]`` = v2."""
+    d, keep = _gemm_desc(a, w_qkv, bias)
+    if a.fmt == FMT_ROWSCALE:
+        raise ValueError("the fused fold pack runs in the block-scaled formats and FP8, not per-row scales")
+    dev = a.codes.device
+    for t, n in ((pos_u, "pos_u"), (pos_v, "pos_v")):
+        _require_cuda(t, n)
+        if t.device != dev or t.dim() != 2 or t.shape != pos_u.shape:
+            raise ValueError("pos_u / pos_v must be [h, dk] tensors on the operands' device")
     h, dk = pos_u.shape
     M, N, K = a.rows, w_qkv.rows, a.k
-    if N != 3 * h * dk or a.k != w_qkv.k or a.fmt != w_qkv.fmt:
-        raise ValueError("w_qkv must be [3 h dk, K] in the format of the activations")
-    dev = a.codes.device
+    if N != 3 * h * dk:
+        raise ValueError("w_qkv must be [3 h dk, K]")
     if packed is None:
         packed = torch.empty((3, h, M, 2 * dk), dtype=torch.bfloat16, device=dev)
-    if packed.shape != (3, h, M, 2 * dk) or packed.dtype != torch.bfloat16 or not packed.is_contiguous():
-        raise ValueError("packed must be a contiguous bf16 [3, h, M, 2 dk] tensor")
+    _require_cuda(packed, "packed")
+    if (packed.shape != (3, h, M, 2 * dk) or packed.dtype != torch.bfloat16 or not packed.is_contiguous()
+            or packed.device != dev):
+        raise ValueError("packed must be a contiguous bf16 [3, h, M, 2 dk] tensor on the operands' device")
     u = pos_u.to(torch.bfloat16).contiguous()
     v = pos_v.to(torch.bfloat16).contiguous()
-    d = _lib.GemmDesc()
-    d.struct_size = C.sizeof(_lib.GemmDesc)
-    d.fmt = a.fmt
-    d.M, d.N, d.K = M, N, K
-    d.a_codes, d.lda = a.codes.data_ptr(), a.codes.stride(0)
-    d.b_codes, d.ldb = w_qkv.codes.data_ptr(), w_qkv.codes.stride(0)
-    sa, sb = a.gemm_scales(), w_qkv.gemm_scales()
-    d.a_scales, d.b_scales = sa.data_ptr(), sb.data_ptr()
-    if a.fmt == FMT_NV16:
-        d.a_amax, d.b_amax = a.amax.data_ptr(), w_qkv.amax.data_ptr()
     d.epilogue = EPI_BIAS_QKVPACK
-    if bias is not None:
-        d.bias = bias.data_ptr()
     d.out_dtype, d.out, d.ldo = DT_BF16, packed.data_ptr(), 2 * dk
     d.heads, d.head_dim = h, dk
     d.pos_u, d.pos_v, d.qk_scale = u.data_ptr(), v.data_ptr(), float(scale)
     _lib.check(_lib.load().vx_bsgemm(C.byref(d), _stream()), "vx_bsgemm")
     _count()
-    del sa, sb, u, v
+    del keep, u, v
     return packed
 
 
@@ -501,30 +512,23 @@ def bsgemm_heads(a: Quantized, w: Quantized, bias: Optional[torch.Tensor], out: 
     """``A . W^T (+ bias)`` written head-major: ``out`` bf16 [h, M, width], result column n goes to
     ``out[n // dk, m, col_off + n % dk]`` with dk = N / h.  With ``out = packed[1]`` and
     ``col_off = dk`` this puts lp(pos_emb) where the attention fold pack wants it."""
+    d, keep = _gemm_desc(a, w, bias)
+    _require_cuda(out, "out")
+    if out.dim() != 3:
+        raise ValueError("out must be [h, M, width]")
     h, M, width = out.shape
     N = w.rows
     dk = N // h
-    if M != a.rows or h * dk != N or out.dtype != torch.bfloat16 or not out.is_contiguous():
-        raise ValueError("out must be a contiguous bf16 [h, M, width] tensor with N = h * dk")
-    d = _lib.GemmDesc()
-    d.struct_size = C.sizeof(_lib.GemmDesc)
-    d.fmt = a.fmt
-    d.M, d.N, d.K = M, N, a.k
-    d.a_codes, d.lda = a.codes.data_ptr(), a.codes.stride(0)
-    d.b_codes, d.ldb = w.codes.data_ptr(), w.codes.stride(0)
-    sa, sb = a.gemm_scales(), w.gemm_scales()
-    d.a_scales, d.b_scales = sa.data_ptr(), sb.data_ptr()
-    if a.fmt == FMT_NV16:
-        d.a_amax, d.b_amax = a.amax.data_ptr(), w.amax.data_ptr()
+    if (M != a.rows or h * dk != N or out.dtype != torch.bfloat16 or not out.is_contiguous()
+            or out.device != a.codes.device):
+        raise ValueError("out must be a contiguous bf16 [h, M, width] tensor with N = h * dk on the operands' device")
     d.epilogue = EPI_BIAS if bias is not None else EPI_NONE
-    if bias is not None:
-        d.bias = bias.data_ptr()
     d.out_dtype, d.out, d.ldo = DT_BF16, out.data_ptr(), width
     d.heads, d.head_dim, d.head_col_off = h, dk, col_off
     d.flags = GEMM_OUT_HEADS
     _lib.check(_lib.load().vx_bsgemm(C.byref(d), _stream()), "vx_bsgemm")
     _count()
-    del sa, sb
+    del keep
     return out
 
 
@@ -664,6 +668,176 @@ def nvfp4_linear(x, wq, ws, P=4, C=8, w_bf16=None):
     b = _as_quantized_rowscale(wq, ws)
     out = bsgemm(a, b, epilogue=EPI_NONE, out_dtype=torch.float32)
     return out.view(*x.shape[:-1], N)
+
+
+def rowscale_linear(x2d: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor, bias: Optional[torch.Tensor] = None):
+    """``x2d [M, K] @ W^T (+ bias)`` on the reference's per-row-scaled FP4 lane, fp32 out, in two
+    launches: quantize the activation rows, then one GEMM whose epilogue applies the row and
+    column scales and adds the bias.  The reference's ``DenseLinear.forward``
+    (``veloxvoice/models/wenet/torch_conformer.py:251-266``) spends a pad copy, a cast, the
+    quantizer, the GEMM, a slice and a bias add on the same result."""
+    a = quantize(x2d, FMT_ROWSCALE, sf=False)
+    b = _as_quantized_rowscale(wq, ws)
+    if bias is None:
+        return bsgemm(a, b, epilogue=EPI_NONE, out_dtype=torch.float32)
+    if bias.dtype != torch.float32 or not bias.is_contiguous():
+        bias = bias.float().contiguous()
+    return bsgemm(a, b, epilogue=EPI_BIAS, bias=bias, out_dtype=torch.float32)
+
+
+# ---- bf16 operator names of the reference, served by the quantized path -----------------------
+# The reference's fused_qkv_wgmma / pwlin_glu are bf16 Hopper kernels whose sources do not build
+# for sm_100a.  Here the same names quantize the activation and run one block-scaled GEMM with
+# the bias (+ GLU) in its epilogue.  The weight is quantized once per (tensor, version) and kept
+# in a small cache; the format is VELOXVOICE_QFORMAT (mx32 by default).
+
+_WEIGHT_CACHE: "dict" = {}
+_WEIGHT_CACHE_MAX = 256
+
+
+def _qformat() -> int:
+    import os
+
+    name = os.environ.get("VELOXVOICE_QFORMAT", "mx32").lower()
+    fmt = _fmt(name)
+    if fmt not in (FMT_MX32, FMT_NV16, FMT_FP8_1X128):
+        raise ValueError("VELOXVOICE_QFORMAT must be mx32, nv16 or fp8_1x128 for the bf16 operator names")
+    return fmt
+
+
+def _packed_weight(w: torch.Tensor, b: Optional[torch.Tensor], fmt: int, glu: bool):
+    from .linear import PackedLinear
+
+    key = (w.data_ptr(), tuple(w.shape), w.dtype, w._version, fmt, glu,
+           None if b is None else (b.data_ptr(), b._version))
+    hit = _WEIGHT_CACHE.get(key)
+    if hit is None:
+        if len(_WEIGHT_CACHE) >= _WEIGHT_CACHE_MAX:
+            _WEIGHT_CACHE.pop(next(iter(_WEIGHT_CACHE)))
+        hit = PackedLinear(w.float(), None if b is None else b.float(), fmt, glu=glu)
+        _WEIGHT_CACHE[key] = hit
+    return hit
+
+
+def _quantized_activation(x2d: torch.Tensor, fmt: int) -> Quantized:
+    return quantize(x2d, fmt, natural=fmt == FMT_FP8_1X128)
+
+
+def _linear_supported(x, w, glu: bool) -> bool:
+    if not (isinstance(x, torch.Tensor) and x.is_cuda and x.dtype == torch.bfloat16):
+        return False
+    K = x.shape[-1]
+    if w.dim() != 2 or w.shape[1] != K or K % 128 != 0:
+        return False
+    if glu:
+        from .linear import glu_tile
+
+        if w.shape[0] % glu_tile(_qformat()) != 0:
+            return False
+    return True
+
+
+def fused_qkv_wgmma(x, w, b, out=None):
+    """``out = x @ w^T + b`` in bf16 for the fused q|k|v projection
+    (``veloxvoice/kernels/ops/cuda_ops.py:480-539``).  Returns ``None`` when the input is not a
+    bf16 CUDA tensor or the shape is not supported, so the caller falls back to ``F.linear``
+    exactly as with the reference; never compiles anything at call time."""
+    if not _linear_supported(x, w, False):
+        return None
+    fmt = _qformat()
+    x2 = x.reshape(-1, x.shape[-1])
+    M, N = x2.shape[0], w.shape[0]
+    if out is None:
+        out = torch.empty(M, N, device=x.device, dtype=x.dtype)
+    o2 = out.reshape(M, N)
+    if o2.data_ptr() != out.data_ptr() or o2.stride(1) != 1:
+        return None
+    lin = _packed_weight(w, b, fmt, False)
+    am = amax(x2) if fmt == FMT_NV16 else None
+    lin(quantize(x2, fmt, natural=fmt == FMT_FP8_1X128, amax_t=am), out=o2)
+    return out
+
+
+def fused_qkv(x, w, bias, out=None):
+    """x [M, K]; w [3N, K]; bias [3N] -> out [M, 3N] (``cuda_ops.py:292-304``; the reference's
+    kernel is an fp32 GEMV for M <= 32).  bf16 inputs run on the quantized path; anything
+    else is computed by ``F.linear`` in the input's dtype, like the reference's result."""
+    r = fused_qkv_wgmma(x, w, bias, out)
+    if r is not None:
+        return r
+    y = torch.nn.functional.linear(x, w.to(x.dtype), None if bias is None else bias.to(x.dtype))
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+def pwlin_glu(x, w, b, out=None):
+    """``out = glu(x @ w^T + b)`` in bf16: value = first half of the channels, gate = second half
+    (``cuda_ops.py:363-401``).  ``None`` for inputs the path does not take (not bf16 / not CUDA /
+    K not a multiple of 128 / channel count not a multiple of the GLU tile)."""
+    if not _linear_supported(x, w, True):
+        return None
+    fmt = _qformat()
+    x2 = x.reshape(-1, x.shape[-1])
+    M, Nh = x2.shape[0], w.shape[0] // 2
+    if out is None:
+        out = torch.empty(x.shape[:-1] + (Nh,), device=x.device, dtype=x.dtype)
+    o2 = out.reshape(M, Nh)
+    if o2.data_ptr() != out.data_ptr() or o2.stride(1) != 1:
+        return None
+    lin = _packed_weight(w, b, fmt, True)
+    am = amax(x2) if fmt == FMT_NV16 else None
+    lin(quantize(x2, fmt, natural=fmt == FMT_FP8_1X128, amax_t=am), out=o2)
+    return out
+
+
+# ---- model-side helper names (veloxvoice/models/wenet/nvfp4_linear.py) -------------------------
+
+_E2M1_THRESHOLDS = (0.25, 0.75, 1.25, 1.75, 2.5, 3.5)
+
+
+def _encode_codes(w: torch.Tensor) -> torch.Tensor:
+    """float -> u8 E2M1 codes (sign << 3 | magnitude 0..6), ``nvfp4_linear.py:22-36``: the
+    magnitude is the number of thresholds strictly exceeded by |w|, the sign bit is ``w < 0``."""
+    edges = torch.tensor(_E2M1_THRESHOLDS, dtype=w.dtype if w.is_floating_point() else torch.float32, device=w.device)
+    mag = torch.bucketize(w.abs().contiguous(), edges, right=False).to(torch.uint8)  # edges strictly below |w|
+    return mag | ((w < 0).to(torch.uint8) << 3)
+
+
+def pack_codes(c: torch.Tensor) -> torch.Tensor:
+    """codes [R, K] -> packed u8 [R, K/2] on the GPU, even k in the low nibble (``nvfp4_linear.py:39-40``)."""
+    lo, hi = c[:, 0::2] & 0xF, c[:, 1::2] & 0xF
+    return (lo | (hi << 4)).to(torch.uint8).cuda()
+
+
+def decode_codes(packed: torch.Tensor) -> torch.Tensor:
+    """packed u8 [R, K/2] -> codes u8 [R, K] (``nvfp4_linear.py:103-107``)."""
+    both = torch.stack((packed & 0xF, (packed >> 4) & 0xF), dim=-1)
+    return both.reshape(packed.shape[0], packed.shape[1] * 2)
+
+
+def ue8m0_from_scale(s) -> int:
+    """Scalar scale -> biased exponent byte with the exponent truncated toward zero
+    (``nvfp4_linear.py:43-49``; not the rule the quantize kernels use)."""
+    import math
+
+    if s <= 0.0:
+        return 0x80
+    return max(0, min(255, math.trunc(math.log2(s)) + 127))
+
+
+def ue8m0_to_float(u) -> float:
+    """``nvfp4_linear.py:52-53``."""
+    return float(2.0 ** (int(u) - 127))
+
+
+def quantize_and_gemm(x, wq, ws, P=1, C=8):
+    """Quantize ``x`` per row, then the per-row-scaled GEMM (``nvfp4_linear.py:81-100``).  The
+    reference quantizes on a side stream and joins with an event; both launches are stream
+    ordered here, which gives the same result without the extra stream."""
+    xq, xs = quantize_w(x)
+    return dgx_mxfp4_gemm(xq, wq, xs, ws, P, C)
 
 
 def fused_layernorm(x, w, b, eps=1e-5, out=None):

@@ -153,8 +153,9 @@ class ConformerLinearStack:
 
     # ---- forward
     def forward(self, x: torch.Tensor, pos: Optional[torch.Tensor] = None, *, return_hidden: bool = False,
-                ids_only: bool = False, keys=None, ids=None):
-        """x: bf16 [T, d_model] residual stream (overwritten in place); returns bf16 logits [T, vocab]."""
+                ids_only: bool = False, keys=None, ids=None, out_logits: Optional[torch.Tensor] = None):
+        """x: bf16 [T, d_model] residual stream (overwritten in place); returns bf16 logits [T, vocab]
+        (written into ``out_logits`` when given: bf16 [T, vocab], unit column stride)."""
         cfg = self.cfg
         if x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != cfg.d_model:
             raise ValueError("x must be bf16 [T, d_model]")
@@ -184,7 +185,7 @@ class ConformerLinearStack:
             q_in = self._lnq("after", x)
         if ids_only:
             return self.p["ctc"].argmax(q_in, keys=keys, ids=ids)
-        logits = self.p["ctc"](q_in)
+        logits = self.p["ctc"](q_in, out=out_logits)
         return (logits, x) if return_hidden else logits
 
     def forward_ids(self, x: torch.Tensor, pos: Optional[torch.Tensor] = None, *, keys=None, ids=None):
