@@ -88,42 +88,76 @@ def glu_interleave_rows(n_out: int, tile: int = 128) -> np.ndarray:
     return np.asarray(idx, dtype=np.int64)
 
 
+def fma32(a, b, c) -> np.ndarray:
+    """Correctly rounded fp32 fused multiply-add ``a * b + c`` (one rounding), elementwise.
+
+    The product of two fp32 numbers is exact in fp64; the sum with ``c`` is formed in fp64, its
+    rounding error recovered exactly (two-sum), and the fp64 result pushed to the neighbour with an
+    odd last bit when it was inexact (round to odd).  Rounding that to fp32 then equals a single
+    rounding of the exact value (fp64 carries more than two extra bits).
+    """
+    a = np.asarray(a, dtype=np.float32).astype(np.float64)
+    b = np.asarray(b, dtype=np.float32).astype(np.float64)
+    c = np.asarray(c, dtype=np.float32).astype(np.float64)
+    p = a * b
+    s = p + c
+    bb = s - p
+    err = (p - (s - bb)) + (c - bb)
+    s, err = np.broadcast_arrays(s, err)
+    bits = s.view(np.int64) if s.flags["C_CONTIGUOUS"] else np.ascontiguousarray(s).view(np.int64)
+    inexact = (err != 0) & np.isfinite(s)
+    even = (bits & 1) == 0
+    toward = np.where(err > 0, np.inf, -np.inf)
+    s_odd = np.where(inexact & even, np.nextafter(s, toward), s)
+    return s_odd.astype(np.float32)
+
+
+def rsqrt32(x) -> np.ndarray:
+    """Correctly rounded fp32 ``1 / sqrt(x)`` (extended precision, then one rounding to fp32)."""
+    x = np.asarray(x, dtype=np.float32).astype(np.longdouble)
+    return (np.longdouble(1.0) / np.sqrt(x)).astype(np.float32)
+
+
 def layernorm_ref(x, gamma, beta, eps: float = 1e-5) -> np.ndarray:
     """Row LayerNorm with the fused CUDA kernel's exact fp32 operation order.
 
-    Formula of ``velox_layernorm.cu:52-57`` (``var = E[x^2] - mean^2`` clamped at 0).  The
-    order of the additions is this library's: lane ``l`` of 32 sums, chunk by chunk of 256
-    elements, its 8 consecutive elements ``[256 c + 8 l, +8)``; lanes are then combined by a
-    butterfly (xor 16, 8, 4, 2, 1).  ``rstd = 1 / sqrt(var + eps)`` with both operations
-    correctly rounded; no fused multiply-add anywhere.
+    Formula of ``velox_layernorm.cu:52-57`` (``var = E[x^2] - mean^2`` clamped at 0), evaluated
+    with fused multiply-adds in this library's order: lane ``l`` of 32 owns, chunk by chunk of
+    256 elements, the eight consecutive elements ``[256 c + 8 l, +8)`` and keeps separate sums
+    for its even and its odd elements (``S += v``, ``Q = fma(v, v, Q)``); the two are added, lanes
+    are combined by a butterfly (xor 16, 8, 4, 2, 1); ``mean = s / K``, ``ex2 = q / K``,
+    ``var = max(fma(-mean, mean, ex2), 0)``, ``rstd = 1 / sqrt(var + eps)`` correctly rounded in
+    one step, ``y = fma(fma(x, rstd, -mean * rstd), gamma, beta)``.
     """
     x = F._f32(x)
     M, K = x.shape
     ch = -(-K // 256)
     xp = np.zeros((M, ch * 256), dtype=np.float32)
     xp[:, :K] = x
-    xl = xp.reshape(M, ch, 32, 8)
-    s = np.zeros((M, 32), dtype=np.float32)
-    sq = np.zeros((M, 32), dtype=np.float32)
+    xl = xp.reshape(M, ch, 32, 4, 2)  # [row, chunk, lane, pair, even/odd]
+    s = np.zeros((M, 32, 2), dtype=np.float32)
+    sq = np.zeros((M, 32, 2), dtype=np.float32)
     for c in range(ch):
-        for j in range(8):
-            v = xl[:, c, :, j]
+        for j in range(4):
+            v = xl[:, c, :, j, :]
             s = (s + v).astype(np.float32)
-            sq = (sq + (v * v).astype(np.float32)).astype(np.float32)
+            sq = fma32(v, v, sq)
+    s = (s[:, :, 0] + s[:, :, 1]).astype(np.float32)
+    sq = (sq[:, :, 0] + sq[:, :, 1]).astype(np.float32)
     lanes = np.arange(32)
     for o in (16, 8, 4, 2, 1):
         s = (s + s[:, lanes ^ o]).astype(np.float32)
         sq = (sq + sq[:, lanes ^ o]).astype(np.float32)
     kf = F32(K)
     mean = (s[:, 0] / kf).astype(np.float32)
-    var = np.maximum(((sq[:, 0] / kf).astype(np.float32) - (mean * mean).astype(np.float32)).astype(np.float32), F32(0))
-    rstd = (F32(1.0) / np.sqrt((var + F32(eps)).astype(np.float32)).astype(np.float32)).astype(np.float32)
+    ex2 = (sq[:, 0] / kf).astype(np.float32)
+    var = np.maximum(fma32(-mean, mean, ex2), F32(0))
+    rstd = rsqrt32((var + F32(eps)).astype(np.float32))
+    nmr = ((-mean) * rstd).astype(np.float32)
     g = np.asarray(gamma, dtype=np.float32)[None, :]
     b = np.asarray(beta, dtype=np.float32)[None, :]
-    y = (x - mean[:, None]).astype(np.float32)
-    y = (y * rstd[:, None]).astype(np.float32)
-    y = (y * g).astype(np.float32)
-    return (y + b).astype(np.float32)
+    t = fma32(x, rstd[:, None], nmr[:, None])
+    return fma32(t, g, b)
 
 
 def qkv_pack_ref(qkv, p0, pos_u, pos_v, scale: float, heads: int):

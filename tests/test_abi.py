@@ -75,6 +75,87 @@ def test_argument_errors_do_not_need_a_device(lib):
     assert lib.vx_quantize_pack(None, 1, 0, 64, 64, 0, None, 32, None, None, None, None) == 0
 
 
+def _gemm_desc(lib, fmt=_lib.FMT_MX32, epi=_lib.EPI_NONE, flags=0):
+    """A descriptor whose pointers are never dereferenced: argument checks come before any launch."""
+    d = _lib.GemmDesc()
+    d.struct_size = C.sizeof(_lib.GemmDesc)
+    d.fmt = fmt
+    d.M, d.N, d.K = 128, 1536, 512
+    d.a_codes, d.b_codes, d.lda, d.ldb = 4096, 8192, 256, 256
+    d.a_scales, d.b_scales = 12288, 16384
+    d.out, d.ldo, d.out_dtype = 20480, 1536, _lib.DT_BF16
+    d.epilogue, d.flags = epi, flags
+    return d
+
+
+def test_gemm_rejects_what_it_cannot_run_before_any_launch(lib):
+    # the fold-pack epilogue has no per-row-scaled route: an argument error, not a launch
+    d = _gemm_desc(lib, fmt=_lib.FMT_ROWSCALE, epi=_lib.EPI_BIAS_QKVPACK)
+    d.heads, d.head_dim, d.ldo = 8, 64, 128
+    d.pos_u, d.pos_v = 24576, 28672
+    assert lib.vx_bsgemm(C.byref(d), None) == -1
+    assert b"QKVPACK" in lib.vx_last_error()
+    # unknown flag bits (anything above the documented VX_GEMM_* values)
+    for bad in (1 << 8, 1 << 9, 1 << 20, 32):
+        d = _gemm_desc(lib, flags=bad)
+        assert lib.vx_bsgemm(C.byref(d), None) == -1
+        assert b"flags" in lib.vx_last_error()
+    # the bounded-wait self-test takes a limit of at most 100 ms and a site below 255
+    assert lib.vx_wait_selftest(0, 1, None) == -1
+    assert lib.vx_wait_selftest(10**9, 1, None) == -1
+    assert lib.vx_wait_selftest(1000, 255, None) == -1
+
+
+def test_host_wrappers_validate_operands_without_a_device():
+    import torch
+
+    from velox_voice_b200 import ops
+
+    cpu_q = ops.Quantized(_lib.FMT_MX32, 4, 64, torch.zeros(4, 32, dtype=torch.uint8), None,
+                          torch.zeros(1, 2, 512, dtype=torch.uint8), None)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.bsgemm(cpu_q, cpu_q)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.bsgemm_argmax(cpu_q, cpu_q)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.bsgemm_heads(cpu_q, cpu_q, None, torch.zeros(1, 4, 64, dtype=torch.bfloat16))
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.bsgemm_qkv_pack(cpu_q, cpu_q, None, torch.zeros(1, 64), torch.zeros(1, 64), 1.0)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.qkv_pack(torch.zeros(4, 192, dtype=torch.bfloat16), torch.zeros(4, 64, dtype=torch.bfloat16),
+                     torch.zeros(1, 64), torch.zeros(1, 64), 1.0)
+    other = ops.Quantized(_lib.FMT_NV16, 4, 64, cpu_q.codes, None, cpu_q.sf, None)
+    with pytest.raises(ValueError, match="formats differ"):
+        ops.bsgemm_heads(cpu_q, other, None, torch.zeros(1, 4, 64, dtype=torch.bfloat16))
+    wider = ops.Quantized(_lib.FMT_MX32, 4, 128, torch.zeros(4, 64, dtype=torch.uint8), None, cpu_q.sf, None)
+    with pytest.raises(ValueError, match="K mismatch"):
+        ops.bsgemm_heads(cpu_q, wider, None, torch.zeros(1, 4, 64, dtype=torch.bfloat16))
+    # the bf16 operator names keep the reference's convention: None means "not taken, fall back"
+    assert ops.fused_qkv_wgmma(torch.zeros(64, 512), torch.zeros(1536, 512), torch.zeros(1536)) is None
+    assert ops.pwlin_glu(torch.zeros(64, 512, dtype=torch.bfloat16), torch.zeros(1024, 512), torch.zeros(1024)) is None
+    x = torch.randn(3, 8)
+    w, b = torch.randn(6, 8), torch.randn(6)
+    assert torch.allclose(ops.fused_qkv(x, w, b), torch.nn.functional.linear(x, w, b))
+
+
+def test_model_side_helpers_follow_the_reference_rules():
+    import numpy as np
+    import torch
+
+    from oracle import formats as F
+    from velox_voice_b200 import ops
+
+    torch.manual_seed(0)
+    w = torch.randn(16, 64) * 2
+    w[0, :8] = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, -0.25, -1e-9])
+    codes = ops._encode_codes(w)
+    assert np.array_equal(codes.numpy(), F.e2m1_encode(w.numpy()))
+    assert np.array_equal(ops.decode_codes(torch.from_numpy(F.pack_codes(codes.numpy()))).numpy(), codes.numpy())
+    assert ops.ue8m0_to_float(127) == 1.0 and ops.ue8m0_to_float(130) == 8.0
+    assert ops.ue8m0_from_scale(1.0) == 127 and ops.ue8m0_from_scale(0.3) == 126 and ops.ue8m0_from_scale(0.0) == 0x80
+    assert ops.ue8m0_from_scale(3.9) == 128 and ops.ue8m0_from_scale(1e-60) == 0
+
+
 def test_ops_refuse_cpu_tensors():
     import torch
 
@@ -98,6 +179,12 @@ def test_install_wires_reference_import_names():
     assert tri.mxfp4_block_quantize is ops.mxfp4_block_quantize
     assert sys.modules["veloxvoice.models.wenet.mxfp4_linear"]._pad16 is ops._pad16
     assert "veloxvoice.models.wenet.nvfp4_linear" in mods
+    nv = sys.modules["veloxvoice.models.wenet.nvfp4_linear"]
+    for name in ("CODE_LUT", "_encode_codes", "dequantize_w", "pack_codes", "quantize_w", "ue8m0_from_scale",
+                 "ue8m0_to_float", "decode_codes", "quantize_and_gemm", "Nvfp4Linear", "nvfp4_gemm"):
+        assert hasattr(nv, name), name  # what the reference's kernel test imports (tests/kernels/test_dgx_mxfp4_gemm.py:24-32)
+    for name in ("fused_qkv", "fused_qkv_wgmma", "pwlin_glu", "qkv_pack", "dgx_mxfp4_gemm"):
+        assert name in install.OPS_PKG_NAMES
     for n in ("veloxvoice.kernels.ops.triton_ops", "veloxvoice.models.wenet.mxfp4_linear", "veloxvoice.models.wenet.nvfp4_linear"):
         del sys.modules[n]
 

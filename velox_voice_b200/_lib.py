@@ -99,7 +99,9 @@ _lib = None
 
 
 def lib_path() -> str:
-    return _build.LIB_PATH
+    """The shared object that gets loaded: ``VELOX_B200_LIB`` (a path to another build of the
+    same ABI) if set, else the in-tree build."""
+    return os.environ.get("VELOX_B200_LIB") or _build.LIB_PATH
 
 
 def load(build_if_missing: bool = True) -> C.CDLL:
@@ -108,8 +110,8 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     with _lock:
         if _lib is not None:
             return _lib
-        path = _build.LIB_PATH
-        if build_if_missing and not _build.is_current():
+        path = lib_path()
+        if path == _build.LIB_PATH and build_if_missing and not _build.is_current():
             try:
                 _build.build()
             except Exception as e:  # no nvcc on this machine: use the shipped binary if any

@@ -158,35 +158,115 @@ __device__ __forceinline__ float rcp_ftz(float x) {
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// Four Swish values with one reciprocal (the special-function unit is the busiest pipe of the
-// Swish epilogues): with d_i = 1 + 2^(-z_i log2 e), 1/d_0 = d_1 (d_2 d_3) / (d_0 d_1 d_2 d_3) and so
-// on -- 1.25 MUFU operations per value instead of 2, nine extra multiplications per four values
-// (measured 152 -> 144 us on the FFN-up kernel).  The exponent is capped at 2^30 so the product
-// of four cannot overflow; a sigmoid below 2^-30 only occurs for z < -20.8, where z * sigmoid(z)
-// is below 1e-7 in magnitude either way.
 __device__ __forceinline__ float sigmoid_f(float z) { return rcp_ftz(1.0f + ex2_ftz(-1.4426950408889634f * z)); }
-// z_i *= sigmoid(g_i) for four values
-__device__ __forceinline__ void mul_sigmoid4(float& z0, float& z1, float& z2, float& z3,
-                                             float g0, float g1, float g2, float g3) {
-  const float d0 = 1.0f + ex2_ftz(fminf(-1.4426950408889634f * g0, 30.0f));
-  const float d1 = 1.0f + ex2_ftz(fminf(-1.4426950408889634f * g1, 30.0f));
-  const float d2 = 1.0f + ex2_ftz(fminf(-1.4426950408889634f * g2, 30.0f));
-  const float d3 = 1.0f + ex2_ftz(fminf(-1.4426950408889634f * g3, 30.0f));
-  const float p01 = __fmul_rn(d0, d1), p23 = __fmul_rn(d2, d3);
-  const float r = rcp_ftz(__fmul_rn(p01, p23));
-  const float r01 = __fmul_rn(r, p23), r23 = __fmul_rn(r, p01);
-  z0 = __fmul_rn(z0, __fmul_rn(r01, d1));
-  z1 = __fmul_rn(z1, __fmul_rn(r01, d0));
-  z2 = __fmul_rn(z2, __fmul_rn(r23, d3));
-  z3 = __fmul_rn(z3, __fmul_rn(r23, d2));
+// Four Swish values z * sigmoid(z), held as two packed pairs za = (z0, z1), zb = (z2, z3), with
+// ONE reciprocal (the special-function unit is the busiest pipe of the Swish epilogues) and packed
+// fp32x2 arithmetic (their cost is instruction issue):
+//   d = 1 + 2^min(-z log2 e, 30)                          mul.f32x2, min, ex2 (MUFU), add.f32x2
+//   A = (d0, d1), B = (d2, d3), P = A * B = (d0 d2, d1 d3), r = 1 / (P.lo P.hi)
+//   (r P.hi, r P.lo) * B = (1/d0, 1/d1),   (r P.hi, r P.lo) * A = (1/d2, 1/d3)
+// -- 1.25 special-function operations per value, seven packed / scalar multiplies per four.
+// The exponent is capped at 2^30 so the product of four cannot overflow; a sigmoid below 2^-30
+// only occurs for z < -20.8, where z * sigmoid(z) is below 1e-7 in magnitude either way.
+// Every Swish of the library goes through this function, so the fp32 / bf16 outputs and the FP4
+// re-quantized output of the same GEMM see the same bits.
+__device__ __forceinline__ void swish4p(uint64_t& za, uint64_t& zb) {
+  const uint64_t nl2e = pack_f32x2(-1.4426950408889634f, -1.4426950408889634f);
+  const uint64_t one2 = pack_f32x2(1.0f, 1.0f);
+  float t0, t1, t2, t3;
+  unpack_f32x2(mul_f32x2(za, nl2e), t0, t1);
+  unpack_f32x2(mul_f32x2(zb, nl2e), t2, t3);
+  const uint64_t da = add_f32x2(pack_f32x2(ex2_ftz(fminf(t0, 30.0f)), ex2_ftz(fminf(t1, 30.0f))), one2);
+  const uint64_t db = add_f32x2(pack_f32x2(ex2_ftz(fminf(t2, 30.0f)), ex2_ftz(fminf(t3, 30.0f))), one2);
+  float p0, p1;
+  unpack_f32x2(mul_f32x2(da, db), p0, p1);
+  const float rr = rcp_ftz(__fmul_rn(p0, p1));
+  const uint64_t rp = mul_f32x2(pack_f32x2(p1, p0), pack_f32x2(rr, rr));
+  za = mul_f32x2(za, mul_f32x2(rp, db));
+  zb = mul_f32x2(zb, mul_f32x2(rp, da));
 }
 __device__ __forceinline__ void silu4_f(float& z0, float& z1, float& z2, float& z3) {
-  mul_sigmoid4(z0, z1, z2, z3, z0, z1, z2, z3);
+  uint64_t za = pack_f32x2(z0, z1), zb = pack_f32x2(z2, z3);
+  swish4p(za, zb);
+  unpack_f32x2(za, z0, z1);
+  unpack_f32x2(zb, z2, z3);
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// Swish + re-quantization of one 32-column chunk of one output row, straight from the accumulator
+// registers to E2M1 codes: the epilogue of the FFN up-projection, whose cost is instruction issue
+// (one thread per row, 32 values each), so everything that can is done two values per
+// instruction with the packed fp32x2 forms:
+//   z = acc (* tensor scales) + bias                      add.f32x2 (mul.f32x2)
+//   s = z * sigmoid(z)                                    swish4p, four values at a time
+//   block maximum with three-input max; the E2M1 encode of e2m1_pack8p.
+// NV16 = false: one UE8M0 scale for the 32 values; true: two E4M3 scales (16 values each).
+// Returns the scale byte(s), little end first.
+template <bool NV16>
+__device__ __forceinline__ uint32_t swish_quant_chunk(const uint32_t (&r)[32], const float* bias_s, bool scale_acc,
+                                                      float g_ab, float g_out, uint32_t (&w)[4]) {
+  uint64_t sv[16];
+  const uint64_t g2 = pack_f32x2(g_ab, g_ab);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    uint64_t za = pack_f32x2(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]));
+    uint64_t zb = pack_f32x2(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+    if (NV16 && scale_acc) {
+      za = mul_f32x2(za, g2);
+      zb = mul_f32x2(zb, g2);
+    }
+    if (bias_s) {
+      const float4 b = *reinterpret_cast<const float4*>(bias_s + 4 * i);
+      za = add_f32x2(za, pack_f32x2(b.x, b.y));
+      zb = add_f32x2(zb, pack_f32x2(b.z, b.w));
+    }
+    swish4p(za, zb);
+    sv[2 * i] = za;
+    sv[2 * i + 1] = zb;
+  }
+  uint32_t sbytes = 0;
+  if constexpr (!NV16) {
+    float a = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      float lo, hi;
+      unpack_f32x2(sv[j], lo, hi);
+      a = max3(a, fabsf(lo), fabsf(hi));
+    }
+    float rcp;
+    ue8m0_from_amax(a, sbytes, rcp);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint64_t v[4] = {sv[4 * q], sv[4 * q + 1], sv[4 * q + 2], sv[4 * q + 3]};
+      w[q] = e2m1_pack8p<true, false, true>(v, rcp);
+    }
+  } else {
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      float a = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float lo, hi;
+        unpack_f32x2(sv[8 * hh + j], lo, hi);
+        a = max3(a, fabsf(lo), fabsf(hi));
+      }
+      uint32_t byte;
+      float rcp;
+      nv16_block(a, g_out, byte, rcp);
+      sbytes |= byte << (8 * hh);
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int b = 8 * hh + 4 * q;
+        const uint64_t v[4] = {sv[b], sv[b + 1], sv[b + 2], sv[b + 3]};
+        w[2 * hh + q] = e2m1_pack8p<false, false, true>(v, rcp);
+      }
+    }
+  }
+  return sbytes;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -395,10 +475,8 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   // MMA -> epilogue -> MMA hand-over: they read the second 32-column chunk only after the first
   // is finished (half the live registers), which releases tensor memory later at no cost.
   constexpr bool SEQ = (EPI == VX_EPI_BIAS_SWISH) && NCH == 2;
-  // Swish with NV16 output on the wide tile: software-pipelined epilogue (see PIPE below).
-  // Measured at T = 90000: NV16 FFN chain 343 -> 331 us with it; the MX32 FFN-up kernel got
-  // slower (154 -> 165 us), so the 32-block kinds keep the plain chunk-after-chunk order.
-  constexpr bool PIPE = SEQ && OUT == 2 && kind_vec4(KIND);
+  // Swish + FP4 output (the FFN up-projection): its own register-lean path, see swish_quant_chunk.
+  constexpr bool SWQ = EPI == VX_EPI_BIAS_SWISH && OUT == 2;
 
   const int out_dtype = OUT == 1 ? static_cast<int>(VX_BF16) : (OUT == 2 ? static_cast<int>(VX_FP4) : p.out_dtype);
   const bool tma_store = OUT == 1 ? true : (OUT == 2 ? false : p.tma_store != 0);
@@ -789,53 +867,6 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         res_inflight = true;
       }
     }
-    // PIPE: the chunk whose Swish is done and whose E2M1 encode is still pending, with where it goes
-    float za[PIPE ? 32 : 1], zb[PIPE ? 32 : 1];
-    float pend_rcp0 = 0.0f, pend_rcp1 = 0.0f;
-    uint32_t pend_sb = 0;
-    bool pend_ok = false, pend_col_ok = false;
-    uint8_t* pend_codes = nullptr;
-    int64_t pend_sf = 0, pend_nat = 0;
-    // Block scale(s) of a finished chunk: MX32 one UE8M0 byte, NV16 two E4M3 bytes.
-    auto chunk_scales = [&](const float (&zc)[32], float& rcp0, float& rcp1) -> uint32_t {
-      if (out_fmt == VX_FMT_MX32) {
-        float a = fabsf(zc[0]);
-#pragma unroll
-        for (int i = 1; i < 32; ++i) a = fmaxf(a, fabsf(zc[i]));
-        uint32_t byte;
-        ue8m0_from_amax(a, byte, rcp0);
-        rcp1 = rcp0;
-        return byte;
-      } else {
-        uint32_t sb2 = 0;
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          float a = fabsf(zc[16 * hh]);
-#pragma unroll
-          for (int i = 1; i < 16; ++i) a = fmaxf(a, fabsf(zc[16 * hh + i]));
-          uint32_t byte;
-          float rcp;
-          nv16_block(a, g_out, byte, rcp);
-          if (hh == 0) rcp0 = rcp; else rcp1 = rcp;
-          sb2 |= byte << (8 * hh);
-        }
-        return sb2;
-      }
-    };
-    // Codes + scale byte(s) of the pending chunk to memory.
-    auto pend_store = [&](const uint32_t (&w)[4]) {
-      if (pend_ok) *reinterpret_cast<uint4*>(pend_codes) = make_uint4(w[0], w[1], w[2], w[3]);
-      if (pend_col_ok) {  // rows of the last tile beyond M get zero scale factors
-        const uint32_t sbw = pend_ok ? pend_sb : 0u;
-        if (out_fmt == VX_FMT_MX32) {
-          p.out_sf[pend_sf] = static_cast<uint8_t>(sbw);
-          if (p.out_scales && pend_ok) p.out_scales[pend_nat] = static_cast<uint8_t>(sbw);
-        } else {
-          *reinterpret_cast<uint16_t*>(p.out_sf + pend_sf) = static_cast<uint16_t>(sbw);
-          if (p.out_scales && pend_ok) *reinterpret_cast<uint16_t*>(p.out_scales + pend_nat) = static_cast<uint16_t>(sbw);
-        }
-      }
-    };
     for (int it = 0; it < my_tiles && ok; ++it) {
       const int64_t row = static_cast<int64_t>(mb) * BM + q * 32 + lane;
       const bool row_ok = row < p.M;
@@ -853,70 +884,49 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         __syncwarp();
         bias_nb = nb;
       }
-      if constexpr (PIPE) {
-        // Software-pipelined epilogue.  Swish is bound by the special-function unit (ex2 + rcp
-        // per value, a quarter of the FMA rate), the E2M1 re-quantization by the FMA / ALU
-        // pipes; run one after the other, each leaves the other's pipe idle.  Here the Swish of
-        // the chunk just read from tensor memory is interleaved, instruction by instruction, with
-        // the encode of the previous chunk (whose block scale needed all of its 32 values first).
-        if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[0], group & 1, p.status, 4, abortp);
+      if constexpr (SWQ) {
+        // FFN up-projection: accumulator -> bias + Swish -> E2M1 codes + scale factors, one
+        // 32-column chunk at a time (the second chunk of a wide tile is read from tensor memory
+        // only after the first is finished, so that one chunk's registers are live at a time;
+        // the MMAs of the next tile then run under the arithmetic of the second chunk)
+        const uint32_t acc = WIDE ? 0u : (group & 1);
+        const uint32_t acc_addr = lane_addr + TM_ACC0 + acc * 128 + col_base;
+        if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[acc], (WIDE ? group : (group >> 1)) & 1, p.status, 4, abortp);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
         tc_fence_after();
         ++group;
-        const uint32_t acc_addr = lane_addr + TM_ACC0 + col_base;
+        const bool scale_acc = kind_vec4(KIND) && p.a_amax != nullptr;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          float (&zn)[32] = h == 0 ? za : zb;  // chunk read now
-          float (&zo)[32] = h == 0 ? zb : za;  // pending chunk: previous tile's second / this tile's first
-          {
-            uint32_t r[32];
-            tc_ld_32x32b_x32(acc_addr + h * 32, r);
-            tc_wait_ld();
-            if (h == 1) {  // both chunks are out of tensor memory
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(&sm.tmem_empty[0]);
-            }
-            const float gs = (kind_vec4(KIND) && p.a_amax) ? g_ab : 1.0f;
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (bias_base) b = *reinterpret_cast<const float4*>(bias_base + h * 32 + i);
-              const float bb[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float t = __uint_as_float(r[i + j]);
-                if (kind_vec4(KIND) && p.a_amax) t = __fmul_rn(t, gs);
-                zn[i + j] = bias_base ? __fadd_rn(t, bb[j]) : t;
-              }
-            }
+        for (int h = 0; h < NCH; ++h) {
+          uint32_t r[32];
+          tc_ld_32x32b_x32(acc_addr + h * 32, r);
+          tc_wait_ld();
+          if (h == NCH - 1) {  // the whole accumulator is out of tensor memory
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.tmem_empty[acc]);
           }
-          uint32_t w[4];
-#pragma unroll
-          for (int g8 = 0; g8 < 4; ++g8) {
-#pragma unroll
-            for (int j = 0; j < 8; j += 4)
-              silu4_f(zn[8 * g8 + j], zn[8 * g8 + j + 1], zn[8 * g8 + j + 2], zn[8 * g8 + j + 3]);
-            const float v[8] = {zo[8 * g8], zo[8 * g8 + 1], zo[8 * g8 + 2], zo[8 * g8 + 3],
-                                zo[8 * g8 + 4], zo[8 * g8 + 5], zo[8 * g8 + 6], zo[8 * g8 + 7]};
-            if (kind_vec4(KIND)) w[g8] = e2m1_pack8<false, false>(v, g8 < 2 ? pend_rcp0 : pend_rcp1);
-            else w[g8] = e2m1_pack8<true, false>(v, pend_rcp0);
-          }
-          pend_store(w);
-          // the chunk just finished becomes the pending one
           const int64_t out_col0 = static_cast<int64_t>(nb) * BNT + col_base + h * 32;
-          pend_sb = chunk_scales(zn, pend_rcp0, pend_rcp1);
-          pend_col_ok = out_col0 < p.N;
-          pend_ok = row_ok && pend_col_ok;
-          pend_codes = static_cast<uint8_t*>(p.out) + row * p.ldo + (out_col0 >> 1);
-          const int64_t sf_row = (row >> 7) * p.out_sf_kg * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4;
-          if (out_fmt == VX_FMT_MX32) {
-            pend_sf = sf_row + (out_col0 >> 7) * 512 + ((out_col0 >> 5) & 3);
-            pend_nat = row * (p.N >> 5) + (out_col0 >> 5);
-          } else {
-            pend_sf = sf_row + (out_col0 >> 6) * 512 + ((out_col0 >> 5) & 1) * 2;
-            pend_nat = row * (p.N >> 4) + (out_col0 >> 4);
+          uint32_t w[4];
+          const uint32_t sb = swish_quant_chunk<kind_vec4(KIND)>(r, bias_base ? bias_base + h * 32 : nullptr, scale_acc, g_ab,
+                                                                 g_out, w);
+          if (out_col0 < p.N) {
+            if (row_ok)
+              *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out) + row * p.ldo + (out_col0 >> 1)) =
+                  make_uint4(w[0], w[1], w[2], w[3]);
+            // rows of the last tile beyond M get zero scale factors (the SF atoms cover whole 128-row tiles)
+            const uint32_t sbw = row_ok ? sb : 0u;
+            const int64_t sf_row = (row >> 7) * p.out_sf_kg * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4;
+            if constexpr (!kind_vec4(KIND)) {
+              p.out_sf[sf_row + (out_col0 >> 7) * 512 + ((out_col0 >> 5) & 3)] = static_cast<uint8_t>(sbw);
+              if (p.out_scales && row_ok) p.out_scales[row * (p.N >> 5) + (out_col0 >> 5)] = static_cast<uint8_t>(sbw);
+            } else {
+              *reinterpret_cast<uint16_t*>(p.out_sf + sf_row + (out_col0 >> 6) * 512 + ((out_col0 >> 5) & 1) * 2) =
+                  static_cast<uint16_t>(sbw);
+              if (p.out_scales && row_ok)
+                *reinterpret_cast<uint16_t*>(p.out_scales + row * (p.N >> 4) + (out_col0 >> 4)) = static_cast<uint16_t>(sbw);
+            }
           }
         }
         mb = mb_next;
@@ -1264,19 +1274,6 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       }
       mb = mb_next;
       nb = nb_next;
-    }
-    if constexpr (PIPE) {
-      if (my_tiles > 0 && ok) {  // encode the last pending chunk (the second of the last tile)
-        uint32_t w[4];
-#pragma unroll
-        for (int g8 = 0; g8 < 4; ++g8) {
-          const float v[8] = {zb[8 * g8], zb[8 * g8 + 1], zb[8 * g8 + 2], zb[8 * g8 + 3],
-                              zb[8 * g8 + 4], zb[8 * g8 + 5], zb[8 * g8 + 6], zb[8 * g8 + 7]};
-          if (kind_vec4(KIND)) w[g8] = e2m1_pack8<false, false>(v, g8 < 2 ? pend_rcp0 : pend_rcp1);
-          else w[g8] = e2m1_pack8<true, false>(v, pend_rcp0);
-        }
-        pend_store(w);
-      }
     }
     if (tma_store && lane == 0) tma_store_wait_all<0>();
     if (!ok) sm.abort_flag = 1;

@@ -48,23 +48,19 @@ struct QuantParams {
 };
 
 // Eight consecutive elements as loaded (not yet converted): lets a kernel issue the loads of
-// its next row before it works on the current one.
-// 64 registers per thread: four 256-thread blocks per SM (more blocks per SM spill and were slower)
-#define VX_QUANT_MIN_BLOCKS 4
-
+// rows it will work on later before it works on the current one.  Converted, the eight values
+// are four packed fp32 pairs (element 2 i in the low half of pair i): the arithmetic below uses
+// the packed fp32x2 instructions of sm_100, which round each half exactly like the scalar ones.
 template <typename T> struct Raw8;
 template <> struct Raw8<__nv_bfloat16> {
   uint4 u;
   // plain (coherent) loads: the LayerNorm kernels may store y over x while other rows are still read
   __device__ __forceinline__ void load(const __nv_bfloat16* p) { u = *reinterpret_cast<const uint4*>(p); }
   __device__ __forceinline__ void zero() { u = make_uint4(0, 0, 0, 0); }
-  __device__ __forceinline__ void get(float (&v)[8]) const {
+  __device__ __forceinline__ void get(uint64_t (&v)[4]) const {
     const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      v[2 * i] = __uint_as_float(w[i] << 16);
-      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
+    for (int i = 0; i < 4; ++i) v[i] = pack_f32x2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
   }
 };
 template <> struct Raw8<float> {
@@ -74,9 +70,9 @@ template <> struct Raw8<float> {
     b = *(reinterpret_cast<const float4*>(p) + 1);
   }
   __device__ __forceinline__ void zero() { a = b = make_float4(0.f, 0.f, 0.f, 0.f); }
-  __device__ __forceinline__ void get(float (&v)[8]) const {
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  __device__ __forceinline__ void get(uint64_t (&v)[4]) const {
+    v[0] = pack_f32x2(a.x, a.y); v[1] = pack_f32x2(a.z, a.w);
+    v[2] = pack_f32x2(b.x, b.y); v[3] = pack_f32x2(b.z, b.w);
   }
 };
 
@@ -113,38 +109,42 @@ __device__ __forceinline__ I sf_offset(I row, I kgroup, I sf_kg) {
 }
 
 // Quantize one 256-element chunk of RP rows held in registers and store codes + scales.
-// `row_rcp` / `row_byte` are used by ROWSCALE only (the row maximum is known beforehand).
+// `row_rcp` is used by ROWSCALE only (the row maximum is known beforehand).
 // I: index type -- 32-bit when every element / byte offset of the call fits (most tensors; half
 // the integer instructions of the 64-bit form), else 64-bit.
 // FAST: the common call shape, fixed at compile time -- K a whole number of 256-element chunks
 // (a power of two behind LayerNorm), scale factors wanted as SF atoms only -- drops the
 // per-chunk bounds predicates, the natural-layout stores and their tests from the inner loop.
-template <int FMT, int RP, typename I, bool FAST>
+// BF16IN: the values are bf16 numbers (straight from a bf16 tensor, no arithmetic in between),
+// which lets the power-of-two-scaled formats skip the tie nudge (see e2m1_pack8p).
+template <int FMT, int RP, typename I, bool FAST, bool BF16IN>
 __device__ __forceinline__ void quant_chunk(const QuantParams& p, I row0, int c, int lane,
-                                            float (&v)[RP][8], float row_rcp, float g) {
+                                            uint64_t (&v)[RP][4], float row_rcp, float g) {
   const I K = static_cast<I>(p.K), M = static_cast<I>(p.M), ldc = static_cast<I>(p.ldc);
   const I k0 = static_cast<I>(c) * 256 + lane * 8;
   const bool active = FAST || k0 < K;
-  float a = amax8(v[0]);
-  if constexpr (RP == 2) a = fmaxf(a, amax8(v[1]));
+  constexpr bool NUDGE = !BF16IN;
 
   if constexpr (FMT == VX_FMT_ROWSCALE) {
     if (active) {
-      *reinterpret_cast<uint32_t*>(p.codes + row0 * ldc + (k0 >> 1)) = e2m1_pack8<true>(v[0], row_rcp);
+      *reinterpret_cast<uint32_t*>(p.codes + row0 * ldc + (k0 >> 1)) = e2m1_pack8p<true, true, NUDGE>(v[0], row_rcp);
     }
   } else if constexpr (FMT == VX_FMT_FP8_1X128) {
+    float a = amax8p(v[0]);
 #pragma unroll
     for (int o = 1; o < 16; o <<= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
     float scale, rcp;
     fp8_block(a, scale, rcp);
     if (active) {
-      *reinterpret_cast<uint2*>(p.codes + row0 * ldc + k0) = fp8_pack8(v[0], rcp);
+      *reinterpret_cast<uint2*>(p.codes + row0 * ldc + k0) = fp8_pack8p(v[0], rcp);
       if (p.scales && (lane & 15) == 0)
         static_cast<float*>(p.scales)[row0 * (K >> 7) + (k0 >> 7)] = scale;
     }
   } else {
     constexpr int BLK = (FMT == VX_FMT_MX32) ? 32 : 16;
     constexpr int LPB = BLK / 8;  // lanes per block
+    float a = amax8p(v[0]);
+    if constexpr (RP == 2) a = fmaxf(a, amax8p(v[1]));
 #pragma unroll
     for (int o = 1; o < LPB; o <<= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
     uint32_t byte;
@@ -155,8 +155,12 @@ __device__ __forceinline__ void quant_chunk(const QuantParams& p, I row0, int c,
     const I kb = k0 / BLK;  // block index along K
 #pragma unroll
     for (int r = 0; r < RP; ++r) {
-      if (active)
-        *reinterpret_cast<uint32_t*>(p.codes + (row0 + r) * ldc + (k0 >> 1)) = e2m1_pack8<FMT != VX_FMT_NV16>(v[r], rcp);
+      if (active) {
+        uint32_t w;
+        if constexpr (FMT == VX_FMT_NV16) w = e2m1_pack8p<false, true, true>(v[r], rcp);
+        else w = e2m1_pack8p<true, true, NUDGE>(v[r], rcp);
+        *reinterpret_cast<uint32_t*>(p.codes + (row0 + r) * ldc + (k0 >> 1)) = w;
+      }
     }
     if (!FAST && p.scales && active && (lane % LPB) == 0) {
       uint8_t* s = static_cast<uint8_t*>(p.scales);
@@ -192,10 +196,28 @@ __device__ __forceinline__ void zero_pad_rows(const QuantParams& p, I gwarp, I w
       *reinterpret_cast<uint32_t*>(p.sf + sf_offset<I>(r, kg, sf_kg)) = 0u;
 }
 
-// Streaming quantizer (no LayerNorm): any K % 8 == 0.
+// Streaming quantizer (no LayerNorm): any K % 8 == 0.  A warp walks its (row, chunk) items in
+// order with the loads of the next QDEPTH items already in flight: the kernel is bound by
+// memory latency, not by arithmetic, so what counts is the number of bytes each SM keeps
+// outstanding (QDEPTH x 512 B per warp for bf16 input).
+#ifndef VX_QUANT_DEPTH
+#define VX_QUANT_DEPTH 4
+#endif
+#ifndef VX_QUANT_MIN_BLOCKS
+#define VX_QUANT_MIN_BLOCKS 5
+#endif
+#ifndef VX_LNQ_MIN_BLOCKS
+#define VX_LNQ_MIN_BLOCKS 4
+#endif
+#ifndef VX_LNQ_DEPTH
+#define VX_LNQ_DEPTH 2
+#endif
+
 template <typename T, int FMT, typename I, bool FAST>
 __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) quant_kernel(const QuantParams p) {
   constexpr int RP = (FMT == VX_FMT_BLK16_A) ? 2 : 1;
+  constexpr bool BF16IN = sizeof(T) == 2;
+  constexpr int DEPTH = (FMT == VX_FMT_ROWSCALE) ? 1 : (BF16IN ? (RP == 2 ? 2 : VX_QUANT_DEPTH) : (RP == 2 ? 1 : 2));
   const int lane = threadIdx.x & 31;
   const I warps = static_cast<I>(gridDim.x) * (blockDim.x >> 5);
   const I nunits = static_cast<I>(p.M) / RP;
@@ -203,58 +225,99 @@ __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) quant_kernel(const Q
   const T* x = static_cast<const T*>(p.x);
   float g = 1.0f;
   if constexpr (FMT == VX_FMT_NV16) g = nv16_global(__ldg(p.amax));
-
-  Raw8<T> raw[RP];
-  auto fetch = [&](I u, int c) {
-    const I k0 = static_cast<I>(c) * 256 + lane * 8;
-#pragma unroll
-    for (int r = 0; r < RP; ++r) {
-      if (FAST || k0 < static_cast<I>(p.K)) raw[r].load(x + (u * RP + r) * static_cast<I>(p.ldx) + k0);
-      else raw[r].zero();
-    }
-  };
   const I u_first = static_cast<I>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  for (I u = u_first; u < nunits; u += warps) {
-    const I row0 = u * RP;
-    float row_rcp = 0.0f;
-    if constexpr (FMT == VX_FMT_ROWSCALE) {
+
+  if constexpr (FMT == VX_FMT_ROWSCALE) {
+    // the row maximum comes first: the row is read twice (the second time from L1 / L2)
+    for (I u = u_first; u < nunits; u += warps) {
       float a = 0.0f;
       for (int c = 0; c < nchunks; ++c) {
         const I k0 = static_cast<I>(c) * 256 + lane * 8;
-        if (FAST || k0 < static_cast<I>(p.K)) {
+        if (k0 < static_cast<I>(p.K)) {
           float t[8];
-          load8(x + row0 * static_cast<I>(p.ldx) + k0, t);
+          load8(x + u * static_cast<I>(p.ldx) + k0, t);
           a = fmaxf(a, amax8(t));
         }
       }
       a = warp_max(a);
       uint32_t byte;
+      float row_rcp;
       ue8m0_from_amax(a, byte, row_rcp);
-      if (p.scales && lane == 0) static_cast<uint8_t*>(p.scales)[row0] = static_cast<uint8_t>(byte);
+      if (p.scales && lane == 0) static_cast<uint8_t*>(p.scales)[u] = static_cast<uint8_t>(byte);
+      for (int c = 0; c < nchunks; ++c) {
+        const I k0 = static_cast<I>(c) * 256 + lane * 8;
+        Raw8<T> raw;
+        if (k0 < static_cast<I>(p.K)) raw.load(x + u * static_cast<I>(p.ldx) + k0);
+        else raw.zero();
+        uint64_t v[1][4];
+        raw.get(v[0]);
+        quant_chunk<FMT, 1, I, false, BF16IN>(p, u, c, lane, v, row_rcp, g);
+      }
     }
-    // chunk c + 1 (or chunk 0 of this warp's next unit) is loaded while chunk c is encoded
-    if (u == u_first || FMT == VX_FMT_ROWSCALE) fetch(u, 0);  // (ROWSCALE reads the row twice: no look-ahead)
-    for (int c = 0; c < nchunks; ++c) {
-      float v[RP][8];
+  } else {
+    Raw8<T> raw[DEPTH][RP];
+    // cursor of the item whose loads are issued next
+    I fu = u_first;
+    int fc = 0;
+    auto fetch = [&](int slot) {
+      // (called with compile-time slot numbers only: `raw` stays in registers)
+      const I k0 = static_cast<I>(fc) * 256 + lane * 8;
 #pragma unroll
-      for (int r = 0; r < RP; ++r) raw[r].get(v[r]);
-      if (c + 1 < nchunks) fetch(u, c + 1);
-      else if (u + warps < nunits && FMT != VX_FMT_ROWSCALE) fetch(u + warps, 0);
-      quant_chunk<FMT, RP, I, FAST>(p, row0, c, lane, v, row_rcp, g);
+      for (int r = 0; r < RP; ++r) {
+        if (fu < nunits && (FAST || k0 < static_cast<I>(p.K))) raw[slot][r].load(x + (fu * RP + r) * static_cast<I>(p.ldx) + k0);
+        else raw[slot][r].zero();
+      }
+      if (++fc == nchunks) { fc = 0; fu += warps; }
+    };
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d) fetch(d);
+    I u = u_first;
+    int c = 0;
+#pragma unroll 1
+    while (u < nunits) {
+#pragma unroll
+      for (int d = 0; d < DEPTH; ++d) {
+        if (u < nunits) {  // warp-uniform
+          uint64_t v[RP][4];
+#pragma unroll
+          for (int r = 0; r < RP; ++r) raw[d][r].get(v[r]);
+          fetch(d);
+          quant_chunk<FMT, RP, I, FAST, BF16IN>(p, u * RP, c, lane, v, 0.0f, g);
+          if (++c == nchunks) { c = 0; u += warps; }
+        }
+      }
     }
   }
   zero_pad_rows<I>(p, u_first, warps, lane);
 }
 
+// One 64-bit value across lanes (two 32-bit shuffles).
+__device__ __forceinline__ uint64_t shfl_xor_b64(uint64_t v, int o) {
+  const uint32_t lo = __shfl_xor_sync(0xffffffffu, static_cast<uint32_t>(v), o);
+  const uint32_t hi = __shfl_xor_sync(0xffffffffu, static_cast<uint32_t>(v >> 32), o);
+  return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+
 // LayerNorm + quantize, row resident in registers (CH chunks of 256 elements, K <= 256 CH).
-// Statistics follow the reference kernel's formula (velox_layernorm.cu:52-57):
-//   mean = sum / K; var = max(sumsq / K - mean^2, 0); y = (x - mean) * rstd * gamma + beta
-// with every operation individually rounded (no FMA contraction), rstd = 1 / sqrt(var + eps)
-// correctly rounded, lane-sequential partial sums and a butterfly (xor 16, 8, 4, 2, 1) warp
-// reduction -- an order a CPU restatement can follow exactly.
+// Statistics follow the reference kernel's formula (velox_layernorm.cu:52-57): mean = sum / K,
+// var = max(E[x^2] - mean^2, 0), y = (x - mean) * rstd * gamma + beta, evaluated with fused
+// multiply-adds in this fixed order (so that a CPU restatement can reproduce every bit):
+//   per lane, pair j of chunk c (elements 2 j, 2 j + 1 of the lane's eight), chunks in order:
+//       S = S + v            Q = fma(v, v, Q)               (packed: even | odd elements)
+//   s = S.even + S.odd, q = Q.even + Q.odd; butterfly over the lanes (xor 16, 8, 4, 2, 1);
+//   mean = s / K, ex2 = q / K (a multiplication when K is a power of two: same rounding),
+//   var = max(fma(-mean, mean, ex2), 0), rstd = 1 / sqrt(var + eps) correctly rounded in one step,
+//   y = fma(fma(x, rstd, -mean * rstd), gamma, beta).
+// gamma / beta of both LayerNorms sit in shared memory, laid out so that the 16-byte reads of a
+// warp touch every bank once.  Rows are loaded VX_LNQ_DEPTH iterations ahead of their use.
+// resident blocks per SM the register budget is set for: the row lives in registers (16 CH values
+// per thread), so the wider rows get fewer, larger-budget blocks
+constexpr int lnq_min_blocks(int ch) { return ch <= 2 ? VX_LNQ_MIN_BLOCKS : (ch <= 4 ? 2 : 1); }
+
 template <typename T, int FMT, int CH, typename I, bool FAST>
-__global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) ln_quant_kernel(const QuantParams p) {
+__global__ void __launch_bounds__(256, lnq_min_blocks(CH)) ln_quant_kernel(const QuantParams p) {
   constexpr int RP = (FMT == VX_FMT_BLK16_A) ? 2 : 1;
+  constexpr int DEPTH = (CH * RP * (sizeof(T) / 2) <= 2) ? VX_LNQ_DEPTH : 1;
   const int lane = threadIdx.x & 31;
   const I warps = static_cast<I>(gridDim.x) * (blockDim.x >> 5);
   const I nunits = static_cast<I>(p.M) / RP;
@@ -264,106 +327,128 @@ __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) ln_quant_kernel(cons
   float g = 1.0f;
   if constexpr (FMT == VX_FMT_NV16) g = nv16_global(__ldg(p.amax));
 
-  // the row(s) of unit u, as loaded; issued one iteration ahead of their use
-  Raw8<T> raw[CH][RP];
-  auto fetch = [&](I u) {
+  // [pass][gamma | beta][16-byte piece: chunk * 2 + half][lane]
+  __shared__ float4 gb_s[2][2][CH * 2][32];
+  for (int i = threadIdx.x; i < npass * 2 * CH * 2 * 32; i += blockDim.x) {
+    const int l = i & 31, piece = (i >> 5) % (CH * 2), which = (i >> 5) / (CH * 2);  // which = pass * 2 + (0 gamma, 1 beta)
+    const float* src = which == 0 ? p.gamma : (which == 1 ? p.beta : (which == 2 ? p.gamma2 : p.beta2));
+    const int k0 = (piece >> 1) * 256 + l * 8 + (piece & 1) * 4;
+    float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (k0 < p.K) val = __ldg(reinterpret_cast<const float4*>(src + k0));
+    gb_s[which >> 1][which & 1][piece][l] = val;
+  }
+  __syncthreads();
+
+  Raw8<T> raw[DEPTH][CH][RP];
+  auto fetch = [&](int slot, I u) {
 #pragma unroll
     for (int r = 0; r < RP; ++r)
 #pragma unroll
       for (int c = 0; c < CH; ++c) {
         const I k0 = static_cast<I>(c) * 256 + lane * 8;
-        if (FAST || k0 < static_cast<I>(p.K)) raw[c][r].load(x + (u * RP + r) * static_cast<I>(p.ldx) + k0);
-        else raw[c][r].zero();
+        if (FAST || k0 < static_cast<I>(p.K)) raw[slot][c][r].load(x + (u * RP + r) * static_cast<I>(p.ldx) + k0);
+        else raw[slot][c][r].zero();
       }
   };
   const I u_first = static_cast<I>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (u_first < nunits) fetch(u_first);
-  for (I u = u_first; u < nunits; u += warps) {
-    const I row0 = u * RP;
-    float v[CH][RP][8];
 #pragma unroll
-    for (int r = 0; r < RP; ++r)
-#pragma unroll
-      for (int c = 0; c < CH; ++c) raw[c][r].get(v[c][r]);
-    if (u + warps < nunits) fetch(u + warps);
-    // one pass per LayerNorm: the second one (if any) normalises the rows as pass 0 stored them
-    const float* ga_p = p.gamma;
-    const float* be_p = p.beta;
+  for (int d = 0; d < DEPTH; ++d)
+    if (u_first + d * warps < nunits) fetch(d, u_first + d * warps);
 #pragma unroll 1
-    for (int pass = 0; pass < npass; ++pass) {
+  for (I ub = u_first; ub < nunits; ub += DEPTH * warps) {
 #pragma unroll
-    for (int r = 0; r < RP; ++r) {
-      float s = 0.0f, sq = 0.0f;
+    for (int d = 0; d < DEPTH; ++d) {
+      const I u = ub + d * warps;
+      if (u >= nunits) break;  // warp-uniform
+      const I row0 = u * RP;
+      uint64_t v[CH][RP][4];
 #pragma unroll
-      for (int c = 0; c < CH; ++c) {
+      for (int r = 0; r < RP; ++r)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          s = __fadd_rn(s, v[c][r][j]);
-          sq = __fadd_rn(sq, __fmul_rn(v[c][r][j], v[c][r][j]));
-        }
-      }
+        for (int c = 0; c < CH; ++c) raw[d][c][r].get(v[c][r]);
+      if (u + DEPTH * warps < nunits) fetch(d, u + DEPTH * warps);
+      // one pass per LayerNorm: the second one (if any) normalises the rows as pass 0 stored them
+#pragma unroll 1
+      for (int pass = 0; pass < npass; ++pass) {
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, o));
-        sq = __fadd_rn(sq, __shfl_xor_sync(0xffffffffu, sq, o));
-      }
-      // FAST: K is a power of two, so multiplying by 1/K gives the same correctly rounded quotient
-      const float mean = FAST ? __fmul_rn(s, 1.0f / (CH * 256)) : __fdiv_rn(s, k_f);
-      const float ex2 = FAST ? __fmul_rn(sq, 1.0f / (CH * 256)) : __fdiv_rn(sq, k_f);
-      const float var = fmaxf(__fsub_rn(ex2, __fmul_rn(mean, mean)), 0.0f);
-      const float rstd = __frcp_rn(__fsqrt_rn(__fadd_rn(var, p.eps)));
+        for (int r = 0; r < RP; ++r) {
+          uint64_t S = pack_f32x2(0.0f, 0.0f), Q = S;
 #pragma unroll
-      for (int c = 0; c < CH; ++c) {
-        const I k0 = static_cast<I>(c) * 256 + lane * 8;
-        if (FAST || k0 < static_cast<I>(p.K)) {
-          float ga[8], be[8];
-          load8(ga_p + k0, ga);
-          load8(be_p + k0, be);
+          for (int c = 0; c < CH; ++c) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            v[c][r][j] = __fadd_rn(
-                __fmul_rn(__fmul_rn(__fsub_rn(v[c][r][j], mean), rstd), ga[j]), be[j]);
-          if (p.y && pass == 0) {
-            if (p.y_bf16) {
-              uint4 u;
-              u.x = pack2_bf16(v[c][r][0], v[c][r][1]);
-              u.y = pack2_bf16(v[c][r][2], v[c][r][3]);
-              u.z = pack2_bf16(v[c][r][4], v[c][r][5]);
-              u.w = pack2_bf16(v[c][r][6], v[c][r][7]);
-              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.y) + (row0 + r) * static_cast<I>(p.ldy) + k0) = u;
-              if (npass > 1) {  // the next LayerNorm reads what was stored
-                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+            for (int j = 0; j < 4; ++j) {
+              S = add_f32x2(S, v[c][r][j]);
+              Q = fma_f32x2(v[c][r][j], v[c][r][j], Q);
+            }
+          }
+          float s0, s1, q0, q1;
+          unpack_f32x2(S, s0, s1);
+          unpack_f32x2(Q, q0, q1);
+          uint64_t SQ = pack_f32x2(__fadd_rn(s0, s1), __fadd_rn(q0, q1));
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  v[c][r][2 * j] = __uint_as_float(w[j] << 16);
-                  v[c][r][2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+          for (int o = 16; o > 0; o >>= 1) SQ = add_f32x2(SQ, shfl_xor_b64(SQ, o));
+          float s, sq;
+          unpack_f32x2(SQ, s, sq);
+          // FAST: K is a power of two, so multiplying by 1/K gives the same correctly rounded quotient
+          const float mean = FAST ? __fmul_rn(s, 1.0f / (CH * 256)) : __fdiv_rn(s, k_f);
+          const float ex2 = FAST ? __fmul_rn(sq, 1.0f / (CH * 256)) : __fdiv_rn(sq, k_f);
+          const float var = fmaxf(__fmaf_rn(-mean, mean, ex2), 0.0f);
+          const float rstd = __frsqrt_rn(__fadd_rn(var, p.eps));
+          const float nmr = __fmul_rn(-mean, rstd);
+          const uint64_t R2 = pack_f32x2(rstd, rstd), N2 = pack_f32x2(nmr, nmr);
+#pragma unroll
+          for (int c = 0; c < CH; ++c) {
+            const I k0 = static_cast<I>(c) * 256 + lane * 8;
+            if (FAST || k0 < static_cast<I>(p.K)) {
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const float4 ga = gb_s[pass][0][c * 2 + h][lane];
+                const float4 be = gb_s[pass][1][c * 2 + h][lane];
+                v[c][r][2 * h] = fma_f32x2(fma_f32x2(v[c][r][2 * h], R2, N2), pack_f32x2(ga.x, ga.y), pack_f32x2(be.x, be.y));
+                v[c][r][2 * h + 1] =
+                    fma_f32x2(fma_f32x2(v[c][r][2 * h + 1], R2, N2), pack_f32x2(ga.z, ga.w), pack_f32x2(be.z, be.w));
+              }
+              if (p.y && pass == 0) {
+                float f[8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) unpack_f32x2(v[c][r][j], f[2 * j], f[2 * j + 1]);
+                if (p.y_bf16) {
+                  uint4 w4;
+                  w4.x = pack2_bf16(f[0], f[1]);
+                  w4.y = pack2_bf16(f[2], f[3]);
+                  w4.z = pack2_bf16(f[4], f[5]);
+                  w4.w = pack2_bf16(f[6], f[7]);
+                  *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.y) + (row0 + r) * static_cast<I>(p.ldy) + k0) = w4;
+                  if (npass > 1) {  // the next LayerNorm reads what was stored
+                    const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                      v[c][r][j] = pack_f32x2(__uint_as_float(w[j] << 16), __uint_as_float(w[j] & 0xffff0000u));
+                  }
+                } else {
+                  float4* yp = reinterpret_cast<float4*>(static_cast<float*>(p.y) + (row0 + r) * static_cast<I>(p.ldy) + k0);
+                  yp[0] = make_float4(f[0], f[1], f[2], f[3]);
+                  yp[1] = make_float4(f[4], f[5], f[6], f[7]);
                 }
               }
-            } else {
-              float4* yp = reinterpret_cast<float4*>(static_cast<float*>(p.y) + (row0 + r) * static_cast<I>(p.ldy) + k0);
-              yp[0] = make_float4(v[c][r][0], v[c][r][1], v[c][r][2], v[c][r][3]);
-              yp[1] = make_float4(v[c][r][4], v[c][r][5], v[c][r][6], v[c][r][7]);
             }
           }
         }
       }
-    }
-      ga_p = p.gamma2;
-      be_p = p.beta2;
-    }
-    if (!FAST && !p.codes) continue;  // plain LayerNorm
-    float row_rcp = 0.0f;
-    if constexpr (FMT == VX_FMT_ROWSCALE) {
-      float a = 0.0f;
+      if (!FAST && !p.codes) continue;  // plain LayerNorm
+      float row_rcp = 0.0f;
+      if constexpr (FMT == VX_FMT_ROWSCALE) {
+        float a = 0.0f;
 #pragma unroll
-      for (int c = 0; c < CH; ++c) a = fmaxf(a, amax8(v[c][0]));
-      a = warp_max(a);
-      uint32_t byte;
-      ue8m0_from_amax(a, byte, row_rcp);
-      if (p.scales && lane == 0) static_cast<uint8_t*>(p.scales)[row0] = static_cast<uint8_t>(byte);
-    }
+        for (int c = 0; c < CH; ++c) a = fmaxf(a, amax8p(v[c][0]));
+        a = warp_max(a);
+        uint32_t byte;
+        ue8m0_from_amax(a, byte, row_rcp);
+        if (p.scales && lane == 0) static_cast<uint8_t*>(p.scales)[row0] = static_cast<uint8_t>(byte);
+      }
 #pragma unroll
-    for (int c = 0; c < CH; ++c) quant_chunk<FMT, RP, I, FAST>(p, row0, c, lane, v[c], row_rcp, g);
+      for (int c = 0; c < CH; ++c) quant_chunk<FMT, RP, I, FAST, false>(p, row0, c, lane, v[c], row_rcp, g);
+    }
   }
   zero_pad_rows<I>(p, u_first, warps, lane);
 }
@@ -408,17 +493,31 @@ __global__ void sf_relayout_kernel(int fmt, const uint8_t* __restrict__ s, int64
   }
 }
 
-int grid_for_rows(int64_t units) {
-  // 8 warps per block; enough blocks to fill 148 SMs x 8 resident blocks, grid-stride beyond.
+int sm_count() {
+  static int cache[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (!cache[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cache[dev] = n;
+  }
+  return cache[dev];
+}
+
+int grid_for_rows(int64_t units, int blocks_per_sm) {
+  // 8 warps per block, one row (pair) per warp and iteration; exactly the blocks that are
+  // resident at once, grid-stride beyond (every warp then takes the same number of rows +- 1).
   const int64_t blocks = (units + 7) / 8;
-  const int64_t cap = 148 * 8;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * blocks_per_sm;
   return static_cast<int>(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
 }
 
 template <typename T, int FMT, typename I, bool FAST>
 void launch_quant_idx(const QuantParams& p, bool ln, cudaStream_t st) {
   constexpr int RP = (FMT == VX_FMT_BLK16_A) ? 2 : 1;
-  const int grid = grid_for_rows(p.M / RP);
+  const int ch = p.K <= 512 ? 2 : (p.K <= 1024 ? 4 : 8);
+  const int grid = grid_for_rows(p.M / RP, ln ? lnq_min_blocks(ch) * (ch > 2 ? 2 : 1) : VX_QUANT_MIN_BLOCKS);
   if (!ln) {
     quant_kernel<T, FMT, I, FAST><<<grid, 256, 0, st>>>(p);
   } else if (p.K <= 512) {

@@ -70,6 +70,40 @@ __device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
   return r;
 }
 constexpr float kTowardZero = 0.99999994f;  // 1 - 2^-24
+
+// max(a, b, c) in one instruction (three-input form of sm_100)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// max |.| over eight values held as four packed pairs
+__device__ __forceinline__ float amax8p(const uint64_t (&p)[4]) {
+  float f[8];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) unpack_f32x2(p[j], f[2 * j], f[2 * j + 1]);
+  float a = max3(fabsf(f[0]), fabsf(f[1]), fabsf(f[2]));
+  a = max3(a, fabsf(f[3]), fabsf(f[4]));
+  a = max3(a, fabsf(f[5]), fabsf(f[6]));
+  return fmaxf(a, fabsf(f[7]));
+}
+
+// Eight already normalised-and-nudged values -> one word of E2M1 codes (low nibble first), with
+// the converter's code 7 (6.0) turned into the reference's cap, code 6 (4.0).
+__device__ __forceinline__ uint32_t e2m1_cvt8(const float (&r)[8]) {
+  uint32_t w;
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+      "mov.b32 %0, {b0, b1, b2, b3};\n\t}"
+      : "=r"(w)
+      : "f"(r[0]), "f"(r[1]), "f"(r[2]), "f"(r[3]), "f"(r[4]), "f"(r[5]), "f"(r[6]), "f"(r[7]));
+  // nibbles with magnitude 7 -> 6: clear bit 0 where bits 0..2 are all set
+  return w ^ (w & (w >> 1) & (w >> 2) & 0x11111111u);
+}
+
 // CANON_ZERO = false skips the "+ (+0)": a product that is (or underflows to) -0 then encodes as
 // nibble 8 (-0) where the reference writes 0 -- the same value.  The GEMM epilogue uses it (its
 // inputs are -0 only for an exactly -0 pre-activation); the quantizers keep the reference's bytes.
@@ -84,17 +118,37 @@ __device__ __forceinline__ uint32_t e2m1_pack8(const float (&v)[8], float rcp) {
     if (!POW2) q = __fmul_rn(q, kTowardZero);
     r[j] = __uint_as_float(__float_as_uint(q) | 1u);
   }
-  uint32_t w;
-  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
-      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
-      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
-      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
-      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
-      "mov.b32 %0, {b0, b1, b2, b3};\n\t}"
-      : "=r"(w)
-      : "f"(r[0]), "f"(r[1]), "f"(r[2]), "f"(r[3]), "f"(r[4]), "f"(r[5]), "f"(r[6]), "f"(r[7]));
-  // nibbles with magnitude 7 -> 6: clear bit 0 where bits 0..2 are all set
-  return w ^ (w & (w >> 1) & (w >> 2) & 0x11111111u);
+  return e2m1_cvt8(r);
+}
+
+// The same encode on four packed pairs with packed fp32 arithmetic (two values per multiply /
+// add; every element sees exactly the operations of e2m1_pack8, so the bytes are the same).
+// NUDGE = false drops the "| 1": allowed when the values are bf16 numbers and rcp is a power of
+// two.  q = v * rcp then has at most 8 significant bits, so its fp32 neighbour toward zero --
+// which the folded factor (1 - 2^-24) produces -- lies on the same side of every threshold as q,
+// below it when q is a threshold, and is never a threshold itself.
+template <bool POW2, bool CANON_ZERO, bool NUDGE>
+__device__ __forceinline__ uint32_t e2m1_pack8p(const uint64_t (&v)[4], float rcp) {
+  const float m = POW2 ? __fmul_rn(rcp, kTowardZero) : rcp;
+  const uint64_t m2 = pack_f32x2(m, m);
+  const uint64_t z2 = pack_f32x2(0.0f, 0.0f);
+  const uint64_t t2 = pack_f32x2(kTowardZero, kTowardZero);
+  float r[8];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint64_t q = mul_f32x2(v[j], m2);
+    if (CANON_ZERO) q = add_f32x2(q, z2);  // -0 -> +0
+    if (!POW2) q = mul_f32x2(q, t2);
+    float lo, hi;
+    unpack_f32x2(q, lo, hi);
+    if (NUDGE) {
+      lo = __uint_as_float(__float_as_uint(lo) | 1u);
+      hi = __uint_as_float(__float_as_uint(hi) | 1u);
+    }
+    r[2 * j] = lo;
+    r[2 * j + 1] = hi;
+  }
+  return e2m1_cvt8(r);
 }
 
 __device__ __forceinline__ float e4m3_to_float(uint32_t b) {
@@ -128,7 +182,12 @@ __device__ __forceinline__ uint2 fp8_pack8(const float (&v)[8], float rcp) {
   }
   return make_uint2(w[0], w[1]);
 }
-
+__device__ __forceinline__ uint2 fp8_pack8p(const uint64_t (&v)[4], float rcp) {
+  float f[8];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) unpack_f32x2(v[j], f[2 * j], f[2 * j + 1]);
+  return fp8_pack8(f, rcp);
+}
 
 // 2^(byte - 127) as fp32, including byte 0 (2^-127 is subnormal).
 __device__ __forceinline__ float ue8m0_to_float(uint32_t byte) {
