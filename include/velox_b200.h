@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define VX_ABI_VERSION 2
+#define VX_ABI_VERSION 3
 
 /* Quantization formats.  values / scale / natural scale layout
  *  ROWSCALE   E2M1, one UE8M0 per row                      u8 [R]
@@ -151,6 +151,7 @@ typedef struct vx_gemm_desc {
   const void* pos_v;
   float qk_scale;       /* BIAS_QKVPACK: scale applied to q + bias */
   int32_t head_col_off; /* VX_GEMM_OUT_HEADS: first column inside the head row (0 or head_dim) */
+  void* lse_partials;   /* BIAS_ARGMAX, FP4 formats: optional f32 pairs [vx_ctc_lse_parts(N)][M], see vx_ctc_finish */
 } vx_gemm_desc;
 
 /* VX_EPI_BIAS_GLU expects the rows of B (and the bias) interleaved per tile of vx_glu_tile(fmt)
@@ -177,6 +178,17 @@ int vx_bsgemm(const vx_gemm_desc* desc, void* stream);
  * equal bf16 logits resolve to the lowest column like torch.argmax.  vx_argmax_ids turns keys
  * into ids i32 [M] and, when max_out != NULL, the winning logits f32 [M]. */
 int vx_argmax_ids(const void* keys, int64_t M, int32_t* ids, float* max_out, void* stream);
+
+/* The CTC tail without the logits: log-softmax needs log sum_n exp(z[m, n]) per frame
+ * (z - logsumexp(z), veloxvoice/models/wenet/torch_conformer.py:945-949).  With `lse_partials`
+ * set, the BIAS_ARGMAX epilogue also keeps, per row and 64-column group, the running maximum and
+ * the sum of exp(z - max) of the bf16-rounded logits (8 bytes per row and group instead of 128
+ * bytes of logits).  vx_ctc_finish merges them: lse_out[m] = log sum exp, logp_out[m] =
+ * log_softmax(z[m])[argmax] = max - lse, next to the ids / winning logits of vx_argmax_ids.
+ * ids, max_out, lse_out, logp_out may each be NULL.  vx_ctc_lse_parts(N) = groups to allocate. */
+int64_t vx_ctc_lse_parts(int64_t N);
+int vx_ctc_finish(const void* keys, const void* lse_partials, int64_t N, int64_t M, int32_t* ids, float* max_out,
+                  float* lse_out, float* logp_out, void* stream);
 
 /* Attention fold pack in one pass: replaces velox_qkv_pack
  * (veloxvoice/kernels/csrc/velox_qkv_pack.cu:34-97; Python wrapper qkv_pack in

@@ -38,8 +38,8 @@ def test_every_declared_symbol_is_exported(lib):
 
 
 def test_abi_version_and_struct_size(lib):
-    assert lib.vx_abi_version() == 2
-    assert C.sizeof(_lib.GemmDesc) == 216
+    assert lib.vx_abi_version() == 3
+    assert C.sizeof(_lib.GemmDesc) == 224
 
 
 def test_sf_geometry(lib):

@@ -353,6 +353,15 @@ def test_argmax_epilogue_equals_argmax_of_the_bf16_logits(fmt, M, N, K):
     assert torch.equal(vmax, logits.float().max(dim=1).values)
     # rows whose maximum sits on the duplicated column must report the first copy
     assert not bool(((ids == N // 2) | (ids == N - 1)).any())
+    if fmt != "fp8_1x128":
+        # the CTC tail: log-sum-exp of the row and the winner's log-probability, without the logits
+        ids2, vmax2, lse, logp = ops.bsgemm_argmax(a, b, bias, return_max=True, return_logp=True)
+        torch.cuda.synchronize()
+        assert torch.equal(ids2, want) and torch.equal(vmax2, vmax)
+        ls = torch.log_softmax(logits.float(), dim=1)
+        want_lse = torch.logsumexp(logits.float(), dim=1)
+        assert (lse - want_lse).abs().max().item() < 1e-3
+        assert (logp - ls.gather(1, want.long()[:, None])[:, 0]).abs().max().item() < 1e-3
 
 
 @pytest.mark.parametrize("fmt", [F.FMT_MX32, F.FMT_NV16, F.FMT_ROWSCALE])

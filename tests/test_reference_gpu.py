@@ -144,6 +144,71 @@ def test_reference_dense_linear_class_on_installed_ops(installed):
     for mode in ("mxfp4", "nvfp4"):
         lin.precision = mode
         lin._wq = None
-        y = lin(x)
+        with torch.no_grad():
+            y = lin(x)
         assert y.shape == (2, 75, 192) and y.dtype == torch.float32
         assert np.array_equal(y.view(-1, 192).cpu().numpy(), ref), mode
+
+
+def test_reference_model_fp4_lane_end_to_end(installed, ref_triton, monkeypatch):
+    """The reference's own ``WenetConformerASR`` (random init, full size: d = 512, 12 blocks,
+    vocab 5538; no checkpoint exists here) in its mxfp4 lane through ``set_precision`` and
+    ``encode_ctc_utterance``, twice on the same features:
+
+      A  every DenseLinear on the operators ``install()`` provides (this library's kernels);
+      B  the same model object with the reference's REAL Triton quantizer and the reference's GEMM
+         definition (unit-scale dot in exact arithmetic, scales afterwards) in plain torch.
+
+    Gate of the reference's tools for two lanes of one model (``tools/bench_wenet.py:187-236``):
+    greedy tokens may diverge in at most max(3, 0.1 %) frames; here they must not diverge at all,
+    because quantizer bytes and GEMM results are bit-identical."""
+    import veloxvoice.kernels.ops as kops
+    from veloxvoice.models.wenet.torch_conformer import DenseLinear
+
+    from oracle import ref_model
+    from velox_voice_b200 import ops, synth
+
+    monkeypatch.setenv("VELOXVOICE_ASR_PRECISION", "mxfp4")  # read by DenseLinear / the attention at construction
+    state = ref_model.random_state(seed=3)
+    model = ref_model.build_reference_asr(state, "cuda:0")
+    model.set_jit(False)
+    model.set_precision("mxfp4")  # pre-quantizes every DenseLinear weight through the installed quantizer
+    n_dense = sum(isinstance(m, DenseLinear) for m in model.encoder.modules()) + 1
+    assert n_dense == 12 * 9 + 2
+    _, mel = synth.encoder_features(1000, 1500, device="cuda")  # 20 s of the synthetic hour: [2000, 80]
+    launches0 = ops.launch_count()
+    with torch.inference_mode():
+        lp_a = model.encode_ctc_utterance(mel[None]).clone()
+    torch.cuda.synchronize()
+    assert ops.launch_count() - launches0 >= 2 * n_dense, "the FP4 lane did not run on this library's kernels"
+    assert lp_a.shape[0] == 1 and lp_a.shape[2] == 5538 and torch.isfinite(lp_a).all()
+
+    lut = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], device="cuda", dtype=torch.float64)
+
+    def unpack(p):
+        c = torch.stack([p & 0xF, p >> 4], -1).reshape(p.shape[0], p.shape[1] * 2)
+        mag = lut[(c & 7).long()]
+        return torch.where((c & 8) > 0, -mag, mag)
+
+    def reference_gemm(pack_a, pack_b, scale_a, scale_b, *args, **kw):
+        raw = unpack(pack_a) @ unpack(pack_b).T  # fp64: exact for these operands
+        sa = 2.0 ** (scale_a.double() - 127)
+        sb = 2.0 ** (scale_b.double() - 127)
+        return (raw * sa[:, None] * sb[None, :]).float()
+
+    monkeypatch.setitem(sys.modules, "veloxvoice.kernels.ops.triton_ops", ref_triton)
+    monkeypatch.setattr(kops, "dgx_mxfp4_gemm", reference_gemm)
+    for m in list(model.encoder.modules()) + [model.ctc_lo]:
+        if isinstance(m, DenseLinear):
+            m._wq = None  # weights are quantized again, by the reference's Triton kernel
+    launches1 = ops.launch_count()
+    with torch.inference_mode():
+        lp_b = model.encode_ctc_utterance(mel[None])
+    torch.cuda.synchronize()
+    assert ops.launch_count() == launches1, "lane B must not touch this library"
+    tok_a, tok_b = lp_a.argmax(-1), lp_b.argmax(-1)
+    n = tok_a.numel()
+    diverged = int((tok_a != tok_b).sum())
+    print(f"[reference model, {n} frames] token divergence {diverged}, max |dlogp| {(lp_a - lp_b).abs().max().item():.3g}")
+    assert diverged <= max(3, n // 1000)
+    assert diverged == 0 and (lp_a - lp_b).abs().max().item() < 1e-4

@@ -23,7 +23,7 @@ FMT_BY_NAME = {
     "fp8_1x128": FMT_FP8_1X128,
 }
 DT_F32, DT_BF16, DT_FP4 = 0, 1, 2
-ABI_VERSION = 2  # VX_ABI_VERSION of include/velox_b200.h
+ABI_VERSION = 3  # VX_ABI_VERSION of include/velox_b200.h
 EPI_NONE, EPI_BIAS, EPI_BIAS_SWISH, EPI_BIAS_GLU, EPI_BIAS_RESIDUAL, EPI_BIAS_ARGMAX, EPI_BIAS_QKVPACK = range(7)
 GEMM_DIRECT_STORE = 1
 GEMM_STREAM_B = 2
@@ -51,6 +51,8 @@ EXPORTS = (
     "vx_qkv_pack",
     "vx_wait_selftest",
     "vx_tmap_cache_stats",
+    "vx_ctc_lse_parts",
+    "vx_ctc_finish",
 )
 
 
@@ -91,6 +93,7 @@ class GemmDesc(C.Structure):
         ("pos_v", C.c_void_p),
         ("qk_scale", C.c_float),
         ("head_col_off", C.c_int32),
+        ("lse_partials", C.c_void_p),
     ]
 
 
@@ -151,6 +154,10 @@ def load(build_if_missing: bool = True) -> C.CDLL:
         lib.vx_qkv_pack.argtypes = [vp, i64, vp, i64, vp, vp, f32, i64, i32, i32, vp, vp, vp, vp]
         lib.vx_argmax_ids.restype = i32
         lib.vx_argmax_ids.argtypes = [vp, i64, vp, vp, vp]
+        lib.vx_ctc_lse_parts.restype = i64
+        lib.vx_ctc_lse_parts.argtypes = [i64]
+        lib.vx_ctc_finish.restype = i32
+        lib.vx_ctc_finish.argtypes = [vp, vp, i64, i64, vp, vp, vp, vp, vp]
         lib.vx_set_trace_buffer.restype = i32
         lib.vx_set_trace_buffer.argtypes = [vp, i64]
         lib.vx_wait_selftest.restype = i32

@@ -49,10 +49,9 @@ constexpr int TILE_BYTES = BM * STAGE_ROW_BYTES;  // 16 KB
 constexpr int MAX_STAGES = 8;          // ring slots (the arena size decides how many are used)
 constexpr int ARENA_BYTES = 156 * 1024;
 constexpr int RESIDENT_MAX_KSTAGES = 4;                  // B kept in shared memory up to 4 K stages
-constexpr int NUM_THREADS = 576;       // 2 + 16 warps
+constexpr int NUM_THREADS = 576;       // 2 + 16 warps (2 + 32 for the FFN up-projection, see epi_warps)
 // Registers are granted to a CTA in units of four warps: 18 warps count as 20, so the budget
 // is 65536 / 640 = 102 -> 96 registers per thread (112 does not launch).
-#define VX_GEMM_BOUNDS __launch_bounds__(NUM_THREADS, 1)
 
 
 constexpr int EPI_WARP0 = 2;
@@ -73,6 +72,18 @@ __host__ __device__ constexpr int kind_bn(int kind) {
   return (kind == KIND_FP4_VEC2 || kind == KIND_FP4_VEC4) ? 256 : 128;
 }
 __host__ __device__ constexpr bool kind_vec4(int kind) { return kind == KIND_FP4_VEC4 || kind == KIND_FP4_VEC4_N128; }
+
+// Epilogue warps of a kernel instance.  Sixteen, each owning 32 rows x 64 columns of a wide tile,
+// for every epilogue but one: Swish + FP4 output on the wide tile (the FFN up-projection) is bound
+// by its own arithmetic (special-function unit first), and the one accumulator of the wide tile
+// cannot be refilled before every warp has read its part.  There 32 warps own 32 rows x 32 columns
+// each: all of tensor memory is drained by one load per warp right after the MMAs finish, the
+// MMAs of the next tile run under the whole epilogue, and eight warps per scheduler instead of
+// four hide the latency of the dependent multiply / ex2 / rcp chains (56 registers per thread).
+__host__ __device__ constexpr int epi_warps(int kind, int epi, int out) {
+  return (epi == VX_EPI_BIAS_SWISH && out == 2 && kind_bn(kind) == 256) ? 32 : 16;
+}
+__host__ __device__ constexpr int num_threads(int kind, int epi, int out) { return (2 + epi_warps(kind, epi, out)) * 32; }
 
 struct GemmParams {
   int64_t M, N, K;
@@ -119,6 +130,7 @@ struct GemmParams {
   const __nv_bfloat16* pos_u;
   const __nv_bfloat16* pos_v;
   float qk_scale;
+  float2* lse_part;       // ARGMAX: per (64-column group, row) running (max, sum of exp) or nullptr
   int* status;
 };
 
@@ -128,7 +140,7 @@ struct GemmParams {
 struct __align__(1024) SmemLayout {
   uint8_t arena[ARENA_BYTES];
   uint8_t staging[16][STAGING_BYTES];
-  float bias_s[16][64];  // per epilogue warp: bias of its columns ([32..63]: second chunk / GLU gate)
+  float bias_s[1024];    // per epilogue warp: bias of its columns (16 warps x 64: second chunk / GLU gate at [32..63]; 32 warps x 32)
   uint64_t full[MAX_STAGES];
   uint64_t empty[MAX_STAGES];
   uint64_t tmem_full[FP8_ACCS];
@@ -451,7 +463,7 @@ unsigned long long* g_trace_buffer = nullptr;
 //   2  FP4 re-quantized in the operands' own block format (MX32 for the 32-block kinds, NV16
 //      for the 16-block kinds).
 template <int KIND, int EPI, int OUT>
-__global__ void VX_GEMM_BOUNDS
+__global__ void __launch_bounds__(num_threads(KIND, EPI, OUT), 1)
 bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
               const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_res,
               const GemmParams p) {
@@ -477,6 +489,9 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   constexpr bool SEQ = (EPI == VX_EPI_BIAS_SWISH) && NCH == 2;
   // Swish + FP4 output (the FFN up-projection): its own register-lean path, see swish_quant_chunk.
   constexpr bool SWQ = EPI == VX_EPI_BIAS_SWISH && OUT == 2;
+  constexpr int EPW = epi_warps(KIND, EPI, OUT);   // epilogue warps
+  constexpr int BIAS_PER_WARP = 1024 / EPW;        // floats of sm.bias_s per epilogue warp
+  constexpr int NCH_SWQ = kind_bn(KIND) / (32 * (EPW / 4));  // 32-column chunks per warp on the Swish + FP4 path
 
   const int out_dtype = OUT == 1 ? static_cast<int>(VX_BF16) : (OUT == 2 ? static_cast<int>(VX_FP4) : p.out_dtype);
   const bool tma_store = OUT == 1 ? true : (OUT == 2 ? false : p.tma_store != 0);
@@ -531,7 +546,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     }
     for (int a = 0; a < FP8_ACCS; ++a) {
       mbar_init(&sm.tmem_full[a], 1);
-      mbar_init(&sm.tmem_empty[a], 16);
+      mbar_init(&sm.tmem_empty[a], EPW);
     }
     mbar_init(&sm.b_full, 1);
     mbar_init(&sm.sfb_done, 1);
@@ -547,12 +562,12 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     // Scale-factor tiles of B that lie beyond N are never loaded; they must read as zero
     // (their B rows are zero-filled by TMA, and 0 x NaN-scale would poison the accumulator).
     uint4* a4 = reinterpret_cast<uint4*>(sm.arena);
-    for (int i = threadIdx.x; i < ARENA_BYTES / 16; i += NUM_THREADS) a4[i] = make_uint4(0, 0, 0, 0);
+    for (int i = threadIdx.x; i < ARENA_BYTES / 16; i += blockDim.x) a4[i] = make_uint4(0, 0, 0, 0);
   }
   uint8_t* unit_sf = sm.staging[0];  // rowscale only: one atom of 0x7F, copied to TMEM before any tile
   if (!FP8 && sf_unit) {
     uint32_t* u = reinterpret_cast<uint32_t*>(unit_sf);
-    for (int i = threadIdx.x; i < 512 / 4; i += NUM_THREADS) u[i] = 0x7F7F7F7Fu;
+    for (int i = threadIdx.x; i < 512 / 4; i += blockDim.x) u[i] = 0x7F7F7F7Fu;
   }
   fence_proxy_async_smem();
   if (warp == 1) {
@@ -831,7 +846,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     if (p.a_amax && p.b_amax) g_ab = nv16_global(__ldg(p.a_amax)) * nv16_global(__ldg(p.b_amax));
     if (p.out_amax) g_out = nv16_global(__ldg(p.out_amax));
     const int kb_count = FP8 ? p.k_stages : 0;
-    uint8_t* const stage0 = sm.staging[ew];
+    uint8_t* const stage0 = sm.staging[ew & 15];
     // TMA residual: the two halves of the staging buffer alternate per 32-column chunk.  The
     // residual block of chunk c lands in half c & 1, the result is formed in place and stored
     // from there, while the block of chunk c + 1 is already in flight into the other half.
@@ -841,7 +856,9 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     uint32_t store_count = 0;
     int bias_nb = -1;
     uint32_t best_key = 0;  // ARGMAX: best (value, column) of this thread's row in the current tile
-    const float* const bias_base = p.bias ? sm.bias_s[ew] : nullptr;
+    float lse_m = -INFINITY, lse_s = 0.0f;  // ARGMAX + log-sum-exp: running max / sum of 2^((z - max) log2 e) of the tile
+    float* const bias_w = sm.bias_s + ew * BIAS_PER_WARP;
+    const float* const bias_base = p.bias ? bias_w : nullptr;
     // FP8: per-warp tables of B scales at the end of the arena, [chunk][quadrant][kb][32];
     // a GLU warp also owns the table of its gate chunk (chunk cc + 2, whose warps are idle)
     int sb_nb = -1;
@@ -859,7 +876,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     };
 
     int mb = mb0, nb = nb0;
-    const int col_base = WIDE ? (GLU ? cc * 32 : cc * 64) : cc * 32;  // first accumulator column of this warp
+    const int col_base = (WIDE && EPW == 16) ? (GLU ? cc * 32 : cc * 64) : cc * 32;  // first accumulator column of this warp
     bool res_inflight = false;
     if constexpr (EPI == VX_EPI_BIAS_RESIDUAL) {
       if (tma_residual && my_tiles > 0 && has_work) {
@@ -879,8 +896,8 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         __syncwarp();
         const int64_t c0 = static_cast<int64_t>(nb) * BNT + col_base + lane;
         const int64_t c1 = GLU ? c0 + GATE_OFF : c0 + 32;
-        sm.bias_s[ew][lane] = c0 < p.N ? __ldg(p.bias + c0) : 0.0f;
-        sm.bias_s[ew][32 + lane] = c1 < p.N ? __ldg(p.bias + c1) : 0.0f;
+        bias_w[lane] = c0 < p.N ? __ldg(p.bias + c0) : 0.0f;
+        if (BIAS_PER_WARP >= 64) bias_w[32 + lane] = c1 < p.N ? __ldg(p.bias + c1) : 0.0f;
         __syncwarp();
         bias_nb = nb;
       }
@@ -891,22 +908,25 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         // the MMAs of the next tile then run under the arithmetic of the second chunk)
         const uint32_t acc = WIDE ? 0u : (group & 1);
         const uint32_t acc_addr = lane_addr + TM_ACC0 + acc * 128 + col_base;
+        if (tr) trace_rec(p, 2, it, 0);
         if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[acc], (WIDE ? group : (group >> 1)) & 1, p.status, 4, abortp);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
         tc_fence_after();
+        if (tr) trace_rec(p, 2, it, 1);
         ++group;
         const bool scale_acc = kind_vec4(KIND) && p.a_amax != nullptr;
 #pragma unroll
-        for (int h = 0; h < NCH; ++h) {
+        for (int h = 0; h < NCH_SWQ; ++h) {
           uint32_t r[32];
           tc_ld_32x32b_x32(acc_addr + h * 32, r);
           tc_wait_ld();
-          if (h == NCH - 1) {  // the whole accumulator is out of tensor memory
+          if (h == NCH_SWQ - 1) {  // the whole accumulator is out of tensor memory
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.tmem_empty[acc]);
           }
+          if (tr && h == 0) trace_rec(p, 2, it, 2);
           const int64_t out_col0 = static_cast<int64_t>(nb) * BNT + col_base + h * 32;
           uint32_t w[4];
           const uint32_t sb = swish_quant_chunk<kind_vec4(KIND)>(r, bias_base ? bias_base + h * 32 : nullptr, scale_acc, g_ab,
@@ -928,6 +948,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                 *reinterpret_cast<uint16_t*>(p.out_scales + row * (p.N >> 4) + (out_col0 >> 4)) = static_cast<uint16_t>(sbw);
             }
           }
+          if (tr && h == 0) trace_rec(p, 2, it, 4);
         }
         mb = mb_next;
         nb = nb_next;
@@ -1193,6 +1214,28 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
               }
               best_key = max(best_key, max(k0, k1));
             }
+            if (p.lse_part && valid > 0) {
+              // log-sum-exp of the bf16-rounded logits, streaming: chunk maximum, then the chunk's
+              // sum relative to it, merged into the running pair of this 64-column group
+              constexpr float L2E = 1.4426950408889634f;
+              float zr[32];
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const uint32_t pk = pack_bf16x2(z[h][i], z[h][i + 1]);
+                zr[i] = i < valid ? __uint_as_float(pk << 16) : -INFINITY;
+                zr[i + 1] = i + 1 < valid ? __uint_as_float(pk & 0xffff0000u) : -INFINITY;
+              }
+              float cm = zr[0];
+#pragma unroll
+              for (int i = 1; i < 32; i += 2) cm = i + 1 < 32 ? max3(cm, zr[i], zr[i + 1]) : fmaxf(cm, zr[i]);
+              const float nb2 = -cm * L2E;
+              float cs = 0.0f;
+#pragma unroll
+              for (int i = 0; i < 32; ++i) cs += ex2_ftz(fmaf(zr[i], L2E, nb2));
+              const float nm = fmaxf(lse_m, cm);
+              lse_s = lse_s * ex2_ftz((lse_m - nm) * L2E) + cs * ex2_ftz((cm - nm) * L2E);
+              lse_m = nm;
+            }
           } else if (out_dtype == VX_FP4) {
             const uint32_t sb = store_chunk_fp4(p, out_fmt, z[h], row, out_col0, g_out, row_ok && out_col0 < n_out);
             if (out_col0 < n_out) {
@@ -1271,6 +1314,11 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
           atomicMax(static_cast<unsigned long long*>(p.out) + row, key);
         }
         best_key = 0;
+        if (p.lse_part) {
+          if (has_work && row_ok) p.lse_part[(static_cast<int64_t>(nb) * 4 + cc) * p.M + row] = make_float2(lse_m, lse_s);
+          lse_m = -INFINITY;
+          lse_s = 0.0f;
+        }
       }
       mb = mb_next;
       nb = nb_next;
@@ -1299,6 +1347,35 @@ __global__ void argmax_ids_kernel(const unsigned long long* __restrict__ keys, i
     const uint32_t u = static_cast<uint32_t>(k >> 32);
     max_out[i] = __uint_as_float((u & 0x80000000u) ? (u ^ 0x80000000u) : ~u & 0xffff0000u);
   }
+}
+
+// Greedy CTC tail: keys -> ids and winning logits, partial (max, sum) pairs -> log-sum-exp, and
+// from both the log-probability of the winner, log_softmax(z)[argmax] = max - lse.
+__global__ void ctc_finish_kernel(const unsigned long long* __restrict__ keys, const float2* __restrict__ parts,
+                                  int n_parts, int64_t M, int32_t* __restrict__ ids, float* __restrict__ max_out,
+                                  float* __restrict__ lse_out, float* __restrict__ logp_out) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= M) return;
+  const unsigned long long k = keys[i];
+  if (ids) ids[i] = static_cast<int32_t>(0xffffffffu - static_cast<uint32_t>(k));
+  const uint32_t u = static_cast<uint32_t>(k >> 32);
+  const float vmax = __uint_as_float((u & 0x80000000u) ? (u ^ 0x80000000u) : ~u & 0xffff0000u);
+  if (max_out) max_out[i] = vmax;
+  if (!parts) return;
+  constexpr float L2E = 1.4426950408889634f;
+  float m = -INFINITY;
+  for (int p = 0; p < n_parts; ++p) {
+    const float2 v = parts[static_cast<int64_t>(p) * M + i];
+    if (v.y > 0.0f) m = fmaxf(m, v.x);
+  }
+  float s = 0.0f;
+  for (int p = 0; p < n_parts; ++p) {
+    const float2 v = parts[static_cast<int64_t>(p) * M + i];
+    if (v.y > 0.0f) s += v.y * exp2f((v.x - m) * L2E);
+  }
+  const float lse = m + logf(s);
+  if (lse_out) lse_out[i] = lse;
+  if (logp_out) logp_out[i] = vmax - lse;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1578,7 +1655,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, 
       grid = groups * p.n_tiles;
     }
   }
-  bsgemm_kernel<KIND, EPI, OUT><<<grid, NUM_THREADS, kSmemBytes, st>>>(ta, tb, to, tr, p);
+  bsgemm_kernel<KIND, EPI, OUT><<<grid, num_threads(KIND, EPI, OUT), kSmemBytes, st>>>(ta, tb, to, tr, p);
   VX_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -1669,6 +1746,9 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
   }
   if (argmax && (reinterpret_cast<uintptr_t>(d->out) & 7)) return fail(-1, "argmax keys must be 8-byte aligned");
   if (argmax && N > 0xffffffffll) return fail(-1, "argmax needs N < 2^32");
+  if (d->lse_partials && (!argmax || fp8 || (reinterpret_cast<uintptr_t>(d->lse_partials) & 7)))
+    return fail(-1, "lse_partials goes with VX_EPI_BIAS_ARGMAX on the FP4 formats and must be 8-byte aligned");
+  if (d->lse_partials && (d->flags & VX_GEMM_NARROW_TILES)) return fail(-1, "lse_partials needs the wide tile");
   if (d->out_dtype != VX_F32 && d->out_dtype != VX_BF16 && d->out_dtype != VX_FP4)
     return fail(-1, "unknown out_dtype %d", d->out_dtype);
   if (d->bias && (reinterpret_cast<uintptr_t>(d->bias) & 15)) return fail(-1, "bias must be 16-byte aligned");
@@ -1687,6 +1767,7 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
     bool narrow = stages <= 2 && epi != VX_EPI_BIAS_SWISH && epi != VX_EPI_BIAS_GLU &&
                   (epi == VX_EPI_BIAS_RESIDUAL || wide_tiles < 148);
     if (d->flags & VX_GEMM_WIDE_TILES) narrow = false;
+    if (argmax && d->lse_partials) narrow = false;  // the partials are laid out per 64-column group of the wide tile
     if ((d->flags & VX_GEMM_NARROW_TILES) && epi != VX_EPI_BIAS_GLU) narrow = true;
     if (narrow) kind = vec2 ? KIND_FP4_VEC2_N128 : KIND_FP4_VEC4_N128;
   }
@@ -1734,6 +1815,7 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
     p.qk_scale = d->qk_scale;
   } else if (argmax) {
     p.out_dtype = VX_F32;
+    p.lse_part = static_cast<float2*>(d->lse_partials);
   } else if (d->out_dtype == VX_FP4) {
     if (d->out_fmt != VX_FMT_MX32 && d->out_fmt != VX_FMT_NV16) return fail(-1, "FP4 output: out_fmt must be MX32 or NV16");
     if (epi == VX_EPI_BIAS_GLU || epi == VX_EPI_BIAS_RESIDUAL) return fail(-1, "FP4 output supports NONE / BIAS / BIAS_SWISH");
@@ -1835,6 +1917,23 @@ int vx_tmap_cache_stats(int64_t* hits, int64_t* misses) {
   using namespace vx;
   if (hits) *hits = static_cast<int64_t>(g_tmap_hits.load());
   if (misses) *misses = static_cast<int64_t>(g_tmap_misses.load());
+  return 0;
+}
+
+int64_t vx_ctc_lse_parts(int64_t N) { return N <= 0 ? 0 : 4 * ((N + 255) / 256); }
+
+int vx_ctc_finish(const void* keys, const void* lse_partials, int64_t N, int64_t M, int32_t* ids, float* max_out,
+                  float* lse_out, float* logp_out, void* stream) {
+  using namespace vx;
+  if (M < 0 || N < 0) return fail(-1, "negative shape");
+  if (M == 0) return 0;
+  if (!keys) return fail(-1, "keys must not be NULL");
+  if ((lse_out || logp_out) && !lse_partials) return fail(-1, "lse_out / logp_out need lse_partials");
+  const int grid = static_cast<int>((M + 255) / 256);
+  ctc_finish_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const unsigned long long*>(keys), static_cast<const float2*>(lse_partials),
+      static_cast<int>(vx_ctc_lse_parts(N)), M, ids, max_out, lse_out, logp_out);
+  VX_CUDA_OK(cudaGetLastError());
   return 0;
 }
 

@@ -23,6 +23,7 @@
 #include <stdint.h>
 
 #include "vx_common.cuh"
+#include "vx_ptx.cuh"
 #include "vx_quant_math.cuh"
 
 namespace vx {
@@ -45,6 +46,7 @@ struct QuantParams {
   void* y;
   int y_bf16;
   int64_t ldy;
+  int* status;  // device status word (bounded waits of the bulk-copy row rings report here)
 };
 
 // Eight consecutive elements as loaded (not yet converted): lets a kernel issue the loads of
@@ -213,10 +215,23 @@ __device__ __forceinline__ void zero_pad_rows(const QuantParams& p, I gwarp, I w
 #define VX_LNQ_DEPTH 2
 #endif
 
-template <typename T, int FMT, typename I, bool FAST>
+// Row source of the bf16 fast lanes (TMA = true): every warp owns a ring of VX_ROW_RING row slots
+// in shared memory that its lane 0 keeps filled with bulk asynchronous copies (cp.async.bulk,
+// completion on one mbarrier per slot), VX_ROW_RING rows ahead of the row the warp works on.  The
+// copies need no registers and no load instructions, so the bytes an SM keeps in flight are set by
+// shared memory (blocks x 8 warps x ring x row bytes), not by the register file -- which is what
+// it takes to keep HBM busy from kernels that spend ~200 instructions on a 1 KB row.  A slot is
+// handed back to the copy engine after a warp-wide barrier (all lanes have read it).
+#ifndef VX_ROW_RING
+#define VX_ROW_RING 4
+#endif
+constexpr int kRingRowBytes = 1024;  // one slot: a bf16 row of up to 512 elements
+
+template <typename T, int FMT, typename I, bool FAST, bool TMA = false>
 __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) quant_kernel(const QuantParams p) {
   constexpr int RP = (FMT == VX_FMT_BLK16_A) ? 2 : 1;
   constexpr bool BF16IN = sizeof(T) == 2;
+  static_assert(!TMA || (BF16IN && RP == 1 && FMT != VX_FMT_ROWSCALE), "bulk-copy ring: bf16 rows, one row per unit");
   constexpr int DEPTH = (FMT == VX_FMT_ROWSCALE) ? 1 : (BF16IN ? (RP == 2 ? 2 : VX_QUANT_DEPTH) : (RP == 2 ? 1 : 2));
   const int lane = threadIdx.x & 31;
   const I warps = static_cast<I>(gridDim.x) * (blockDim.x >> 5);
@@ -227,7 +242,50 @@ __global__ void __launch_bounds__(256, VX_QUANT_MIN_BLOCKS) quant_kernel(const Q
   if constexpr (FMT == VX_FMT_NV16) g = nv16_global(__ldg(p.amax));
   const I u_first = static_cast<I>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
 
-  if constexpr (FMT == VX_FMT_ROWSCALE) {
+  if constexpr (TMA) {
+    __shared__ __align__(128) uint8_t ring_s[8 * VX_ROW_RING * kRingRowBytes];
+    __shared__ uint64_t full_s[8 * VX_ROW_RING];
+    const int w = threadIdx.x >> 5;
+    uint8_t* const ring_w = ring_s + w * VX_ROW_RING * kRingRowBytes;
+    uint64_t* const full_w = full_s + w * VX_ROW_RING;
+    const uint32_t row_bytes = static_cast<uint32_t>(p.K) * 2;
+    if (lane == 0) {
+#pragma unroll
+      for (int d = 0; d < VX_ROW_RING; ++d) mbar_init(&full_w[d], 1);
+      mbar_fence_init();
+    }
+    __syncwarp();
+    auto issue = [&](int slot, I u) {
+      if (lane == 0) {
+        mbar_expect_tx(&full_w[slot], row_bytes);
+        bulk_load(ring_w + slot * kRingRowBytes, x + u * static_cast<I>(p.ldx), row_bytes, &full_w[slot]);
+      }
+    };
+#pragma unroll
+    for (int d = 0; d < VX_ROW_RING; ++d)
+      if (u_first + d * warps < nunits) issue(d, u_first + d * warps);
+    int slot = 0;
+    uint32_t par = 0;
+#pragma unroll 1
+    for (I u = u_first; u < nunits; u += warps) {
+      if (!mbar_wait(&full_w[slot], par, p.status, 8)) break;
+      uint64_t v[2][1][4];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int k0 = c * 256 + lane * 8;
+        Raw8<T> raw;
+        if ((FAST && c < nchunks) || k0 < p.K) raw.u = *reinterpret_cast<const uint4*>(ring_w + slot * kRingRowBytes + k0 * 2);
+        else raw.zero();
+        raw.get(v[c][0]);
+      }
+      __syncwarp();  // every lane has read the slot: hand it back
+      if (u + VX_ROW_RING * warps < nunits) issue(slot, u + VX_ROW_RING * warps);
+      if (++slot == VX_ROW_RING) { slot = 0; par ^= 1; }
+#pragma unroll
+      for (int c = 0; c < 2; ++c)
+        if (c < nchunks) quant_chunk<FMT, 1, I, FAST, BF16IN>(p, u, c, lane, v[c], 0.0f, g);
+    }
+  } else if constexpr (FMT == VX_FMT_ROWSCALE) {
     // the row maximum comes first: the row is read twice (the second time from L1 / L2)
     for (I u = u_first; u < nunits; u += warps) {
       float a = 0.0f;
@@ -314,10 +372,11 @@ __device__ __forceinline__ uint64_t shfl_xor_b64(uint64_t v, int o) {
 // per thread), so the wider rows get fewer, larger-budget blocks
 constexpr int lnq_min_blocks(int ch) { return ch <= 2 ? VX_LNQ_MIN_BLOCKS : (ch <= 4 ? 2 : 1); }
 
-template <typename T, int FMT, int CH, typename I, bool FAST>
+template <typename T, int FMT, int CH, typename I, bool FAST, bool TMA = false>
 __global__ void __launch_bounds__(256, lnq_min_blocks(CH)) ln_quant_kernel(const QuantParams p) {
   constexpr int RP = (FMT == VX_FMT_BLK16_A) ? 2 : 1;
   constexpr int DEPTH = (CH * RP * (sizeof(T) / 2) <= 2) ? VX_LNQ_DEPTH : 1;
+  static_assert(!TMA || (sizeof(T) == 2 && RP == 1 && CH == 2), "bulk-copy ring: bf16 rows of up to 512 elements");
   const int lane = threadIdx.x & 31;
   const I warps = static_cast<I>(gridDim.x) * (blockDim.x >> 5);
   const I nunits = static_cast<I>(p.M) / RP;
@@ -339,34 +398,10 @@ __global__ void __launch_bounds__(256, lnq_min_blocks(CH)) ln_quant_kernel(const
   }
   __syncthreads();
 
-  Raw8<T> raw[DEPTH][CH][RP];
-  auto fetch = [&](int slot, I u) {
-#pragma unroll
-    for (int r = 0; r < RP; ++r)
-#pragma unroll
-      for (int c = 0; c < CH; ++c) {
-        const I k0 = static_cast<I>(c) * 256 + lane * 8;
-        if (FAST || k0 < static_cast<I>(p.K)) raw[slot][c][r].load(x + (u * RP + r) * static_cast<I>(p.ldx) + k0);
-        else raw[slot][c][r].zero();
-      }
-  };
   const I u_first = static_cast<I>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-#pragma unroll
-  for (int d = 0; d < DEPTH; ++d)
-    if (u_first + d * warps < nunits) fetch(d, u_first + d * warps);
-#pragma unroll 1
-  for (I ub = u_first; ub < nunits; ub += DEPTH * warps) {
-#pragma unroll
-    for (int d = 0; d < DEPTH; ++d) {
-      const I u = ub + d * warps;
-      if (u >= nunits) break;  // warp-uniform
+  // LayerNorm(s) + quantization of unit u, whose RP rows arrive converted in v
+  auto process = [&](const I u, uint64_t (&v)[CH][RP][4]) {
       const I row0 = u * RP;
-      uint64_t v[CH][RP][4];
-#pragma unroll
-      for (int r = 0; r < RP; ++r)
-#pragma unroll
-        for (int c = 0; c < CH; ++c) raw[d][c][r].get(v[c][r]);
-      if (u + DEPTH * warps < nunits) fetch(d, u + DEPTH * warps);
       // one pass per LayerNorm: the second one (if any) normalises the rows as pass 0 stored them
 #pragma unroll 1
       for (int pass = 0; pass < npass; ++pass) {
@@ -435,7 +470,7 @@ __global__ void __launch_bounds__(256, lnq_min_blocks(CH)) ln_quant_kernel(const
           }
         }
       }
-      if (!FAST && !p.codes) continue;  // plain LayerNorm
+      if (!FAST && !p.codes) return;  // plain LayerNorm
       float row_rcp = 0.0f;
       if constexpr (FMT == VX_FMT_ROWSCALE) {
         float a = 0.0f;
@@ -448,6 +483,80 @@ __global__ void __launch_bounds__(256, lnq_min_blocks(CH)) ln_quant_kernel(const
       }
 #pragma unroll
       for (int c = 0; c < CH; ++c) quant_chunk<FMT, RP, I, FAST, false>(p, row0, c, lane, v[c], row_rcp, g);
+  };
+
+  if constexpr (TMA) {
+    __shared__ __align__(128) uint8_t ring_s[8 * VX_ROW_RING * kRingRowBytes];
+    __shared__ uint64_t full_s[8 * VX_ROW_RING];
+    const int w = threadIdx.x >> 5;
+    uint8_t* const ring_w = ring_s + w * VX_ROW_RING * kRingRowBytes;
+    uint64_t* const full_w = full_s + w * VX_ROW_RING;
+    const uint32_t row_bytes = static_cast<uint32_t>(p.K) * 2;
+    if (lane == 0) {
+#pragma unroll
+      for (int d = 0; d < VX_ROW_RING; ++d) mbar_init(&full_w[d], 1);
+      mbar_fence_init();
+    }
+    __syncwarp();
+    auto issue = [&](int slot, I u) {
+      if (lane == 0) {
+        mbar_expect_tx(&full_w[slot], row_bytes);
+        bulk_load(ring_w + slot * kRingRowBytes, x + u * static_cast<I>(p.ldx), row_bytes, &full_w[slot]);
+      }
+    };
+#pragma unroll
+    for (int d = 0; d < VX_ROW_RING; ++d)
+      if (u_first + d * warps < nunits) issue(d, u_first + d * warps);
+    int slot = 0;
+    uint32_t par = 0;
+#pragma unroll 1
+    for (I u = u_first; u < nunits; u += warps) {
+      if (!mbar_wait(&full_w[slot], par, p.status, 8)) break;
+      uint64_t v[CH][RP][4];
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        const int k0 = c * 256 + lane * 8;
+        Raw8<T> raw;
+        if constexpr (sizeof(T) == 2) {
+          if (FAST || k0 < p.K) raw.u = *reinterpret_cast<const uint4*>(ring_w + slot * kRingRowBytes + k0 * 2);
+          else raw.zero();
+        }
+        raw.get(v[c][0]);
+      }
+      __syncwarp();  // every lane has read the slot: hand it back
+      if (u + VX_ROW_RING * warps < nunits) issue(slot, u + VX_ROW_RING * warps);
+      if (++slot == VX_ROW_RING) { slot = 0; par ^= 1; }
+      process(u, v);
+    }
+  } else {
+    Raw8<T> raw[DEPTH][CH][RP];
+    auto fetch = [&](int slot, I u) {
+#pragma unroll
+      for (int r = 0; r < RP; ++r)
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+          const I k0 = static_cast<I>(c) * 256 + lane * 8;
+          if (FAST || k0 < static_cast<I>(p.K)) raw[slot][c][r].load(x + (u * RP + r) * static_cast<I>(p.ldx) + k0);
+          else raw[slot][c][r].zero();
+        }
+    };
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d)
+      if (u_first + d * warps < nunits) fetch(d, u_first + d * warps);
+#pragma unroll 1
+    for (I ub = u_first; ub < nunits; ub += DEPTH * warps) {
+#pragma unroll
+      for (int d = 0; d < DEPTH; ++d) {
+        const I u = ub + d * warps;
+        if (u >= nunits) break;  // warp-uniform
+        uint64_t v[CH][RP][4];
+#pragma unroll
+        for (int r = 0; r < RP; ++r)
+#pragma unroll
+          for (int c = 0; c < CH; ++c) raw[d][c][r].get(v[c][r]);
+        if (u + DEPTH * warps < nunits) fetch(d, u + DEPTH * warps);
+        process(u, v);
+      }
     }
   }
   zero_pad_rows<I>(p, u_first, warps, lane);
@@ -518,9 +627,22 @@ void launch_quant_idx(const QuantParams& p, bool ln, cudaStream_t st) {
   constexpr int RP = (FMT == VX_FMT_BLK16_A) ? 2 : 1;
   const int ch = p.K <= 512 ? 2 : (p.K <= 1024 ? 4 : 8);
   const int grid = grid_for_rows(p.M / RP, ln ? lnq_min_blocks(ch) * (ch > 2 ? 2 : 1) : VX_QUANT_MIN_BLOCKS);
+  // bf16 rows of up to 512 elements, one row per unit: rows come through the per-warp bulk-copy rings
+  constexpr bool tma_ok = sizeof(T) == 2 && RP == 1;
+  const bool tma = tma_ok && p.K <= 512;
   if (!ln) {
+    if constexpr (tma_ok && FMT != VX_FMT_ROWSCALE) {
+      if (tma) {
+        quant_kernel<T, FMT, I, FAST, true><<<grid, 256, 0, st>>>(p);
+        return;
+      }
+    }
     quant_kernel<T, FMT, I, FAST><<<grid, 256, 0, st>>>(p);
   } else if (p.K <= 512) {
+    if constexpr (tma_ok) {
+      ln_quant_kernel<T, FMT, 2, I, FAST, true><<<grid, 256, 0, st>>>(p);
+      return;
+    }
     ln_quant_kernel<T, FMT, 2, I, FAST><<<grid, 256, 0, st>>>(p);
   } else if (p.K <= 1024) {
     ln_quant_kernel<T, FMT, 4, I, FAST><<<grid, 256, 0, st>>>(p);
@@ -612,6 +734,7 @@ int quantize_common(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ld
   p.codes = static_cast<uint8_t*>(codes); p.ldc = ldc;
   p.scales = scales; p.sf = static_cast<uint8_t*>(scales_sf);
   p.sf_kg = sf_kgroups(fmt, K);
+  p.status = device_status_ptr();
   p.amax = amax; p.gamma = gamma; p.beta = beta; p.gamma2 = gamma2; p.beta2 = beta2; p.eps = eps; p.y = y; p.y_bf16 = (y_dtype == VX_BF16); p.ldy = ldy;
   if (scales_sf) {
     // k-groups beyond K must read as zero scale factors (rows beyond M: cleared by the kernel)

@@ -92,11 +92,12 @@ class PackedLinear:
     __call__ = forward
 
     def argmax(self, a: Quantized, *, keys: Optional[torch.Tensor] = None, ids: Optional[torch.Tensor] = None,
-               return_max: bool = False):
-        """First column of the row maximum of the bf16 result, without writing the result."""
+               return_max: bool = False, return_logp: bool = False):
+        """First column of the row maximum of the bf16 result, without writing the result
+        (``return_logp``: also the row's log-sum-exp and the winner's log-probability)."""
         if self.glu:
             raise ValueError("argmax head on a GLU layer")
-        return ops.bsgemm_argmax(a, self.q, self.bias, keys=keys, ids=ids, return_max=return_max)
+        return ops.bsgemm_argmax(a, self.q, self.bias, keys=keys, ids=ids, return_max=return_max, return_logp=return_logp)
 
 
 # --------------------------------------------------------------------------------------

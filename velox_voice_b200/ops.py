@@ -419,10 +419,15 @@ def bsgemm(
 
 def bsgemm_argmax(a: Quantized, b: Quantized, bias: Optional[torch.Tensor] = None, *,
                   return_max: bool = False, keys: Optional[torch.Tensor] = None,
-                  ids: Optional[torch.Tensor] = None):
+                  ids: Optional[torch.Tensor] = None, return_logp: bool = False):
     """Per row of ``A . B^T + bias``: the first column holding the maximum of the bf16-rounded
     result -- ``bsgemm(..., out_dtype=bfloat16).argmax(1)`` without writing the [M, N] matrix
-    (the greedy CTC head).  Returns int32 ids [M] (and the winning values as float32 [M])."""
+    (the greedy CTC head).  Returns int32 ids [M] (and the winning values as float32 [M]).
+
+    ``return_logp`` (FP4 formats) also returns ``(lse, logp)`` float32 [M]: the log-sum-exp of the
+    row's bf16 logits and ``log_softmax(row)[argmax] = max - lse`` -- what the reference's
+    ``ctc_logp`` (``torch_conformer.py:945-949``) holds at the greedy token, still without the
+    logits."""
     d, keep = _gemm_desc(a, b, bias)
     M, N, K = a.rows, b.rows, a.k
     dev = a.codes.device
@@ -435,9 +440,23 @@ def bsgemm_argmax(a: Quantized, b: Quantized, bias: Optional[torch.Tensor] = Non
     d.epilogue = EPI_BIAS_ARGMAX
     d.out_dtype, d.out, d.ldo = DT_F32, keys.data_ptr(), 1
     lib = _lib.load()
+    parts = None
+    if return_logp:
+        if a.fmt == FMT_FP8_1X128:
+            raise ValueError("return_logp runs on the FP4 formats")
+        parts = torch.empty((int(lib.vx_ctc_lse_parts(N)), M, 2), dtype=torch.float32, device=dev)
+        d.lse_partials = parts.data_ptr()
     _lib.check(lib.vx_bsgemm(C.byref(d), _stream()), "vx_bsgemm")
     _count()
     vmax = torch.empty((M,), dtype=torch.float32, device=dev) if return_max else None
+    if return_logp:
+        lse = torch.empty((M,), dtype=torch.float32, device=dev)
+        logp = torch.empty((M,), dtype=torch.float32, device=dev)
+        _lib.check(lib.vx_ctc_finish(keys.data_ptr(), parts.data_ptr(), N, M, ids.data_ptr(), _ptr(vmax), lse.data_ptr(),
+                                     logp.data_ptr(), _stream()), "vx_ctc_finish")
+        _count()
+        del keep, parts
+        return (ids, vmax, lse, logp) if return_max else (ids, lse, logp)
     _lib.check(lib.vx_argmax_ids(keys.data_ptr(), M, ids.data_ptr(), _ptr(vmax), _stream()), "vx_argmax_ids")
     _count()
     del keep
