@@ -73,16 +73,11 @@ __host__ __device__ constexpr int kind_bn(int kind) {
 }
 __host__ __device__ constexpr bool kind_vec4(int kind) { return kind == KIND_FP4_VEC4 || kind == KIND_FP4_VEC4_N128; }
 
-// Epilogue warps of a kernel instance.  Sixteen, each owning 32 rows x 64 columns of a wide tile,
-// for every epilogue but one: Swish + FP4 output on the wide tile (the FFN up-projection) is bound
-// by its own arithmetic (special-function unit first), and the one accumulator of the wide tile
-// cannot be refilled before every warp has read its part.  There 32 warps own 32 rows x 32 columns
-// each: all of tensor memory is drained by one load per warp right after the MMAs finish, the
-// MMAs of the next tile run under the whole epilogue, and eight warps per scheduler instead of
-// four hide the latency of the dependent multiply / ex2 / rcp chains (56 registers per thread).
-__host__ __device__ constexpr int epi_warps(int kind, int epi, int out) {
-  return (epi == VX_EPI_BIAS_SWISH && out == 2 && kind_bn(kind) == 256) ? 32 : 16;
-}
+// Epilogue warps of a kernel instance: sixteen, each owning 32 rows x 64 columns of a wide tile
+// (32 x 32 of a narrow one).  A CTA holds at most 32 warps and the epilogue needs whole groups of
+// four (one warp per 32-lane quadrant of tensor memory), so 28 is the ceiling; 256 columns do not
+// split evenly over seven warps per quadrant, which leaves 16.
+__host__ __device__ constexpr int epi_warps(int kind, int epi, int out) { return 16; }
 __host__ __device__ constexpr int num_threads(int kind, int epi, int out) { return (2 + epi_warps(kind, epi, out)) * 32; }
 
 struct GemmParams {

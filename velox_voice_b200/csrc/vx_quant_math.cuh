@@ -131,13 +131,18 @@ template <bool POW2, bool CANON_ZERO, bool NUDGE>
 __device__ __forceinline__ uint32_t e2m1_pack8p(const uint64_t (&v)[4], float rcp) {
   const float m = POW2 ? __fmul_rn(rcp, kTowardZero) : rcp;
   const uint64_t m2 = pack_f32x2(m, m);
-  const uint64_t z2 = pack_f32x2(0.0f, 0.0f);
   const uint64_t t2 = pack_f32x2(kTowardZero, kTowardZero);
   float r[8];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     uint64_t q = mul_f32x2(v[j], m2);
-    if (CANON_ZERO) q = add_f32x2(q, z2);  // -0 -> +0
+    if (CANON_ZERO) {
+      // -0 -> +0 with scalar additions: the packed add of a constant (+0, +0) was seen to leave a
+      // product that underflowed to -0 negative (tiny negative value next to a huge one in a block)
+      float a, b;
+      unpack_f32x2(q, a, b);
+      q = pack_f32x2(__fadd_rn(a, 0.0f), __fadd_rn(b, 0.0f));
+    }
     if (!POW2) q = mul_f32x2(q, t2);
     float lo, hi;
     unpack_f32x2(q, lo, hi);
