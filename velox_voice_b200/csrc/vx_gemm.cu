@@ -213,29 +213,33 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 //   block maximum with three-input max; the E2M1 encode of e2m1_pack8p.
 // NV16 = false: one UE8M0 scale for the 32 values; true: two E4M3 scales (16 values each).
 // Returns the scale byte(s), little end first.
+// Eight accumulator values r[8 g .. 8 g + 7] -> (* tensor scales) + bias -> Swish, as four packed pairs.
 template <bool NV16>
-__device__ __forceinline__ uint32_t swish_quant_chunk(const uint32_t (&r)[32], const float* bias_s, bool scale_acc,
-                                                      float g_ab, float g_out, uint32_t (&w)[4]) {
-  uint64_t sv[16];
-  const uint64_t g2 = pack_f32x2(g_ab, g_ab);
+__device__ __forceinline__ void swish_group8(const uint32_t (&r)[32], int g, const float* bias_s, bool scale_acc,
+                                             uint64_t g2, uint64_t (&out)[4]) {
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    uint64_t za = pack_f32x2(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]));
-    uint64_t zb = pack_f32x2(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+  for (int i = 0; i < 2; ++i) {
+    const int q4 = 2 * g + i;
+    uint64_t za = pack_f32x2(__uint_as_float(r[4 * q4]), __uint_as_float(r[4 * q4 + 1]));
+    uint64_t zb = pack_f32x2(__uint_as_float(r[4 * q4 + 2]), __uint_as_float(r[4 * q4 + 3]));
     if (NV16 && scale_acc) {
       za = mul_f32x2(za, g2);
       zb = mul_f32x2(zb, g2);
     }
     if (bias_s) {
-      const float4 b = *reinterpret_cast<const float4*>(bias_s + 4 * i);
+      const float4 b = *reinterpret_cast<const float4*>(bias_s + 4 * q4);
       za = add_f32x2(za, pack_f32x2(b.x, b.y));
       zb = add_f32x2(zb, pack_f32x2(b.z, b.w));
     }
     swish4p(za, zb);
-    sv[2 * i] = za;
-    sv[2 * i + 1] = zb;
+    out[2 * i] = za;
+    out[2 * i + 1] = zb;
   }
-  uint32_t sbytes = 0;
+}
+// Block scale(s) of 32 finished values (16 packed pairs): the scale byte(s), little end first, and
+// the reciprocal(s) to normalise with (NV16: rcp0 for values 0..15, rcp1 for 16..31).
+template <bool NV16>
+__device__ __forceinline__ uint32_t chunk_scales_p(const uint64_t (&sv)[16], float g_out, float& rcp0, float& rcp1) {
   if constexpr (!NV16) {
     float a = 0.0f;
 #pragma unroll
@@ -244,14 +248,12 @@ __device__ __forceinline__ uint32_t swish_quant_chunk(const uint32_t (&r)[32], c
       unpack_f32x2(sv[j], lo, hi);
       a = max3(a, fabsf(lo), fabsf(hi));
     }
-    float rcp;
-    ue8m0_from_amax(a, sbytes, rcp);
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const uint64_t v[4] = {sv[4 * q], sv[4 * q + 1], sv[4 * q + 2], sv[4 * q + 3]};
-      w[q] = e2m1_pack8p<true, false, true>(v, rcp);
-    }
+    uint32_t byte;
+    ue8m0_from_amax(a, byte, rcp0);
+    rcp1 = rcp0;
+    return byte;
   } else {
+    uint32_t sb = 0;
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
       float a = 0.0f;
@@ -264,15 +266,36 @@ __device__ __forceinline__ uint32_t swish_quant_chunk(const uint32_t (&r)[32], c
       uint32_t byte;
       float rcp;
       nv16_block(a, g_out, byte, rcp);
-      sbytes |= byte << (8 * hh);
-#pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        const int b = 8 * hh + 4 * q;
-        const uint64_t v[4] = {sv[b], sv[b + 1], sv[b + 2], sv[b + 3]};
-        w[2 * hh + q] = e2m1_pack8p<false, false, true>(v, rcp);
-      }
+      if (hh == 0) rcp0 = rcp; else rcp1 = rcp;
+      sb |= byte << (8 * hh);
     }
+    return sb;
   }
+}
+// Codes of values 8 g .. 8 g + 7 of a finished chunk.
+template <bool NV16>
+__device__ __forceinline__ uint32_t encode_group8(const uint64_t (&sv)[16], int g, float rcp0, float rcp1) {
+  const uint64_t v[4] = {sv[4 * g], sv[4 * g + 1], sv[4 * g + 2], sv[4 * g + 3]};
+  if constexpr (NV16) return e2m1_pack8p<false, false, true>(v, g < 2 ? rcp0 : rcp1);
+  else return e2m1_pack8p<true, false, true>(v, rcp0);
+}
+
+template <bool NV16>
+__device__ __forceinline__ uint32_t swish_quant_chunk(const uint32_t (&r)[32], const float* bias_s, bool scale_acc,
+                                                      float g_ab, float g_out, uint32_t (&w)[4]) {
+  uint64_t sv[16];
+  const uint64_t g2 = pack_f32x2(g_ab, g_ab);
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    uint64_t o[4];
+    swish_group8<NV16>(r, g, bias_s, scale_acc, g2, o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) sv[4 * g + j] = o[j];
+  }
+  float rcp0, rcp1;
+  const uint32_t sbytes = chunk_scales_p<NV16>(sv, g_out, rcp0, rcp1);
+#pragma unroll
+  for (int g = 0; g < 4; ++g) w[g] = encode_group8<NV16>(sv, g, rcp0, rcp1);
   return sbytes;
 }
 
@@ -487,6 +510,9 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   constexpr int EPW = epi_warps(KIND, EPI, OUT);   // epilogue warps
   constexpr int BIAS_PER_WARP = 1024 / EPW;        // floats of sm.bias_s per epilogue warp
   constexpr int NCH_SWQ = kind_bn(KIND) / (32 * (EPW / 4));  // 32-column chunks per warp on the Swish + FP4 path
+  // Wide tile: software-pipelined (see the epilogue): the Swish of the chunk just read from tensor
+  // memory is interleaved with the E2M1 encode of the chunk before it.
+  constexpr bool SWQ_PIPE = SWQ && NCH_SWQ == 2;
 
   const int out_dtype = OUT == 1 ? static_cast<int>(VX_BF16) : (OUT == 2 ? static_cast<int>(VX_FP4) : p.out_dtype);
   const bool tma_store = OUT == 1 ? true : (OUT == 2 ? false : p.tma_store != 0);
@@ -879,6 +905,29 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         res_inflight = true;
       }
     }
+    // SWQ_PIPE: the chunk whose Swish is done and whose encode is still pending (two register sets
+    // that alternate per chunk), its block scale(s) and where its codes / scale bytes go
+    uint64_t pz[2][SWQ_PIPE ? 16 : 1];
+    float pend_rcp0 = 0.0f, pend_rcp1 = 0.0f;
+    uint32_t pend_sb = 0;
+    bool pend_row_ok = false, pend_col_ok = false;
+    int64_t pend_row = 0, pend_col = 0;
+    auto pend_store = [&](const uint32_t (&w)[4]) {
+      if (!pend_col_ok) return;
+      if (pend_row_ok)
+        *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out) + pend_row * p.ldo + (pend_col >> 1)) = make_uint4(w[0], w[1], w[2], w[3]);
+      // rows of the last tile beyond M get zero scale factors (the SF atoms cover whole 128-row tiles)
+      const uint32_t sbw = pend_row_ok ? pend_sb : 0u;
+      const int64_t sf_row = (pend_row >> 7) * p.out_sf_kg * 512 + (pend_row & 31) * 16 + ((pend_row >> 5) & 3) * 4;
+      if constexpr (!kind_vec4(KIND)) {
+        p.out_sf[sf_row + (pend_col >> 7) * 512 + ((pend_col >> 5) & 3)] = static_cast<uint8_t>(sbw);
+        if (p.out_scales && pend_row_ok) p.out_scales[pend_row * (p.N >> 5) + (pend_col >> 5)] = static_cast<uint8_t>(sbw);
+      } else {
+        *reinterpret_cast<uint16_t*>(p.out_sf + sf_row + (pend_col >> 6) * 512 + ((pend_col >> 5) & 1) * 2) = static_cast<uint16_t>(sbw);
+        if (p.out_scales && pend_row_ok)
+          *reinterpret_cast<uint16_t*>(p.out_scales + pend_row * (p.N >> 4) + (pend_col >> 4)) = static_cast<uint16_t>(sbw);
+      }
+    };
     for (int it = 0; it < my_tiles && ok; ++it) {
       const int64_t row = static_cast<int64_t>(mb) * BM + q * 32 + lane;
       const bool row_ok = row < p.M;
@@ -896,7 +945,59 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         __syncwarp();
         bias_nb = nb;
       }
-      if constexpr (SWQ) {
+      if constexpr (SWQ_PIPE) {
+        // FFN up-projection on the wide tile, software-pipelined.  Swish is bound by the
+        // special-function unit (ex2 per value, rcp per four), the E2M1 encode by the ALU / FMA
+        // pipes, and the block scale between them needs all 32 values of a chunk: run one after
+        // the other, each phase leaves the other's pipes idle, and the four warps of a scheduler
+        // reach the same phase together (they all start when the accumulator is published).
+        // Here every group of eight new values goes through Swish next to the encode of eight
+        // values of the PREVIOUS chunk, whose scale is already known.
+        if (tr) trace_rec(p, 2, it, 0);
+        if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[0], group & 1, p.status, 4, abortp);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        tc_fence_after();
+        if (tr) trace_rec(p, 2, it, 1);
+        ++group;
+        const bool scale_acc = kind_vec4(KIND) && p.a_amax != nullptr;
+        const uint64_t g2 = pack_f32x2(g_ab, g_ab);
+        const uint32_t acc_addr = lane_addr + TM_ACC0 + col_base;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint64_t (&zn)[16] = pz[h];      // chunk read now
+          uint64_t (&zo)[16] = pz[h ^ 1];  // pending: the previous tile's second chunk / this tile's first
+          uint32_t r[32];
+          tc_ld_32x32b_x32(acc_addr + h * 32, r);
+          tc_wait_ld();
+          if (h == 1) {  // the whole accumulator is out of tensor memory
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.tmem_empty[0]);
+          }
+          if (tr && h == 0) trace_rec(p, 2, it, 2);
+          uint32_t w[4];
+#pragma unroll
+          for (int g8 = 0; g8 < 4; ++g8) {
+            uint64_t o[4];
+            swish_group8<kind_vec4(KIND)>(r, g8, bias_base ? bias_base + h * 32 : nullptr, scale_acc, g2, o);
+            w[g8] = encode_group8<kind_vec4(KIND)>(zo, g8, pend_rcp0, pend_rcp1);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) zn[4 * g8 + j] = o[j];
+          }
+          pend_store(w);
+          // the chunk just finished becomes the pending one
+          pend_sb = chunk_scales_p<kind_vec4(KIND)>(zn, g_out, pend_rcp0, pend_rcp1);
+          pend_col = static_cast<int64_t>(nb) * BNT + col_base + h * 32;
+          pend_col_ok = pend_col < p.N;
+          pend_row = row;
+          pend_row_ok = row_ok;
+          if (tr && h == 0) trace_rec(p, 2, it, 4);
+        }
+        mb = mb_next;
+        nb = nb_next;
+        continue;
+      } else if constexpr (SWQ) {
         // FFN up-projection: accumulator -> bias + Swish -> E2M1 codes + scale factors, one
         // 32-column chunk at a time (the second chunk of a wide tile is read from tensor memory
         // only after the first is finished, so that one chunk's registers are live at a time;
@@ -1317,6 +1418,14 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       }
       mb = mb_next;
       nb = nb_next;
+    }
+    if constexpr (SWQ_PIPE) {
+      if (my_tiles > 0 && ok) {  // encode the last pending chunk (the second chunk of the last tile)
+        uint32_t w[4];
+#pragma unroll
+        for (int g8 = 0; g8 < 4; ++g8) w[g8] = encode_group8<kind_vec4(KIND)>(pz[1], g8, pend_rcp0, pend_rcp1);
+        pend_store(w);
+      }
     }
     if (tma_store && lane == 0) tma_store_wait_all<0>();
     if (!ok) sm.abort_flag = 1;

@@ -119,7 +119,11 @@ __device__ __forceinline__ I sf_offset(I row, I kgroup, I sf_kg) {
 // per-chunk bounds predicates, the natural-layout stores and their tests from the inner loop.
 // BF16IN: the values are bf16 numbers (straight from a bf16 tensor, no arithmetic in between),
 // which lets the power-of-two-scaled formats skip the tie nudge (see e2m1_pack8p).
-template <int FMT, int RP, typename I, bool FAST, bool BF16IN>
+// CANON: turn a normalised value that is (or underflows to) -0 into +0 before the encode, as the
+// reference's `q < 0` sign test does.  The quantizers of plain tensors keep it; behind LayerNorm
+// it is dropped (a LayerNorm output is -0 only for beta = -0, and y / scale underflows only when a
+// block holds a value more than 2^125 times smaller than its maximum).
+template <int FMT, int RP, typename I, bool FAST, bool BF16IN, bool CANON = true>
 __device__ __forceinline__ void quant_chunk(const QuantParams& p, I row0, int c, int lane,
                                             uint64_t (&v)[RP][4], float row_rcp, float g) {
   const I K = static_cast<I>(p.K), M = static_cast<I>(p.M), ldc = static_cast<I>(p.ldc);
@@ -129,7 +133,7 @@ __device__ __forceinline__ void quant_chunk(const QuantParams& p, I row0, int c,
 
   if constexpr (FMT == VX_FMT_ROWSCALE) {
     if (active) {
-      *reinterpret_cast<uint32_t*>(p.codes + row0 * ldc + (k0 >> 1)) = e2m1_pack8p<true, true, NUDGE>(v[0], row_rcp);
+      *reinterpret_cast<uint32_t*>(p.codes + row0 * ldc + (k0 >> 1)) = e2m1_pack8p<true, CANON, NUDGE>(v[0], row_rcp);
     }
   } else if constexpr (FMT == VX_FMT_FP8_1X128) {
     float a = amax8p(v[0]);
@@ -159,8 +163,8 @@ __device__ __forceinline__ void quant_chunk(const QuantParams& p, I row0, int c,
     for (int r = 0; r < RP; ++r) {
       if (active) {
         uint32_t w;
-        if constexpr (FMT == VX_FMT_NV16) w = e2m1_pack8p<false, true, true>(v[r], rcp);
-        else w = e2m1_pack8p<true, true, NUDGE>(v[r], rcp);
+        if constexpr (FMT == VX_FMT_NV16) w = e2m1_pack8p<false, CANON, true>(v[r], rcp);
+        else w = e2m1_pack8p<true, CANON, NUDGE>(v[r], rcp);
         *reinterpret_cast<uint32_t*>(p.codes + (row0 + r) * ldc + (k0 >> 1)) = w;
       }
     }
@@ -171,15 +175,13 @@ __device__ __forceinline__ void quant_chunk(const QuantParams& p, I row0, int c,
       else s[row0 * (K / BLK) + kb] = byte;
     }
     if (FAST || p.sf) {
-      // assemble the 4 scale bytes of one k-group into a word held by every lane of the group
-      uint32_t w = byte << (8 * ((lane / LPB) & 3));
-#pragma unroll
-      for (int o = LPB; o < 4 * LPB; o <<= 1) w |= __shfl_xor_sync(0xffffffffu, w, o);
-      if (active && (lane % (4 * LPB)) == 0) {
+      // one byte per block, stored by the first lane of the block (the byte sits at
+      // [k-group atom][row slot][kb % 4]); the 8 / 16 byte stores of a chunk are one instruction
+      if ((FAST || active) && (lane % LPB) == 0) {
         const I kg = kb >> 2;
 #pragma unroll
         for (int r = 0; r < RP; ++r)
-          *reinterpret_cast<uint32_t*>(p.sf + sf_offset<I>(row0 + r, kg, static_cast<I>(p.sf_kg))) = w;
+          p.sf[sf_offset<I>(row0 + r, kg, static_cast<I>(p.sf_kg)) + (kb & 3)] = static_cast<uint8_t>(byte);
       }
     }
   }
@@ -482,7 +484,7 @@ __global__ void __launch_bounds__(256, lnq_min_blocks(CH)) ln_quant_kernel(const
         if (p.scales && lane == 0) static_cast<uint8_t*>(p.scales)[row0] = static_cast<uint8_t>(byte);
       }
 #pragma unroll
-      for (int c = 0; c < CH; ++c) quant_chunk<FMT, RP, I, FAST, false>(p, row0, c, lane, v[c], row_rcp, g);
+      for (int c = 0; c < CH; ++c) quant_chunk<FMT, RP, I, FAST, false, false>(p, row0, c, lane, v[c], row_rcp, g);
   };
 
   if constexpr (TMA) {
