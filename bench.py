@@ -45,8 +45,6 @@ def parse():
     ap.add_argument("--fmt", default="mx32", choices=["mx32", "nv16", "fp8_1x128"])
     ap.add_argument("--blocks", type=int, default=12)
     ap.add_argument("--cpu-frames", type=int, default=4096, help="frames per step of the CPU arms' sample")
-    ap.add_argument("--chunks", type=int, default=1,
-                    help="row ranges the captured step takes one after the other (activations stay in L2 between launches)")
     ap.add_argument("--no-breakdown", action="store_true", help="skip the per-launch timings (no roofline object)")
     ap.add_argument("--no-extras", action="store_true", help="skip the logits-gather and weak-scaling legs")
     ap.add_argument("--traffic-bytes", type=float, default=None,
@@ -258,7 +256,7 @@ def run_ours(a):
     pos = torch.randn(cap, cfg.d_model, generator=g).bfloat16().to(dev)
     if a.fmt == "nv16":
         stack.calibrate(feats_host[:4096].to(dev), pos[:4096])
-    comp = stack.compile(cap, chunks=a.chunks)
+    comp = stack.compile(cap)
     comp.pos.copy_(pos)
     comp.x_in.copy_(feats_host)
     ids_all = torch.empty((world * cap,), dtype=torch.int32, device=dev)
@@ -473,7 +471,6 @@ def run_ours(a):
                       "fp8_1x128": "fp8 (e4m3, f32 per 1x128) -> f32"}[a.fmt],
             "data": "synthetic",
             "config": {"workload": workload_name(a), "total_frames": T, "frames_per_gpu": cap, "format": a.fmt, "blocks": a.blocks,
-                       "row_ranges_per_step": len(comp.ranges),
                        "l2": ("working set per launch > L2 (126 MB) at one GPU; per-launch timings flush L2 (512 MB write) "
                               "before every timed launch"),
                        "parallelism": f"{world} equal frame shards of one {T}-frame job, weights replicated, ids all-gather"},

@@ -44,6 +44,38 @@ def gemm_ref(fmt: int, aq, asc, bq, bsc, ga=None, gb=None) -> np.ndarray:
     return matmul_f32(F.dequantize(aq, asc, fmt, ga), F.dequantize(bq, bsc, fb, gb))
 
 
+def gemm_kernel_order(fmt: int, aq, asc, bq, bsc, ga=None, gb=None) -> np.ndarray:
+    """The block-scaled product evaluated the way the tensor-core kernel groups it, with every
+    group's dot product taken exactly (fp64) and rounded once -- an idealised tensor core:
+
+    * NV16: ``fp32(sum_k (a_code sfa)(b_code sfb)) * fp32(ga * gb)`` (the hardware applies the E4M3
+      block scales inside the MMA; the two per-tensor scales multiply the accumulator);
+    * FP8 1x128: per 128-wide K block ``p = fp32(sum_k a8 b8)``, then ``acc = fma(p, fp32(sa sb), acc)``
+      block after block (the kernel promotes each block's accumulator in fp32 registers);
+    * the power-of-two-scaled formats: identical to :func:`gemm_ref` (every operation is exact).
+
+    :func:`gemm_ref` -- dequantize every element to fp32, then an fp32 matmul in the BLAS
+    library's summation order -- stays the acceptance reference; this variant separates what two
+    correct implementations differ by (rounding of the dequantized elements, summation order)
+    from what the kernel itself adds."""
+    if fmt == F.FMT_NV16:
+        a = F.e2m1_decode(F.unpack_codes(aq)).astype(np.float64) * np.repeat(F.e4m3_decode(asc), 16, axis=1).astype(np.float64)
+        b = F.e2m1_decode(F.unpack_codes(bq)).astype(np.float64) * np.repeat(F.e4m3_decode(bsc), 16, axis=1).astype(np.float64)
+        acc = (a @ b.T).astype(np.float32)
+        return (acc * (F32(ga) * F32(gb))).astype(np.float32)
+    if fmt == F.FMT_FP8_1X128:
+        a = F.e4m3_decode(aq).astype(np.float64)
+        b = F.e4m3_decode(bq).astype(np.float64)
+        M, K = a.shape
+        acc = np.zeros((M, b.shape[0]), dtype=np.float32)
+        for kb in range(K // 128):
+            part = (a[:, 128 * kb: 128 * kb + 128] @ b[:, 128 * kb: 128 * kb + 128].T).astype(np.float32)
+            sc = (asc[:, kb].astype(np.float32)[:, None] * bsc[:, kb].astype(np.float32)[None, :]).astype(np.float32)
+            acc = fma32(part, sc, acc)
+        return acc
+    return gemm_ref(fmt, aq, asc, bq, bsc, ga, gb)
+
+
 def silu(x: np.ndarray) -> np.ndarray:
     x = x.astype(np.float32)
     return (x / (1.0 + np.exp(-x.astype(np.float64)))).astype(np.float32)

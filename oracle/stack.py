@@ -25,7 +25,8 @@ from . import gemm as G
 
 class OracleStack:
     def __init__(self, weights: Dict[str, np.ndarray], fmt: int, blocks: int, d_model: int = 512,
-                 eps: float = 1e-5, amax: Optional[Dict[str, float]] = None, fuse_ffn: bool = True):
+                 eps: float = 1e-5, amax: Optional[Dict[str, float]] = None, fuse_ffn: bool = True,
+                 kernel_order: bool = False):
         self.w = {k: np.asarray(v, dtype=np.float32) for k, v in weights.items()}
         self.fmt = fmt
         self.blocks = blocks
@@ -33,7 +34,11 @@ class OracleStack:
         self.eps = eps
         self.amax = amax or {}
         self.fuse_ffn = fuse_ffn
+        # kernel_order: every product through gemm.gemm_kernel_order (the kernel's grouping of the
+        # sum with exact group sums) instead of dequantize -> fp32 matmul; see that function
+        self.kernel_order = kernel_order
         self._wd: Dict[str, np.ndarray] = {}
+        self._wq: Dict[str, tuple] = {}
 
     # weight quantized then dequantized, once
     def _weight(self, key: str) -> np.ndarray:
@@ -42,15 +47,24 @@ class OracleStack:
             self._wd[key] = F.dequantize(q, s, self.fmt, g)
         return self._wd[key]
 
-    def _act(self, x: np.ndarray, key: str) -> np.ndarray:
+    def _act(self, x: np.ndarray, key: str):
         kw = {}
         if self.fmt == F.FMT_NV16:
             kw["amax_t"] = np.float32(self.amax[key]) if key in self.amax else None
         q, s, g = F.quantize(x, self.fmt, **kw)
+        if self.kernel_order:
+            return (q, s, g)
         return F.dequantize(q, s, self.fmt, g)
 
-    def _lin(self, xq: np.ndarray, wkey: str, bkey: Optional[str]) -> np.ndarray:
-        y = G.matmul_f32(xq, self._weight(wkey))
+    def _lin(self, xq, wkey: str, bkey: Optional[str]) -> np.ndarray:
+        if self.kernel_order:
+            if wkey not in self._wq:
+                self._wq[wkey] = F.quantize(self.w[wkey], self.fmt)
+            wq, ws, wg = self._wq[wkey]
+            aq, asc, ag = xq
+            y = G.gemm_kernel_order(self.fmt, aq, asc, wq, ws, ag, wg)
+        else:
+            y = G.matmul_f32(xq, self._weight(wkey))
         if bkey is not None:
             y = y + self.w[bkey][None, :]
         return y.astype(np.float32)

@@ -212,3 +212,42 @@ def test_reference_model_fp4_lane_end_to_end(installed, ref_triton, monkeypatch)
     print(f"[reference model, {n} frames] token divergence {diverged}, max |dlogp| {(lp_a - lp_b).abs().max().item():.3g}")
     assert diverged <= max(3, n // 1000)
     assert diverged == 0 and (lp_a - lp_b).abs().max().item() < 1e-4
+
+
+def test_reference_fp4_filterbank_lane_through_install(installed):
+    """The front-end's FP4 mel projection, ``power_mel_log_mxfp4`` of the reference
+    (``veloxvoice/kernels/ops/cuda_ops.py:149-192``: power spectrum -> ``mxfp4_block_quantize`` ->
+    ``dgx_mxfp4_blkscale_gemm`` -> log -> CMVN), executed unchanged on the installed operators and
+    compared with the same chain on the CPU oracle (bit-exact product) and with the reference's own
+    fp32 formula (``reference_power_mel_log``, FP4 tolerance)."""
+    import veloxvoice.kernels.ops.cuda_ops as cu
+
+    from oracle import formats as F
+    from oracle import gemm as G
+    from velox_voice_b200 import ops
+
+    torch.manual_seed(31)
+    T, Fbins, M = 300, 257, 80
+    spec = torch.randn(T, Fbins, dtype=torch.complex64, device="cuda") * 100.0
+    mel = torch.rand(M, Fbins, device="cuda") * (torch.rand(M, Fbins, device="cuda") < 0.1)
+    F_padded, M_padded = 320, 128
+    mel_p = torch.zeros(M_padded, F_padded, device="cuda")
+    mel_p[:M, :Fbins] = mel
+    mel_codes, mel_scales = ops.mxfp4_block_quantize(mel_p, mode="B")
+    mean, istd = torch.randn(M, device="cuda"), torch.rand(M, device="cuda") + 0.5
+    out = cu.power_mel_log_mxfp4(spec, mel_codes, mel_scales, mean, istd, F_padded, M_padded)
+    assert out.shape == (T, M) and out.dtype == torch.float32 and torch.isfinite(out).all()
+    # oracle: same quantizers, block-scaled product of the dequantized operands, log, CMVN
+    power = (spec.real ** 2 + spec.imag ** 2).cpu().numpy()
+    pp = np.zeros((384, F_padded), dtype=np.float32)
+    pp[:T, :Fbins] = power
+    aq, asc, _ = F.quantize(pp, F.FMT_BLK16_A)
+    bq, bsc, _ = F.quantize(mel_p.cpu().numpy(), F.FMT_BLK16_B)
+    assert np.array_equal(bq, mel_codes.cpu().numpy()) and np.array_equal(bsc, mel_scales.cpu().numpy())
+    acc = G.gemm_ref(F.FMT_BLK16_A, aq, asc, bq, bsc)[:T, :M]
+    ref = (np.log(np.maximum(acc, np.float32(1.1920929e-7))) - mean.cpu().numpy()[None, :]) * istd.cpu().numpy()[None, :]
+    assert np.abs(out.cpu().numpy() - ref).max() < 1e-4
+    # against the unquantized formula of the reference: FP4 noise only
+    full = cu.reference_power_mel_log(spec.real, spec.imag, mel, mean, istd)
+    nz = (mel.sum(1) > 0).cpu().numpy()
+    assert np.median(np.abs(out.cpu().numpy() - full.cpu().numpy())[:, nz]) < 0.2

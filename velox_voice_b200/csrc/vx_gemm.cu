@@ -49,7 +49,7 @@ constexpr int TILE_BYTES = BM * STAGE_ROW_BYTES;  // 16 KB
 constexpr int MAX_STAGES = 8;          // ring slots (the arena size decides how many are used)
 constexpr int ARENA_BYTES = 156 * 1024;
 constexpr int RESIDENT_MAX_KSTAGES = 4;                  // B kept in shared memory up to 4 K stages
-constexpr int NUM_THREADS = 576;       // 2 + 16 warps (2 + 32 for the FFN up-projection, see epi_warps)
+constexpr int NUM_THREADS = 576;       // 2 + 16 warps (2 + 28 for the FFN up-projection, see epi_warps)
 // Registers are granted to a CTA in units of four warps: 18 warps count as 20, so the budget
 // is 65536 / 640 = 102 -> 96 registers per thread (112 does not launch).
 
@@ -73,11 +73,22 @@ __host__ __device__ constexpr int kind_bn(int kind) {
 }
 __host__ __device__ constexpr bool kind_vec4(int kind) { return kind == KIND_FP4_VEC4 || kind == KIND_FP4_VEC4_N128; }
 
-// Epilogue warps of a kernel instance: sixteen, each owning 32 rows x 64 columns of a wide tile
-// (32 x 32 of a narrow one).  A CTA holds at most 32 warps and the epilogue needs whole groups of
-// four (one warp per 32-lane quadrant of tensor memory), so 28 is the ceiling; 256 columns do not
-// split evenly over seven warps per quadrant, which leaves 16.
-__host__ __device__ constexpr int epi_warps(int kind, int epi, int out) { return 16; }
+// Epilogue warps of a kernel instance.  A CTA holds at most 32 warps and the epilogue needs whole
+// groups of four (one warp per 32-lane quadrant of tensor memory; the quadrant is also the warp's
+// scheduler), so 28 is the ceiling.
+//   16  every epilogue but one: warp (quadrant, column group) owns 32 rows x 64 columns of a wide
+//       tile (32 x 32 of a narrow one), the same part of every tile;
+//   28  Swish + FP4 output on the narrow tile (the FFN up-projection).  That epilogue is bound by
+//       the latency of its own arithmetic -- dependent multiply / ex2 / rcp chains, four warps
+//       per scheduler, all in the same phase because one barrier starts them -- so it runs on
+//       seven warps per scheduler which take the 32 x 32 chunks of the tile stream ROUND ROBIN
+//       (chunk n = 4 * tile + column group goes to warp n mod 7 of the quadrant): the warps of a
+//       scheduler then sit in different tiles and different phases, and the two accumulators of
+//       the narrow tile keep the MMAs two tiles ahead.
+__host__ __device__ constexpr bool epi_round_robin(int kind, int epi, int out) {
+  return epi == VX_EPI_BIAS_SWISH && out == 2 && kind_bn(kind) == 128;
+}
+__host__ __device__ constexpr int epi_warps(int kind, int epi, int out) { return epi_round_robin(kind, epi, out) ? 28 : 16; }
 __host__ __device__ constexpr int num_threads(int kind, int epi, int out) { return (2 + epi_warps(kind, epi, out)) * 32; }
 
 struct GemmParams {
@@ -509,10 +520,8 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   constexpr bool SWQ = EPI == VX_EPI_BIAS_SWISH && OUT == 2;
   constexpr int EPW = epi_warps(KIND, EPI, OUT);   // epilogue warps
   constexpr int BIAS_PER_WARP = 1024 / EPW;        // floats of sm.bias_s per epilogue warp
-  constexpr int NCH_SWQ = kind_bn(KIND) / (32 * (EPW / 4));  // 32-column chunks per warp on the Swish + FP4 path
-  // Wide tile: software-pipelined (see the epilogue): the Swish of the chunk just read from tensor
-  // memory is interleaved with the E2M1 encode of the chunk before it.
-  constexpr bool SWQ_PIPE = SWQ && NCH_SWQ == 2;
+  constexpr bool SWQ_RR = epi_round_robin(KIND, EPI, OUT);     // chunks of the tile stream dealt round robin
+  constexpr int NCH_SWQ = kind_bn(KIND) / 128;                 // 32-column chunks per warp on the Swish + FP4 path (16 warps)
 
   const int out_dtype = OUT == 1 ? static_cast<int>(VX_BF16) : (OUT == 2 ? static_cast<int>(VX_FP4) : p.out_dtype);
   const bool tma_store = OUT == 1 ? true : (OUT == 2 ? false : p.tma_store != 0);
@@ -567,7 +576,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     }
     for (int a = 0; a < FP8_ACCS; ++a) {
       mbar_init(&sm.tmem_full[a], 1);
-      mbar_init(&sm.tmem_empty[a], EPW);
+      mbar_init(&sm.tmem_empty[a], 16);  // sixteen 32 x 32 parts per accumulator half, one arrival each
     }
     mbar_init(&sm.b_full, 1);
     mbar_init(&sm.sfb_done, 1);
@@ -905,30 +914,52 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         res_inflight = true;
       }
     }
-    // SWQ_PIPE: the chunk whose Swish is done and whose encode is still pending (two register sets
-    // that alternate per chunk), its block scale(s) and where its codes / scale bytes go
-    uint64_t pz[2][SWQ_PIPE ? 16 : 1];
-    float pend_rcp0 = 0.0f, pend_rcp1 = 0.0f;
-    uint32_t pend_sb = 0;
-    bool pend_row_ok = false, pend_col_ok = false;
-    int64_t pend_row = 0, pend_col = 0;
-    auto pend_store = [&](const uint32_t (&w)[4]) {
-      if (!pend_col_ok) return;
-      if (pend_row_ok)
-        *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out) + pend_row * p.ldo + (pend_col >> 1)) = make_uint4(w[0], w[1], w[2], w[3]);
-      // rows of the last tile beyond M get zero scale factors (the SF atoms cover whole 128-row tiles)
-      const uint32_t sbw = pend_row_ok ? pend_sb : 0u;
-      const int64_t sf_row = (pend_row >> 7) * p.out_sf_kg * 512 + (pend_row & 31) * 16 + ((pend_row >> 5) & 3) * 4;
-      if constexpr (!kind_vec4(KIND)) {
-        p.out_sf[sf_row + (pend_col >> 7) * 512 + ((pend_col >> 5) & 3)] = static_cast<uint8_t>(sbw);
-        if (p.out_scales && pend_row_ok) p.out_scales[pend_row * (p.N >> 5) + (pend_col >> 5)] = static_cast<uint8_t>(sbw);
-      } else {
-        *reinterpret_cast<uint16_t*>(p.out_sf + sf_row + (pend_col >> 6) * 512 + ((pend_col >> 5) & 1) * 2) = static_cast<uint16_t>(sbw);
-        if (p.out_scales && pend_row_ok)
-          *reinterpret_cast<uint16_t*>(p.out_scales + pend_row * (p.N >> 4) + (pend_col >> 4)) = static_cast<uint16_t>(sbw);
+    if constexpr (SWQ_RR) {
+      // FFN up-projection, round robin: this quadrant's chunks n = 4 * tile + column group, this
+      // warp takes n = j, j + 7, j + 14, ...  Accumulator of tile t: t & 1, published for the
+      // (t >> 1)-th time; every chunk is read by exactly one warp, which arrives once.
+      const int j = ew >> 2;
+      const bool scale_acc = kind_vec4(KIND) && p.a_amax != nullptr;
+      int t_cur = 0;
+      for (int n = j; n < 4 * my_tiles && ok; n += EPW / 4) {
+        const int t = n >> 2, ccn = n & 3;
+        while (t_cur < t) { next_tile(mb, nb); ++t_cur; }
+        const uint32_t acc = t & 1;
+        if (tr) trace_rec(p, 2, t, 0);
+        if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[acc], (t >> 1) & 1, p.status, 4, abortp);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        tc_fence_after();
+        if (tr) trace_rec(p, 2, t, 1);
+        uint32_t r[32];
+        tc_ld_32x32b_x32(lane_addr + TM_ACC0 + acc * 128 + ccn * 32, r);
+        tc_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.tmem_empty[acc]);
+        if (tr) trace_rec(p, 2, t, 2);
+        const int64_t row = static_cast<int64_t>(mb) * BM + q * 32 + lane;
+        const bool row_ok = row < p.M;
+        const int64_t out_col0 = static_cast<int64_t>(nb) * BNT + ccn * 32;  // N % 128 == 0: the chunk is whole
+        uint32_t w[4];
+        const uint32_t sb = swish_quant_chunk<kind_vec4(KIND)>(r, p.bias ? p.bias + out_col0 : nullptr, scale_acc, g_ab, g_out, w);
+        if (row_ok)
+          *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out) + row * p.ldo + (out_col0 >> 1)) = make_uint4(w[0], w[1], w[2], w[3]);
+        // rows of the last tile beyond M get zero scale factors (the SF atoms cover whole 128-row tiles)
+        const uint32_t sbw = row_ok ? sb : 0u;
+        const int64_t sf_row = (row >> 7) * p.out_sf_kg * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4;
+        if constexpr (!kind_vec4(KIND)) {
+          p.out_sf[sf_row + (out_col0 >> 7) * 512 + ((out_col0 >> 5) & 3)] = static_cast<uint8_t>(sbw);
+          if (p.out_scales && row_ok) p.out_scales[row * (p.N >> 5) + (out_col0 >> 5)] = static_cast<uint8_t>(sbw);
+        } else {
+          *reinterpret_cast<uint16_t*>(p.out_sf + sf_row + (out_col0 >> 6) * 512 + ((out_col0 >> 5) & 1) * 2) = static_cast<uint16_t>(sbw);
+          if (p.out_scales && row_ok)
+            *reinterpret_cast<uint16_t*>(p.out_scales + row * (p.N >> 4) + (out_col0 >> 4)) = static_cast<uint16_t>(sbw);
+        }
+        if (tr) trace_rec(p, 2, t, 4);
       }
-    };
-    for (int it = 0; it < my_tiles && ok; ++it) {
+    }
+    for (int it = 0; it < (SWQ_RR ? 0 : my_tiles) && ok; ++it) {
       const int64_t row = static_cast<int64_t>(mb) * BM + q * 32 + lane;
       const bool row_ok = row < p.M;
       const bool rows_ok = static_cast<int64_t>(mb) * BM + q * 32 < p.M;
@@ -945,59 +976,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         __syncwarp();
         bias_nb = nb;
       }
-      if constexpr (SWQ_PIPE) {
-        // FFN up-projection on the wide tile, software-pipelined.  Swish is bound by the
-        // special-function unit (ex2 per value, rcp per four), the E2M1 encode by the ALU / FMA
-        // pipes, and the block scale between them needs all 32 values of a chunk: run one after
-        // the other, each phase leaves the other's pipes idle, and the four warps of a scheduler
-        // reach the same phase together (they all start when the accumulator is published).
-        // Here every group of eight new values goes through Swish next to the encode of eight
-        // values of the PREVIOUS chunk, whose scale is already known.
-        if (tr) trace_rec(p, 2, it, 0);
-        if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[0], group & 1, p.status, 4, abortp);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) break;
-        tc_fence_after();
-        if (tr) trace_rec(p, 2, it, 1);
-        ++group;
-        const bool scale_acc = kind_vec4(KIND) && p.a_amax != nullptr;
-        const uint64_t g2 = pack_f32x2(g_ab, g_ab);
-        const uint32_t acc_addr = lane_addr + TM_ACC0 + col_base;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint64_t (&zn)[16] = pz[h];      // chunk read now
-          uint64_t (&zo)[16] = pz[h ^ 1];  // pending: the previous tile's second chunk / this tile's first
-          uint32_t r[32];
-          tc_ld_32x32b_x32(acc_addr + h * 32, r);
-          tc_wait_ld();
-          if (h == 1) {  // the whole accumulator is out of tensor memory
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sm.tmem_empty[0]);
-          }
-          if (tr && h == 0) trace_rec(p, 2, it, 2);
-          uint32_t w[4];
-#pragma unroll
-          for (int g8 = 0; g8 < 4; ++g8) {
-            uint64_t o[4];
-            swish_group8<kind_vec4(KIND)>(r, g8, bias_base ? bias_base + h * 32 : nullptr, scale_acc, g2, o);
-            w[g8] = encode_group8<kind_vec4(KIND)>(zo, g8, pend_rcp0, pend_rcp1);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) zn[4 * g8 + j] = o[j];
-          }
-          pend_store(w);
-          // the chunk just finished becomes the pending one
-          pend_sb = chunk_scales_p<kind_vec4(KIND)>(zn, g_out, pend_rcp0, pend_rcp1);
-          pend_col = static_cast<int64_t>(nb) * BNT + col_base + h * 32;
-          pend_col_ok = pend_col < p.N;
-          pend_row = row;
-          pend_row_ok = row_ok;
-          if (tr && h == 0) trace_rec(p, 2, it, 4);
-        }
-        mb = mb_next;
-        nb = nb_next;
-        continue;
-      } else if constexpr (SWQ) {
+      if constexpr (SWQ) {
         // FFN up-projection: accumulator -> bias + Swish -> E2M1 codes + scale factors, one
         // 32-column chunk at a time (the second chunk of a wide tile is read from tensor memory
         // only after the first is finished, so that one chunk's registers are live at a time;
@@ -1418,14 +1397,6 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       }
       mb = mb_next;
       nb = nb_next;
-    }
-    if constexpr (SWQ_PIPE) {
-      if (my_tiles > 0 && ok) {  // encode the last pending chunk (the second chunk of the last tile)
-        uint32_t w[4];
-#pragma unroll
-        for (int g8 = 0; g8 < 4; ++g8) w[g8] = encode_group8<kind_vec4(KIND)>(pz[1], g8, pend_rcp0, pend_rcp1);
-        pend_store(w);
-      }
     }
     if (tma_store && lane == 0) tma_store_wait_all<0>();
     if (!ok) sm.abort_flag = 1;
@@ -1870,6 +1841,8 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
     const int64_t wide_tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
     bool narrow = stages <= 2 && epi != VX_EPI_BIAS_SWISH && epi != VX_EPI_BIAS_GLU &&
                   (epi == VX_EPI_BIAS_RESIDUAL || wide_tiles < 148);
+    // Swish + FP4 output (the FFN up-projection): the narrow tile runs that epilogue on 28 warps
+    if (epi == VX_EPI_BIAS_SWISH && d->out_dtype == VX_FP4 && stages <= RESIDENT_MAX_KSTAGES) narrow = true;
     if (d->flags & VX_GEMM_WIDE_TILES) narrow = false;
     if (argmax && d->lse_partials) narrow = false;  // the partials are laid out per 64-column group of the wide tile
     if ((d->flags & VX_GEMM_NARROW_TILES) && epi != VX_EPI_BIAS_GLU) narrow = true;

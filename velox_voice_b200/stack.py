@@ -196,11 +196,10 @@ class ConformerLinearStack:
 
     # ---- captured execution (launch-bound at small T; the reference keeps a CUDA-graph cache
     # for the same reason, torch_conformer.py:1055-1066)
-    def compile(self, frames: int, with_pos: bool = True, chunks: int = 1):
+    def compile(self, frames: int, with_pos: bool = True):
         """Capture one forward + per-frame argmax for ``frames`` rows into a CUDA graph with
-        static buffers.  Returns the :class:`CompiledStack`.  ``chunks`` > 1 runs the stack over
-        that many row ranges one after the other inside the graph (see :class:`CompiledStack`)."""
-        return CompiledStack(self, frames, with_pos, chunks)
+        static buffers.  Returns the :class:`CompiledStack`."""
+        return CompiledStack(self, frames, with_pos)
 
     def calibrate(self, x: torch.Tensor, pos: Optional[torch.Tensor] = None) -> Dict[str, float]:
         """One bf16 pass with plain torch ops recording max |.| of every tensor the NV16 path
@@ -265,21 +264,11 @@ class CompiledStack:
     :meth:`run` replays on the current stream, :meth:`encode_ctc_host` is the end-to-end call:
     pinned host features in, greedy CTC ids on the host out.
 
-    ``chunks``: frames are independent, so the graph may take the rows in ``chunks`` ranges
-    (cut at multiples of 128 rows), each through the whole stack before the next.  The tensors
-    that one kernel writes and the next one reads (residual stream, FP4 activations, q/k/v) then
-    shrink by that factor and stay in the 126 MB L2 between the two launches instead of making a
-    round trip through HBM; the price is ``chunks`` times the launches.  The reference itself
-    feeds its encoder spans of at most 3,750 encoder frames (``veloxvoice/api.py:416-433``).
     """
 
-    def __init__(self, stack: "ConformerLinearStack", frames: int, with_pos: bool = True, chunks: int = 1):
+    def __init__(self, stack: "ConformerLinearStack", frames: int, with_pos: bool = True):
         self.stack = stack
         self.frames = frames
-        chunks = max(1, min(int(chunks), max(1, frames // 128)))
-        per = -(-frames // chunks)
-        per = -(-per // 128) * 128
-        self.ranges = [(a, min(a + per, frames)) for a in range(0, frames, per)]
         cfg = stack.cfg
         dev = stack.device
         self.x_in = torch.zeros((frames, cfg.d_model), dtype=torch.bfloat16, device=dev)
@@ -301,10 +290,7 @@ class CompiledStack:
 
     def _body(self):
         self._x.copy_(self.x_in)
-        for a, b in self.ranges:
-            self.stack.forward_ids(self._x[a:b], None if self.pos is None else self.pos[a:b],
-                                   keys=self._keys[a:b], ids=self._ids[a:b])
-        self.ids = self._ids
+        self.ids = self.stack.forward_ids(self._x, self.pos, keys=self._keys, ids=self._ids)
 
     def run(self):
         self.graph.replay()
