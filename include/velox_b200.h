@@ -232,7 +232,8 @@ int vx_blkscale_gemm_noalloc(const void* pack_a, const void* pack_b, const void*
  * cycle counter at [role][tile][event]: role 0 = TMA producer (event k: slot for K stage k
  * acquired), 1 = MMA issuer (0 accumulator free, 1 + k stage k landed, 6 tile committed),
  * 2 = epilogue warp 0 (0 waiting, 1 accumulator ready, 2 TMEM read, 3 / 4 before / after the
- * epilogue math, 5 staged, 6 store issued).  NULL switches it off. */
+ * epilogue math, 5 staged, 6 store issued).  NULL switches it off.  The stamps are compiled in only
+ * when the library is built with -DVX_PHASE_TRACE=1; otherwise registering a buffer returns -4. */
 int vx_set_trace_buffer(void* device_buffer, int64_t bytes);
 
 /* Tensor-core peak probe: times `iters` back-to-back MMAs (no memory traffic) per SM.

@@ -78,7 +78,8 @@ __host__ __device__ constexpr bool kind_vec4(int kind) { return kind == KIND_FP4
 // scheduler), so 28 is the ceiling.
 //   16  every epilogue but one: warp (quadrant, column group) owns 32 rows x 64 columns of a wide
 //       tile (32 x 32 of a narrow one), the same part of every tile;
-//   28  Swish + FP4 output on the narrow tile (the FFN up-projection).  That epilogue is bound by
+//   28  Swish + FP4 output on the narrow tile (the FFN up-projection when the caller asks for
+//       narrow tiles; the wide tile is the default).  That epilogue is bound by
 //       the latency of its own arithmetic -- dependent multiply / ex2 / rcp chains, four warps
 //       per scheduler, all in the same phase because one barrier starts them -- so it runs on
 //       seven warps per scheduler which take the 32 x 32 chunks of the tile stream ROUND ROBIN
@@ -155,7 +156,6 @@ struct __align__(1024) SmemLayout {
   uint64_t sfb_done;   // sfb_resident: the scale-factor copies out of the borrowed ring slot are complete
   uint64_t res_full[2][16];  // residual block landed, per buffer and epilogue warp
   uint32_t tmem_base;
-  int abort_flag;
 };
 
 // sigmoid(g) = 1 / (1 + 2^(-g log2 e)) via ex2.approx + rcp.approx (relative error ~1e-6).  Alternatives measured and
@@ -477,6 +477,12 @@ __device__ __forceinline__ uint32_t store_chunk_fp4(const GemmParams& p, const i
 
 // Phase trace: SM cycle counter stamps of CTA 0's first 32 tiles, [role][tile][event].
 // roles: 0 producer, 1 MMA issuer, 2 epilogue warp 0.  Enabled by vx_set_trace_buffer().
+// Compiled in only with -DVX_PHASE_TRACE=1 (the stamps cost the epilogues a predicate and a branch per
+// phase; the shipped build leaves them out and vx_set_trace_buffer reports that).
+#ifndef VX_PHASE_TRACE
+#define VX_PHASE_TRACE 0
+#endif
+constexpr bool kPhaseTrace = VX_PHASE_TRACE != 0;
 constexpr int TRACE_TILES = 32, TRACE_EVENTS = 8;
 __device__ __forceinline__ void trace_rec(const GemmParams& p, int role, int tile, int ev) {
   if (p.trace && blockIdx.x == 0 && tile < TRACE_TILES)
@@ -515,7 +521,10 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   // Swish (+ FP4 re-quantization) epilogues are bound by their own arithmetic, not by the
   // MMA -> epilogue -> MMA hand-over: they read the second 32-column chunk only after the first
   // is finished (half the live registers), which releases tensor memory later at no cost.
-  constexpr bool SEQ = (EPI == VX_EPI_BIAS_SWISH) && NCH == 2;
+#ifndef VX_SEQ_ALL
+#define VX_SEQ_ALL 0
+#endif
+  constexpr bool SEQ = (EPI == VX_EPI_BIAS_SWISH || (VX_SEQ_ALL && EPI != VX_EPI_BIAS_ARGMAX && EPI != VX_EPI_BIAS_QKVPACK)) && NCH == 2;
   // Swish + FP4 output (the FFN up-projection): its own register-lean path, see swish_quant_chunk.
   constexpr bool SWQ = EPI == VX_EPI_BIAS_SWISH && OUT == 2;
   constexpr int EPW = epi_warps(KIND, EPI, OUT);   // epilogue warps
@@ -528,11 +537,14 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   const bool tma_residual = OUT == 1 ? EPI == VX_EPI_BIAS_RESIDUAL : (OUT == 2 ? false : p.tma_residual != 0);
   const bool sf_unit = OUT != 0 ? false : p.sf_unit != 0;
   const int out_fmt = OUT == 2 ? static_cast<int>(kind_vec4(KIND) ? VX_FMT_NV16 : VX_FMT_MX32) : p.out_fmt;
-  const bool tr_on = p.trace != nullptr && blockIdx.x == 0;  // phase trace requested (CTA 0 only)
+  const bool tr_on = kPhaseTrace && p.trace != nullptr && blockIdx.x == 0;  // phase trace requested (CTA 0 only)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  volatile int* const abortp = &sm.abort_flag;  // raised by the first role whose bounded wait expires
+  // (The waits below take no abort flag: a flag that the roles poll was built and measured -- the
+  // extra exits from every wait loop cost the 96-register epilogues spills, the fused-QKV kernel went
+  // from 65 to 83 us -- and it buys little: when the pipeline stalls, every role has been waiting
+  // since about the same moment, so their limits run out together, not one after the other.)
   const int nslots = p.num_slots;
   const bool resident = p.b_resident != 0;
   const bool with_sf = !(FP8 || sf_unit);
@@ -581,7 +593,6 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     mbar_init(&sm.b_full, 1);
     mbar_init(&sm.sfb_done, 1);
     for (int w = 0; w < 16; ++w) { mbar_init(&sm.res_full[0][w], 1); mbar_init(&sm.res_full[1][w], 1); }
-    sm.abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
@@ -662,9 +673,9 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         const uint8_t* sfa_row = p.sfa + (static_cast<int64_t>(mb) * p.sf_kg) * 512;
         const uint32_t slot_tx = TILE_BYTES + sf_atom_bytes + (resident ? 0u : b_tx(nb));
         for (int kg = 0; kg < k_groups; ++kg) {
-          if (!mbar_wait(&sm.empty[s], ph ^ 1, p.status, 1, abortp)) { ok = false; break; }
+          if (!mbar_wait(&sm.empty[s], ph ^ 1, p.status, 1)) { ok = false; break; }
           if (sfb_pending && s == static_cast<uint32_t>(nslots - 1)) {
-            if (!mbar_wait(&sm.sfb_done, 0, p.status, 7, abortp)) { ok = false; break; }
+            if (!mbar_wait(&sm.sfb_done, 0, p.status, 7)) { ok = false; break; }
             sfb_pending = false;
           }
           if (tr_on) trace_rec(p, 0, i, kg < 4 ? kg : 3);
@@ -680,7 +691,6 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         }
         next_tile(mb, nb);
       }
-      if (!ok) sm.abort_flag = 1;
     }
   } else if (warp == 1) {
     // =========================== MMA issuer ===========================
@@ -738,12 +748,12 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             CP(col0 + a * SFB_COLS + rt * 4, desc(b_lo + b_sf_lo + (rt * APS + a) * 32, sf_hi));
       };
       if (resident) {
-        if (!mbar_wait(&sm.b_full, 0, p.status, 5, abortp)) ok = false;
+        if (!mbar_wait(&sm.b_full, 0, p.status, 5)) ok = false;
         tc_fence_after();
         if (ok && with_sf)  // B's scale factors stay in tensor memory for the whole kernel
           for (int ks = 0; ks < p.k_stages; ++ks) cp_sfb(arena_lo + ks * bslot_lo, tm_sfb + ks * APS * SFB_COLS);
       } else if (sfb_res) {
-        if (!mbar_wait(&sm.b_full, 0, p.status, 5, abortp)) ok = false;
+        if (!mbar_wait(&sm.b_full, 0, p.status, 5)) ok = false;
         tc_fence_after();
         if (ok) {
           const uint32_t st_lo = (arena_u32 + (nslots - 1) * slot_bytes + a_slot) >> 4;
@@ -772,12 +782,12 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
               if ((u & 1) == 0) {
                 const int pr = u >> 1;
                 const uint32_t use = pr ? use1 : use0;
-                if (!mbar_wait_spin(&sm.tmem_empty[pr], (use & 1) ^ 1, p.status, 2, abortp)) { ok = false; break; }
+                if (!mbar_wait_spin(&sm.tmem_empty[pr], (use & 1) ^ 1, p.status, 2)) { ok = false; break; }
                 if (pr) ++use1; else ++use0;
                 tc_fence_after();  // orders the epilogue's tcgen05.ld of these buffers before the MMAs
               }
               if (in_group == 0) {
-                if (!mbar_wait_spin(&sm.full[s], ph, p.status, 3, abortp)) { ok = false; break; }
+                if (!mbar_wait_spin(&sm.full[s], ph, p.status, 3)) { ok = false; break; }
                 tc_fence_after();
               }
               if (kb0 == 0) TRACE(i, 2 * u);
@@ -805,11 +815,11 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             const uint32_t acc = WIDE ? 0u : (group & 1);
             if (kg == 0) {
               const uint32_t use = WIDE ? group : (group >> 1);
-              if (!mbar_wait_spin(&sm.tmem_empty[acc], (use & 1) ^ 1, p.status, 2, abortp)) { ok = false; break; }
+              if (!mbar_wait_spin(&sm.tmem_empty[acc], (use & 1) ^ 1, p.status, 2)) { ok = false; break; }
               tc_fence_after();  // orders the epilogue's tcgen05.ld of this buffer before the MMAs
               TRACE(i, 0);
             }
-            if (!mbar_wait_spin(&sm.full[s], ph, p.status, 3, abortp)) { ok = false; break; }
+            if (!mbar_wait_spin(&sm.full[s], ph, p.status, 3)) { ok = false; break; }
             TRACE(i, kg < 2 ? 1 + kg : 2);
             const uint32_t d_tmem = tmem_base + TM_ACC0 + acc * 128;
             const uint32_t a_lo0 = ring_lo + s * G * slot_lo;
@@ -856,7 +866,6 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
           }
         }
       }
-      if (!ok && leader) sm.abort_flag = 1;
     }
   } else {
     // =========================== epilogue ===========================
@@ -926,7 +935,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         while (t_cur < t) { next_tile(mb, nb); ++t_cur; }
         const uint32_t acc = t & 1;
         if (tr) trace_rec(p, 2, t, 0);
-        if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[acc], (t >> 1) & 1, p.status, 4, abortp);
+        if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[acc], (t >> 1) & 1, p.status, 4);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
         tc_fence_after();
@@ -984,7 +993,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         const uint32_t acc = WIDE ? 0u : (group & 1);
         const uint32_t acc_addr = lane_addr + TM_ACC0 + acc * 128 + col_base;
         if (tr) trace_rec(p, 2, it, 0);
-        if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[acc], (WIDE ? group : (group >> 1)) & 1, p.status, 4, abortp);
+        if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[acc], (WIDE ? group : (group >> 1)) & 1, p.status, 4);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
         tc_fence_after();
@@ -1056,7 +1065,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         for (int kb0 = 0; kb0 < kb_count && ok; kb0 += FP8_ACCS) {
           // one round: up to four K blocks, block u in accumulator u, published together
           const int nkb = kb_count - kb0 < FP8_ACCS ? kb_count - kb0 : FP8_ACCS;
-          if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[0], group & 1, p.status, 4, abortp);
+          if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[0], group & 1, p.status, 4);
           ok = __shfl_sync(0xffffffffu, ok, 0);
           if (!ok) break;
           ++group;
@@ -1117,7 +1126,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         // one polling lane per warp (512 polling threads would starve the MMA-issuing thread)
         const uint32_t acc = WIDE ? 0u : (group & 1);
         const uint32_t acc_addr = lane_addr + TM_ACC0 + acc * 128 + col_base;
-        if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[acc], (WIDE ? group : (group >> 1)) & 1, p.status, 4, abortp);
+        if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[acc], (WIDE ? group : (group >> 1)) & 1, p.status, 4);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
         tc_fence_after();
@@ -1198,7 +1207,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                 if (h + 1 < NCH) res_issue(res_chunk + 1, mb, out_col0 + 32);
                 else res_issue(res_chunk + 1, mb_next, static_cast<int64_t>(nb_next) * OUT_TILE_COLS + col_base);
               }
-              if (!mbar_wait(&sm.res_full[res_chunk & 1][ew], (res_chunk >> 1) & 1, p.status, 6, abortp)) { ok = false; break; }
+              if (!mbar_wait(&sm.res_full[res_chunk & 1][ew], (res_chunk >> 1) & 1, p.status, 6)) { ok = false; break; }
               res_smem = res_half;
             }
           }
@@ -1399,7 +1408,6 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       nb = nb_next;
     }
     if (tma_store && lane == 0) tma_store_wait_all<0>();
-    if (!ok) sm.abort_flag = 1;
   }
 
   // ---- tear-down
@@ -1841,8 +1849,10 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
     const int64_t wide_tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
     bool narrow = stages <= 2 && epi != VX_EPI_BIAS_SWISH && epi != VX_EPI_BIAS_GLU &&
                   (epi == VX_EPI_BIAS_RESIDUAL || wide_tiles < 148);
-    // Swish + FP4 output (the FFN up-projection): the narrow tile runs that epilogue on 28 warps
-    if (epi == VX_EPI_BIAS_SWISH && d->out_dtype == VX_FP4 && stages <= RESIDENT_MAX_KSTAGES) narrow = true;
+    // Swish + FP4 output (the FFN up-projection) stays on the wide tile: the narrow tile's
+    // 28-warp round-robin epilogue is faster per value, but its N = 128 MMAs read A from shared
+    // memory twice as often and that chain then bounds the tile (measured 144 vs 134 us at
+    // T = 90000); VX_GEMM_NARROW_TILES selects it.
     if (d->flags & VX_GEMM_WIDE_TILES) narrow = false;
     if (argmax && d->lse_partials) narrow = false;  // the partials are laid out per 64-column group of the wide tile
     if ((d->flags & VX_GEMM_NARROW_TILES) && epi != VX_EPI_BIAS_GLU) narrow = true;
@@ -2018,6 +2028,7 @@ int vx_glu_tile(int fmt) { return vx::kind_bn(fmt == VX_FMT_FP8_1X128 ? vx::KIND
 
 int vx_set_trace_buffer(void* device_buffer, int64_t bytes) {
   using namespace vx;
+  if (device_buffer && !kPhaseTrace) return fail(-4, "this build has no phase trace (compile with -DVX_PHASE_TRACE=1)");
   if (device_buffer && bytes < static_cast<int64_t>(3 * TRACE_TILES * TRACE_EVENTS * sizeof(unsigned long long)))
     return fail(-1, "trace buffer needs %d bytes", (int)(3 * TRACE_TILES * TRACE_EVENTS * sizeof(unsigned long long)));
   g_trace_buffer = static_cast<unsigned long long*>(device_buffer);
