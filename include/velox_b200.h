@@ -190,6 +190,21 @@ int64_t vx_ctc_lse_parts(int64_t N);
 int vx_ctc_finish(const void* keys, const void* lse_partials, int64_t N, int64_t M, int32_t* ids, float* max_out,
                   float* lse_out, float* logp_out, void* stream);
 
+/* Filterbank projection of the audio front-end in one pass: replaces power_mel_log
+ * (veloxvoice/kernels/ops/cuda_ops.py:95-135; kernel veloxvoice/kernels/csrc/dgx/dgx_power_mel_log.cu:20-79,
+ * dgx/block/nv_block_power_mel_log.h:35-190) and the formula of reference_power_mel_log (cuda_ops.py:195-202):
+ *   out[t, m] = (log(max(sum_f (re[t,f]^2 + im[t,f]^2) * mel[m, f], 2^-23)) - mean[m]) * istd[m]
+ * spec: complex64 [T, F] (interleaved re, im as torch.fft.rfft returns it; 8-byte aligned; row stride ld_spec
+ * complex elements), mel f32 [M, F] (row stride ld_mel), cmvn_mean / cmvn_istd f32 [M] or both NULL,
+ * out f32 [T, M] (row stride ldo).  The product runs on the tensor cores with tf32 operands (the low 13
+ * mantissa bits of power and mel are dropped) and fp32 accumulation -- the reference kernel's precision
+ * contract (tests/kernels/test_power_mel_log.py:1-16).  Any T >= 0; M <= 256 and the filterbank must fit in
+ * shared memory next to two input stages: vx_power_mel_log_supported(F, M) says whether it does (the
+ * reference falls back to cuBLAS above M = 80 or below T = 64, cuda_ops.py:110-134). */
+int vx_power_mel_log_supported(int64_t F, int64_t M);
+int vx_power_mel_log(const void* spec, int64_t T, int64_t F, int64_t ld_spec, const float* mel, int64_t M, int64_t ld_mel,
+                     const float* cmvn_mean, const float* cmvn_istd, float* out, int64_t ldo, void* stream);
+
 /* Attention fold pack in one pass: replaces velox_qkv_pack
  * (veloxvoice/kernels/csrc/velox_qkv_pack.cu:34-97; Python wrapper qkv_pack in
  * veloxvoice/kernels/ops/cuda_ops.py:554-581), i.e. the torch fold chain of

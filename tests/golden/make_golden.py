@@ -12,11 +12,15 @@ What runs, unmodified, from the reference tree:
 * ``veloxvoice/kernels/ops/cuda_ops.py``: ``_dequantize_to_bf16``;
 * ``veloxvoice/models/wenet/nvfp4_linear.py``: ``_encode_codes``, ``decode_codes``;
 * ``tests/kernels/test_dgx_mxfp4_gemm.py``: ``unpack`` and ``torch_matmul_ref`` (the
-  reference's definition of the FP4 GEMM result).
+  reference's definition of the FP4 GEMM result);
+* ``veloxvoice/kernels/ops/cuda_ops.py``: ``reference_power_mel_log`` and
+  ``tests/kernels/test_power_mel_log.py``: ``emulated_power_mel_log``, ``_tf32_rz`` (the fp32 formula
+  of the filterbank projection and the reference's restatement of its tensor-core kernel).
 
 The two reference modules create a lookup table with ``device="cuda"`` at import time; the
 only accommodation made here is to map that one ``torch.tensor(..., device="cuda")`` call to
-the CPU while the modules are imported.  No reference source is copied.
+the CPU while the modules are imported (and to answer the compute-capability query a skip mark
+of the mel test file makes at import).  No reference source is copied.
 
 Outputs (small ``.npz`` files next to this script) hold the seeded inputs and the bytes the
 reference produced for them.
@@ -45,6 +49,8 @@ def _import_reference(ref_root: str):
         return orig_tensor(*a, **k)
 
     torch.tensor = tensor_on_cpu
+    orig_cap = torch.cuda.get_device_capability
+    torch.cuda.get_device_capability = lambda *a, **k: (0, 0)  # a skip mark of the mel test file asks for it at import
     sys.path.insert(0, ref_root)
     try:
         tri = importlib.import_module("veloxvoice.kernels.ops.triton_ops")
@@ -55,9 +61,15 @@ def _import_reference(ref_root: str):
         )
         tg = importlib.util.module_from_spec(spec)
         spec.loader.exec_module(tg)
+        spec = importlib.util.spec_from_file_location(
+            "_ref_test_mel", os.path.join(ref_root, "tests/kernels/test_power_mel_log.py")
+        )
+        tm = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(tm)
     finally:
         torch.tensor = orig_tensor
-    return tri, cu, nv, tg
+        torch.cuda.get_device_capability = orig_cap
+    return tri, cu, nv, tg, tm
 
 
 def _edge_rows(K: int) -> torch.Tensor:
@@ -86,7 +98,9 @@ def main() -> None:
     ap.add_argument("--reference", required=True)
     ap.add_argument("--out", default=os.path.dirname(os.path.abspath(__file__)))
     args = ap.parse_args()
-    tri, cu, nv, tg = _import_reference(os.path.abspath(args.reference))
+    tri, cu, nv, tg, tm = _import_reference(os.path.abspath(args.reference))
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+    from oracle import mel as mel_oracle
 
     # ---------------- per-row quantizer (per_row_col_quantize) + _dequantize_to_bf16
     row = {}
@@ -157,6 +171,23 @@ def main() -> None:
         g[f"gemm{seed}_ws"] = ws.numpy()
         g[f"gemm{seed}_ref"] = ref.numpy()
     np.savez_compressed(os.path.join(args.out, "gemm_rowscale.npz"), **g)
+    # ---------------- filterbank projection: the reference's fp32 formula and its test's tf32 emulation
+    m = {}
+    for name, seed, (T, F, M), bank, cmvn in [("rand", 42, (40, 257, 80), "randn", True), ("tri", 5, (24, 201, 80), "triangles", False),
+                                              ("small", 3, (7, 64, 3), "randn", False)]:
+        torch.manual_seed(seed)
+        spec_t = torch.randn(T, F, dtype=torch.cfloat)
+        mel_t = torch.randn(M, F) if bank == "randn" else torch.from_numpy(mel_oracle.mel_filterbank(F, M, seed))
+        mean = torch.randn(M) if cmvn else None
+        istd = (torch.rand(M) + 0.5) if cmvn else None
+        m[f"{name}_spec"] = torch.view_as_real(spec_t).numpy()
+        m[f"{name}_mel"] = mel_t.numpy()
+        if cmvn:
+            m[f"{name}_mean"], m[f"{name}_istd"] = mean.numpy(), istd.numpy()
+        m[f"{name}_fp32"] = cu.reference_power_mel_log(spec_t.real, spec_t.imag, mel_t, mean, istd).numpy()
+        m[f"{name}_tf32"] = tm.emulated_power_mel_log(spec_t, mel_t, mean, istd).numpy()
+        m[f"{name}_rz_bits"] = tm._tf32_rz(mel_t).numpy()
+    np.savez_compressed(os.path.join(args.out, "mel.npz"), **m)
     print("golden vectors written to", args.out)
 
 

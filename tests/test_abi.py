@@ -73,6 +73,18 @@ def test_argument_errors_do_not_need_a_device(lib):
     assert lib.vx_quantize_pack(C.c_void_p(256), 1, 4, 64, 64, _lib.FMT_NV16, C.c_void_p(256), 32, None, None, None, None) == -1
     # empty problems are a no-op
     assert lib.vx_quantize_pack(None, 1, 0, 64, 64, 0, None, 32, None, None, None, None) == 0
+    # filterbank projection: shape limits, NULL operands, misaligned spectrum, one-sided CMVN
+    assert lib.vx_power_mel_log_supported(257, 80) == 1 and lib.vx_power_mel_log_supported(513, 80) == 1
+    assert lib.vx_power_mel_log_supported(257, 257) == 0 and lib.vx_power_mel_log_supported(4096, 256) == 0
+    mel_args = lambda **k: [k.get("spec", C.c_void_p(256)), k.get("T", 8), k.get("F", 64), k.get("ld", 64), k.get("mel", C.c_void_p(512)),
+                            k.get("M", 16), 64, k.get("mean", None), None, C.c_void_p(1024), k.get("ldo", 16), None]
+    assert lib.vx_power_mel_log(*mel_args(T=0)) == 0
+    assert lib.vx_power_mel_log(*mel_args(M=300, ldo=300)) == -1 and b"256" in lib.vx_last_error()
+    assert lib.vx_power_mel_log(*mel_args(spec=None)) == -1
+    assert lib.vx_power_mel_log(*mel_args(spec=C.c_void_p(260))) == -1 and b"aligned" in lib.vx_last_error()
+    assert lib.vx_power_mel_log(*mel_args(mean=C.c_void_p(2048))) == -1 and b"together" in lib.vx_last_error()
+    assert lib.vx_power_mel_log(*mel_args(ld=32)) == -1
+    assert lib.vx_power_mel_log(*mel_args(ldo=8)) == -1
 
 
 def _gemm_desc(lib, fmt=_lib.FMT_MX32, epi=_lib.EPI_NONE, flags=0):
@@ -183,7 +195,7 @@ def test_install_wires_reference_import_names():
     for name in ("CODE_LUT", "_encode_codes", "dequantize_w", "pack_codes", "quantize_w", "ue8m0_from_scale",
                  "ue8m0_to_float", "decode_codes", "quantize_and_gemm", "Nvfp4Linear", "nvfp4_gemm"):
         assert hasattr(nv, name), name  # what the reference's kernel test imports (tests/kernels/test_dgx_mxfp4_gemm.py:24-32)
-    for name in ("fused_qkv", "fused_qkv_wgmma", "pwlin_glu", "qkv_pack", "dgx_mxfp4_gemm"):
+    for name in ("fused_qkv", "fused_qkv_wgmma", "pwlin_glu", "qkv_pack", "dgx_mxfp4_gemm", "power_mel_log", "reference_power_mel_log"):
         assert name in install.OPS_PKG_NAMES
     for n in ("veloxvoice.kernels.ops.triton_ops", "veloxvoice.models.wenet.mxfp4_linear", "veloxvoice.models.wenet.nvfp4_linear"):
         del sys.modules[n]

@@ -13,6 +13,7 @@ import torch
 
 from oracle import formats as F
 from oracle import gemm as G
+from oracle import mel as ML
 
 
 def _cases(npz, suffix):
@@ -91,3 +92,38 @@ def test_gemm_definition_matches_reference(gemm):
         ref = G.gemm_rowscale_ref(xq, wq, xs, ws)
         # exact: E2M1 products are multiples of 0.25 and the partial sums fit 24 bits
         assert np.array_equal(ref, gemm[f"gemm{seed}_ref"]), seed
+
+
+@pytest.fixture(scope="module")
+def mel(golden_dir):
+    return np.load(os.path.join(golden_dir, "mel.npz"))
+
+
+def _mel_case(npz, name):
+    sp = npz[f"{name}_spec"]
+    spec = (sp[..., 0] + 1j * sp[..., 1]).astype(np.complex64)
+    mean = npz[f"{name}_mean"] if f"{name}_mean" in npz.files else None
+    istd = npz[f"{name}_istd"] if mean is not None else None
+    return spec, npz[f"{name}_mel"], mean, istd
+
+
+def test_filterbank_projection_matches_reference(mel):
+    """oracle/mel.py against outputs of the reference's fp32 formula (``reference_power_mel_log``) and
+    of its test's tf32 emulation (``emulated_power_mel_log``).  A non-negative filterbank has no
+    cancellation: fp32-grade agreement.  A random-sign filterbank is compared the way the reference's
+    own test compares (pre-log absolute error, 99.9th percentile of the log error on meaningful values,
+    tests/kernels/test_power_mel_log.py:90-116), with bounds 100x tighter than its kernel's."""
+    for name in _cases(mel, "_spec"):
+        spec, bank, mean, istd = _mel_case(mel, name)
+        assert np.array_equal(ML.tf32_rz(bank), mel[f"{name}_rz_bits"])
+        for kind, fn in (("fp32", ML.power_mel_log_fp32), ("tf32", ML.power_mel_log_tf32)):
+            ref, out = mel[f"{name}_{kind}"], fn(spec, bank, mean, istd)
+            assert out.shape == ref.shape and out.dtype == np.float32
+            if (bank >= 0).all():
+                assert np.abs(out - ref).max() < 2e-6, (name, kind)
+            else:
+                scale = 1.0 if istd is None else float(np.max(istd))
+                lin = np.abs(np.exp(out.astype(np.float64)) - np.exp(ref.astype(np.float64)))
+                ok = ref > -9.0
+                assert lin.max() < 3.5e-3 * max(1.0, float(np.exp(ref).max()) * 1e-3), (name, kind)
+                assert np.quantile(np.abs(out - ref)[ok], 0.999) < 5e-4 * scale, (name, kind)

@@ -251,3 +251,25 @@ def test_reference_fp4_filterbank_lane_through_install(installed):
     full = cu.reference_power_mel_log(spec.real, spec.imag, mel, mean, istd)
     nz = (mel.sum(1) > 0).cpu().numpy()
     assert np.median(np.abs(out.cpu().numpy() - full.cpu().numpy())[:, nz]) < 0.2
+
+
+def test_reference_filterbank_test_bodies_through_install(installed):
+    """tests/kernels/test_power_mel_log.py of the reference (class TestPowerMelLogBf16), imported with
+    ``power_mel_log`` / ``reference_power_mel_log`` replaced by this library's: its tf32-emulation
+    comparisons, CMVN, real filterbank vs fp32, tiny and odd frame counts, shape and finiteness."""
+    mod = _load_file("_velox_ref_test_power_mel_log", os.path.join(REF, "ref_tests", "test_power_mel_log.py"))
+    from velox_voice_b200 import ops
+
+    assert mod.power_mel_log is ops.power_mel_log and mod.reference_power_mel_log is ops.reference_power_mel_log
+    t = mod.TestPowerMelLogBf16()
+    before = ops.launch_count()
+    t.test_matches_tf32_truncation_emulation()
+    t.test_matches_emulation_various_sizes()
+    t.test_with_cmvn()
+    if mod._real_mel_fbank_available():
+        t.test_real_mel_fbank_matches_fp32()
+    t.test_tiny_input()
+    t.test_various_T_values()
+    t.test_output_shape()
+    t.test_numerical_stability()
+    assert ops.launch_count() > before  # the kernel ran, not only the fp32 lane

@@ -53,6 +53,8 @@ EXPORTS = (
     "vx_tmap_cache_stats",
     "vx_ctc_lse_parts",
     "vx_ctc_finish",
+    "vx_power_mel_log_supported",
+    "vx_power_mel_log",
 )
 
 
@@ -158,6 +160,10 @@ def load(build_if_missing: bool = True) -> C.CDLL:
         lib.vx_ctc_lse_parts.argtypes = [i64]
         lib.vx_ctc_finish.restype = i32
         lib.vx_ctc_finish.argtypes = [vp, vp, i64, i64, vp, vp, vp, vp, vp]
+        lib.vx_power_mel_log_supported.restype = i32
+        lib.vx_power_mel_log_supported.argtypes = [i64, i64]
+        lib.vx_power_mel_log.restype = i32
+        lib.vx_power_mel_log.argtypes = [vp, i64, i64, i64, vp, i64, i64, vp, vp, vp, i64, vp]
         lib.vx_set_trace_buffer.restype = i32
         lib.vx_set_trace_buffer.argtypes = [vp, i64]
         lib.vx_wait_selftest.restype = i32

@@ -518,13 +518,14 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   constexpr int SFB_COLS = 4 * NRT;          // TMEM columns of one K atom of B scale factors
   constexpr int NCH = (WIDE && !GLU) ? 2 : 1;  // 32-column chunks per epilogue warp
   constexpr int GATE_OFF = BNT / 2;          // GLU: gate columns follow the value columns
-  // Swish (+ FP4 re-quantization) epilogues are bound by their own arithmetic, not by the
-  // MMA -> epilogue -> MMA hand-over: they read the second 32-column chunk only after the first
-  // is finished (half the live registers), which releases tensor memory later at no cost.
-#ifndef VX_SEQ_ALL
-#define VX_SEQ_ALL 0
-#endif
-  constexpr bool SEQ = (EPI == VX_EPI_BIAS_SWISH || (VX_SEQ_ALL && EPI != VX_EPI_BIAS_ARGMAX && EPI != VX_EPI_BIAS_QKVPACK)) && NCH == 2;
+  // Chunk-sequential reads of the wide tile: the second 32-column chunk is read only after the
+  // first is finished.  That halves the live accumulator registers (the kernel is capped at 96
+  // per thread; with both chunks live the plain-bias epilogue spills, 75 vs 67 us for the fused
+  // QKV projection at T = 90000) and releases tensor memory a little later.  Swish epilogues
+  // are bound by their own arithmetic, so the later release costs them nothing; the residual
+  // epilogue is the one that loses by it (77 vs 79 us for the FFN down-projection) and keeps both
+  // chunks in flight.
+  constexpr bool SEQ = (EPI == VX_EPI_BIAS_SWISH || EPI == VX_EPI_BIAS || EPI == VX_EPI_NONE) && NCH == 2;
   // Swish + FP4 output (the FFN up-projection): its own register-lean path, see swish_quant_chunk.
   constexpr bool SWQ = EPI == VX_EPI_BIAS_SWISH && OUT == 2;
   constexpr int EPW = epi_warps(KIND, EPI, OUT);   // epilogue warps

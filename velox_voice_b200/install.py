@@ -16,6 +16,9 @@
 * ``veloxvoice.models.wenet.nvfp4_linear``: ``quantize_w``, ``Nvfp4Linear``, ``nvfp4_gemm``,
   ``quantize_and_gemm`` and the pure-torch helpers ``_encode_codes``, ``pack_codes``,
   ``decode_codes``, ``ue8m0_from_scale``, ``ue8m0_to_float``, ``CODE_LUT``;
+* ``power_mel_log`` / ``reference_power_mel_log`` (``cuda_ops.py:95-135,195-202``): the front-end's
+  filterbank projection on the tcgen05 tf32 kernel (the reference's is an ``mma.sync`` build for
+  sm_121a);
 * the bf16 operator names ``fused_qkv``, ``fused_qkv_wgmma``, ``pwlin_glu`` (the reference's
   builds of the last two are sm_90a sources, ``cuda_ops.py:363-401,480-539``) run quantize + one
   GEMM with the bias (+ GLU) in its epilogue and keep the ``Tensor | None`` convention.
@@ -39,7 +42,7 @@ _MXFP4_LINEAR = "veloxvoice.models.wenet.mxfp4_linear"
 _NVFP4_LINEAR = "veloxvoice.models.wenet.nvfp4_linear"
 
 GEMM_NAMES = ("dgx_mxfp4_gemm", "dgx_mxfp4_blkscale_gemm", "mxfp4_gemm", "nvfp4_linear", "_dequantize_to_bf16",
-              "qkv_pack", "fused_qkv", "fused_qkv_wgmma", "pwlin_glu")
+              "qkv_pack", "fused_qkv", "fused_qkv_wgmma", "pwlin_glu", "power_mel_log", "reference_power_mel_log")
 # names of veloxvoice.kernels.ops (the package re-exports these; the reference's own tests import them from there)
 OPS_PKG_NAMES = tuple(n for n in GEMM_NAMES if n != "_dequantize_to_bf16")
 QUANT_NAMES = ("per_row_col_quantize", "triton_quantize_w", "mxfp4_block_quantize", "mxfp4_dequant")

@@ -859,6 +859,66 @@ def quantize_and_gemm(x, wq, ws, P=1, C=8):
     return dgx_mxfp4_gemm(xq, wq, xs, ws, P, C)
 
 
+def reference_power_mel_log(re, im, mel, cmvn_mean, cmvn_istd):
+    """fp32 formula of the filterbank projection (``veloxvoice/kernels/ops/cuda_ops.py:195-202``),
+    on whatever device the inputs are; also what ``power_mel_log`` runs for shapes its kernel does
+    not take, as the reference does with cuBLAS (``cuda_ops.py:138-148``)."""
+    power = re.float() ** 2 + im.float() ** 2
+    feat = (power @ mel.T).clamp_min(1.1920929e-7).log()
+    if cmvn_mean is not None:
+        feat = (feat - cmvn_mean) * cmvn_istd
+    return feat
+
+
+def power_mel_log_tf32(spec, mel, cmvn_mean=None, cmvn_istd=None):
+    """Power spectrum -> mel GEMM -> log -> CMVN in one launch of ``vx_power_mel_log`` (tf32 operands on
+    the tensor cores, fp32 accumulation), for any number of frames.  spec complex64 [T, F]
+    (``torch.fft.rfft`` output), mel f32 [M, F], cmvn_mean / cmvn_istd f32 [M] or None -> f32 [T, M].
+    Raises when the filterbank does not fit the kernel (``vx_power_mel_log_supported``)."""
+    _require_cuda(spec, "spec")
+    _require_cuda(mel, "mel")
+    if spec.dim() != 2 or mel.dim() != 2 or spec.shape[1] != mel.shape[1]:
+        raise ValueError(f"shapes: spec [T, F], mel [M, F]; got {tuple(spec.shape)} and {tuple(mel.shape)}")
+    if not spec.is_complex():
+        raise TypeError("spec must be complex (torch.fft.rfft output)")
+    if (cmvn_mean is None) != (cmvn_istd is None):
+        raise ValueError("cmvn_mean and cmvn_istd go together")
+    if mel.device != spec.device:
+        raise ValueError(f"mel is on {mel.device}, spec on {spec.device}")
+    T, F = spec.shape
+    M = mel.shape[0]
+    lib = _lib.load()
+    if not lib.vx_power_mel_log_supported(F, M):
+        raise ValueError(f"a {M} x {F} filterbank does not fit the kernel (M <= 256, filterbank resident in shared memory)")
+    ri = torch.view_as_real(spec.to(torch.complex64).contiguous())  # f32 [T, F, 2], interleaved
+    melc = _rows2d(mel.float(), "mel")
+    mean = istd = None
+    if cmvn_mean is not None:
+        mean, istd = cmvn_mean.float().contiguous(), cmvn_istd.float().contiguous()
+        _check_vector(mean, "cmvn_mean", M, spec.device)
+        _check_vector(istd, "cmvn_istd", M, spec.device)
+    out = torch.empty((T, M), dtype=torch.float32, device=spec.device)
+    rc = lib.vx_power_mel_log(ri.data_ptr(), T, F, F, melc.data_ptr(), M, melc.stride(0), _ptr(mean), _ptr(istd),
+                              out.data_ptr(), M, _stream())
+    _lib.check(rc, "vx_power_mel_log")
+    _count()
+    return out
+
+
+def power_mel_log(spec, mel, cmvn_mean, cmvn_istd):
+    """Signature and dispatch of the reference's ``power_mel_log``
+    (``veloxvoice/kernels/ops/cuda_ops.py:95-135``): from 64 frames on, the tensor-core kernel
+    (``power_mel_log_tf32``; the reference's takes M <= 80, this one M <= 256); below 64 frames, or
+    for a filterbank the kernel does not take, the fp32 formula the reference runs through cuBLAS
+    (``cuda_ops.py:138-148``), so short inputs stay fp32-grade as its tests expect
+    (``tests/kernels/test_power_mel_log.py:80-88,180-203``)."""
+    _require_cuda(spec, "spec")
+    _require_cuda(mel, "mel")
+    if spec.dim() == 2 and mel.dim() == 2 and spec.shape[0] >= 64 and _lib.load().vx_power_mel_log_supported(spec.shape[1], mel.shape[0]):
+        return power_mel_log_tf32(spec, mel, cmvn_mean, cmvn_istd)
+    return reference_power_mel_log(spec.real, spec.imag, mel.float(), cmvn_mean, cmvn_istd)
+
+
 def fused_layernorm(x, w, b, eps=1e-5, out=None):
     """Row LayerNorm (``cuda_ops.py:204-210``)."""
     return layernorm(x, w, b, eps, out=out)
