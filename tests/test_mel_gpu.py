@@ -90,7 +90,7 @@ def test_floor_large_values_and_unsupported_shapes(ops):
     # silence: every bin zero -> log of the 2^-23 floor; loud input stays finite
     bank = ML.mel_filterbank(257, 80, 0)
     out = _run(ops, np.zeros((70, 257), np.complex64), bank)
-    assert np.array_equal(out, np.full((70, 80), np.log(np.float32(1.1920929e-7)), np.float32))
+    assert np.abs(out - np.log(np.float32(1.1920929e-7))).max() < 2e-6
     assert np.isfinite(_run(ops, _spec(128, 257, 3, scale=100.0), np.random.default_rng(3).standard_normal((80, 257)).astype(np.float32))).all()
     # the reference's dispatch: a filterbank the kernel does not take, or fewer than 64 frames, goes through the
     # fp32 formula (its cuBLAS lane); the kernel entry itself refuses the filterbank

@@ -10,7 +10,8 @@
 //
 //   warps 0..3    epilogue: tcgen05.ld of the fp32 accumulator (one frame per thread), log, CMVN, store;
 //   warps 4..11   loaders: read the spectrum with coalesced 8-byte loads (one complex bin per lane, sixteen
-//                 rows in flight per warp), form re^2 + im^2 and write it straight into the 128-byte-swizzled
+//                 rows per stage, the loads of the next stage in flight while the current one is
+//                 processed), form re^2 + im^2 and write it straight into the 128-byte-swizzled
 //                 K-major tile layout the MMA reads -- the power spectrum never exists in global memory;
 //   warp 12       MMA issuer: four K = 8 MMAs per 32-bin stage, tcgen05.commit hands ring slots back and
 //                 publishes finished accumulators (two of them, so the epilogue of frame tile i runs under the
@@ -134,32 +135,47 @@ __global__ void __launch_bounds__(MEL_THREADS, 1) power_mel_log_kernel(const Mel
 
   if (warp >= 4 && warp < 4 + MEL_LOADERS) {
     // =========================== loaders ===========================
+    // The (tile, stage) items of this CTA form one sequence; the sixteen loads of item n + 1 are in
+    // flight while item n is squared and written to its ring slot.
     const int lw = warp - 4;
+    const int64_t items = static_cast<int64_t>(my_tiles) * p.stages;
+    auto fetch = [&](int64_t n, float2 (&c)[16]) {
+      const int64_t tile = static_cast<int64_t>(blockIdx.x) + (n / p.stages) * gridDim.x;
+      const int64_t row0 = tile * MEL_BM + lw * 16;
+      const int64_t f = (n % p.stages) * MEL_KS + lane;
+#pragma unroll
+      for (int r = 0; r < 16; ++r) {
+        const int64_t row = row0 + r;
+        c[r] = (n < items && row < p.T && f < p.F) ? __ldg(p.spec + row * p.ld_spec + f) : make_float2(0.0f, 0.0f);
+      }
+    };
+    auto publish = [&](uint32_t s, const float2 (&c)[16]) {
+      uint8_t* const slot = ring + s * MEL_SLOT;
+#pragma unroll
+      for (int r = 0; r < 16; ++r)  // two rounded squares and one rounded add, as spec.real**2 + spec.imag**2
+        *reinterpret_cast<float*>(slot + sw128(lw * 16 + r, lane)) = __fadd_rn(__fmul_rn(c[r].x, c[r].x), __fmul_rn(c[r].y, c[r].y));
+      fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's reads
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar.full[s]);
+    };
     uint32_t s = 0, ph = 0;
     bool ok = true;
-    for (int i = 0; i < my_tiles && ok; ++i) {
-      const int64_t row0 = (static_cast<int64_t>(blockIdx.x) + static_cast<int64_t>(i) * gridDim.x) * MEL_BM + lw * 16;
-      for (int ks = 0; ks < p.stages && ok; ++ks) {
-        // sixteen rows x one bin per lane: all sixteen loads are issued before the first is used
-        const int64_t f = static_cast<int64_t>(ks) * MEL_KS + lane;
-        float2 c[16];
-#pragma unroll
-        for (int r = 0; r < 16; ++r) {
-          const int64_t row = row0 + r;
-          c[r] = (row < p.T && f < p.F) ? __ldg(p.spec + row * p.ld_spec + f) : make_float2(0.0f, 0.0f);
-        }
-        if (lane == 0) ok = mbar_wait(&bar.empty[s], ph ^ 1, p.status, 11, abortp);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) break;
-        uint8_t* const slot = ring + s * MEL_SLOT;
-#pragma unroll
-        for (int r = 0; r < 16; ++r)
-          *reinterpret_cast<float*>(slot + sw128(lw * 16 + r, lane)) = __fadd_rn(__fmul_rn(c[r].x, c[r].x), __fmul_rn(c[r].y, c[r].y));  // two rounded squares, as spec.real**2 + spec.imag**2
-        fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's reads
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bar.full[s]);
-        if (++s == static_cast<uint32_t>(p.ring)) { s = 0; ph ^= 1; }
-      }
+    float2 ca[16], cb[16];
+    fetch(0, ca);
+    for (int64_t n = 0; n < items && ok; n += 2) {
+      fetch(n + 1, cb);
+      if (lane == 0) ok = mbar_wait(&bar.empty[s], ph ^ 1, p.status, 11, abortp);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      publish(s, ca);
+      if (++s == static_cast<uint32_t>(p.ring)) { s = 0; ph ^= 1; }
+      if (n + 1 >= items) break;
+      fetch(n + 2, ca);
+      if (lane == 0) ok = mbar_wait(&bar.empty[s], ph ^ 1, p.status, 11, abortp);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      publish(s, cb);
+      if (++s == static_cast<uint32_t>(p.ring)) { s = 0; ph ^= 1; }
     }
     if (!ok) bar.abort_flag = 1;
   } else if (warp == 4 + MEL_LOADERS) {
