@@ -150,34 +150,61 @@ def rsqrt32(x) -> np.ndarray:
     return (np.longdouble(1.0) / np.sqrt(x)).astype(np.float32)
 
 
-def layernorm_ref(x, gamma, beta, eps: float = 1e-5) -> np.ndarray:
-    """Row LayerNorm with the fused CUDA kernel's exact fp32 operation order.
+def ln_half_rows(K: int, bf16_input: bool, fmt=None) -> bool:
+    """Which of the library's two LayerNorm summation orders a call uses: bf16 rows of exactly 512
+    elements that are quantized to an SF-atom FP4 format or FP8 (or not quantized at all) go through
+    the half-warp-per-row kernel (``rows2_kernel`` in ``csrc/vx_quant.cu``); everything else through
+    the warp-per-row kernels."""
+    return bool(bf16_input) and K == 512 and fmt in (None, F.FMT_MX32, F.FMT_NV16, F.FMT_FP8_1X128)
+
+
+def layernorm_ref(x, gamma, beta, eps: float = 1e-5, half_rows: bool = False) -> np.ndarray:
+    """Row LayerNorm with the fused CUDA kernels' exact fp32 operation order.
 
     Formula of ``velox_layernorm.cu:52-57`` (``var = E[x^2] - mean^2`` clamped at 0), evaluated
-    with fused multiply-adds in this library's order: lane ``l`` of 32 owns, chunk by chunk of
-    256 elements, the eight consecutive elements ``[256 c + 8 l, +8)`` and keeps separate sums
-    for its even and its odd elements (``S += v``, ``Q = fma(v, v, Q)``); the two are added, lanes
-    are combined by a butterfly (xor 16, 8, 4, 2, 1); ``mean = s / K``, ``ex2 = q / K``,
-    ``var = max(fma(-mean, mean, ex2), 0)``, ``rstd = 1 / sqrt(var + eps)`` correctly rounded in
-    one step, ``y = fma(fma(x, rstd, -mean * rstd), gamma, beta)``.
+    with fused multiply-adds in this library's order.  Warp-per-row kernels (``half_rows=False``):
+    lane ``l`` of 32 owns, chunk by chunk of 256 elements, the eight consecutive elements
+    ``[256 c + 8 l, +8)`` and keeps separate sums for its even and its odd elements (``S += v``,
+    ``Q = fma(v, v, Q)``); the two are added, lanes are combined by a butterfly (xor 16, 8, 4, 2, 1).
+    Half-warp-per-row kernel (``half_rows=True``, K = 512, see ``ln_half_rows``): lane ``j`` of 16 owns
+    elements ``[32 j, +32)`` as four pieces of eight, accumulated in the rotated order it reads them
+    (piece ``(c + (j >> 1)) & 3`` at step ``c``), butterfly xor 8, 4, 2, 1.  Then for both:
+    ``mean = s / K``, ``ex2 = q / K``, ``var = max(fma(-mean, mean, ex2), 0)``,
+    ``rstd = 1 / sqrt(var + eps)`` correctly rounded in one step,
+    ``y = fma(fma(x, rstd, -mean * rstd), gamma, beta)``.
     """
     x = F._f32(x)
     M, K = x.shape
-    ch = -(-K // 256)
-    xp = np.zeros((M, ch * 256), dtype=np.float32)
-    xp[:, :K] = x
-    xl = xp.reshape(M, ch, 32, 4, 2)  # [row, chunk, lane, pair, even/odd]
-    s = np.zeros((M, 32, 2), dtype=np.float32)
-    sq = np.zeros((M, 32, 2), dtype=np.float32)
-    for c in range(ch):
-        for j in range(4):
-            v = xl[:, c, :, j, :]
-            s = (s + v).astype(np.float32)
-            sq = fma32(v, v, sq)
+    if half_rows:
+        assert K == 512
+        xl = x.reshape(M, 16, 4, 4, 2)  # [row, lane, piece, pair, even/odd]
+        lanes = np.arange(16)
+        s = np.zeros((M, 16, 2), dtype=np.float32)
+        sq = np.zeros((M, 16, 2), dtype=np.float32)
+        for c in range(4):
+            piece = (c + (lanes >> 1)) & 3
+            for j in range(4):
+                v = xl[:, lanes, piece, j, :]
+                s = (s + v).astype(np.float32)
+                sq = fma32(v, v, sq)
+        rounds = (8, 4, 2, 1)
+    else:
+        ch = -(-K // 256)
+        xp = np.zeros((M, ch * 256), dtype=np.float32)
+        xp[:, :K] = x
+        xl = xp.reshape(M, ch, 32, 4, 2)  # [row, chunk, lane, pair, even/odd]
+        lanes = np.arange(32)
+        s = np.zeros((M, 32, 2), dtype=np.float32)
+        sq = np.zeros((M, 32, 2), dtype=np.float32)
+        for c in range(ch):
+            for j in range(4):
+                v = xl[:, c, :, j, :]
+                s = (s + v).astype(np.float32)
+                sq = fma32(v, v, sq)
+        rounds = (16, 8, 4, 2, 1)
     s = (s[:, :, 0] + s[:, :, 1]).astype(np.float32)
     sq = (sq[:, :, 0] + sq[:, :, 1]).astype(np.float32)
-    lanes = np.arange(32)
-    for o in (16, 8, 4, 2, 1):
+    for o in rounds:
         s = (s + s[:, lanes ^ o]).astype(np.float32)
         sq = (sq + sq[:, lanes ^ o]).astype(np.float32)
     kf = F32(K)

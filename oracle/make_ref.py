@@ -12,7 +12,8 @@ this repository.  The copy exists so that, on a machine that has no checkout of 
 
     python oracle/make_ref.py [path to a checkout of the reference]
 
-The source tree is only read.  Re-running replaces the copy.
+The source tree is only read.  Re-running replaces the copy.  Only Python files are copied: the
+reference's kernel sources stay where they are.
 """
 
 from __future__ import annotations
@@ -48,7 +49,9 @@ def make(src: str = DEFAULT_SRC, quiet: bool = False) -> bool:
     for rel_src, rel_dst in WANTED:
         s, d = os.path.join(src, rel_src), os.path.join(tmp, rel_dst)
         if os.path.isdir(s):
-            shutil.copytree(s, d, ignore=shutil.ignore_patterns("__pycache__", "*.pyc"))
+            # Python only: the reference's CUDA / C++ kernel sources (veloxvoice/kernels/csrc) are never
+            # compiled or run by anything here -- its operators are replaced before they would be built
+            shutil.copytree(s, d, ignore=shutil.ignore_patterns("__pycache__", "*.pyc", "csrc", "*.cu", "*.cuh", "*.h", "*.cpp"))
         elif os.path.isfile(s):
             os.makedirs(os.path.dirname(d), exist_ok=True)
             shutil.copy2(s, d)

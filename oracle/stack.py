@@ -70,7 +70,9 @@ class OracleStack:
         return y.astype(np.float32)
 
     def _ln(self, x: np.ndarray, key: str) -> np.ndarray:
-        return G.layernorm_ref(x, self.w[key + ".g"], self.w[key + ".b"], self.eps)
+        # the stack's activations are bf16 tensors: rows of 512 go through the half-warp-per-row kernel
+        half = G.ln_half_rows(x.shape[1], True, self.fmt)
+        return G.layernorm_ref(x, self.w[key + ".g"], self.w[key + ".b"], self.eps, half_rows=half)
 
     def _ffn(self, x: np.ndarray, b: str, ff: str, ln: str) -> np.ndarray:
         a = self._act(self._ln(x, b + ln), b + ln)

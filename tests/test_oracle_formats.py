@@ -106,6 +106,11 @@ def test_layernorm_ref_close_to_torch():
     y = G.layernorm_ref(x, g, b, 1e-5)
     t = torch.nn.functional.layer_norm(torch.from_numpy(x), (512,), torch.from_numpy(g), torch.from_numpy(b), 1e-5).numpy()
     assert np.abs(y - t).max() < 1e-4  # the reference's own LayerNorm tolerance
+    # the half-warp-per-row order of the 512-element bf16 lanes: same formula, other summation tree
+    yh = G.layernorm_ref(x, g, b, 1e-5, half_rows=True)
+    assert np.abs(yh - t).max() < 1e-4 and np.abs(yh - y).max() < 1e-5
+    assert G.ln_half_rows(512, True, F.FMT_MX32) and G.ln_half_rows(512, True) and not G.ln_half_rows(512, False, F.FMT_MX32)
+    assert not G.ln_half_rows(1024, True, F.FMT_MX32) and not G.ln_half_rows(512, True, F.FMT_ROWSCALE)
 
 
 def test_glu_interleave_is_a_permutation():

@@ -178,7 +178,8 @@ def test_layernorm_fused_quantize_bit_exact(ops, fmt, dtype, K):
     am = torch.tensor([9.0], device="cuda") if fmt == F.FMT_NV16 else None
     q, y = ops.ln_quantize(x, g, b, 1e-5, fmt, natural=True, amax_t=am, y_dtype=torch.float32)
     torch.cuda.synchronize()
-    yo = G.layernorm_ref(x.float().cpu().numpy(), g.cpu().numpy(), b.cpu().numpy(), 1e-5)
+    half = G.ln_half_rows(K, dtype == torch.bfloat16, fmt)
+    yo = G.layernorm_ref(x.float().cpu().numpy(), g.cpu().numpy(), b.cpu().numpy(), 1e-5, half_rows=half)
     assert np.array_equal(y.cpu().numpy(), yo), "fused LayerNorm differs from its CPU restatement"
     oq, os_, _ = F.quantize(yo, fmt, **({"amax_t": 9.0} if fmt == F.FMT_NV16 else {}))
     assert np.array_equal(q.codes.cpu().numpy(), oq)
@@ -194,15 +195,55 @@ def test_layernorm_only_and_bf16_output(ops):
     g = torch.rand(512, device="cuda") + 0.5
     b = torch.randn(512, device="cuda")
     y = ops.layernorm(x, g, b, 1e-5)
-    yo = G.layernorm_ref(x.float().cpu().numpy(), g.cpu().numpy(), b.cpu().numpy(), 1e-5)
+    yo = G.layernorm_ref(x.float().cpu().numpy(), g.cpu().numpy(), b.cpu().numpy(), 1e-5, half_rows=G.ln_half_rows(512, True))
     assert y.dtype == torch.bfloat16
     assert np.array_equal(y.float().cpu().numpy(), G.to_bf16(yo))
-    y32 = ops.fused_layernorm(x.float(), g, b)
-    assert np.array_equal(y32.cpu().numpy(), yo)
+    y32 = ops.fused_layernorm(x.float(), g, b)  # fp32 rows: the warp-per-row order
+    assert np.array_equal(y32.cpu().numpy(), G.layernorm_ref(x.float().cpu().numpy(), g.cpu().numpy(), b.cpu().numpy(), 1e-5))
     # in place
     x2 = x.clone()
     ops.layernorm(x2, g, b, 1e-5, out=x2)
     assert torch.equal(x2, y)
+
+
+@pytest.mark.parametrize("fmt", [F.FMT_MX32, F.FMT_NV16, F.FMT_FP8_1X128])
+@pytest.mark.parametrize("M", [1, 2, 129, 4097])
+def test_half_warp_per_row_lanes(ops, fmt, M):
+    """bf16 rows of 512 elements (the activation shape of the encoder): two rows per warp.  Odd row
+    counts leave the second half of the last warp without a row; every combination of outputs -- SF
+    atoms, natural scales, y in bf16 / fp32 / in place, one or two LayerNorms -- gives the oracle's bytes."""
+    torch.manual_seed(M + fmt)
+    K = 512
+    x = (torch.randn(M, K, device="cuda") * 2 - 0.3).bfloat16()
+    x[0, :32] = 0  # an all-zero block
+    g1, b1 = torch.rand(K, device="cuda") + 0.5, torch.randn(K, device="cuda") * 0.2
+    g2, b2 = torch.rand(K, device="cuda") + 0.5, torch.randn(K, device="cuda") * 0.2
+    am = torch.tensor([9.0], device="cuda") if fmt == F.FMT_NV16 else None
+    kw = {"amax_t": 9.0} if fmt == F.FMT_NV16 else {}
+    xn = x.float().cpu().numpy()
+    # plain quantize: natural scales, and the SF atoms agree with the relayout of the natural ones
+    q = ops.quantize(x, fmt, natural=True, amax_t=am)
+    oq, os_, _ = F.quantize(xn, fmt, **kw)
+    assert np.array_equal(q.codes.cpu().numpy(), oq) and np.array_equal(q.scales.cpu().numpy(), os_)
+    if fmt != F.FMT_FP8_1X128:
+        q_sf = ops.quantize(x, fmt, natural=False, amax_t=am)
+        assert torch.equal(q_sf.codes, q.codes)
+        assert torch.equal(q_sf.sf, ops.sf_from_natural(fmt, q.scales, M, K))
+    # LayerNorm + quantize, y in fp32 and in bf16
+    y1 = G.layernorm_ref(xn, g1.cpu().numpy(), b1.cpu().numpy(), 1e-5, half_rows=True)
+    ql, y = ops.ln_quantize(x, g1, b1, 1e-5, fmt, natural=True, amax_t=am, y_dtype=torch.float32)
+    assert np.array_equal(y.cpu().numpy(), y1)
+    oq, os_, _ = F.quantize(y1, fmt, **kw)
+    assert np.array_equal(ql.codes.cpu().numpy(), oq) and np.array_equal(ql.scales.cpu().numpy(), os_)
+    yb = ops.layernorm(x, g1, b1, 1e-5)
+    assert np.array_equal(yb.float().cpu().numpy(), G.to_bf16(y1))
+    # two LayerNorms, the first stored in place
+    xin = x.clone()
+    q2 = ops.ln2_quantize(xin, g1, b1, g2, b2, 1e-5, fmt, y=xin, natural=True, amax_t=am)
+    assert np.array_equal(xin.float().cpu().numpy(), G.to_bf16(y1))
+    y2 = G.layernorm_ref(G.to_bf16(y1), g2.cpu().numpy(), b2.cpu().numpy(), 1e-5, half_rows=True)
+    oq, os_, _ = F.quantize(y2, fmt, **kw)
+    assert np.array_equal(q2.codes.cpu().numpy(), oq) and np.array_equal(q2.scales.cpu().numpy(), os_)
 
 
 @pytest.mark.parametrize("fmt", [F.FMT_MX32, F.FMT_FP8_1X128, F.FMT_NV16])

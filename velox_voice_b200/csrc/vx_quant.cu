@@ -564,6 +564,271 @@ __global__ void __launch_bounds__(256, lnq_min_blocks(CH)) ln_quant_kernel(const
   zero_pad_rows<I>(p, u_first, warps, lane);
 }
 
+// ---------------------------------------------------------------------------------------------
+// The hot shape -- bf16 rows of exactly 512 elements, SF-atom formats / FP8 -- on HALF a warp per
+// row: lane j of a half owns elements [32 j, 32 j + 32), a whole MX32 block (two NV16 blocks, a
+// quarter of an FP8 block).  Against the warp-per-row kernels above that halves what a row costs
+// in instructions: the per-row work (statistics butterfly, rsqrt, loop and ring handling) is shared
+// by two rows per warp instruction, a block maximum needs no shuffle, and a scale is computed once
+// per 32 elements instead of once per 8 by each of four lanes.
+//
+// Rows arrive through the per-warp bulk-copy ring (two rows per slot).  A lane reads its 64 bytes
+// as four 16-byte pieces in ROTATED order -- step c reads piece (c + rot) & 3, rot = (j >> 1) & 3 --
+// so that the eight lanes of a shared-memory phase touch eight different 16-byte columns (lanes
+// 64 bytes apart would otherwise collide four ways).  Codes are rotated back in registers and
+// leave as one 16-byte store per lane; y leaves piece by piece.
+//
+// LayerNorm arithmetic: as in ln_quant_kernel, with the lane's 32 values accumulated in the order
+// they are read (steps c = 0..3, pairs 0..3 of each piece, packed even | odd) and the butterfly
+// over the 16 lanes of the half (xor 8, 4, 2, 1).
+#ifndef VX_R2_RING
+#define VX_R2_RING 2
+#endif
+#ifndef VX_R2_MIN_BLOCKS
+#define VX_R2_MIN_BLOCKS 4
+#endif
+#ifndef VX_R2_MIN_BLOCKS_LN
+#define VX_R2_MIN_BLOCKS_LN 3  // 85 registers per thread: the LayerNorm lanes spill at 64
+#endif
+constexpr int kR2SlotBytes = 2048;  // two bf16 rows of 512 elements
+
+template <int FMT, bool LN>
+__global__ void __launch_bounds__(256, LN ? VX_R2_MIN_BLOCKS_LN : VX_R2_MIN_BLOCKS) rows2_kernel(const QuantParams p) {
+  static_assert(FMT == VX_FMT_MX32 || FMT == VX_FMT_NV16 || FMT == VX_FMT_FP8_1X128, "SF-atom FP4 formats and FP8");
+  constexpr bool CANON = !LN;            // see quant_chunk
+  constexpr bool NUDGE = LN;             // plain bf16 values with a power-of-two scale need no tie nudge
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int h = lane >> 4, j = lane & 15, rot = (j >> 1) & 3;
+  const int M = static_cast<int>(p.M);
+  const int warps = static_cast<int>(gridDim.x) * 8;
+  const int nunits = (M + 1) >> 1;
+  const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(p.x);
+  const int ldx = static_cast<int>(p.ldx), ldc = static_cast<int>(p.ldc), ldy = static_cast<int>(p.ldy);
+  const int npass = LN ? (p.gamma2 ? 2 : 1) : 0;
+  float g = 1.0f;
+  if constexpr (FMT == VX_FMT_NV16) g = nv16_global(__ldg(p.amax));
+
+  __shared__ __align__(128) uint8_t ring_s[8 * VX_R2_RING * kR2SlotBytes];
+  __shared__ uint64_t full_s[8 * VX_R2_RING];
+  // [pass][gamma | beta][step c * 2 + half of the piece][lane of the half]: the eight values lane j
+  // needs at step c, i.e. those of piece (c + rot_j) & 3 of its block
+  __shared__ float4 gb_s[LN ? 2 : 1][2][8][16];
+  if constexpr (LN) {
+    for (int i = threadIdx.x; i < npass * 2 * 8 * 16; i += blockDim.x) {
+      const int l = i & 15, piece = (i >> 4) & 7, which = i >> 7;  // which = pass * 2 + (0 gamma, 1 beta)
+      const float* src = which == 0 ? p.gamma : (which == 1 ? p.beta : (which == 2 ? p.gamma2 : p.beta2));
+      const int k0 = l * 32 + ((((piece >> 1) + (l >> 1)) & 3) << 3) + (piece & 1) * 4;
+      gb_s[which >> 1][which & 1][piece][l] = __ldg(reinterpret_cast<const float4*>(src + k0));
+    }
+  }
+  uint8_t* const ring_w = ring_s + w * VX_R2_RING * kR2SlotBytes;
+  uint64_t* const full_w = full_s + w * VX_R2_RING;
+  if (lane == 0) {
+#pragma unroll
+    for (int d = 0; d < VX_R2_RING; ++d) mbar_init(&full_w[d], 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  auto issue = [&](int slot, int u) {
+    if (lane == 0) {
+      const int r0 = 2 * u;
+      const bool two = r0 + 1 < M;
+      mbar_expect_tx(&full_w[slot], two ? 2048u : 1024u);
+      bulk_load(ring_w + slot * kR2SlotBytes, x + static_cast<int64_t>(r0) * ldx, 1024u, &full_w[slot]);
+      if (two) bulk_load(ring_w + slot * kR2SlotBytes + 1024, x + static_cast<int64_t>(r0 + 1) * ldx, 1024u, &full_w[slot]);
+    }
+  };
+  const int u_first = static_cast<int>(blockIdx.x) * 8 + w;
+#pragma unroll
+  for (int d = 0; d < VX_R2_RING; ++d)
+    if (u_first + d * warps < nunits) issue(d, u_first + d * warps);
+  int poff[4];  // byte offset of the piece read at step c within the lane's 64 bytes
+#pragma unroll
+  for (int c = 0; c < 4; ++c) poff[c] = ((c + rot) & 3) << 4;
+  int slot = 0;
+  uint32_t par = 0;
+#pragma unroll 1
+  for (int u = u_first; u < nunits; u += warps) {
+    if (!mbar_wait(&full_w[slot], par, p.status, 8)) break;
+    const int row = 2 * u + h;
+    const bool valid = row < M;
+    uint64_t v[4][4];
+    {
+      // (a half without a row -- the last unit of an odd M -- works on the other half's row and stores nothing)
+      const uint8_t* src = ring_w + slot * kR2SlotBytes + (valid ? h : 0) * 1024 + j * 64;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        Raw8<__nv_bfloat16> raw;
+        raw.u = *reinterpret_cast<const uint4*>(src + poff[c]);
+        raw.get(v[c]);
+      }
+    }
+    __syncwarp();  // every lane has read the slot: hand it back
+    if (u + VX_R2_RING * warps < nunits) issue(slot, u + VX_R2_RING * warps);
+    if (++slot == VX_R2_RING) { slot = 0; par ^= 1; }
+
+    if constexpr (LN) {
+#pragma unroll 1
+      for (int pass = 0; pass < npass; ++pass) {
+        uint64_t S = pack_f32x2(0.0f, 0.0f), Q = S;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            S = add_f32x2(S, v[c][i]);
+            Q = fma_f32x2(v[c][i], v[c][i], Q);
+          }
+        }
+        float s0, s1, q0, q1;
+        unpack_f32x2(S, s0, s1);
+        unpack_f32x2(Q, q0, q1);
+        uint64_t SQ = pack_f32x2(__fadd_rn(s0, s1), __fadd_rn(q0, q1));
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) SQ = add_f32x2(SQ, shfl_xor_b64(SQ, o));
+        float sm, sq;
+        unpack_f32x2(SQ, sm, sq);
+        const float mean = __fmul_rn(sm, 1.0f / 512.0f);
+        const float ex2 = __fmul_rn(sq, 1.0f / 512.0f);
+        const float var = fmaxf(__fmaf_rn(-mean, mean, ex2), 0.0f);
+        const float rstd = __frsqrt_rn(__fadd_rn(var, p.eps));
+        const float nmr = __fmul_rn(-mean, rstd);
+        const uint64_t R2 = pack_f32x2(rstd, rstd), N2 = pack_f32x2(nmr, nmr);
+        auto normalise = [&](int c) {
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const float4 ga = gb_s[pass][0][c * 2 + hh][j];
+            const float4 be = gb_s[pass][1][c * 2 + hh][j];
+            v[c][2 * hh] = fma_f32x2(fma_f32x2(v[c][2 * hh], R2, N2), pack_f32x2(ga.x, ga.y), pack_f32x2(be.x, be.y));
+            v[c][2 * hh + 1] = fma_f32x2(fma_f32x2(v[c][2 * hh + 1], R2, N2), pack_f32x2(ga.z, ga.w), pack_f32x2(be.z, be.w));
+          }
+        };
+        if (!(p.y && pass == 0)) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) normalise(c);
+        } else if (p.y_bf16) {
+          __nv_bfloat16* const yrow = static_cast<__nv_bfloat16*>(p.y) + static_cast<int64_t>(row) * ldy + j * 32;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            normalise(c);
+            float f[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) unpack_f32x2(v[c][i], f[2 * i], f[2 * i + 1]);
+            uint4 w4;
+            w4.x = pack2_bf16(f[0], f[1]);
+            w4.y = pack2_bf16(f[2], f[3]);
+            w4.z = pack2_bf16(f[4], f[5]);
+            w4.w = pack2_bf16(f[6], f[7]);
+            if (valid) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(yrow) + poff[c]) = w4;
+            // a LayerNorm that follows reads what was stored
+            const uint32_t ww[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[c][i] = pack_f32x2(__uint_as_float(ww[i] << 16), __uint_as_float(ww[i] & 0xffff0000u));
+          }
+        } else {
+          float* const yrow = static_cast<float*>(p.y) + static_cast<int64_t>(row) * ldy + j * 32;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            normalise(c);
+            float f[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) unpack_f32x2(v[c][i], f[2 * i], f[2 * i + 1]);
+            if (valid) {
+              float4* yp = reinterpret_cast<float4*>(reinterpret_cast<uint8_t*>(yrow) + 2 * poff[c]);
+              yp[0] = make_float4(f[0], f[1], f[2], f[3]);
+              yp[1] = make_float4(f[4], f[5], f[6], f[7]);
+            }
+          }
+        }
+      }
+    }
+
+    // ---- quantize the lane's 32 values ----
+    if (LN && !p.codes) continue;  // plain LayerNorm
+    float a[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) a[c] = amax8p(v[c]);
+    if constexpr (FMT == VX_FMT_FP8_1X128) {
+      float am = fmaxf(max3(a[0], a[1], a[2]), a[3]);
+      am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+      am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
+      float scale, rcp;
+      fp8_block(am, scale, rcp);
+      if (valid) {
+        uint8_t* dst = p.codes + static_cast<int64_t>(row) * ldc + j * 32;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) *reinterpret_cast<uint2*>(dst + (poff[c] >> 1)) = fp8_pack8p(v[c], rcp);
+        if (p.scales && (j & 3) == 0) static_cast<float*>(p.scales)[row * 4 + (j >> 2)] = scale;
+      }
+    } else {
+      uint32_t wd[4];
+      if constexpr (FMT == VX_FMT_MX32) {
+        uint32_t byte;
+        float rcp;
+        ue8m0_from_amax(fmaxf(max3(a[0], a[1], a[2]), a[3]), byte, rcp);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) wd[c] = e2m1_pack8p<true, CANON, NUDGE>(v[c], rcp);
+        if (valid) {
+          if (p.sf) p.sf[sf_offset<int>(row, j >> 2, static_cast<int>(p.sf_kg)) + (j & 3)] = static_cast<uint8_t>(byte);
+          if (p.scales) static_cast<uint8_t*>(p.scales)[row * 16 + j] = static_cast<uint8_t>(byte);
+        }
+      } else {
+        // two 16-element blocks: pieces 0, 1 and pieces 2, 3; piece of step c is (c + rot) & 3
+        float a_lo = 0.0f, a_hi = 0.0f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const bool lo = ((c + rot) & 2) == 0;
+          a_lo = fmaxf(a_lo, lo ? a[c] : 0.0f);
+          a_hi = fmaxf(a_hi, lo ? 0.0f : a[c]);
+        }
+        uint32_t b_lo, b_hi;
+        float r_lo, r_hi;
+        nv16_block(a_lo, g, b_lo, r_lo);
+        nv16_block(a_hi, g, b_hi, r_hi);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) wd[c] = e2m1_pack8p<false, CANON, true>(v[c], ((c + rot) & 2) == 0 ? r_lo : r_hi);
+        if (valid) {
+          if (p.sf)
+            *reinterpret_cast<uint16_t*>(p.sf + sf_offset<int>(row, j >> 1, static_cast<int>(p.sf_kg)) + (j & 1) * 2) =
+                static_cast<uint16_t>(b_lo | (b_hi << 8));
+          if (p.scales) {
+            uint8_t* sc = static_cast<uint8_t*>(p.scales) + row * 32 + 2 * j;
+            sc[0] = static_cast<uint8_t>(b_lo);
+            sc[1] = static_cast<uint8_t>(b_hi);
+          }
+        }
+      }
+      // word of step c belongs to piece (c + rot) & 3: rotate the four words back by rot
+      if (rot & 1) { const uint32_t t = wd[3]; wd[3] = wd[2]; wd[2] = wd[1]; wd[1] = wd[0]; wd[0] = t; }
+      if (rot & 2) { uint32_t t = wd[0]; wd[0] = wd[2]; wd[2] = t; t = wd[1]; wd[1] = wd[3]; wd[3] = t; }
+      if (valid) *reinterpret_cast<uint4*>(p.codes + static_cast<int64_t>(row) * ldc + j * 16) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+    }
+  }
+  zero_pad_rows<int>(p, u_first, warps, lane);
+}
+
+int grid_for_rows(int64_t units, int blocks_per_sm);
+
+// rows2_kernel takes every bf16 call with rows of 512 elements in an SF-atom FP4 format or FP8 (whatever
+// scale layouts, y and LayerNorms are asked for), provided offsets fit 32 bits and code rows are 16-byte
+// aligned -- so that for those calls the LayerNorm summation order does not depend on the options.
+template <int FMT>
+bool launch_rows2(const QuantParams& p, bool ln, cudaStream_t st) {
+  if constexpr (FMT == VX_FMT_MX32 || FMT == VX_FMT_NV16 || FMT == VX_FMT_FP8_1X128) {
+    int64_t ld = p.ldx > p.ldy ? p.ldx : p.ldy;
+    if (p.codes && p.ldc > ld) ld = p.ldc;
+    const bool small = (p.M + 128) * ld < (1ll << 31) && (p.M + 128) * (p.sf_kg * 4 + 1) < (1ll << 31);
+    if (p.K != 512 || !small) return false;
+    if (p.codes && ((p.ldc & 15) || (reinterpret_cast<uintptr_t>(p.codes) & 15))) return false;
+    if (!p.codes && !ln) return false;
+    if (ln) rows2_kernel<FMT, true><<<grid_for_rows((p.M + 1) / 2, VX_R2_MIN_BLOCKS_LN), 256, 0, st>>>(p);
+    else rows2_kernel<FMT, false><<<grid_for_rows((p.M + 1) / 2, VX_R2_MIN_BLOCKS), 256, 0, st>>>(p);
+    return true;
+  } else {
+    return false;
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) amax_kernel(const T* x, int64_t M, int64_t K, int64_t ldx,
                                                    float* out) {
@@ -655,6 +920,9 @@ void launch_quant_idx(const QuantParams& p, bool ln, cudaStream_t st) {
 
 template <typename T, int FMT>
 void launch_quant(const QuantParams& p, bool ln, cudaStream_t st) {
+  if constexpr (sizeof(T) == 2) {
+    if (launch_rows2<FMT>(p, ln, st)) return;
+  }
   // 32-bit indices when every offset the kernels form stays below 2^31 (rows padded to 128 for
   // the scale-factor atoms; strides in elements, y possibly fp32)
   int64_t ld = p.K;
