@@ -277,7 +277,7 @@ def test_two_layernorms_fused_equal_the_two_launches(fmt, dtype):
     g1, b1 = torch.rand(K, device="cuda") + 0.5, torch.randn(K, device="cuda") * 0.1
     g2, b2 = torch.rand(K, device="cuda") + 0.5, torch.randn(K, device="cuda") * 0.1
     am = torch.tensor([8.0], device="cuda") if fmt == "nv16" else None
-    y_ref = ops.layernorm(x.clone(), g1, b1, 1e-5)
+    y_ref = ops.layernorm(x.clone(), g1, b1, 1e-5, fmt=fmt)
     q_ref = ops.ln_quantize(y_ref, g2, b2, 1e-5, fmt, natural=True, amax_t=am)
     xin = x.clone()
     q = ops.ln2_quantize(xin, g1, b1, g2, b2, 1e-5, fmt, y=xin, natural=True, amax_t=am)  # in place

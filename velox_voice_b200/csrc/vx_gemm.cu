@@ -72,6 +72,8 @@ __host__ __device__ constexpr int kind_bn(int kind) {
   return (kind == KIND_FP4_VEC2 || kind == KIND_FP4_VEC4) ? 256 : 128;
 }
 __host__ __device__ constexpr bool kind_vec4(int kind) { return kind == KIND_FP4_VEC4 || kind == KIND_FP4_VEC4_N128; }
+// MX32 and the per-row-scaled format: every scale a power of two (see swish4p)
+__host__ __device__ constexpr bool kind_pow2_scales(int kind) { return kind == KIND_FP4_VEC2 || kind == KIND_FP4_VEC2_N128; }
 
 // Epilogue warps of a kernel instance.  A CTA holds at most 32 warps and the epilogue needs whole
 // groups of four (one warp per 32-lane quadrant of tensor memory; the quadrant is also the warp's
@@ -188,7 +190,33 @@ __device__ __forceinline__ float sigmoid_f(float z) { return rcp_ftz(1.0f + ex2_
 // only occurs for z < -20.8, where z * sigmoid(z) is below 1e-7 in magnitude either way.
 // Every Swish of the library goes through this function, so the fp32 / bf16 outputs and the FP4
 // re-quantized output of the same GEMM see the same bits.
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+//
+// TANH = true: z sigmoid(z) = h + h tanh(h), h = z / 2, with tanh.approx -- one special-function
+// operation, one packed multiply and one packed fused multiply-add per pair: 2 instructions per value
+// instead of 5 (these epilogues are bound by instruction issue).  Used by the GEMMs whose operands carry
+// power-of-two block scales (MX32, per-row): there the activation is re-quantized with power-of-two
+// scales too, which absorbs the difference -- the 12-block MX32 stack still reproduces the CPU
+// oracle's logits bit for bit (T = 1000) and agrees in every arg-max at M = 24000.  The formats with
+// fp32 / E4M3 scales (NV16, FP8) keep the exponential form: their scales move with the last bits of a
+// block maximum, and the same swap costs them arg-max agreement over 12 blocks (NV16 1.000 -> 0.991,
+// FP8 0.992 -> 0.966 against the oracle in kernel order).
+template <bool TANH>
 __device__ __forceinline__ void swish4p(uint64_t& za, uint64_t& zb) {
+  if constexpr (TANH) {
+    const uint64_t half2 = pack_f32x2(0.5f, 0.5f);
+    const uint64_t ha = mul_f32x2(za, half2), hb = mul_f32x2(zb, half2);
+    float h0, h1, h2, h3;
+    unpack_f32x2(ha, h0, h1);
+    unpack_f32x2(hb, h2, h3);
+    za = fma_f32x2(ha, pack_f32x2(tanh_approx(h0), tanh_approx(h1)), ha);
+    zb = fma_f32x2(hb, pack_f32x2(tanh_approx(h2), tanh_approx(h3)), hb);
+    return;
+  }
   const uint64_t nl2e = pack_f32x2(-1.4426950408889634f, -1.4426950408889634f);
   const uint64_t one2 = pack_f32x2(1.0f, 1.0f);
   float t0, t1, t2, t3;
@@ -203,9 +231,10 @@ __device__ __forceinline__ void swish4p(uint64_t& za, uint64_t& zb) {
   za = mul_f32x2(za, mul_f32x2(rp, db));
   zb = mul_f32x2(zb, mul_f32x2(rp, da));
 }
+template <bool TANH>
 __device__ __forceinline__ void silu4_f(float& z0, float& z1, float& z2, float& z3) {
   uint64_t za = pack_f32x2(z0, z1), zb = pack_f32x2(z2, z3);
-  swish4p(za, zb);
+  swish4p<TANH>(za, zb);
   unpack_f32x2(za, z0, z1);
   unpack_f32x2(zb, z2, z3);
 }
@@ -242,7 +271,7 @@ __device__ __forceinline__ void swish_group8(const uint32_t (&r)[32], int g, con
       za = add_f32x2(za, pack_f32x2(b.x, b.y));
       zb = add_f32x2(zb, pack_f32x2(b.z, b.w));
     }
-    swish4p(za, zb);
+    swish4p<!NV16>(za, zb);
     out[2 * i] = za;
     out[2 * i + 1] = zb;
   }
@@ -314,7 +343,7 @@ __device__ __forceinline__ uint32_t swish_quant_chunk(const uint32_t (&r)[32], c
 // Epilogue of one 32-column chunk held in registers by one thread (one output row).
 //   z[i]  accumulator value of logical column `ncol0 + i` (after scales)
 //   For GLU the caller passes value and gate chunks and `ncol0` in OUTPUT columns.
-template <int EPI, bool RES_TMA>
+template <int EPI, bool RES_TMA, bool TANH = false>
 struct ChunkOut {
   // Applies bias / activation / residual in place.  `bias_s` / `gate_s`: 32 bias values of the
   // chunk (and of its GLU gate chunk) in shared memory, or nullptr; `out_col0`: output column.
@@ -344,7 +373,7 @@ struct ChunkOut {
     }
     if constexpr (EPI == VX_EPI_BIAS_SWISH) {
 #pragma unroll
-      for (int i = 0; i < 32; i += 4) silu4_f(z[i], z[i + 1], z[i + 2], z[i + 3]);
+      for (int i = 0; i < 32; i += 4) silu4_f<TANH>(z[i], z[i + 1], z[i + 2], z[i + 3]);
     } else if constexpr (EPI == VX_EPI_BIAS_GLU) {
 #pragma unroll
       // (one reciprocal per value here: the shared-reciprocal form's extra roundings flip enough
@@ -1213,7 +1242,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             }
           }
           if (tr && h == 0 && !FP8) trace_rec(p, 2, it, 3);
-          ChunkOut<EPI, OUT == 1>::apply(p, z[h], gate, row, bias_base ? bias_base + h * 32 : nullptr, bias_base + 32, out_col0,
+          ChunkOut<EPI, OUT == 1, kind_pow2_scales(KIND)>::apply(p, z[h], gate, row, bias_base ? bias_base + h * 32 : nullptr, bias_base + 32, out_col0,
                                row_ok, res_smem, lane);
           if (tr && h == 0 && !FP8) trace_rec(p, 2, it, 4);
 

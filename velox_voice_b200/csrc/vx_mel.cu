@@ -8,8 +8,7 @@
 // (tcgen05.mma kind::tf32, accumulator in tensor memory) and the kernel is shaped by what bounds it,
 // the 2 KB of complex spectrum per frame that have to come out of HBM:
 //
-//   warps 0..3    epilogue: tcgen05.ld of the fp32 accumulator (one frame per thread), log, CMVN, then out
-//                 through a shared-memory tile so that every store instruction writes one row segment;
+//   warps 0..3    epilogue: tcgen05.ld of the fp32 accumulator (one frame per thread), log, CMVN, store;
 //   warps 4..11   loaders: read the spectrum with coalesced 8-byte loads (one complex bin per lane, sixteen
 //                 rows per stage, the loads of the next stage in flight while the current one is
 //                 processed), form re^2 + im^2 and write it straight into the 128-byte-swizzled
@@ -51,7 +50,6 @@ struct MelParams {
   float* out;
   int64_t ldo;
   int n_pad, stages, tiles, ring;
-  int stage_out;  // epilogue writes through a shared-memory tile (coalesced rows) when it fits
   int* status;
 };
 
@@ -98,7 +96,6 @@ __global__ void __launch_bounds__(MEL_THREADS, 1) power_mel_log_kernel(const Mel
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* const ring = base;                                  // p.ring x 16 KB
   uint8_t* const bres = base + p.ring * MEL_SLOT;              // stages x n_pad x 128 B (n_pad % 8 == 0: 1 KB atoms hold)
-  float* const ostage = reinterpret_cast<float*>(bres + static_cast<size_t>(p.stages) * p.n_pad * 128);  // 4 x 32 x (n_pad + 1) f32
   __shared__ MelBarriers bar;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* const abortp = &bar.abort_flag;
@@ -221,35 +218,27 @@ __global__ void __launch_bounds__(MEL_THREADS, 1) power_mel_log_kernel(const Mel
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       tc_fence_after();
-      const int64_t row_w = (static_cast<int64_t>(blockIdx.x) + static_cast<int64_t>(i) * gridDim.x) * MEL_BM + warp * 32;
-      const int64_t row = row_w + lane;
+      const int64_t row = (static_cast<int64_t>(blockIdx.x) + static_cast<int64_t>(i) * gridDim.x) * MEL_BM + warp * 32 + lane;
       const uint32_t taddr = tmem_base + a * 256 + (static_cast<uint32_t>(warp * 32) << 16);
-      const int pitch = p.n_pad + 1;  // odd: the 32 rows of a column fall into 32 different banks
-      float* const mine = ostage + (warp * 32 + lane) * pitch;
       for (int c0 = 0; c0 < p.n_pad; c0 += 16) {
         uint32_t r[16];
         tc_ld_32x32b_x16(taddr + c0, r);
         tc_wait_ld();
+        if (row < p.T) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int m = c0 + j;
-          float v = __logf(fmaxf(__uint_as_float(r[j]), 1.1920929e-7f));
-          if (p.mean && m < p.M) v = (v - __ldg(p.mean + m)) * __ldg(p.istd + m);
-          if (p.stage_out) mine[m] = v;
-          else if (row < p.T && m < p.M) p.out[row * p.ldo + m] = v;
+          for (int j = 0; j < 16; ++j) {
+            const int m = c0 + j;
+            if (m < p.M) {
+              float v = __logf(fmaxf(__uint_as_float(r[j]), 1.1920929e-7f));
+              if (p.mean) v = (v - __ldg(p.mean + m)) * __ldg(p.istd + m);
+              p.out[row * p.ldo + m] = v;
+            }
+          }
         }
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bar.acc_empty[a]);  // the accumulator is read: the MMAs of tile i + 2 may start
-      if (p.stage_out) {
-        // one thread holds one frame, so direct stores would touch 32 rows per instruction; through the
-        // tile every store instruction writes 128 contiguous bytes of one row
-        const float* const tile = ostage + warp * 32 * pitch;
-        for (int rr = 0; rr < 32 && row_w + rr < p.T; ++rr)
-          for (int m = lane; m < p.M; m += 32) p.out[(row_w + rr) * p.ldo + m] = tile[rr * pitch + m];
-        __syncwarp();
-      }
+      if (lane == 0) mbar_arrive(&bar.acc_empty[a]);
     }
     if (!ok) bar.abort_flag = 1;
   }
@@ -271,7 +260,7 @@ namespace {
 size_t mel_smem_bytes(int64_t F, int64_t M, int ring) {
   if (M <= 0 || F <= 0 || M > 256) return 0;
   const size_t n_pad = static_cast<size_t>((M + 15) / 16 * 16), stages = static_cast<size_t>((F + MEL_KS - 1) / MEL_KS);
-  return stages * n_pad * 128 + 1024 + static_cast<size_t>(ring) * MEL_SLOT;  // (+ the optional output tile)
+  return stages * n_pad * 128 + 1024 + static_cast<size_t>(ring) * MEL_SLOT;
 }
 }  // namespace
 }  // namespace vx
@@ -304,15 +293,7 @@ extern "C" int vx_power_mel_log(const void* spec, int64_t T, int64_t F, int64_t 
   const size_t bank = static_cast<size_t>(p.stages) * p.n_pad * 128 + 1024;
   p.ring = MEL_RING_MAX;
   while (p.ring > 2 && bank + static_cast<size_t>(p.ring) * MEL_SLOT > static_cast<size_t>(MEL_MAX_SMEM)) --p.ring;
-  size_t smem = bank + static_cast<size_t>(p.ring) * MEL_SLOT;
-  const size_t out_tile = static_cast<size_t>(MEL_BM) * (p.n_pad + 1) * sizeof(float);
-  if (smem <= static_cast<size_t>(MEL_MAX_SMEM) && smem + out_tile > static_cast<size_t>(MEL_MAX_SMEM) && p.ring > 2 &&
-      bank + 2 * static_cast<size_t>(MEL_SLOT) + out_tile <= static_cast<size_t>(MEL_MAX_SMEM)) {
-    p.ring = 2;  // a coalesced output is worth more than ring depth
-    smem = bank + 2 * static_cast<size_t>(MEL_SLOT);
-  }
-  p.stage_out = smem + out_tile <= static_cast<size_t>(MEL_MAX_SMEM);
-  if (p.stage_out) smem += out_tile;
+  const size_t smem = bank + static_cast<size_t>(p.ring) * MEL_SLOT;
   if (smem > static_cast<size_t>(MEL_MAX_SMEM))
     return fail(-1, "filterbank of %lld x %lld does not fit in shared memory (%zu bytes needed, %d available)", (long long)M,
                 (long long)F, smem, MEL_MAX_SMEM);

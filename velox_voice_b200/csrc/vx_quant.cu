@@ -671,7 +671,25 @@ __global__ void __launch_bounds__(256, LN ? VX_R2_MIN_BLOCKS_LN : VX_R2_MIN_BLOC
     if constexpr (LN) {
 #pragma unroll 1
       for (int pass = 0; pass < npass; ++pass) {
+#ifndef VX_R2_SPLIT_STATS
+#define VX_R2_SPLIT_STATS 0
+#endif
         uint64_t S = pack_f32x2(0.0f, 0.0f), Q = S;
+#if VX_R2_SPLIT_STATS
+        uint64_t Sb = S, Qb = S;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            S = add_f32x2(S, v[c][i]);
+            Q = fma_f32x2(v[c][i], v[c][i], Q);
+            Sb = add_f32x2(Sb, v[c + 2][i]);
+            Qb = fma_f32x2(v[c + 2][i], v[c + 2][i], Qb);
+          }
+        }
+        S = add_f32x2(S, Sb);
+        Q = add_f32x2(Q, Qb);
+#else
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
 #pragma unroll
@@ -680,6 +698,7 @@ __global__ void __launch_bounds__(256, LN ? VX_R2_MIN_BLOCKS_LN : VX_R2_MIN_BLOC
             Q = fma_f32x2(v[c][i], v[c][i], Q);
           }
         }
+#endif
         float s0, s1, q0, q1;
         unpack_f32x2(S, s0, s1);
         unpack_f32x2(Q, q0, q1);

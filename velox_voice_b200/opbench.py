@@ -3,6 +3,7 @@
 
     python -m velox_voice_b200.opbench                     # every launch of one Conformer block + CTC
     python -m velox_voice_b200.opbench --ops ffn-up        # only launches whose name contains "ffn-up"
+    python -m velox_voice_b200.opbench --ops mel           # the front-end's filterbank projection (4 x frames rows)
     python -m velox_voice_b200.opbench --configs           # the three single-GPU benchmark configurations
     python -m velox_voice_b200.opbench --frames 11250 --fmt nv16
 
@@ -97,6 +98,14 @@ def op_breakdown(stack, T, fmt_name, only=""):
         2 * T * d * 2 * d)
     add("gemm ctc 512->5538 bias + argmax (no logits written)", 1, lambda: stack.p["ctc"].argmax(xq),
         qbytes(T, d) + qbytes(V, d) + T * 12, 2 * T * d * V)
+    if only and "mel" in only:
+        # the audio front-end's filterbank projection (not part of the encoder step): one hour of 10 ms frames
+        Tm, Fm, Mm = 4 * T, 257, 80
+        spec = torch.randn(Tm, Fm, dtype=torch.cfloat, device=dev)
+        bank = torch.rand(Mm, Fm, device=dev)
+        mean, istd = torch.randn(Mm, device=dev), torch.rand(Mm, device=dev) + 0.5
+        add(f"power_mel_log [{Tm} x {Fm}] -> {Mm} mel (tf32)", 0, lambda: ops.power_mel_log_tf32(spec, bank, mean, istd),
+            Tm * Fm * 8 + Tm * Mm * 4 + Mm * Fm * 4, 2 * Tm * Fm * Mm)
     del flush
     return cases
 

@@ -262,8 +262,13 @@ def ln2_quantize(x: torch.Tensor, gamma1, beta1, gamma2, beta2, eps: float, fmt,
     return Quantized(fmt, M, K, codes, scales, sf_t, amax_t)
 
 
-def layernorm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: float = 1e-5, out=None, out_dtype=None):
-    """Row LayerNorm with fp32 statistics; output f32 or bf16."""
+def layernorm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: float = 1e-5, out=None, out_dtype=None,
+              fmt="mx32"):
+    """Row LayerNorm with fp32 statistics; output f32 or bf16.  ``fmt`` names the quantization lane the
+    result belongs to: the LayerNorm runs on the kernel (and so with the summation order, which shows in
+    the last bit) that ``ln_quantize(..., fmt)`` would use, so that a stored LayerNorm followed by
+    ``ln_quantize`` equals ``ln2_quantize`` exactly in every format."""
+    fmt = _fmt(fmt)
     _require_cuda(x, "x")
     shape = x.shape
     x2 = _rows2d(x.reshape(-1, shape[-1]), "x")
@@ -274,7 +279,7 @@ def layernorm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: flo
     gamma = gamma.float().contiguous()
     beta = beta.float().contiguous()
     rc = _lib.load().vx_ln_quantize_pack(
-        x2.data_ptr(), _dt(x2, "x"), M, K, x2.stride(0), gamma.data_ptr(), beta.data_ptr(), float(eps), FMT_MX32,
+        x2.data_ptr(), _dt(x2, "x"), M, K, x2.stride(0), gamma.data_ptr(), beta.data_ptr(), float(eps), fmt,
         None, 0, None, None, None, out2.data_ptr(), _dt(out2, "out"), out2.stride(0), _stream(),
     )
     _lib.check(rc, "vx_ln_quantize_pack")
