@@ -2,6 +2,7 @@
 
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "vx_common.cuh"
 
@@ -21,6 +22,14 @@ int fail(int code, const char* fmt, ...) {
   vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
   va_end(ap);
   return code;
+}
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("VELOX_B200_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
 }
 
 int* device_status_ptr() {

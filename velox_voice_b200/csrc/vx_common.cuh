@@ -40,6 +40,29 @@ inline int64_t sf_kgroups(int fmt, int64_t K) {
   return ((K + kStageK4 - 1) / kStageK4) * per_stage;
 }
 
+// Whether launches of the kernels that call pdl_wait() carry the programmatic-serialization
+// attribute (environment VELOX_B200_PDL, default on; "0" gives plain stream order).
+bool pdl_enabled();
+
+// Launch of a kernel that executes pdl_wait() before its first dependent access: its blocks may be
+// scheduled while the previous kernel of the stream drains, so launch latency and the kernel's own
+// set-up (barriers, tensor memory, constant operands) overlap the predecessor's tail.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                    Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 #define VX_CUDA_OK(expr)                                                        \
   do {                                                                          \
     cudaError_t _e = (expr);                                                    \

@@ -88,8 +88,13 @@ __host__ __device__ constexpr bool kind_pow2_scales(int kind) { return kind == K
 //       (chunk n = 4 * tile + column group goes to warp n mod 7 of the quadrant): the warps of a
 //       scheduler then sit in different tiles and different phases, and the two accumulators of
 //       the narrow tile keep the MMAs two tiles ahead.
+// (The same round-robin hand-out on the WIDE tile was measured too: 178 vs 115 us -- its one
+// accumulator is released only when the last of its eight chunks has found a free warp.)
+#ifndef VX_RR_WIDE
+#define VX_RR_WIDE 0
+#endif
 __host__ __device__ constexpr bool epi_round_robin(int kind, int epi, int out) {
-  return epi == VX_EPI_BIAS_SWISH && out == 2 && kind_bn(kind) == 128;
+  return epi == VX_EPI_BIAS_SWISH && out == 2 && (VX_RR_WIDE || kind_bn(kind) == 128);
 }
 __host__ __device__ constexpr int epi_warps(int kind, int epi, int out) { return epi_round_robin(kind, epi, out) ? 28 : 16; }
 __host__ __device__ constexpr int num_threads(int kind, int epi, int out) { return (2 + epi_warps(kind, epi, out)) * 32; }
@@ -531,6 +536,7 @@ __global__ void __launch_bounds__(num_threads(KIND, EPI, OUT), 1)
 bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
               const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_res,
               const GemmParams p) {
+  pdl_launch_dependents();  // the next kernel of the stream may be scheduled as SMs free up (it waits for this one)
   extern __shared__ uint8_t smem_raw[];
   SmemLayout& sm = *reinterpret_cast<SmemLayout*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -618,7 +624,9 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     }
     for (int a = 0; a < FP8_ACCS; ++a) {
       mbar_init(&sm.tmem_full[a], 1);
-      mbar_init(&sm.tmem_empty[a], 16);  // sixteen 32 x 32 parts per accumulator half, one arrival each
+      // one arrival per 32 x 32 part (16 per accumulator; a wide accumulator read chunk by chunk has 32),
+      // or one per warp where a warp reads its two chunks of the wide tile itself
+      mbar_init(&sm.tmem_empty[a], (SWQ_RR && WIDE) ? 32 : 16);
     }
     mbar_init(&sm.b_full, 1);
     mbar_init(&sm.sfb_done, 1);
@@ -629,9 +637,11 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     if (tma_store) prefetch_tmap(&tmap_out);
     if (tma_residual) prefetch_tmap(&tmap_res);
   }
-  {
+  if (FP8 || p.N % BNT != 0) {
     // Scale-factor tiles of B that lie beyond N are never loaded; they must read as zero
     // (their B rows are zero-filled by TMA, and 0 x NaN-scale would poison the accumulator).
+    // With N a whole number of column blocks every tile exists and is loaded: nothing to clear
+    // (200 KB of shared-memory stores per CTA, about a microsecond of every launch).
     uint4* a4 = reinterpret_cast<uint4*>(sm.arena);
     for (int i = threadIdx.x; i < ARENA_BYTES / 16; i += blockDim.x) a4[i] = make_uint4(0, 0, 0, 0);
   }
@@ -650,6 +660,11 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = sm.tmem_base;
   const int n_sf_tiles = static_cast<int>((p.N + 127) >> 7);  // 128-row SF tiles of B that exist
+  // Set-up is done.  Everything below may touch what the previous kernel of the stream produced (A,
+  // residual, output buffers), so every thread waits for it here -- except the producer thread, which
+  // first starts the loads of its resident weights (constants of the model) and then waits.
+  const bool producer_thread = warp == 0 && lane == 0 && my_tiles > 0;
+  if (!producer_thread) pdl_wait();
 
   if (warp == 0) {
     // =========================== TMA producer ===========================
@@ -697,6 +712,7 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                         p.sfb + (static_cast<int64_t>(nb0 * NRT + rt) * p.sf_kg) * 512 + ks * sf_stage, APS * 512,
                         &sm.b_full);
       }
+      pdl_wait();
       int mb = mb0, nb = nb0;
       const int G = p.group, k_groups = p.k_stages / G, ngs = nslots / G;
       for (int i = 0; i < my_tiles && ok; ++i) {
@@ -954,18 +970,20 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
       }
     }
     if constexpr (SWQ_RR) {
-      // FFN up-projection, round robin: this quadrant's chunks n = 4 * tile + column group, this
-      // warp takes n = j, j + 7, j + 14, ...  Accumulator of tile t: t & 1, published for the
-      // (t >> 1)-th time; every chunk is read by exactly one warp, which arrives once.
+      // FFN up-projection, round robin: this quadrant's chunks n = CPT * tile + column group, this
+      // warp takes n = j, j + 7, j + 14, ...  Narrow tile: accumulator t & 1, published for the
+      // (t >> 1)-th time; wide tile: the one accumulator, published for the t-th time.  Every chunk
+      // is read by exactly one warp, which arrives once.
+      constexpr int CPT = BNT / 32;  // 32-column chunks per tile
       const int j = ew >> 2;
       const bool scale_acc = kind_vec4(KIND) && p.a_amax != nullptr;
       int t_cur = 0;
-      for (int n = j; n < 4 * my_tiles && ok; n += EPW / 4) {
-        const int t = n >> 2, ccn = n & 3;
+      for (int n = j; n < CPT * my_tiles && ok; n += EPW / 4) {
+        const int t = n / CPT, ccn = n % CPT;
         while (t_cur < t) { next_tile(mb, nb); ++t_cur; }
-        const uint32_t acc = t & 1;
+        const uint32_t acc = WIDE ? 0u : (t & 1);
         if (tr) trace_rec(p, 2, t, 0);
-        if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[acc], (t >> 1) & 1, p.status, 4);
+        if (lane == 0) ok = mbar_wait_spin(&sm.tmem_full[acc], (WIDE ? t : (t >> 1)) & 1, p.status, 4);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
         tc_fence_after();
@@ -979,7 +997,8 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         if (tr) trace_rec(p, 2, t, 2);
         const int64_t row = static_cast<int64_t>(mb) * BM + q * 32 + lane;
         const bool row_ok = row < p.M;
-        const int64_t out_col0 = static_cast<int64_t>(nb) * BNT + ccn * 32;  // N % 128 == 0: the chunk is whole
+        const int64_t out_col0 = static_cast<int64_t>(nb) * BNT + ccn * 32;
+        if (out_col0 >= p.N) continue;  // N % 128 == 0: a chunk is whole or (wide tile, last column block) absent
         uint32_t w[4];
         const uint32_t sb = swish_quant_chunk<kind_vec4(KIND)>(r, p.bias ? p.bias + out_col0 : nullptr, scale_acc, g_ab, g_out, w);
         if (row_ok)
@@ -1768,7 +1787,8 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, 
       grid = groups * p.n_tiles;
     }
   }
-  bsgemm_kernel<KIND, EPI, OUT><<<grid, num_threads(KIND, EPI, OUT), kSmemBytes, st>>>(ta, tb, to, tr, p);
+  VX_CUDA_OK(launch_dependent(bsgemm_kernel<KIND, EPI, OUT>, dim3(grid), dim3(num_threads(KIND, EPI, OUT)), kSmemBytes, st, ta, tb,
+                              to, tr, p));
   VX_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -1879,6 +1899,26 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
     const int64_t wide_tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
     bool narrow = stages <= 2 && epi != VX_EPI_BIAS_SWISH && epi != VX_EPI_BIAS_GLU &&
                   (epi == VX_EPI_BIAS_RESIDUAL || wide_tiles < 148);
+    // Few rows (a shard of a job cut over several GPUs): CTAs own column blocks and walk the row
+    // blocks in rounds of sms / column-blocks, so what counts is the number of rounds times the cost of
+    // a tile -- a narrow tile costs about 0.55 of a wide one.  88 row blocks, N = 512: the wide tiling
+    // takes 2 rounds on 74 groups, the narrow one 3 half-size rounds on 37.
+    if (!narrow && epi != VX_EPI_BIAS_SWISH && epi != VX_EPI_BIAS_GLU) {
+      static int sm_cache[64] = {};
+      int sms = 148, dev = 0;
+      if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) {
+        if (!sm_cache[dev] && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0)
+          sm_cache[dev] = sms;
+        if (sm_cache[dev]) sms = sm_cache[dev];
+      }
+      const int64_t mt = (M + BM - 1) / BM, ntw = (N + 255) / 256, ntn = (N + 127) / 128;
+      auto rounds = [&](int64_t nt) {
+        int64_t groups = nt <= sms ? sms / nt : 1;
+        if (groups > mt) groups = mt;
+        return nt <= sms ? (mt + groups - 1) / groups : (mt * nt + sms - 1) / sms;
+      };
+      if (0.55 * static_cast<double>(rounds(ntn)) < 0.95 * static_cast<double>(rounds(ntw))) narrow = true;
+    }
     // Swish + FP4 output (the FFN up-projection) stays on the wide tile: the narrow tile's
     // 28-warp round-robin epilogue is faster per value, but its N = 128 MMAs read A from shared
     // memory twice as often and that chain then bounds the tile (measured 144 vs 134 us at

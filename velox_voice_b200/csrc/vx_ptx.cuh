@@ -224,6 +224,15 @@ __device__ __forceinline__ void tc_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[3
       : "memory");
 }
 
+// ------------------------------------------------------------------ programmatic dependent launch
+// A kernel launched with the programmatic-serialization attribute may start while its predecessor
+// in the stream is still running; it must execute pdl_wait() before it touches anything the
+// predecessor reads or writes (the wait returns once the predecessor grid has completed and its
+// memory is visible).  pdl_launch_dependents() lets the successor's blocks be scheduled as soon as
+// this grid's blocks have all issued it (or exited).  Both are no-ops in a plain launch.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ------------------------------------------------------------------ descriptors
 // 64-bit shared-memory matrix descriptor, K-major operand stored as rows of 128 bytes with
 // the 128-byte swizzle (what a TMA load with SWIZZLE_128B writes): 8-row groups are 1024

@@ -605,8 +605,7 @@ __global__ void __launch_bounds__(256, LN ? VX_R2_MIN_BLOCKS_LN : VX_R2_MIN_BLOC
   const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(p.x);
   const int ldx = static_cast<int>(p.ldx), ldc = static_cast<int>(p.ldc), ldy = static_cast<int>(p.ldy);
   const int npass = LN ? (p.gamma2 ? 2 : 1) : 0;
-  float g = 1.0f;
-  if constexpr (FMT == VX_FMT_NV16) g = nv16_global(__ldg(p.amax));
+  pdl_launch_dependents();
 
   __shared__ __align__(128) uint8_t ring_s[8 * VX_R2_RING * kR2SlotBytes];
   __shared__ uint64_t full_s[8 * VX_R2_RING];
@@ -629,6 +628,11 @@ __global__ void __launch_bounds__(256, LN ? VX_R2_MIN_BLOCKS_LN : VX_R2_MIN_BLOC
     mbar_fence_init();
   }
   __syncthreads();
+  // set-up done (LayerNorm parameters are constants of the model): from here on the kernel touches what
+  // the previous kernel of the stream produced
+  pdl_wait();
+  float g = 1.0f;
+  if constexpr (FMT == VX_FMT_NV16) g = nv16_global(__ldg(p.amax));
 
   auto issue = [&](int slot, int u) {
     if (lane == 0) {
@@ -840,8 +844,8 @@ bool launch_rows2(const QuantParams& p, bool ln, cudaStream_t st) {
     if (p.K != 512 || !small) return false;
     if (p.codes && ((p.ldc & 15) || (reinterpret_cast<uintptr_t>(p.codes) & 15))) return false;
     if (!p.codes && !ln) return false;
-    if (ln) rows2_kernel<FMT, true><<<grid_for_rows((p.M + 1) / 2, VX_R2_MIN_BLOCKS_LN), 256, 0, st>>>(p);
-    else rows2_kernel<FMT, false><<<grid_for_rows((p.M + 1) / 2, VX_R2_MIN_BLOCKS), 256, 0, st>>>(p);
+    if (ln) launch_dependent(rows2_kernel<FMT, true>, dim3(grid_for_rows((p.M + 1) / 2, VX_R2_MIN_BLOCKS_LN)), dim3(256), 0, st, p);
+    else launch_dependent(rows2_kernel<FMT, false>, dim3(grid_for_rows((p.M + 1) / 2, VX_R2_MIN_BLOCKS)), dim3(256), 0, st, p);
     return true;
   } else {
     return false;
