@@ -259,7 +259,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 // NV16 = false: one UE8M0 scale for the 32 values; true: two E4M3 scales (16 values each).
 // Returns the scale byte(s), little end first.
 // Eight accumulator values r[8 g .. 8 g + 7] -> (* tensor scales) + bias -> Swish, as four packed pairs.
-template <bool NV16>
+template <bool NV16, bool BIAS>
 __device__ __forceinline__ void swish_group8(const uint32_t (&r)[32], int g, const float* bias_s, bool scale_acc,
                                              uint64_t g2, uint64_t (&out)[4]) {
 #pragma unroll
@@ -271,7 +271,7 @@ __device__ __forceinline__ void swish_group8(const uint32_t (&r)[32], int g, con
       za = mul_f32x2(za, g2);
       zb = mul_f32x2(zb, g2);
     }
-    if (bias_s) {
+    if constexpr (BIAS) {
       const float4 b = *reinterpret_cast<const float4*>(bias_s + 4 * q4);
       za = add_f32x2(za, pack_f32x2(b.x, b.y));
       zb = add_f32x2(zb, pack_f32x2(b.z, b.w));
@@ -330,12 +330,23 @@ __device__ __forceinline__ uint32_t swish_quant_chunk(const uint32_t (&r)[32], c
                                                       float g_ab, float g_out, uint32_t (&w)[4]) {
   uint64_t sv[16];
   const uint64_t g2 = pack_f32x2(g_ab, g_ab);
+  // (the bias test once per chunk, not once per four values: the epilogue is bound by instruction issue)
+  if (bias_s) {
 #pragma unroll
-  for (int g = 0; g < 4; ++g) {
-    uint64_t o[4];
-    swish_group8<NV16>(r, g, bias_s, scale_acc, g2, o);
+    for (int g = 0; g < 4; ++g) {
+      uint64_t o[4];
+      swish_group8<NV16, true>(r, g, bias_s, scale_acc, g2, o);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) sv[4 * g + j] = o[j];
+      for (int j = 0; j < 4; ++j) sv[4 * g + j] = o[j];
+    }
+  } else {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      uint64_t o[4];
+      swish_group8<NV16, false>(r, g, bias_s, scale_acc, g2, o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) sv[4 * g + j] = o[j];
+    }
   }
   float rcp0, rcp1;
   const uint32_t sbytes = chunk_scales_p<NV16>(sv, g_out, rcp0, rcp1);
