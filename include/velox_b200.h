@@ -190,6 +190,19 @@ int64_t vx_ctc_lse_parts(int64_t N);
 int vx_ctc_finish(const void* keys, const void* lse_partials, int64_t N, int64_t M, int32_t* ids, float* max_out,
                   float* lse_out, float* logp_out, void* stream);
 
+/* Relative-position attention on the folded operands of the attention fold pack (vx_qkv_pack or the
+ * fold-pack epilogue of the QKV GEMM): replaces
+ *   scaled_dot_product_attention(q2, k2, v2, scale = 1.0)[..., :dk].transpose(1, 2).reshape(T, d)
+ * of the encoder's attention (veloxvoice/models/wenet/torch_conformer.py:514-519; the reference's own
+ * kernel for its chunked lane is veloxvoice/kernels/csrc/velox_chunk_rel_pos_attn.cu:23-114).
+ *   q2, k2, v2: bf16 [heads, T, 2 head_dim] contiguous; the second half of v2 is not read;
+ *   out[t, h head_dim + c] = sum_j softmax_j(q2[h, t, :] . k2[h, j, :]) v2[h, j, c], keys j < kv_len
+ *   (kv_len <= 0 or > T: all T keys); out bf16 [T, >= heads head_dim], row stride ldo elements.
+ * tcgen05 bf16 MMAs with fp32 accumulation, probabilities rounded to bf16 for the second product, like
+ * the fused attention kernels torch dispatches to.  head_dim must be 64. */
+int vx_relpos_attention(const void* q2, const void* k2, const void* v2, int64_t T, int heads, int head_dim,
+                        int64_t kv_len, void* out, int64_t ldo, void* stream);
+
 /* Filterbank projection of the audio front-end in one pass: replaces power_mel_log
  * (veloxvoice/kernels/ops/cuda_ops.py:95-135; kernel veloxvoice/kernels/csrc/dgx/dgx_power_mel_log.cu:20-79,
  * dgx/block/nv_block_power_mel_log.h:35-190) and the formula of reference_power_mel_log (cuda_ops.py:195-202):

@@ -85,6 +85,13 @@ def test_argument_errors_do_not_need_a_device(lib):
     assert lib.vx_power_mel_log(*mel_args(mean=C.c_void_p(2048))) == -1 and b"together" in lib.vx_last_error()
     assert lib.vx_power_mel_log(*mel_args(ld=32)) == -1
     assert lib.vx_power_mel_log(*mel_args(ldo=8)) == -1
+    # attention: head dimension, NULL operands, alignment
+    assert lib.vx_relpos_attention(C.c_void_p(256), C.c_void_p(512), C.c_void_p(768), 0, 8, 64, 0, C.c_void_p(1024), 512, None) == 0
+    assert lib.vx_relpos_attention(C.c_void_p(256), C.c_void_p(512), C.c_void_p(768), 16, 8, 32, 0, C.c_void_p(1024), 512, None) == -1
+    assert b"head_dim" in lib.vx_last_error()
+    assert lib.vx_relpos_attention(None, C.c_void_p(512), C.c_void_p(768), 16, 8, 64, 0, C.c_void_p(1024), 512, None) == -1
+    assert lib.vx_relpos_attention(C.c_void_p(258), C.c_void_p(512), C.c_void_p(768), 16, 8, 64, 0, C.c_void_p(1024), 512, None) == -1
+    assert lib.vx_relpos_attention(C.c_void_p(256), C.c_void_p(512), C.c_void_p(768), 16, 8, 64, 0, C.c_void_p(1024), 100, None) == -1
 
 
 def _gemm_desc(lib, fmt=_lib.FMT_MX32, epi=_lib.EPI_NONE, flags=0):

@@ -55,6 +55,7 @@ EXPORTS = (
     "vx_ctc_finish",
     "vx_power_mel_log_supported",
     "vx_power_mel_log",
+    "vx_relpos_attention",
 )
 
 
@@ -164,6 +165,8 @@ def load(build_if_missing: bool = True) -> C.CDLL:
         lib.vx_power_mel_log_supported.argtypes = [i64, i64]
         lib.vx_power_mel_log.restype = i32
         lib.vx_power_mel_log.argtypes = [vp, i64, i64, i64, vp, i64, i64, vp, vp, vp, i64, vp]
+        lib.vx_relpos_attention.restype = i32
+        lib.vx_relpos_attention.argtypes = [vp, vp, vp, i64, i32, i32, i64, vp, i64, vp]
         lib.vx_set_trace_buffer.restype = i32
         lib.vx_set_trace_buffer.argtypes = [vp, i64]
         lib.vx_wait_selftest.restype = i32

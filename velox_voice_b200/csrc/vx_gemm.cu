@@ -39,6 +39,7 @@
 #include "vx_common.cuh"
 #include "vx_ptx.cuh"
 #include "vx_quant_math.cuh"
+#include "vx_tmap.cuh"
 
 namespace vx {
 namespace {
@@ -1833,6 +1834,12 @@ int dispatch_epi(int epi, int out, const CUtensorMap& ta, const CUtensorMap& tb,
 }
 
 }  // namespace
+
+int make_tmap_2d(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, int64_t rows, int64_t cols, int64_t pitch_bytes,
+                 int box_cols, int box_rows) {
+  return make_tmap(m, dt, 0, ptr, rows, cols, pitch_bytes, box_cols, box_rows);
+}
+
 }  // namespace vx
 
 extern "C" {

@@ -4,6 +4,7 @@
     python -m velox_voice_b200.opbench                     # every launch of one Conformer block + CTC
     python -m velox_voice_b200.opbench --ops ffn-up        # only launches whose name contains "ffn-up"
     python -m velox_voice_b200.opbench --ops mel           # the front-end's filterbank projection (4 x frames rows)
+    python -m velox_voice_b200.opbench --ops attention     # one 3,750-frame span of the rel-pos attention, and torch's SDPA
     python -m velox_voice_b200.opbench --configs           # the three single-GPU benchmark configurations
     python -m velox_voice_b200.opbench --frames 11250 --fmt nv16
 
@@ -106,6 +107,17 @@ def op_breakdown(stack, T, fmt_name, only=""):
         mean, istd = torch.randn(Mm, device=dev), torch.rand(Mm, device=dev) + 0.5
         add(f"power_mel_log [{Tm} x {Fm}] -> {Mm} mel (tf32)", 0, lambda: ops.power_mel_log_tf32(spec, bank, mean, istd),
             Tm * Fm * 8 + Tm * Mm * 4 + Mm * Fm * 4, 2 * Tm * Fm * Mm)
+    if only and "attention" in only:
+        # one span of one layer (not part of the linear-stack step): 3,750 frames, 8 heads of 64, on the fold pack
+        Ta, h, dk = 3750, 8, 64
+        q2 = (torch.randn(h, Ta, 2 * dk, device=dev) * 0.25).bfloat16()
+        k2 = torch.randn(h, Ta, 2 * dk, device=dev).bfloat16()
+        v2 = torch.randn(h, Ta, 2 * dk, device=dev).bfloat16()
+        fl = 2 * h * Ta * Ta * (2 * dk + dk)
+        nbytes = 3 * h * Ta * 2 * dk * 2 + Ta * h * dk * 2
+        add(f"relpos attention [{h} x {Ta} x {2 * dk}] (tcgen05 bf16)", 0, lambda: ops.relpos_attention(q2, k2, v2), nbytes, fl)
+        add("relpos attention, torch scaled_dot_product_attention on the same tensors", 0,
+            lambda: torch.nn.functional.scaled_dot_product_attention(q2[None], k2[None], v2[None], scale=1.0), nbytes, fl)
     del flush
     return cases
 

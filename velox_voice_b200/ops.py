@@ -496,6 +496,33 @@ def qkv_pack(qkv: torch.Tensor, p0: torch.Tensor, pos_u: torch.Tensor, pos_v: to
     return packed[0], packed[1], packed[2]
 
 
+def relpos_attention(q2: torch.Tensor, k2: torch.Tensor, v2: torch.Tensor, kv_len: Optional[int] = None,
+                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The encoder's relative-position attention on the fold pack: q2, k2, v2 bf16 [h, T, 2 dk] (what
+    ``qkv_pack`` / ``bsgemm_qkv_pack`` + ``bsgemm_heads`` produce) -> bf16 [T, h dk], i.e.
+    ``scaled_dot_product_attention(q2, k2, v2, scale=1.0)[..., :dk].transpose(0, 1).reshape(T, h * dk)``
+    of ``veloxvoice/models/wenet/torch_conformer.py:514-519`` in one launch (``vx_relpos_attention``);
+    keys at and beyond ``kv_len`` are masked (a padded span)."""
+    for t, n in ((q2, "q2"), (k2, "k2"), (v2, "v2")):
+        _require_cuda(t, n)
+        if t.dtype != torch.bfloat16 or t.dim() != 3 or t.shape != q2.shape or t.device != q2.device:
+            raise ValueError("q2, k2, v2 must be bfloat16 [heads, T, 2 head_dim] tensors of one shape on one device")
+    h, T, d2 = q2.shape
+    dk = d2 // 2
+    if d2 != 128:
+        raise ValueError(f"head_dim must be 64 (folded 128), got {dk}")
+    q2, k2, v2 = q2.contiguous(), k2.contiguous(), v2.contiguous()
+    if out is None:
+        out = torch.empty((T, h * dk), dtype=torch.bfloat16, device=q2.device)
+    elif out.dtype != torch.bfloat16 or out.dim() != 2 or out.shape[0] != T or out.shape[1] < h * dk or out.stride(1) != 1:
+        raise ValueError("out must be bfloat16 [T, >= heads * head_dim] with unit column stride")
+    rc = _lib.load().vx_relpos_attention(q2.data_ptr(), k2.data_ptr(), v2.data_ptr(), T, h, dk,
+                                         0 if kv_len is None else int(kv_len), out.data_ptr(), out.stride(0), _stream())
+    _lib.check(rc, "vx_relpos_attention")
+    _count()
+    return out
+
+
 def bsgemm_qkv_pack(a: Quantized, w_qkv: Quantized, bias: Optional[torch.Tensor], pos_u: torch.Tensor,
                     pos_v: torch.Tensor, scale: float, *, packed: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Fused QKV projection written straight into the attention fold pack (``qkv_pack`` of the
