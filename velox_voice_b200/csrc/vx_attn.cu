@@ -11,7 +11,7 @@
 //
 // One CTA = 128 queries of one head, all on the 5th-generation tensor cores (tcgen05.mma kind::f16, bf16
 // operands, fp32 accumulators in tensor memory):
-//   warp 0      TMA producer: Q once, then K (and V) tiles of 128 keys through a two-stage ring;
+//   warp 0      TMA producer: Q once, then K (and V) tiles of 128 keys through a three-stage ring;
 //   warp 1      MMA issuer: S = Q K^T (128 x 128 x 128) into one of two S accumulators, O += P V
 //               (128 x 64 x 128; V is read in its natural [key][dv] layout as an MN-major operand);
 //   warps 2..9  softmax, one query row per thread straight out of tensor memory; two warps share a row
@@ -46,7 +46,8 @@ constexpr int AT_K_BYTES = 2 * AT_PANEL;          // 32 KB
 constexpr int AT_V_BYTES = AT_BN * AT_DV * 2;     // 16 KB
 constexpr int AT_STAGE = AT_K_BYTES + AT_V_BYTES; // 48 KB
 constexpr int AT_P_BYTES = 2 * AT_PANEL;          // 32 KB
-constexpr int AT_SMEM = AT_Q_BYTES + 2 * AT_STAGE + AT_P_BYTES + 1024;
+constexpr int AT_NS = 3;                          // K / V stages in flight
+constexpr int AT_SMEM = AT_Q_BYTES + AT_NS * AT_STAGE + AT_P_BYTES + 1024;
 constexpr int AT_SOFTMAX_WARPS = 8;  // two per 32-row quadrant of tensor memory: 64 of a tile's 128 keys each
 constexpr int AT_THREADS = (2 + AT_SOFTMAX_WARPS) * 32;
 constexpr uint32_t AT_TM_S = 0, AT_TM_O = 256;    // S0 | S1 (128 columns each) | O (64 columns)
@@ -61,7 +62,7 @@ struct AttnParams {
 };
 
 struct AttnBarriers {
-  uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, p_empty, o_full;
+  uint64_t q_full, kv_full[AT_NS], kv_empty[AT_NS], s_full[2], s_empty[2], p_full, p_empty, o_full;
   uint32_t tmem_base;
   float xch[2][AT_BM];  // row maxima, later row sums, of the two warps that share a row
 };
@@ -104,8 +105,8 @@ relpos_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   uint8_t* const base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* const q_s = base;
-  uint8_t* const st_s = base + AT_Q_BYTES;        // two stages of [K | V]
-  uint8_t* const p_s = st_s + 2 * AT_STAGE;
+  uint8_t* const st_s = base + AT_Q_BYTES;        // AT_NS stages of [K | V]
+  uint8_t* const p_s = st_s + AT_NS * AT_STAGE;
   __shared__ AttnBarriers bar;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.y;
@@ -116,9 +117,11 @@ relpos_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
   if (threadIdx.x == 0) {
     mbar_init(&bar.q_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < AT_NS; ++s) {
       mbar_init(&bar.kv_full[s], 1);
       mbar_init(&bar.kv_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(&bar.s_full[s], 1);
       mbar_init(&bar.s_empty[s], AT_SOFTMAX_WARPS);
     }
@@ -146,9 +149,9 @@ relpos_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tma_load_2d(q_s, &tm_q, 0, row_base + static_cast<int>(q0), &bar.q_full);
       tma_load_2d(q_s + AT_PANEL, &tm_q, 64, row_base + static_cast<int>(q0), &bar.q_full);
       for (int it = 0; it < iters; ++it) {
-        const int s = it & 1, j = it % nkb;
+        const int s = it % AT_NS, j = it % nkb;
         const bool pass2 = it >= nkb;
-        if (!mbar_wait(&bar.kv_empty[s], ((it >> 1) & 1) ^ 1, p.status, 20)) break;
+        if (!mbar_wait(&bar.kv_empty[s], ((it / AT_NS) & 1) ^ 1, p.status, 20)) break;
         uint8_t* const dst = st_s + s * AT_STAGE;
         mbar_expect_tx(&bar.kv_full[s], AT_K_BYTES + (pass2 ? AT_V_BYTES : 0));
         tma_load_2d(dst, &tm_k, 0, row_base + j * AT_BN, &bar.kv_full[s]);
@@ -165,19 +168,19 @@ relpos_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     bool ok = mbar_wait_spin(&bar.q_full, 0, p.status, 21);
     // S(it) = Q K_j^T into accumulator it & 1
     auto issue_s = [&](int it) {
-      const int s = it & 1;
-      if (!mbar_wait_spin(&bar.kv_full[s], (it >> 1) & 1, p.status, 22)) return false;
+      const int s = it & 1, ks = it % AT_NS;  // S accumulator, K / V stage
+      if (!mbar_wait_spin(&bar.kv_full[ks], (it / AT_NS) & 1, p.status, 22)) return false;
       if (!mbar_wait_spin(&bar.s_empty[s], ((it >> 1) & 1) ^ 1, p.status, 23)) return false;
       tc_fence_after();
       if (leader) {
-        const uint32_t k_u32 = st_u32 + s * AT_STAGE;
+        const uint32_t k_u32 = st_u32 + ks * AT_STAGE;
 #pragma unroll
         for (int i = 0; i < AT_D / 16; ++i) {
           const uint32_t off = (i >> 2) * AT_PANEL + (i & 3) * 32;
           mma_bf16(tmem_base + AT_TM_S + s * 128, make_desc_k128(q_u32 + off), make_desc_k128(k_u32 + off), idesc_s, i != 0);
         }
         tc_commit(&bar.s_full[s]);
-        if (it < nkb) tc_commit(&bar.kv_empty[s]);  // pass 1: the stage holds K only
+        if (it < nkb) tc_commit(&bar.kv_empty[ks]);  // pass 1: the stage holds K only
       }
       __syncwarp();
       return true;
@@ -191,7 +194,7 @@ relpos_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (!mbar_wait_spin(&bar.p_full, n & 1, p.status, 24)) { ok = false; break; }
         tc_fence_after();
         if (leader) {
-          const uint32_t v_u32 = st_u32 + (it & 1) * AT_STAGE + AT_K_BYTES;
+          const uint32_t v_u32 = st_u32 + (it % AT_NS) * AT_STAGE + AT_K_BYTES;
 #pragma unroll
           for (int i = 0; i < AT_BN / 16; ++i) {
             const uint32_t aoff = (i >> 2) * AT_PANEL + (i & 3) * 32;
@@ -202,7 +205,7 @@ relpos_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                      idesc_o, (n | i) != 0);
           }
           tc_commit(&bar.p_empty);
-          tc_commit(&bar.kv_empty[it & 1]);
+          tc_commit(&bar.kv_empty[it % AT_NS]);
           if (it == iters - 1) tc_commit(&bar.o_full);
         }
         __syncwarp();
@@ -251,20 +254,23 @@ relpos_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           __syncwarp();
           if (lane == 0) mbar_arrive(&bar.s_empty[b]);
         }
+        if (n_valid < AT_BN) {
+          // the last tile of a span whose length is not a multiple of 128: keys beyond kv_len count as -inf
+          // (2^(-inf) = 0 in the second pass); whole tiles skip the tests
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i >= n_valid) r[i] = 0xff800000u;
+        }
         if (!pass2) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float v = (c * 32 + i < n_valid) ? __uint_as_float(r[i]) : NEG_INF;
-            m4[i & 3] = fmaxf(m4[i & 3], v);
-          }
+          for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(r[i]));
         } else {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             float e[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-              const int k = c * 32 + g * 8 + i;
-              e[i] = (k < n_valid) ? ex2f(__fmaf_rn(__uint_as_float(r[g * 8 + i]), L2E, nml)) : 0.0f;
+              e[i] = ex2f(__fmaf_rn(__uint_as_float(r[g * 8 + i]), L2E, nml));
               l4[i & 3] += e[i];
             }
             const int c8 = c * 4 + g;  // 16-byte chunk of the row: 8 keys
