@@ -16,10 +16,13 @@
 //               (128 x 64 x 128; V is read in its natural [key][dv] layout as an MN-major operand);
 //   warps 2..9  softmax, one query row per thread straight out of tensor memory; two warps share a row
 //               (64 of a tile's 128 keys each) and exchange their maxima / sums through shared memory once.
-// Two passes over the keys: the first only takes the row maxima (S is recomputed in the second, which is
-// cheap next to keeping O rescaled: no accumulator ever has to be read back and corrected); the second
-// forms p = 2^((s - m) log2 e), adds it up in fp32, writes P as bf16 into the swizzled K-major tile the
-// P V product reads, and the O accumulator is divided by the row sum once at the end.
+// One pass over the keys with a lazily updated reference maximum: p = 2^((s - m_ref) log2 e) is formed
+// against the reference m_ref the row has used so far, which only moves when a tile's maximum exceeds it by
+// more than 2^8 (so p never exceeds 256 and nothing overflows in bf16 or fp32).  When it moves -- typically in
+// the first tiles of a row only -- the row sum and the row's part of the O accumulator in tensor memory are
+// multiplied by 2^((m_old - m_new) log2 e) (tcgen05.ld / tcgen05.st of 32 columns per warp) before the next
+// P V product is released.  P is written as bf16 into the swizzled K-major tile the P V product reads; O is
+// divided by the row sum once at the end.
 // Every mbarrier wait is bounded.
 
 #include <cuda.h>
@@ -64,7 +67,7 @@ struct AttnParams {
 struct AttnBarriers {
   uint64_t q_full, kv_full[AT_NS], kv_empty[AT_NS], s_full[2], s_empty[2], p_full, p_empty, o_full;
   uint32_t tmem_base;
-  float xch[2][AT_BM];  // row maxima, later row sums, of the two warps that share a row
+  float xch[2][2][AT_BM];  // [tile parity][half][row]: tile maxima (finally row sums) of the two warps that share a row
 };
 
 // bf16 x bf16 -> fp32, A K-major; B K-major or MN-major (b_mn)
@@ -89,6 +92,18 @@ __device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr, uint32_t
   d |= static_cast<uint64_t>(2) << 61;
   return d;
 }
+__device__ __forceinline__ void tc_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ float ex2f(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -112,7 +127,7 @@ relpos_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const int head = blockIdx.y;
   const int64_t q0 = static_cast<int64_t>(blockIdx.x) * AT_BM;
   const int nkb = static_cast<int>((p.kv_len + AT_BN - 1) / AT_BN);
-  const int iters = 2 * nkb;                      // pass 1 (maxima), pass 2 (P, O)
+  const int iters = nkb;
   const int row_base = static_cast<int>(head * p.T);  // this head's token 0 in the [heads * T, 128] views
 
   if (threadIdx.x == 0) {
@@ -149,14 +164,13 @@ relpos_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tma_load_2d(q_s, &tm_q, 0, row_base + static_cast<int>(q0), &bar.q_full);
       tma_load_2d(q_s + AT_PANEL, &tm_q, 64, row_base + static_cast<int>(q0), &bar.q_full);
       for (int it = 0; it < iters; ++it) {
-        const int s = it % AT_NS, j = it % nkb;
-        const bool pass2 = it >= nkb;
+        const int s = it % AT_NS, j = it;
         if (!mbar_wait(&bar.kv_empty[s], ((it / AT_NS) & 1) ^ 1, p.status, 20)) break;
         uint8_t* const dst = st_s + s * AT_STAGE;
-        mbar_expect_tx(&bar.kv_full[s], AT_K_BYTES + (pass2 ? AT_V_BYTES : 0));
+        mbar_expect_tx(&bar.kv_full[s], AT_K_BYTES + AT_V_BYTES);
         tma_load_2d(dst, &tm_k, 0, row_base + j * AT_BN, &bar.kv_full[s]);
         tma_load_2d(dst + AT_PANEL, &tm_k, 64, row_base + j * AT_BN, &bar.kv_full[s]);
-        if (pass2) tma_load_2d(dst + AT_K_BYTES, &tm_v, 0, row_base + j * AT_BN, &bar.kv_full[s]);
+        tma_load_2d(dst + AT_K_BYTES, &tm_v, 0, row_base + j * AT_BN, &bar.kv_full[s]);
       }
     }
   } else if (warp == 1) {
@@ -180,7 +194,6 @@ relpos_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           mma_bf16(tmem_base + AT_TM_S + s * 128, make_desc_k128(q_u32 + off), make_desc_k128(k_u32 + off), idesc_s, i != 0);
         }
         tc_commit(&bar.s_full[s]);
-        if (it < nkb) tc_commit(&bar.kv_empty[ks]);  // pass 1: the stage holds K only
       }
       __syncwarp();
       return true;
@@ -189,8 +202,8 @@ relpos_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     for (int it = 0; it < iters && ok; ++it) {
       if (it + 1 < iters) ok = issue_s(it + 1);
       if (!ok) break;
-      if (it >= nkb) {
-        const int n = it - nkb;
+      {
+        const int n = it;
         if (!mbar_wait_spin(&bar.p_full, n & 1, p.status, 24)) { ok = false; break; }
         tc_fence_after();
         if (leader) {
@@ -213,77 +226,99 @@ relpos_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     }
   } else {
     // =========================== softmax: warps 2..9 ===========================
-    // warp -> (quadrant q of tensor memory = rows 32 q .. 32 q + 31, half of the tile's keys)
+    // warp -> (quadrant q of tensor memory = rows 32 q .. 32 q + 31, half of the tile's keys / of O's columns)
     const int q = warp & 3, half = (warp - 2) >> 2;
     const int row = q * 32 + lane;
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     constexpr float L2E = 1.4426950408889634f;
     const float NEG_INF = __int_as_float(0xff800000);
-    float m4[4] = {NEG_INF, NEG_INF, NEG_INF, NEG_INF}, l4[4] = {0.0f, 0.0f, 0.0f, 0.0f}, nml = 0.0f;
+    float m_ref = NEG_INF;  // reference maximum of the row, in units of log2 (s * log2 e)
+    float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     auto softmax_sync = [] { asm volatile("bar.sync 1, %0;" ::"n"(AT_SOFTMAX_WARPS * 32) : "memory"); };
     bool ok = true;
-    bool exchanged = false;  // whether this thread went through the two barriers of the maxima exchange
+    int syncs = 0;  // named barriers this thread has executed (every softmax thread executes nkb + 1 of them)
     for (int it = 0; it < iters && ok; ++it) {
-      const int b = it & 1, j = it % nkb;
-      const bool pass2 = it >= nkb;
-      if (it == nkb) {
-        exchanged = true;
-        // end of pass 1: the row maximum over both halves
-        const float mine = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-        bar.xch[half][row] = mine;
-        softmax_sync();
-        nml = -fmaxf(mine, bar.xch[half ^ 1][row]) * L2E;
-        softmax_sync();  // xch is used again for the sums
-      }
+      const int b = it & 1;
       if (lane == 0) {
         ok = mbar_wait(&bar.s_full[b], (it >> 1) & 1, p.status, 25);
-        if (ok && pass2) ok = mbar_wait(&bar.p_empty, ((it - nkb) & 1) ^ 1, p.status, 26);
+        // P V of the previous tile is complete: the P tile may be overwritten and O may be corrected
+        if (ok) ok = mbar_wait(&bar.p_empty, (it & 1) ^ 1, p.status, 26);
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       tc_fence_after();
-      const int n_valid = static_cast<int>(p.kv_len - static_cast<int64_t>(j) * AT_BN);  // >= 128: the whole tile
-#pragma unroll 1
+      const int n_valid = static_cast<int>(p.kv_len - static_cast<int64_t>(it) * AT_BN);  // >= 128: the whole tile
+      // this warp's 64 keys of the tile, scaled to log2 units
+      float t[2][32];
+#pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
-        const int c = half * 2 + cc;  // 32-key chunk of the tile
         uint32_t r[32];
-        tc_ld_32x32b_x32(lane_addr + AT_TM_S + b * 128 + c * 32, r);
+        tc_ld_32x32b_x32(lane_addr + AT_TM_S + b * 128 + (half * 2 + cc) * 32, r);
         tc_wait_ld();
-        if (cc == 1) {  // this warp's part of S is in registers
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&bar.s_empty[b]);
-        }
-        if (n_valid < AT_BN) {
-          // the last tile of a span whose length is not a multiple of 128: keys beyond kv_len count as -inf
-          // (2^(-inf) = 0 in the second pass); whole tiles skip the tests
+#pragma unroll
+        for (int i = 0; i < 32; ++i) t[cc][i] = __uint_as_float(r[i]) * L2E;
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar.s_empty[b]);  // S is in registers: the accumulator may be overwritten
+      if (n_valid < AT_BN) {
+        // the last tile of a span whose length is not a multiple of 128: keys beyond kv_len count as -inf
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (c * 32 + i >= n_valid) r[i] = 0xff800000u;
+            if ((half * 2 + cc) * 32 + i >= n_valid) t[cc][i] = NEG_INF;
+      }
+      float m4[4] = {NEG_INF, NEG_INF, NEG_INF, NEG_INF};
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], t[cc][i]);
+      const float mine = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      bar.xch[it & 1][half][row] = mine;
+      softmax_sync();
+      ++syncs;
+      const float m_tile = fmaxf(mine, bar.xch[it & 1][half ^ 1][row]);
+      // The reference of a row moves when the tile's maximum exceeds it by more than 8 (both warps of a row
+      // decide alike: same lanes, same values).  Then the row sum and this warp's 32 columns of O are scaled by
+      // 2^(m_ref - m_tile).  The tensor-memory accesses are warp-wide, so the warp goes through them when any of
+      // its rows moves; the other rows scale by one.  Before the first P V product there is nothing to scale.
+      const bool moves = m_tile > m_ref + 8.0f;
+      if (__any_sync(0xffffffffu, moves)) {
+        const float alpha = moves ? ex2f(m_ref - m_tile) : 1.0f;  // 0 for m_ref = -inf
+        if (moves) m_ref = m_tile;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) l4[i] *= alpha;
+        if (it > 0) {
+          uint32_t o[32];
+          tc_ld_32x32b_x32(lane_addr + AT_TM_O + half * 32, o);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tc_st_32x32b_x32(lane_addr + AT_TM_O + half * 32, o);
+          tc_wait_st();
         }
-        if (!pass2) {
+      }
 #pragma unroll
-          for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(r[i]));
-        } else {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            float e[8];
+        for (int g = 0; g < 4; ++g) {
+          float e[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              e[i] = ex2f(__fmaf_rn(__uint_as_float(r[g * 8 + i]), L2E, nml));
-              l4[i & 3] += e[i];
-            }
-            const int c8 = c * 4 + g;  // 16-byte chunk of the row: 8 keys
-            uint8_t* dst = p_s + (c8 >> 3) * AT_PANEL + row * 128 + (((c8 & 7) ^ (row & 7)) << 4);
-            *reinterpret_cast<uint4*>(dst) = make_uint4(bf16x2(e[0], e[1]), bf16x2(e[2], e[3]), bf16x2(e[4], e[5]), bf16x2(e[6], e[7]));
+          for (int i = 0; i < 8; ++i) {
+            e[i] = ex2f(t[cc][g * 8 + i] - m_ref);
+            l4[i & 3] += e[i];
           }
+          const int c8 = c * 4 + g;  // 16-byte chunk of the row: 8 keys
+          uint8_t* dst = p_s + (c8 >> 3) * AT_PANEL + row * 128 + (((c8 & 7) ^ (row & 7)) << 4);
+          *reinterpret_cast<uint4*>(dst) = make_uint4(bf16x2(e[0], e[1]), bf16x2(e[2], e[3]), bf16x2(e[4], e[5]), bf16x2(e[6], e[7]));
         }
       }
-      if (pass2) {
-        fence_proxy_async_smem();  // P written by the generic proxy -> visible to the tensor core
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bar.p_full);
-      }
+      tc_fence_before();         // O corrections before the P V product that the arrival below releases
+      fence_proxy_async_smem();  // P written by the generic proxy -> visible to the tensor core
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar.p_full);
     }
     // O / l -> bf16 -> out[t, head * dk + :]; this warp stores 32 of the 64 value columns
     if (ok) {
@@ -291,21 +326,20 @@ relpos_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       ok = __shfl_sync(0xffffffffu, ok, 0);
     }
     // Every softmax thread executes the same number of named barriers whatever happened above: a warp whose
-    // bounded wait ran out before the maxima exchange makes up for its two barriers here, so that the others
-    // cannot be left waiting for it.
-    if (!exchanged) { softmax_sync(); softmax_sync(); }
+    // bounded wait ran out makes up for the ones it skipped, so that the others cannot be left waiting for it.
+    while (syncs < iters) { softmax_sync(); ++syncs; }
     const float lmine = (l4[0] + l4[1]) + (l4[2] + l4[3]);
-    bar.xch[half][row] = lmine;
+    bar.xch[iters & 1][half][row] = lmine;
     softmax_sync();
-    const float inv = 1.0f / (lmine + bar.xch[half ^ 1][row]);
+    const float inv = 1.0f / (lmine + bar.xch[iters & 1][half ^ 1][row]);
     if (ok) {
       tc_fence_after();
-      const int64_t t = q0 + row;
+      const int64_t tq = q0 + row;
       uint32_t r[32];
       tc_ld_32x32b_x32(lane_addr + AT_TM_O + half * 32, r);
       tc_wait_ld();
-      if (t < p.T) {
-        uint4* dst = reinterpret_cast<uint4*>(p.out + t * p.ldo + head * AT_DV + half * 32);
+      if (tq < p.T) {
+        uint4* dst = reinterpret_cast<uint4*>(p.out + tq * p.ldo + head * AT_DV + half * 32);
 #pragma unroll
         for (int g = 0; g < 4; ++g)
           dst[g] = make_uint4(bf16x2(__uint_as_float(r[8 * g]) * inv, __uint_as_float(r[8 * g + 1]) * inv),
