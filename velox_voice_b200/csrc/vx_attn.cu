@@ -239,11 +239,7 @@ relpos_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     int syncs = 0;  // named barriers this thread has executed (every softmax thread executes nkb + 1 of them)
     for (int it = 0; it < iters && ok; ++it) {
       const int b = it & 1;
-      if (lane == 0) {
-        ok = mbar_wait(&bar.s_full[b], (it >> 1) & 1, p.status, 25);
-        // P V of the previous tile is complete: the P tile may be overwritten and O may be corrected
-        if (ok) ok = mbar_wait(&bar.p_empty, (it & 1) ^ 1, p.status, 26);
-      }
+      if (lane == 0) ok = mbar_wait(&bar.s_full[b], (it >> 1) & 1, p.status, 25);
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       tc_fence_after();
@@ -284,32 +280,40 @@ relpos_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       // 2^(m_ref - m_tile).  The tensor-memory accesses are warp-wide, so the warp goes through them when any of
       // its rows moves; the other rows scale by one.  Before the first P V product there is nothing to scale.
       const bool moves = m_tile > m_ref + 8.0f;
-      if (__any_sync(0xffffffffu, moves)) {
-        const float alpha = moves ? ex2f(m_ref - m_tile) : 1.0f;  // 0 for m_ref = -inf
-        if (moves) m_ref = m_tile;
+      const bool any_moves = __any_sync(0xffffffffu, moves);
+      const float alpha = moves ? ex2f(m_ref - m_tile) : 1.0f;  // 0 for m_ref = -inf
+      if (moves) m_ref = m_tile;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) l4[i] *= alpha;
-        if (it > 0) {
-          uint32_t o[32];
-          tc_ld_32x32b_x32(lane_addr + AT_TM_O + half * 32, o);
-          tc_wait_ld();
+      for (int i = 0; i < 4; ++i) l4[i] *= alpha;
+      // the exponentials (the special-function unit is the busiest pipe here) run while the tensor core is still
+      // on the previous tile's P V product
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tc_st_32x32b_x32(lane_addr + AT_TM_O + half * 32, o);
-          tc_wait_st();
+      for (int cc = 0; cc < 2; ++cc)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          t[cc][i] = ex2f(t[cc][i] - m_ref);
+          l4[i & 3] += t[cc][i];
         }
+      // P V of the previous tile complete: the P tile may be overwritten and O may be corrected
+      if (lane == 0) ok = mbar_wait(&bar.p_empty, (it & 1) ^ 1, p.status, 26);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      if (any_moves && it > 0) {
+        tc_fence_after();
+        uint32_t o[32];
+        tc_ld_32x32b_x32(lane_addr + AT_TM_O + half * 32, o);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+        tc_st_32x32b_x32(lane_addr + AT_TM_O + half * 32, o);
+        tc_wait_st();
       }
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int c = half * 2 + cc;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          float e[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            e[i] = ex2f(t[cc][g * 8 + i] - m_ref);
-            l4[i & 3] += e[i];
-          }
+          const float* e = &t[cc][g * 8];
           const int c8 = c * 4 + g;  // 16-byte chunk of the row: 8 keys
           uint8_t* dst = p_s + (c8 >> 3) * AT_PANEL + row * 128 + (((c8 & 7) ^ (row & 7)) << 4);
           *reinterpret_cast<uint4*>(dst) = make_uint4(bf16x2(e[0], e[1]), bf16x2(e[2], e[3]), bf16x2(e[4], e[5]), bf16x2(e[6], e[7]));
