@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define VX_ABI_VERSION 3
+#define VX_ABI_VERSION 4
 
 /* Quantization formats.  values / scale / natural scale layout
  *  ROWSCALE   E2M1, one UE8M0 per row                      u8 [R]
@@ -152,6 +152,11 @@ typedef struct vx_gemm_desc {
   float qk_scale;       /* BIAS_QKVPACK: scale applied to q + bias */
   int32_t head_col_off; /* VX_GEMM_OUT_HEADS: first column inside the head row (0 or head_dim) */
   void* lse_partials;   /* BIAS_ARGMAX, FP4 formats: optional f32 pairs [vx_ctc_lse_parts(N)][M], see vx_ctc_finish */
+  const float* topk_threshold; /* BIAS_ARGMAX with lse_partials: optional f32 [M]; every bf16-rounded logit >= its row's    */
+  void* topk_candidates;       /*   threshold is appended to that row's list: u64 [M][topk_capacity] =                      */
+  int32_t* topk_count;         /*   (order-preserving logit bits << 32) | (0xFFFFFFFF - column); i32 [M], zeroed by the caller */
+  int32_t topk_capacity;       /*   entries per row; appends beyond it are counted but not stored (see vx_ctc_topk_finish)  */
+  int32_t reserved0;
 } vx_gemm_desc;
 
 /* VX_EPI_BIAS_GLU expects the rows of B (and the bias) interleaved per tile of vx_glu_tile(fmt)
@@ -217,6 +222,20 @@ int vx_relpos_attention(const void* q2, const void* k2, const void* v2, int64_t 
 int vx_power_mel_log_supported(int64_t F, int64_t M);
 int vx_power_mel_log(const void* spec, int64_t T, int64_t F, int64_t ld_spec, const float* mel, int64_t M, int64_t ld_mel,
                      const float* cmvn_mean, const float* cmvn_istd, float* out, int64_t ldo, void* stream);
+
+/* Top-k of the CTC log-probabilities without the logits: what torch.topk(log_softmax(ctc_lo(x)), k) feeds the
+ * prefix beam search with (veloxvoice/stream/rescore.py:252-262, veloxvoice/kernels/ops/cuda_ops.py:836-893).
+ * Two launches of the CTC GEMM: the first as for vx_ctc_finish (arg-max keys + lse_partials, whose running
+ * maxima are the maxima of every 64-column group); vx_ctc_topk_threshold takes the k-th largest group maximum
+ * of each row -- at least k logits of the row are >= it and every one of the row's k largest is; the second
+ * launch, with topk_threshold / topk_candidates / topk_count set, appends every logit >= the threshold to its
+ * row's list; vx_ctc_topk_finish picks the k largest of each list (equal values: lowest column first) and
+ * writes ids i32 [M, k] and logp f32 [M, k] = logit - logsumexp.  A row whose list overflowed topk_capacity
+ * (many equal bf16 logits) sets overflow[0] (i32, zeroed by the caller) and gets ids -1: the caller falls
+ * back to the logits for those rows.  k <= 16, topk_capacity <= 256. */
+int vx_ctc_topk_threshold(const void* lse_partials, int64_t N, int64_t M, int k, float* threshold, void* stream);
+int vx_ctc_topk_finish(const void* candidates, const int32_t* count, int capacity, const void* lse_partials, int64_t N,
+                       int64_t M, int k, int32_t* ids, float* logp, int32_t* overflow, void* stream);
 
 /* Attention fold pack in one pass: replaces velox_qkv_pack
  * (veloxvoice/kernels/csrc/velox_qkv_pack.cu:34-97; Python wrapper qkv_pack in

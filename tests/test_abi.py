@@ -38,8 +38,8 @@ def test_every_declared_symbol_is_exported(lib):
 
 
 def test_abi_version_and_struct_size(lib):
-    assert lib.vx_abi_version() == 3
-    assert C.sizeof(_lib.GemmDesc) == 224
+    assert lib.vx_abi_version() == 4
+    assert C.sizeof(_lib.GemmDesc) == 256
 
 
 def test_sf_geometry(lib):
@@ -85,6 +85,13 @@ def test_argument_errors_do_not_need_a_device(lib):
     assert lib.vx_power_mel_log(*mel_args(mean=C.c_void_p(2048))) == -1 and b"together" in lib.vx_last_error()
     assert lib.vx_power_mel_log(*mel_args(ld=32)) == -1
     assert lib.vx_power_mel_log(*mel_args(ldo=8)) == -1
+    # CTC top-k helpers: k range, NULL arguments
+    assert lib.vx_ctc_topk_threshold(C.c_void_p(256), 5538, 0, 5, C.c_void_p(512), None) == 0
+    assert lib.vx_ctc_topk_threshold(C.c_void_p(256), 5538, 8, 17, C.c_void_p(512), None) == -1
+    assert lib.vx_ctc_topk_threshold(None, 5538, 8, 5, C.c_void_p(512), None) == -1
+    assert lib.vx_ctc_topk_threshold(C.c_void_p(256), 100, 8, 9, C.c_void_p(512), None) == -1  # 8 groups of 64 columns only
+    assert lib.vx_ctc_topk_finish(C.c_void_p(256), C.c_void_p(512), 4, C.c_void_p(768), 5538, 8, 5, C.c_void_p(1024),
+                                  C.c_void_p(1280), C.c_void_p(1536), None) == -1  # capacity < k
     # attention: head dimension, NULL operands, alignment
     assert lib.vx_relpos_attention(C.c_void_p(256), C.c_void_p(512), C.c_void_p(768), 0, 8, 64, 0, C.c_void_p(1024), 512, None) == 0
     assert lib.vx_relpos_attention(C.c_void_p(256), C.c_void_p(512), C.c_void_p(768), 16, 8, 32, 0, C.c_void_p(1024), 512, None) == -1
@@ -119,6 +126,13 @@ def test_gemm_rejects_what_it_cannot_run_before_any_launch(lib):
         d = _gemm_desc(lib, flags=bad)
         assert lib.vx_bsgemm(C.byref(d), None) == -1
         assert b"flags" in lib.vx_last_error()
+    # the top-k candidate pass goes with the log-sum-exp partials and a sane capacity
+    d = _gemm_desc(lib, epi=_lib.EPI_BIAS_ARGMAX)
+    d.out_dtype, d.ldo = _lib.DT_F32, 1
+    d.topk_threshold, d.topk_candidates, d.topk_count, d.topk_capacity = 32768, 36864, 40960, 64
+    assert lib.vx_bsgemm(C.byref(d), None) == -1 and b"top-k" in lib.vx_last_error()  # no lse_partials
+    d.lse_partials, d.topk_capacity = 45056, 1000
+    assert lib.vx_bsgemm(C.byref(d), None) == -1 and b"top-k" in lib.vx_last_error()
     # the bounded-wait self-test takes a limit of at most 100 ms and a site below 255
     assert lib.vx_wait_selftest(0, 1, None) == -1
     assert lib.vx_wait_selftest(10**9, 1, None) == -1

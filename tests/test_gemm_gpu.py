@@ -388,3 +388,41 @@ def test_wide_and_narrow_tiles_give_the_same_bytes(ops, fmt, M, N, K, epi):
               for t in ("wide", "narrow")]
         assert torch.equal(qs[0].codes, qs[1].codes) and torch.equal(qs[0].sf, qs[1].sf)
         assert torch.equal(qs[0].scales, qs[1].scales)
+
+
+@pytest.mark.parametrize("fmt", [F.FMT_MX32, F.FMT_NV16])
+@pytest.mark.parametrize("M,k", [(300, 5), (1, 1), (129, 8), (2000, 16)])
+def test_ctc_topk_without_logits(ops, fmt, M, k):
+    """torch.topk(log_softmax(bf16 logits), k) from two launches of the head and two small kernels, no [M, N]
+    matrix: values within 1e-3 (the log-sum-exp is summed in another order), ids equal wherever the k-th and
+    (k+1)-th logits differ (equal bf16 logits may come in either order from torch.topk; here: lowest column first)."""
+    torch.manual_seed(M + k)
+    N, K = 5538, 512
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = (0.05 * torch.randn(N, K, device="cuda")).bfloat16()
+    bias = torch.randn(N, device="cuda")
+    am = torch.tensor([8.0], device="cuda") if fmt == F.FMT_NV16 else None
+    a, b = ops.quantize(x, fmt, natural=False, amax_t=am), ops.quantize(w, fmt)
+    logp, ids = ops.bsgemm_topk(a, b, bias, k)
+    assert logp.shape == (M, k) and ids.shape == (M, k) and ids.dtype == torch.int64
+    z = ops.bsgemm(a, b, epilogue=G.EPI_BIAS, bias=bias, out_dtype=torch.bfloat16)
+    ref = torch.log_softmax(z.float(), dim=-1)
+    rv, ri = torch.topk(ref, k, dim=-1)
+    assert (logp - rv).abs().max().item() < 1e-3
+    # the gathered reference log-probabilities of the returned ids are the top-k values: ids are right up to ties
+    assert (ref.gather(1, ids) - rv).abs().max().item() == 0.0
+    assert (logp[:, :-1] >= logp[:, 1:]).all() if k > 1 else True
+    # rows sorted by ascending column among equal values
+    eq = (logp[:, :-1] == logp[:, 1:]) if k > 1 else torch.zeros(M, 0, dtype=torch.bool, device="cuda")
+    assert (ids[:, :-1][eq] < ids[:, 1:][eq]).all()
+
+
+def test_ctc_topk_overflowing_rows_fall_back_to_logits(ops):
+    """All-equal logits: every column reaches the threshold, the candidate lists overflow, and the rows are redone
+    from explicit logits."""
+    M, N, K = 40, 512, 256
+    x = torch.zeros(M, K, device="cuda").bfloat16()
+    w = torch.randn(N, K, device="cuda").bfloat16()
+    a, b = ops.quantize(x, F.FMT_MX32, natural=False), ops.quantize(w, F.FMT_MX32)
+    logp, ids = ops.bsgemm_topk(a, b, None, 5, capacity=16)
+    assert (ids >= 0).all() and torch.allclose(logp, torch.full_like(logp, -float(np.log(N))), atol=1e-4)

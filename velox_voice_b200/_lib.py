@@ -23,7 +23,7 @@ FMT_BY_NAME = {
     "fp8_1x128": FMT_FP8_1X128,
 }
 DT_F32, DT_BF16, DT_FP4 = 0, 1, 2
-ABI_VERSION = 3  # VX_ABI_VERSION of include/velox_b200.h
+ABI_VERSION = 4  # VX_ABI_VERSION of include/velox_b200.h
 EPI_NONE, EPI_BIAS, EPI_BIAS_SWISH, EPI_BIAS_GLU, EPI_BIAS_RESIDUAL, EPI_BIAS_ARGMAX, EPI_BIAS_QKVPACK = range(7)
 GEMM_DIRECT_STORE = 1
 GEMM_STREAM_B = 2
@@ -53,6 +53,8 @@ EXPORTS = (
     "vx_tmap_cache_stats",
     "vx_ctc_lse_parts",
     "vx_ctc_finish",
+    "vx_ctc_topk_threshold",
+    "vx_ctc_topk_finish",
     "vx_power_mel_log_supported",
     "vx_power_mel_log",
     "vx_relpos_attention",
@@ -97,6 +99,11 @@ class GemmDesc(C.Structure):
         ("qk_scale", C.c_float),
         ("head_col_off", C.c_int32),
         ("lse_partials", C.c_void_p),
+        ("topk_threshold", C.c_void_p),
+        ("topk_candidates", C.c_void_p),
+        ("topk_count", C.c_void_p),
+        ("topk_capacity", C.c_int32),
+        ("reserved0", C.c_int32),
     ]
 
 
@@ -167,6 +174,10 @@ def load(build_if_missing: bool = True) -> C.CDLL:
         lib.vx_power_mel_log.argtypes = [vp, i64, i64, i64, vp, i64, i64, vp, vp, vp, i64, vp]
         lib.vx_relpos_attention.restype = i32
         lib.vx_relpos_attention.argtypes = [vp, vp, vp, i64, i32, i32, i64, vp, i64, vp]
+        lib.vx_ctc_topk_threshold.restype = i32
+        lib.vx_ctc_topk_threshold.argtypes = [vp, i64, i64, i32, vp, vp]
+        lib.vx_ctc_topk_finish.restype = i32
+        lib.vx_ctc_topk_finish.argtypes = [vp, vp, i32, vp, i64, i64, i32, vp, vp, vp, vp]
         lib.vx_set_trace_buffer.restype = i32
         lib.vx_set_trace_buffer.argtypes = [vp, i64]
         lib.vx_wait_selftest.restype = i32

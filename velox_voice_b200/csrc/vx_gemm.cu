@@ -146,6 +146,10 @@ struct GemmParams {
   const __nv_bfloat16* pos_v;
   float qk_scale;
   float2* lse_part;       // ARGMAX: per (64-column group, row) running (max, sum of exp) or nullptr
+  const float* topk_thr;  // ARGMAX + lse_part: per-row threshold of the candidate pass, or nullptr
+  unsigned long long* topk_cand;
+  int* topk_cnt;
+  int topk_cap;
   int* status;
 };
 
@@ -583,7 +587,8 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
   const int out_dtype = OUT == 1 ? static_cast<int>(VX_BF16) : (OUT == 2 ? static_cast<int>(VX_FP4) : p.out_dtype);
   const bool tma_store = OUT == 1 ? true : (OUT == 2 ? false : p.tma_store != 0);
   const bool tma_residual = OUT == 1 ? EPI == VX_EPI_BIAS_RESIDUAL : (OUT == 2 ? false : p.tma_residual != 0);
-  const bool sf_unit = OUT != 0 ? false : p.sf_unit != 0;
+  const bool sf_unit = (OUT == 1 || OUT == 2) ? false : p.sf_unit != 0;
+  constexpr bool TOPK = EPI == VX_EPI_BIAS_ARGMAX && OUT == 3;  // OUT 3: the run-time route + the top-k candidate pass
   const int out_fmt = OUT == 2 ? static_cast<int>(kind_vec4(KIND) ? VX_FMT_NV16 : VX_FMT_MX32) : p.out_fmt;
   const bool tr_on = kPhaseTrace && p.trace != nullptr && blockIdx.x == 0;  // phase trace requested (CTA 0 only)
 
@@ -1380,6 +1385,25 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
               const float nm = fmaxf(lse_m, cm);
               lse_s = lse_s * ex2_ftz((lse_m - nm) * L2E) + cs * ex2_ftz((cm - nm) * L2E);
               lse_m = nm;
+              if (TOPK && row_ok) {
+                // candidate pass of the top-k: append every logit of this chunk that reaches the row's threshold
+                // (few chunks of a row hold one; the chunk maximum decides whether to look at all)
+                const float thr = __ldg(p.topk_thr + row);
+                if (cm >= thr) {
+#pragma unroll
+                  for (int i = 0; i < 32; ++i) {
+                    if (zr[i] >= thr) {
+                      const int slot = atomicAdd(p.topk_cnt + row, 1);
+                      if (slot < p.topk_cap) {
+                        const uint32_t x = __float_as_uint(zr[i]);
+                        const uint32_t u = x ^ (static_cast<uint32_t>(static_cast<int32_t>(x) >> 31) | 0x80000000u);
+                        p.topk_cand[row * p.topk_cap + slot] =
+                            (static_cast<unsigned long long>(u) << 32) | (0xffffffffu - static_cast<uint32_t>(acc_col0 + i));
+                      }
+                    }
+                  }
+                }
+              }
             }
           } else if (out_dtype == VX_FP4) {
             const uint32_t sb = store_chunk_fp4(p, out_fmt, z[h], row, out_col0, g_out, row_ok && out_col0 < n_out);
@@ -1490,6 +1514,73 @@ __global__ void argmax_ids_kernel(const unsigned long long* __restrict__ keys, i
   if (max_out) {
     const uint32_t u = static_cast<uint32_t>(k >> 32);
     max_out[i] = __uint_as_float((u & 0x80000000u) ? (u ^ 0x80000000u) : ~u & 0xffff0000u);
+  }
+}
+
+// Top-k of the CTC head, step 2 of 3: the k-th largest 64-column-group maximum of every row (the running
+// maxima of the log-sum-exp partials).  At least k logits of the row reach it and each of the row's k largest
+// does, so it is the threshold of the candidate pass.
+__global__ void topk_threshold_kernel(const float2* __restrict__ parts, int nparts, int64_t M, int k, float* __restrict__ thr) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (row >= M) return;
+  float top[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) top[i] = -INFINITY;
+  for (int g = 0; g < nparts; ++g) {
+    float v = parts[static_cast<int64_t>(g) * M + row].x;
+    // insert into the descending list (registers only: fixed trip counts)
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float hi = fmaxf(top[i], v);
+      v = fminf(top[i], v);
+      top[i] = hi;
+    }
+  }
+  float t = top[0];
+#pragma unroll
+  for (int i = 1; i < 16; ++i)
+    if (i < k) t = top[i];
+  thr[row] = t;
+}
+
+// Step 3 of 3: the k largest candidates of every row (equal logits: lowest column first -- the packed entry
+// orders exactly that way), as ids and log-probabilities.
+__global__ void topk_finish_kernel(const unsigned long long* __restrict__ cand, const int* __restrict__ cnt, int cap,
+                                   const float2* __restrict__ parts, int nparts, int64_t M, int k, int32_t* __restrict__ ids,
+                                   float* __restrict__ logp, int* __restrict__ overflow) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (row >= M) return;
+  constexpr float L2E = 1.4426950408889634f;
+  // log-sum-exp exactly as ctc_finish_kernel forms it
+  float m = -INFINITY, s = 0.0f;
+  for (int g = 0; g < nparts; ++g) {
+    const float2 pr = parts[static_cast<int64_t>(g) * M + row];
+    if (pr.y > 0.0f) m = fmaxf(m, pr.x);
+  }
+  for (int g = 0; g < nparts; ++g) {
+    const float2 pr = parts[static_cast<int64_t>(g) * M + row];
+    if (pr.y > 0.0f) s += pr.y * exp2f((pr.x - m) * L2E);
+  }
+  const float lse = m + logf(s);
+  const int n = cnt[row];
+  if (n > cap || n < k) {  // overflowed list (or an inconsistent call): the caller goes back to the logits
+    if (n > cap) atomicExch(overflow, 1);
+    for (int j = 0; j < k; ++j) { ids[row * k + j] = -1; logp[row * k + j] = -INFINITY; }
+    return;
+  }
+  const unsigned long long* c = cand + row * cap;
+  unsigned long long below = ~0ull;  // entries are distinct (distinct columns): take the largest one below the last
+  for (int j = 0; j < k; ++j) {
+    unsigned long long best = 0;
+    for (int i = 0; i < n; ++i) {
+      const unsigned long long e = c[i];
+      if (e < below && e > best) best = e;
+    }
+    below = best;
+    const uint32_t u = static_cast<uint32_t>(best >> 32);
+    const float z = __uint_as_float((u & 0x80000000u) ? (u ^ 0x80000000u) : ~u);
+    ids[row * k + j] = static_cast<int32_t>(0xffffffffu - static_cast<uint32_t>(best));
+    logp[row * k + j] = z - lse;
   }
 }
 
@@ -1815,6 +1906,10 @@ int dispatch_out(int out, const CUtensorMap& ta, const CUtensorMap& tb, const CU
       if (out == 2) return launch<KIND, EPI, 2>(ta, tb, to, tr, p, res, st);
     }
   }
+  if constexpr (EPI == VX_EPI_BIAS_ARGMAX && KIND != KIND_FP8) {
+    // the candidate pass of the top-k is an instance of its own: the plain arg-max kernel keeps its registers
+    if (p.topk_thr) return launch<KIND, EPI, 3>(ta, tb, to, tr, p, res, st);
+  }
   return launch<KIND, EPI, 0>(ta, tb, to, tr, p, res, st);
 }
 
@@ -1900,6 +1995,12 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
   if (d->lse_partials && (!argmax || fp8 || (reinterpret_cast<uintptr_t>(d->lse_partials) & 7)))
     return fail(-1, "lse_partials goes with VX_EPI_BIAS_ARGMAX on the FP4 formats and must be 8-byte aligned");
   if (d->lse_partials && (d->flags & VX_GEMM_NARROW_TILES)) return fail(-1, "lse_partials needs the wide tile");
+  if (d->topk_threshold || d->topk_candidates || d->topk_count) {
+    if (!d->lse_partials || !d->topk_threshold || !d->topk_candidates || !d->topk_count || d->topk_capacity <= 0 ||
+        d->topk_capacity > 256 || (reinterpret_cast<uintptr_t>(d->topk_candidates) & 7))
+      return fail(-1, "the top-k candidate pass needs lse_partials, topk_threshold, topk_candidates (8-byte aligned), "
+                      "topk_count and 0 < topk_capacity <= 256");
+  }
   if (d->out_dtype != VX_F32 && d->out_dtype != VX_BF16 && d->out_dtype != VX_FP4)
     return fail(-1, "unknown out_dtype %d", d->out_dtype);
   if (d->bias && (reinterpret_cast<uintptr_t>(d->bias) & 15)) return fail(-1, "bias must be 16-byte aligned");
@@ -1991,6 +2092,10 @@ int vx_bsgemm(const vx_gemm_desc* d, void* stream) {
   } else if (argmax) {
     p.out_dtype = VX_F32;
     p.lse_part = static_cast<float2*>(d->lse_partials);
+    p.topk_thr = d->topk_threshold;
+    p.topk_cand = static_cast<unsigned long long*>(d->topk_candidates);
+    p.topk_cnt = d->topk_count;
+    p.topk_cap = d->topk_capacity;
   } else if (d->out_dtype == VX_FP4) {
     if (d->out_fmt != VX_FMT_MX32 && d->out_fmt != VX_FMT_NV16) return fail(-1, "FP4 output: out_fmt must be MX32 or NV16");
     if (epi == VX_EPI_BIAS_GLU || epi == VX_EPI_BIAS_RESIDUAL) return fail(-1, "FP4 output supports NONE / BIAS / BIAS_SWISH");
@@ -2073,6 +2178,33 @@ int vx_argmax_ids(const void* keys, int64_t M, int32_t* ids, float* max_out, voi
   const int grid = static_cast<int>((M + 255) / 256);
   argmax_ids_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const unsigned long long*>(keys), M, ids, max_out);
+  VX_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+int vx_ctc_topk_threshold(const void* lse_partials, int64_t N, int64_t M, int k, float* threshold, void* stream) {
+  using namespace vx;
+  if (M < 0 || N <= 0) return fail(-1, "bad shape");
+  if (M == 0) return 0;
+  if (!lse_partials || !threshold) return fail(-1, "lse_partials and threshold must not be NULL");
+  const int nparts = static_cast<int>(vx_ctc_lse_parts(N));
+  if (k <= 0 || k > 16 || k > nparts) return fail(-1, "k must be in 1..16 and at most the number of 64-column groups (%d)", nparts);
+  topk_threshold_kernel<<<static_cast<int>((M + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float2*>(lse_partials), nparts, M, k, threshold);
+  VX_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+int vx_ctc_topk_finish(const void* candidates, const int32_t* count, int capacity, const void* lse_partials, int64_t N,
+                       int64_t M, int k, int32_t* ids, float* logp, int32_t* overflow, void* stream) {
+  using namespace vx;
+  if (M < 0 || N <= 0) return fail(-1, "bad shape");
+  if (M == 0) return 0;
+  if (!candidates || !count || !lse_partials || !ids || !logp || !overflow) return fail(-1, "NULL argument");
+  if (k <= 0 || k > 16 || capacity < k || capacity > 256) return fail(-1, "k must be in 1..16, capacity in k..256");
+  topk_finish_kernel<<<static_cast<int>((M + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const unsigned long long*>(candidates), count, capacity, static_cast<const float2*>(lse_partials),
+      static_cast<int>(vx_ctc_lse_parts(N)), M, k, ids, logp, overflow);
   VX_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -100,6 +100,14 @@ class PackedLinear:
         return ops.bsgemm_argmax(a, self.q, self.bias, keys=keys, ids=ids, return_max=return_max, return_logp=return_logp)
 
 
+    def topk(self, a: Quantized, k: int = 5):
+        """``torch.topk(log_softmax(logits), k)`` of the bf16 logits without writing them (the stream of the
+        reference's prefix beam search): ``(logp [M, k], ids [M, k])``."""
+        if self.glu:
+            raise ValueError("top-k head on a GLU layer")
+        return ops.bsgemm_topk(a, self.q, self.bias, k)
+
+
 # --------------------------------------------------------------------------------------
 # Reference-compatible modules
 

@@ -468,6 +468,55 @@ def bsgemm_argmax(a: Quantized, b: Quantized, bias: Optional[torch.Tensor] = Non
     return (ids, vmax) if return_max else ids
 
 
+def bsgemm_topk(a: Quantized, b: Quantized, bias: Optional[torch.Tensor] = None, k: int = 5, *, capacity: int = 64):
+    """``torch.topk(log_softmax(A . B^T + bias), k)`` of the bf16-rounded logits without writing the [M, N] matrix:
+    the stream the reference's prefix beam search takes (``veloxvoice/stream/rescore.py:252-262``,
+    ``cuda_ops.py:836-893``).  Returns ``(logp f32 [M, k], ids int64 [M, k])``, largest first, equal logits by
+    ascending column.  Two launches of the GEMM (arg-max + log-sum-exp partials, then the candidate pass against
+    the k-th largest 64-column-group maximum of each row) and two small kernels; rows whose candidate list
+    overflowed ``capacity`` (many equal bf16 logits) are redone from explicit logits."""
+    if a.fmt == FMT_FP8_1X128:
+        raise ValueError("bsgemm_topk runs on the FP4 formats")
+    if not 1 <= k <= 16:
+        raise ValueError("k must be in 1..16")
+    d, keep = _gemm_desc(a, b, bias)
+    M, N = a.rows, b.rows
+    dev = a.codes.device
+    lib = _lib.load()
+    nparts = int(lib.vx_ctc_lse_parts(N))
+    if k > nparts:
+        raise ValueError(f"k = {k} exceeds the number of 64-column groups ({nparts})")
+    keys = torch.empty((M,), dtype=torch.int64, device=dev)
+    parts = torch.empty((nparts, M, 2), dtype=torch.float32, device=dev)
+    d.epilogue = EPI_BIAS_ARGMAX
+    d.out_dtype, d.out, d.ldo = DT_F32, keys.data_ptr(), 1
+    d.lse_partials = parts.data_ptr()
+    _lib.check(lib.vx_bsgemm(C.byref(d), _stream()), "vx_bsgemm")
+    thr = torch.empty((M,), dtype=torch.float32, device=dev)
+    _lib.check(lib.vx_ctc_topk_threshold(parts.data_ptr(), N, M, k, thr.data_ptr(), _stream()), "vx_ctc_topk_threshold")
+    cand = torch.empty((M, capacity), dtype=torch.int64, device=dev)
+    cnt = torch.zeros((M,), dtype=torch.int32, device=dev)
+    over = torch.zeros((1,), dtype=torch.int32, device=dev)
+    d.topk_threshold, d.topk_candidates, d.topk_count, d.topk_capacity = thr.data_ptr(), cand.data_ptr(), cnt.data_ptr(), capacity
+    _lib.check(lib.vx_bsgemm(C.byref(d), _stream()), "vx_bsgemm")
+    ids = torch.empty((M, k), dtype=torch.int32, device=dev)
+    logp = torch.empty((M, k), dtype=torch.float32, device=dev)
+    _lib.check(lib.vx_ctc_topk_finish(cand.data_ptr(), cnt.data_ptr(), capacity, parts.data_ptr(), N, M, k, ids.data_ptr(),
+                                      logp.data_ptr(), over.data_ptr(), _stream()), "vx_ctc_topk_finish")
+    _count(4)
+    ids = ids.long()
+    if int(over.item()):
+        # rare: some rows hold more than `capacity` logits at or above their threshold (many equal bf16 values);
+        # those rows are redone from explicit logits
+        rows = (ids[:, 0] < 0).nonzero()[:, 0]
+        z = bsgemm(a, b, epilogue=EPI_BIAS if bias is not None else EPI_NONE, bias=bias, out_dtype=torch.bfloat16)
+        v, i = torch.topk(torch.log_softmax(z[rows].float(), dim=-1), k, dim=-1)
+        del z
+        logp[rows], ids[rows] = v, i
+    del keep
+    return logp, ids
+
+
 def qkv_pack(qkv: torch.Tensor, p0: torch.Tensor, pos_u: torch.Tensor, pos_v: torch.Tensor, scale: float):
     """Single-pass attention fold pack, signature of the reference's ``qkv_pack``
     (``veloxvoice/kernels/ops/cuda_ops.py:554-581``): qkv bf16 [T, 3d], p0 bf16 [T, d],
