@@ -44,7 +44,7 @@ def parse():
                     help="encoder frames of the whole job (default: the synthetic hour, 89,999)")
     ap.add_argument("--fmt", default="mx32", choices=["mx32", "nv16", "fp8_1x128"])
     ap.add_argument("--blocks", type=int, default=12)
-    ap.add_argument("--cpu-frames", type=int, default=32768, help="frames per step of the CPU arms' sample")
+    ap.add_argument("--cpu-frames", type=int, default=65536, help="frames per step of the CPU arms' sample")
     ap.add_argument("--no-breakdown", action="store_true", help="skip the per-launch timings (no roofline object)")
     ap.add_argument("--no-extras", action="store_true", help="skip the logits-gather and weak-scaling legs")
     ap.add_argument("--traffic-bytes", type=float, default=None,
