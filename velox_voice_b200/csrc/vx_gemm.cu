@@ -1347,37 +1347,40 @@ bsgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
               tma_store_commit();
             }
           } else if constexpr (EPI == VX_EPI_BIAS_ARGMAX) {
-            // key: order-preserving bits of bf16(z) (high half) | 0xFFFF - tile column (low half)
+            // key: order-preserving bits of bf16(z) (high half) | 0xFFFF - tile column (low half).  The chunk's
+            // maximum is taken on the bf16-rounded values themselves (three-input max), then the first column
+            // holding it is looked up: cheaper than forming a key per value (this epilogue is bound by its
+            // integer arithmetic), and equal values -- -0 and +0 included -- resolve to the lowest column.
             const uint32_t cbase = 0xffffu - static_cast<uint32_t>(col_base + h * 32);
             const int valid = p.N - acc_col0 >= 32 ? 32 : static_cast<int>(p.N - acc_col0);
+            float zr[32];
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
               const uint32_t pk = pack_bf16x2(z[h][i], z[h][i + 1]);
-              const uint32_t x0 = pk << 16, x1 = pk & 0xffff0000u;
-              const uint32_t u0 = x0 ^ (static_cast<uint32_t>(static_cast<int32_t>(x0) >> 31) | 0x80000000u);
-              const uint32_t u1 = x1 ^ (static_cast<uint32_t>(static_cast<int32_t>(x1) >> 31) | 0x80000000u);
-              uint32_t k0 = (u0 & 0xffff0000u) | (cbase - i);
-              uint32_t k1 = (u1 & 0xffff0000u) | (cbase - i - 1);
-              if (valid < 32) {
-                if (i >= valid) k0 = 0;
-                if (i + 1 >= valid) k1 = 0;
-              }
-              best_key = max(best_key, max(k0, k1));
+              zr[i] = __uint_as_float(pk << 16);
+              zr[i + 1] = __uint_as_float(pk & 0xffff0000u);
+            }
+            if (valid < 32) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (i >= valid) zr[i] = -INFINITY;
+            }
+            float cm = zr[0];
+#pragma unroll
+            for (int i = 1; i < 32; i += 2) cm = i + 1 < 32 ? max3(cm, zr[i], zr[i + 1]) : fmaxf(cm, zr[i]);
+            if (valid > 0) {
+              int first = 31;
+#pragma unroll
+              for (int i = 30; i >= 0; --i)
+                if (zr[i] == cm) first = i;
+              const uint32_t x = __float_as_uint(__fadd_rn(cm, 0.0f));  // -0 -> +0: one key for both
+              const uint32_t u = x ^ (static_cast<uint32_t>(static_cast<int32_t>(x) >> 31) | 0x80000000u);
+              best_key = max(best_key, (u & 0xffff0000u) | (cbase - static_cast<uint32_t>(first)));
             }
             if (p.lse_part && valid > 0) {
-              // log-sum-exp of the bf16-rounded logits, streaming: chunk maximum, then the chunk's
-              // sum relative to it, merged into the running pair of this 64-column group
+              // log-sum-exp of the bf16-rounded logits, streaming: the chunk's sum relative to its maximum,
+              // merged into the running pair of this 64-column group
               constexpr float L2E = 1.4426950408889634f;
-              float zr[32];
-#pragma unroll
-              for (int i = 0; i < 32; i += 2) {
-                const uint32_t pk = pack_bf16x2(z[h][i], z[h][i + 1]);
-                zr[i] = i < valid ? __uint_as_float(pk << 16) : -INFINITY;
-                zr[i + 1] = i + 1 < valid ? __uint_as_float(pk & 0xffff0000u) : -INFINITY;
-              }
-              float cm = zr[0];
-#pragma unroll
-              for (int i = 1; i < 32; i += 2) cm = i + 1 < 32 ? max3(cm, zr[i], zr[i + 1]) : fmaxf(cm, zr[i]);
               const float nb2 = -cm * L2E;
               float cs = 0.0f;
 #pragma unroll
