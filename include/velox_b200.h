@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define VX_ABI_VERSION 4
+#define VX_ABI_VERSION 5
 
 /* Quantization formats.  values / scale / natural scale layout
  *  ROWSCALE   E2M1, one UE8M0 per row                      u8 [R]
@@ -175,6 +175,21 @@ int vx_glu_tile(int fmt);
                                   buffer this is where lp(pos_emb) belongs (torch_conformer.py:472,507) */
 
 int vx_bsgemm(const vx_gemm_desc* desc, void* stream);
+
+/* The residual GEMM that ends a Conformer module together with the LayerNorm + quantizer that opens the
+ * next one, in one launch: replaces vx_bsgemm(BIAS_RESIDUAL, bf16) followed by vx_ln_quantize_pack(fmt = MX32)
+ * -- in the reference a GEMM, a bias / residual add, a LayerNorm launch and a quantizer launch
+ * (veloxvoice/models/wenet/torch_conformer.py:706, 251-262; velox_layernorm.cu:13-58).
+ *   desc       as for vx_bsgemm with fmt = MX32, N = 512, K % 256 == 0, epilogue = BIAS_RESIDUAL, bf16 output and
+ *              bf16 residual (rows 16-byte aligned; out may alias residual), flags = 0;
+ *   out        x = bf16(alpha (A B^T + bias) + residual), stored as by vx_bsgemm;
+ *   codes / scales_sf   MX32 codes u8 [M, 256] (row stride ldc bytes) and SF atoms (vx_sf_bytes(MX32, M, 512)) of
+ *              LayerNorm(x as stored; gamma, beta, eps) -- the same bits as vx_ln_quantize_pack on x.
+ * A cluster of two CTAs owns each block of 128 rows (256 columns each) and exchanges the row statistics
+ * through distributed shared memory.  vx_bsgemm_residual_ln_supported: 1 when (fmt, N, K) is covered. */
+int vx_bsgemm_residual_ln_supported(int fmt, int64_t N, int64_t K);
+int vx_bsgemm_residual_ln(const vx_gemm_desc* desc, const float* gamma, const float* beta, float eps, void* codes,
+                          int64_t ldc, void* scales_sf, void* stream);
 
 /* Greedy (argmax) head without materialising the logits: what the reference computes as
  * ctc_lo(x).argmax(-1) on [T, vocab] logits (veloxvoice/models/wenet/torch_conformer.py:810-814).

@@ -38,7 +38,7 @@ def test_every_declared_symbol_is_exported(lib):
 
 
 def test_abi_version_and_struct_size(lib):
-    assert lib.vx_abi_version() == 4
+    assert lib.vx_abi_version() == 5
     assert C.sizeof(_lib.GemmDesc) == 256
 
 
@@ -133,6 +133,24 @@ def test_gemm_rejects_what_it_cannot_run_before_any_launch(lib):
     assert lib.vx_bsgemm(C.byref(d), None) == -1 and b"top-k" in lib.vx_last_error()  # no lse_partials
     d.lse_partials, d.topk_capacity = 45056, 1000
     assert lib.vx_bsgemm(C.byref(d), None) == -1 and b"top-k" in lib.vx_last_error()
+    # the residual GEMM with the LayerNorm + quantizer behind it: MX32, N = 512, K % 256 == 0, bf16 in and out
+    assert lib.vx_bsgemm_residual_ln_supported(_lib.FMT_MX32, 512, 512) == 1
+    assert lib.vx_bsgemm_residual_ln_supported(_lib.FMT_MX32, 512, 2048) == 1
+    assert lib.vx_bsgemm_residual_ln_supported(_lib.FMT_NV16, 512, 512) == 0
+    assert lib.vx_bsgemm_residual_ln_supported(_lib.FMT_MX32, 1536, 512) == 0
+    assert lib.vx_bsgemm_residual_ln_supported(_lib.FMT_MX32, 512, 384) == 0
+    vp = C.c_void_p
+    d = _gemm_desc(lib, epi=_lib.EPI_BIAS_RESIDUAL)  # N = 1536
+    assert lib.vx_bsgemm_residual_ln(C.byref(d), vp(256), vp(512), 1e-5, vp(1024), 256, vp(2048), None) == -1
+    d.N, d.ldo, d.residual, d.ldr, d.residual_dtype = 512, 512, 24576, 512, _lib.DT_F32
+    assert lib.vx_bsgemm_residual_ln(C.byref(d), vp(256), vp(512), 1e-5, vp(1024), 256, vp(2048), None) == -1  # f32 residual
+    assert b"bf16" in lib.vx_last_error()
+    d.residual_dtype = _lib.DT_BF16
+    assert lib.vx_bsgemm_residual_ln(C.byref(d), None, vp(512), 1e-5, vp(1024), 256, vp(2048), None) == -1  # no gamma
+    assert lib.vx_bsgemm_residual_ln(C.byref(d), vp(256), vp(512), 1e-5, vp(1024), 100, vp(2048), None) == -1  # ldc
+    assert lib.vx_bsgemm_residual_ln(C.byref(d), vp(256), vp(512), 1e-5, vp(1024), 256, None, None) == -1  # no scale factors
+    d.M = 0
+    assert lib.vx_bsgemm_residual_ln(C.byref(d), vp(256), vp(512), 1e-5, vp(1024), 256, vp(2048), None) == 0  # nothing to do
     # the bounded-wait self-test takes a limit of at most 100 ms and a site below 255
     assert lib.vx_wait_selftest(0, 1, None) == -1
     assert lib.vx_wait_selftest(10**9, 1, None) == -1

@@ -18,7 +18,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libvelox_b200.so")
 STAMP = os.path.join(LIB_DIR, "libvelox_b200.stamp")
-SOURCES = ("vx_api.cu", "vx_quant.cu", "vx_gemm.cu", "vx_noalloc.cu", "vx_pack.cu", "vx_mel.cu", "vx_attn.cu")
+SOURCES = ("vx_api.cu", "vx_quant.cu", "vx_gemm.cu", "vx_noalloc.cu", "vx_pack.cu", "vx_mel.cu", "vx_attn.cu", "vx_gemm_ln.cu")
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",

@@ -91,6 +91,17 @@ class PackedLinear:
 
     __call__ = forward
 
+    def residual_ln_supported(self) -> bool:
+        """Whether :meth:`residual_ln` covers this layer (MX32, 512 outputs, K a multiple of 256)."""
+        return (not self.glu) and ops.residual_ln_supported(self.q.fmt, self.q.rows, self.q.k)
+
+    def residual_ln(self, a: Quantized, *, residual: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor,
+                    eps: float, alpha: float = 1.0, out: Optional[torch.Tensor] = None):
+        """``x = alpha (a W^T + bias) + residual`` and ``ln_quantize(x, gamma, beta, eps)`` in one launch:
+        ``(x, q)`` with the bits of the two separate calls."""
+        return ops.bsgemm_residual_ln(a, self.q, bias=self.bias, residual=residual, gamma=gamma, beta=beta,
+                                      eps=eps, alpha=alpha, out=out)
+
     def argmax(self, a: Quantized, *, keys: Optional[torch.Tensor] = None, ids: Optional[torch.Tensor] = None,
                return_max: bool = False, return_logp: bool = False):
         """First column of the row maximum of the bf16 result, without writing the result

@@ -422,6 +422,48 @@ def bsgemm(
     return result
 
 
+def residual_ln_supported(fmt, N: int, K: int) -> bool:
+    """Whether :func:`bsgemm_residual_ln` covers a residual GEMM of this format and shape."""
+    return bool(_lib.load().vx_bsgemm_residual_ln_supported(_fmt(fmt), int(N), int(K)))
+
+
+def bsgemm_residual_ln(a: Quantized, b: Quantized, *, bias: Optional[torch.Tensor], residual: torch.Tensor,
+                       gamma: torch.Tensor, beta: torch.Tensor, eps: float, alpha: float = 1.0,
+                       out: Optional[torch.Tensor] = None):
+    """The residual GEMM and the LayerNorm + MX32 quantizer behind it in one launch:
+    ``x = bf16(alpha (A . B^T + bias) + residual)`` and ``q = ln_quantize(x, gamma, beta, eps, MX32)``
+    -- the same bits as ``bsgemm(..., epilogue=EPI_BIAS_RESIDUAL)`` followed by :func:`ln_quantize`.
+    MX32 operands, N = 512, K a multiple of 256; ``residual`` / ``out`` bf16 [M, 512] (``out`` may be
+    ``residual``).  Returns ``(x, q)``."""
+    d, keep = _gemm_desc(a, b, bias)
+    M, N = a.rows, b.rows
+    dev = a.codes.device
+    _require_cuda(residual, "residual")
+    residual = _rows2d(residual, "residual")
+    if residual.shape[0] != M or residual.shape[1] != N or residual.device != dev:
+        raise ValueError(f"residual must be [{M}, {N}] on {dev}")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    _require_cuda(out, "out")
+    if out.dim() != 2 or out.shape[0] != M or out.shape[1] != N or out.stride(1) != 1 or out.device != dev:
+        raise ValueError(f"out must be [{M}, {N}] with unit column stride on {dev}")
+    d.epilogue = EPI_BIAS_RESIDUAL
+    d.residual, d.residual_dtype, d.ldr = residual.data_ptr(), _dt(residual, "residual"), residual.stride(0)
+    d.alpha = float(alpha)
+    d.out_dtype, d.out, d.ldo = _dt(out, "out"), out.data_ptr(), out.stride(0)
+    gamma = gamma.float().contiguous()
+    beta = beta.float().contiguous()
+    _check_vector(gamma, "gamma", N, dev)
+    _check_vector(beta, "beta", N, dev)
+    codes, scales, sf_t = _alloc_outputs(FMT_MX32, M, N, dev, False, True)
+    _lib.check(_lib.load().vx_bsgemm_residual_ln(C.byref(d), gamma.data_ptr(), beta.data_ptr(), float(eps),
+                                                 codes.data_ptr(), codes.stride(0), sf_t.data_ptr(), _stream()),
+               "vx_bsgemm_residual_ln")
+    _count()
+    del keep
+    return out, Quantized(FMT_MX32, M, N, codes, scales, sf_t, None)
+
+
 def bsgemm_argmax(a: Quantized, b: Quantized, bias: Optional[torch.Tensor] = None, *,
                   return_max: bool = False, keys: Optional[torch.Tensor] = None,
                   ids: Optional[torch.Tensor] = None, return_logp: bool = False):

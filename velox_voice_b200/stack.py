@@ -51,6 +51,7 @@ class StackConfig:
     fmt: str = "mx32"
     eps: float = 1e-5
     fuse_ffn: bool = True  # keep the FFN intermediate in FP4 (re-quantized in the up-GEMM epilogue)
+    fuse_ln: bool = True   # MX32, d_model 512: the residual GEMMs also run the LayerNorm + quantizer behind them
 
     def flops_per_frame(self) -> int:
         """Algorithmic FLOPs of the linears per encoder frame (2 * N * K each)."""
@@ -97,6 +98,7 @@ class ConformerLinearStack:
             raise ValueError("the stack runs in mx32, nv16 or fp8_1x128")
         self.device = torch.device(device)
         self.fuse_ffn = cfg.fuse_ffn and self.fmt != FMT_FP8_1X128
+        self.fuse_ln = bool(cfg.fuse_ln) and ops.residual_ln_supported(self.fmt, cfg.d_model, cfg.d_model)
         dev = self.device
         self.p: Dict[str, PackedLinear] = {}
         self.ln: Dict[str, Tuple[torch.Tensor, torch.Tensor]] = {}
@@ -142,14 +144,26 @@ class ConformerLinearStack:
     def _q(self, key: str, x: torch.Tensor):
         return ops.quantize(x, self.fmt, natural=self.fmt == FMT_FP8_1X128, amax_t=self._amax(key, x))
 
-    def _ffn(self, b: str, ff: str, ln: str, x: torch.Tensor, q=None) -> torch.Tensor:
+    def _residual(self, name: str, a, x: torch.Tensor, alpha: float, next_ln: Optional[str]):
+        """``x <- alpha * linear(a) + x`` and, when ``next_ln`` names the LayerNorm that reads x next, its
+        quantized output: one launch where the fused kernel covers the layer, else two."""
+        lin = self.p[name]
+        if next_ln is None:
+            return lin(a, residual=x, alpha=alpha, out=x), None
+        if self.fuse_ln and lin.residual_ln_supported():
+            g, be = self.ln[next_ln]
+            return lin.residual_ln(a, residual=x, gamma=g, beta=be, eps=self.cfg.eps, alpha=alpha, out=x)
+        x = lin(a, residual=x, alpha=alpha, out=x)
+        return x, self._lnq(next_ln, x)
+
+    def _ffn(self, b: str, ff: str, ln: str, x: torch.Tensor, q=None, next_ln: Optional[str] = None):
         if q is None:
             q = self._lnq(b + ln, x)
         if self.fuse_ffn:
             h = self.p[b + ff + ".w1"](q, act="swish", out_fmt=self.fmt, out_amax=self._amax(b + ff + ".h", None))
         else:
             h = self._q(b + ff + ".h", self.p[b + ff + ".w1"](q, act="swish"))
-        return self.p[b + ff + ".w2"](h, residual=x, alpha=0.5, out=x)
+        return self._residual(b + ff + ".w2", h, x, 0.5, next_ln)
 
     # ---- forward
     def forward(self, x: torch.Tensor, pos: Optional[torch.Tensor] = None, *, return_hidden: bool = False,
@@ -164,17 +178,15 @@ class ConformerLinearStack:
         q_in = None  # first LayerNorm of the block, already applied by the previous block's last kernel
         for i in range(cfg.blocks):
             b = f"b{i}."
-            x = self._ffn(b, "ffm", "ln_ffm", x, q_in)
-            q = self._lnq(b + "ln_mha", x)
+            x, q = self._ffn(b, "ffm", "ln_ffm", x, q_in, next_ln=b + "ln_mha")
             qkv = self.p[b + "qkv"](q)
             if pos_q is not None:
                 self.p[b + "lp"](pos_q)  # feeds the attention scores only
             ctx = self._q(b + "ctx", qkv[:, 2 * d:])
-            x = self.p[b + "lo"](ctx, residual=x, alpha=1.0, out=x)
-            q = self._lnq(b + "ln_conv", x)
+            x, q = self._residual(b + "lo", ctx, x, 1.0, b + "ln_conv")
             gl = self.p[b + "pw1"](q)
-            x = self.p[b + "pw2"](self._q(b + "glu", gl), residual=x, alpha=1.0, out=x)
-            x = self._ffn(b, "ff", "ln_ff", x)
+            x, q = self._residual(b + "pw2", self._q(b + "glu", gl), x, 1.0, b + "ln_ff")
+            x, _ = self._ffn(b, "ff", "ln_ff", x, q)
             # norm_final of this block + the LayerNorm that reads it next (first of the next block,
             # or after_norm), one kernel: x <- LN_final(x), q_in <- quantize(LN_next(x))
             nxt = f"b{i + 1}.ln_ffm" if i + 1 < cfg.blocks else "after"
