@@ -96,3 +96,47 @@ def test_argument_checks(ops):
     assert not ops.residual_ln_supported("mx32", 256, 512)
     assert not ops.residual_ln_supported("mx32", 512, 384)
     assert ops.residual_ln_supported("mx32", 512, 2048)
+
+
+def test_stack_with_fused_layernorms_reproduces_the_oracle():
+    """The 12-block MX32 stack with every eligible residual GEMM running the LayerNorm + quantizer behind it (no
+    frame threshold): the same logits, bit for bit, as the stack with separate launches, and the CPU oracle's."""
+    from velox_voice_b200 import _lib
+    from velox_voice_b200.stack import ConformerLinearStack, StackConfig, make_weights
+    from oracle.stack import OracleStack
+
+    T = 1000
+    cfg_f = StackConfig(blocks=12, fmt="mx32", fuse_ln=True, fuse_ln_min_frames=0)
+    cfg_u = StackConfig(blocks=12, fmt="mx32", fuse_ln=False)
+    w = make_weights(cfg_f, seed=0)
+    # non-trivial LayerNorm parameters (make_weights leaves them at identity)
+    g = torch.Generator().manual_seed(3)
+    for k in list(w):
+        if k.endswith(".g"):
+            w[k] = 1.0 + 0.1 * torch.randn(w[k].shape, generator=g)
+        elif k.endswith(".b") and ("ln_" in k or k.startswith("after")):
+            w[k] = 0.05 * torch.randn(w[k].shape, generator=g)
+    fused, plain = ConformerLinearStack(cfg_f, w), ConformerLinearStack(cfg_u, w)
+    assert fused.fuse_ln and not plain.fuse_ln
+    torch.manual_seed(0)
+    x = torch.randn(T, cfg_f.d_model).bfloat16()
+    pos = torch.randn(T, cfg_f.d_model).bfloat16().cuda()
+    n0 = ops_count()
+    lf = fused.forward(x.cuda().clone(), pos)
+    n1 = ops_count()
+    lu = plain.forward(x.cuda().clone(), pos)
+    n2 = ops_count()
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    assert (n2 - n1) - (n1 - n0) == 3 * cfg_f.blocks  # three launches fewer per block
+    assert torch.equal(lf, lu)
+    ref = OracleStack({k: v.numpy() for k, v in w.items()}, F.FMT_NAMES["mx32"], cfg_f.blocks, fuse_ffn=fused.fuse_ffn).forward(x.float().numpy())
+    got = lf.float().cpu().numpy()
+    assert np.abs(got - ref).max() / np.abs(ref).max() < 1e-2
+    assert float((got.argmax(1) == ref.argmax(1)).mean()) >= 0.999
+
+
+def ops_count():
+    from velox_voice_b200 import ops
+
+    return ops.launch_count()

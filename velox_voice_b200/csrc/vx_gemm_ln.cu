@@ -8,10 +8,12 @@
 // CTA r computes columns [256 r, 256 r + 256) with 128 x 256 x 64 MXF4 MMAs, and the two exchange the
 // per-row partial sums of the LayerNorm statistics through distributed shared memory (st.async with
 // mbarrier completion, double-buffered per tile).  Per CTA, 18 warps:
-//   warp 0      TMA producer: A / B tiles (128-byte swizzle) + scale-factor atoms into a 3-slot ring;
+//   warp 0      TMA producer: A tiles (128-byte swizzle) + scale-factor atoms into a ring; the CTA's half of B stays
+//               resident in shared memory when K <= 512, else it streams through the ring with A;
 //   warp 1      owns tensor memory, copies scale factors shared -> tensor memory and issues the MMAs;
 //   warps 2..17 epilogue, warp (q, g) = TMEM lane quadrant q, 32-column blocks 2 g and 2 g + 1 of the CTA:
-//     pass 1  accumulator -> + bias, alpha, residual -> bf16 -> global x; the bf16 pairs go back to
+//     pass 1  accumulator -> + bias, alpha, residual (its 32 x 64 block prefetched by TMA into the warp's
+//             staging buffer) -> bf16, formed in place and stored by TMA; the bf16 pairs also go back to
 //             tensor memory (128 columns next to the accumulator), the accumulator is released to the
 //             MMAs of the next tile; per-block (sum, sum of squares) sent to both CTAs;
 //     pass 2  after the exchange: mean / rstd, normalise the bf16 values read back from tensor memory,
@@ -42,16 +44,25 @@ constexpr int LN_SFA = 2 * 512;               // two SF atoms per stage (UE8M0 p
 constexpr int LN_B_TILE = LN_BN * 128;        // 32 KB
 constexpr int LN_SFB = 2 * 2 * 512;           // two 128-row tiles x two atoms
 constexpr int LN_B_OFF = LN_A_TILE + LN_SFA;  // 17 KB: keeps the B tile 1024-byte aligned
-constexpr int LN_SLOT = LN_B_OFF + LN_B_TILE + LN_SFB;  // 51 KB
-constexpr int LN_SLOTS = 3;
+constexpr int LN_A_SLOT = LN_B_OFF;                     // 17 KB: A tile + its scale factors
+constexpr int LN_B_SLOT = LN_B_TILE + LN_SFB;           // 34 KB: B tile + its scale factors
+constexpr int LN_SLOT = LN_A_SLOT + LN_B_SLOT;          // 51 KB
+// Operand arena, two plans (as in vx_gemm.cu):
+//   B resident (K <= 512)  [B stage 0 | B stage 1] then three ring slots [A | SFA];
+//   streaming              two ring slots [A | SFA | B | SFB].
+constexpr int LN_RESIDENT_MAX_STAGES = 2;
+constexpr int LN_ARENA = LN_RESIDENT_MAX_STAGES * LN_B_SLOT + 3 * LN_A_SLOT;  // 119 KB
+constexpr int LN_MAX_SLOTS = 3;
+constexpr int LN_STAGING = 32 * 128;                    // per epilogue warp: 32 rows x 64 bf16 columns, 128-byte swizzle
 constexpr int LN_THREADS = 18 * 32;
-constexpr uint32_t LN_XCH_BYTES = 2 * 16 * 32 * 16;  // per CTA and tile: 2 CTAs x 16 warps x 32 lanes x 16 bytes
+constexpr uint32_t LN_XCH_BYTES = 2 * 4 * 32 * 16;  // per CTA, tile and lane quadrant: 2 CTAs x 4 warps x 32 lanes x 16 bytes
 // tensor-memory columns
 constexpr uint32_t LN_TM_ACC = 0, LN_TM_XP = 256, LN_TM_SFA = 384, LN_TM_SFB = 448;
 
 struct LnParams {
   int64_t M, K;
   int m_tiles, k_stages;
+  int b_resident;  // 1: the CTA keeps its half of B (all K stages) in shared memory
   const uint8_t* sfa;
   const uint8_t* sfb;
   int64_t sf_kg;
@@ -71,12 +82,14 @@ struct LnParams {
 };
 
 struct __align__(1024) LnSmem {
-  uint8_t ring[LN_SLOTS * LN_SLOT];
+  uint8_t arena[LN_ARENA];
+  uint8_t staging[16][LN_STAGING];  // residual block in (TMA), x block out (TMA), per epilogue warp
   float4 part[2][8][LN_BM];  // [tile parity][block pair of the row][row] = (S, Q) of blocks 2 i and 2 i + 1
   float bias[LN_BN], gamma[LN_BN], beta[LN_BN];
-  uint64_t full[LN_SLOTS], empty[LN_SLOTS];
-  uint64_t tmem_full, tmem_empty;
-  uint64_t xch[2];
+  uint64_t full[LN_MAX_SLOTS], empty[LN_MAX_SLOTS];
+  uint64_t tmem_full, tmem_empty, b_full;
+  uint64_t res_full[16];
+  uint64_t xch[2][4];  // [tile parity][lane quadrant]: the rows of a quadrant depend on that quadrant's warps only
   uint32_t tmem_base;
 };
 
@@ -131,6 +144,7 @@ __device__ __forceinline__ uint32_t bf16_pair(float lo, float hi) {
 
 __global__ void __launch_bounds__(LN_THREADS, 1)
 bsgemm_residual_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                          const __grid_constant__ CUtensorMap tmap_res, const __grid_constant__ CUtensorMap tmap_out,
                           const LnParams p) {
   pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
@@ -140,23 +154,32 @@ bsgemm_residual_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   const uint32_t rank = cluster_rank();  // column half of this CTA
   const int cluster = static_cast<int>(blockIdx.x >> 1), nclusters = static_cast<int>(gridDim.x >> 1);
   const int my_tiles = cluster < p.m_tiles ? (p.m_tiles - cluster + nclusters - 1) / nclusters : 0;
+  const bool resident = p.b_resident != 0;
+  const int nslots = resident ? 3 : 2;
+  const uint32_t slot_bytes = resident ? LN_A_SLOT : LN_SLOT;
+  const uint32_t ring_off = resident ? p.k_stages * LN_B_SLOT : 0;
 
   // ---- set-up
   if (threadIdx.x == 0) {
-    for (int s = 0; s < LN_SLOTS; ++s) {
+    for (int s = 0; s < LN_MAX_SLOTS; ++s) {
       mbar_init(&sm.full[s], 1);
       mbar_init(&sm.empty[s], 1);
     }
     mbar_init(&sm.tmem_full, 1);
     mbar_init(&sm.tmem_empty, 16);  // one arrival per epilogue warp
+    mbar_init(&sm.b_full, 1);
+    for (int w = 0; w < 16; ++w) mbar_init(&sm.res_full[w], 1);
     // exchange barriers: the one arrival is the arming below / after each use; the partial sums arrive as bytes
-    mbar_init(&sm.xch[0], 1);
-    mbar_init(&sm.xch[1], 1);
-    mbar_expect_tx(&sm.xch[0], LN_XCH_BYTES);
-    mbar_expect_tx(&sm.xch[1], LN_XCH_BYTES);
+    for (int b = 0; b < 2; ++b)
+      for (int qq = 0; qq < 4; ++qq) {
+        mbar_init(&sm.xch[b][qq], 1);
+        mbar_expect_tx(&sm.xch[b][qq], LN_XCH_BYTES);
+      }
     mbar_fence_init();
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
+    prefetch_tmap(&tmap_res);
+    prefetch_tmap(&tmap_out);
   }
   for (int i = threadIdx.x; i < LN_BN; i += blockDim.x) {  // constants of the model
     sm.bias[i] = p.bias ? __ldg(p.bias + rank * LN_BN + i) : 0.0f;
@@ -172,29 +195,38 @@ bsgemm_residual_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   tc_fence_after();
   cluster_sync_all();  // the peer's barriers exist before anything is sent to them
   const uint32_t tmem_base = sm.tmem_base;
-  pdl_wait();
+  const bool producer_thread = warp == 0 && lane == 0 && my_tiles > 0;
+  if (!producer_thread) pdl_wait();
 
   if (warp == 0) {
     // =========================== TMA producer ===========================
     if (lane == 0 && my_tiles > 0) {
       uint32_t s = 0, ph = 0;
       bool ok = true;
+      // B tile + scale factors of K stage ks -> dst
+      auto load_b = [&](uint8_t* dst, int ks, uint64_t* bar) {
+        tma_load_2d(dst, &tmap_b, ks * 128, static_cast<int>(rank) * LN_BN, bar);
+#pragma unroll
+        for (int rt = 0; rt < 2; ++rt)
+          bulk_load(dst + LN_B_TILE + rt * 1024,
+                    p.sfb + (static_cast<int64_t>(rank * 2 + rt) * p.sf_kg) * 512 + static_cast<int64_t>(ks) * 1024, 1024, bar);
+      };
+      if (resident) {  // weights: constants of the model, loaded before the wait for the previous kernel
+        mbar_expect_tx(&sm.b_full, p.k_stages * LN_B_SLOT);
+        for (int ks = 0; ks < p.k_stages; ++ks) load_b(sm.arena + ks * LN_B_SLOT, ks, &sm.b_full);
+      }
+      pdl_wait();
       int mb = cluster;
       for (int i = 0; i < my_tiles && ok; ++i, mb += nclusters) {
         const uint8_t* sfa_row = p.sfa + (static_cast<int64_t>(mb) * p.sf_kg) * 512;
         for (int ks = 0; ks < p.k_stages; ++ks) {
           if (!mbar_wait(&sm.empty[s], ph ^ 1, p.status, 21)) { ok = false; break; }
-          uint8_t* dst = sm.ring + s * LN_SLOT;
-          mbar_expect_tx(&sm.full[s], LN_SLOT);
+          uint8_t* dst = sm.arena + ring_off + s * slot_bytes;
+          mbar_expect_tx(&sm.full[s], slot_bytes);
           tma_load_2d(dst, &tmap_a, ks * 128, mb * LN_BM, &sm.full[s]);
           bulk_load(dst + LN_A_TILE, sfa_row + static_cast<int64_t>(ks) * LN_SFA, LN_SFA, &sm.full[s]);
-          tma_load_2d(dst + LN_B_OFF, &tmap_b, ks * 128, static_cast<int>(rank) * LN_BN, &sm.full[s]);
-#pragma unroll
-          for (int rt = 0; rt < 2; ++rt)
-            bulk_load(dst + LN_B_OFF + LN_B_TILE + rt * 1024,
-                      p.sfb + (static_cast<int64_t>(rank * 2 + rt) * p.sf_kg) * 512 + static_cast<int64_t>(ks) * 1024, 1024,
-                      &sm.full[s]);
-          if (++s == LN_SLOTS) { s = 0; ph ^= 1; }
+          if (!resident) load_b(dst + LN_A_SLOT, ks, &sm.full[s]);
+          if (++s == static_cast<uint32_t>(nslots)) { s = 0; ph ^= 1; }
         }
       }
     }
@@ -208,7 +240,23 @@ bsgemm_residual_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       const uint32_t k128_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
       const uint32_t sf_hi = (128u >> 4) | (1u << 14);
       auto desc = [](uint32_t lo, uint32_t hi) -> uint64_t { return (static_cast<uint64_t>(hi) << 32) | (lo & 0x3fffu); };
-      const uint32_t ring_lo = smem_u32(sm.ring) >> 4;
+      const uint32_t arena_lo = smem_u32(sm.arena) >> 4;
+      const uint32_t ring_lo = arena_lo + (ring_off >> 4);
+      // B scale factors of one stage: shared (b_lo = B tile >> 4) -> 16 TMEM columns at col0
+      auto cp_sfb = [&](uint32_t b_lo, uint32_t col0) {
+#pragma unroll
+        for (int a = 0; a < 2; ++a)
+#pragma unroll
+          for (int rt = 0; rt < 2; ++rt)
+            tc_cp_32x128b_warpx4(col0 + a * 8 + rt * 4, desc(b_lo + (LN_B_TILE >> 4) + (rt * 2 + a) * 32, sf_hi));
+      };
+      if (resident) {
+        if (!mbar_wait(&sm.b_full, 0, p.status, 26)) ok = false;
+        tc_fence_after();
+        if (ok && leader)  // B's scale factors stay in tensor memory for the whole kernel
+          for (int ks = 0; ks < p.k_stages; ++ks) cp_sfb(arena_lo + ks * (LN_B_SLOT >> 4), tmem_base + LN_TM_SFB + ks * 16);
+        __syncwarp();
+      }
       for (int i = 0; i < my_tiles && ok; ++i) {
         // the epilogue has read the previous accumulator out (pass 1 of tile i - 1)
         if (!mbar_wait_spin(&sm.tmem_empty, (i & 1) ^ 1, p.status, 22)) { ok = false; break; }
@@ -216,16 +264,14 @@ bsgemm_residual_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         for (int ks = 0; ks < p.k_stages; ++ks) {
           if (!mbar_wait_spin(&sm.full[s], ph, p.status, 23)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a_lo = ring_lo + s * (LN_SLOT >> 4), b_lo = a_lo + (LN_B_OFF >> 4);
-          const uint32_t sfa_buf = tmem_base + LN_TM_SFA + sfsel * 32, sfb_buf = tmem_base + LN_TM_SFB + sfsel * 32;
+          const uint32_t a_lo = ring_lo + s * (slot_bytes >> 4);
+          const uint32_t b_lo = resident ? arena_lo + ks * (LN_B_SLOT >> 4) : a_lo + (LN_A_SLOT >> 4);
+          const uint32_t sfa_buf = tmem_base + LN_TM_SFA + sfsel * 32;
+          const uint32_t sfb_buf = tmem_base + LN_TM_SFB + (resident ? ks * 16 : sfsel * 32);
           if (leader) {
 #pragma unroll
-            for (int a = 0; a < 2; ++a) {
-              tc_cp_32x128b_warpx4(sfa_buf + a * 4, desc(a_lo + (LN_A_TILE >> 4) + a * 32, sf_hi));
-#pragma unroll
-              for (int rt = 0; rt < 2; ++rt)
-                tc_cp_32x128b_warpx4(sfb_buf + a * 8 + rt * 4, desc(b_lo + (LN_B_TILE >> 4) + (rt * 2 + a) * 32, sf_hi));
-            }
+            for (int a = 0; a < 2; ++a) tc_cp_32x128b_warpx4(sfa_buf + a * 4, desc(a_lo + (LN_A_TILE >> 4) + a * 32, sf_hi));
+            if (!resident) cp_sfb(b_lo, sfb_buf);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const uint32_t atom = j >> 1, sf_id = (j & 1) * 2;
@@ -238,13 +284,14 @@ bsgemm_residual_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
           }
           __syncwarp();
           sfsel ^= 1;
-          if (++s == LN_SLOTS) { s = 0; ph ^= 1; }
+          if (++s == static_cast<uint32_t>(nslots)) { s = 0; ph ^= 1; }
         }
       }
     }
   } else {
     // =========================== epilogue ===========================
     const int q = warp & 3, g = (warp - 2) >> 2;  // TMEM lane quadrant; blocks 2 g, 2 g + 1 of this CTA's eight
+    const int ew = warp - 2;
     const int row_in = q * 32 + lane;
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     // piece (8 columns) handled at step c of a block: (c + rot) & 3, rot = (block >> 1) & 3 = g for both blocks
@@ -252,32 +299,38 @@ bsgemm_residual_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
 #pragma unroll
     for (int c = 0; c < 4; ++c) piece[c] = (c + g) & 3;
     const uint32_t part0 = smem_u32(&sm.part[0][rank * 4 + g][row_in]);
-    const uint32_t bar0 = smem_u32(&sm.xch[0]);
+    const uint32_t bar0 = smem_u32(&sm.xch[0][q]);
     const uint32_t dst_part[2] = {map_to_cta(part0, 0), map_to_cta(part0, 1)};
     const uint32_t dst_bar[2] = {map_to_cta(bar0, 0), map_to_cta(bar0, 1)};
     constexpr uint32_t PART_STRIDE = 8 * LN_BM * 16;
     const int sf_kg_out = 4;  // SF atoms per 128 rows of a 512-wide MX32 operand
+    // Staging block of this warp: rows [32 q, +32) x columns [256 rank + 64 g, +64) of the tile as bf16, rows of
+    // 128 bytes with the 128-byte swizzle: 16-byte unit u of row r sits at unit u ^ (r & 7).  The residual block
+    // lands here by TMA, x is formed in place and leaves by TMA (rows beyond M: zero-filled / clipped).
+    uint8_t* const stage_row = sm.staging[ew] + lane * 128;
+    const int sw = lane & 7;
+    const int tile_col = static_cast<int>(rank) * LN_BN + g * 64;
+    const uint64_t A2 = pack_f32x2(p.alpha, p.alpha);
     bool ok = true;
     int mb = cluster;
+    if (lane == 0 && my_tiles > 0) {
+      mbar_expect_tx(&sm.res_full[ew], LN_STAGING);
+      tma_load_2d(sm.staging[ew], &tmap_res, tile_col, mb * LN_BM + q * 32, &sm.res_full[ew]);
+    }
     for (int i = 0; i < my_tiles && ok; ++i, mb += nclusters) {
       const int64_t row = static_cast<int64_t>(mb) * LN_BM + row_in;
       const bool row_ok = row < p.M;
       if (!mbar_wait(&sm.tmem_full, i & 1, p.status, 24)) { ok = false; break; }
       tc_fence_after();
+      if (!mbar_wait(&sm.res_full[ew], i & 1, p.status, 27)) { ok = false; break; }
       // ---- pass 1: x = bf16(alpha (acc + bias) + residual), block statistics
       float SQ[4];
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
         const int k = 2 * g + t;
-        const int64_t col = static_cast<int64_t>(rank) * LN_BN + k * 32;
-        uint4 res[4];
         uint32_t z[4][8];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          res[c] = row_ok ? *reinterpret_cast<const uint4*>(p.residual + row * p.ldr + col + piece[c] * 8)  // plain load: may alias out
-                          : make_uint4(0, 0, 0, 0);
-          tc_ld_x8(lane_addr + LN_TM_ACC + k * 32 + piece[c] * 8, z[c]);
-        }
+        for (int c = 0; c < 4; ++c) tc_ld_x8(lane_addr + LN_TM_ACC + k * 32 + piece[c] * 8, z[c]);
         tc_wait_ld();
         uint32_t xp[16];
         uint64_t S = pack_f32x2(0.0f, 0.0f), Q = S;
@@ -285,21 +338,25 @@ bsgemm_residual_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         for (int c = 0; c < 4; ++c) {
           const float* bs = sm.bias + k * 32 + piece[c] * 8;
           const float4 b0 = *reinterpret_cast<const float4*>(bs), b1 = *reinterpret_cast<const float4*>(bs + 4);
-          const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-          const uint32_t rw[4] = {res[c].x, res[c].y, res[c].z, res[c].w};
+          const uint64_t bb[4] = {pack_f32x2(b0.x, b0.y), pack_f32x2(b0.z, b0.w), pack_f32x2(b1.x, b1.y), pack_f32x2(b1.z, b1.w)};
+          uint4* const slot = reinterpret_cast<uint4*>(stage_row + (((4 * t + piece[c]) ^ sw) << 4));
+          const uint4 res = *slot;
+          const uint32_t rw[4] = {res.x, res.y, res.z, res.w};
           uint32_t w[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float lo = fmaf(p.alpha, __fadd_rn(__uint_as_float(z[c][2 * e]), bb[2 * e]), __uint_as_float(rw[e] << 16));
-            const float hi = fmaf(p.alpha, __fadd_rn(__uint_as_float(z[c][2 * e + 1]), bb[2 * e + 1]),
-                                  __uint_as_float(rw[e] & 0xffff0000u));
+            // (packed fp32 pairs: each half rounds exactly like the scalar add / fused multiply-add)
+            const uint64_t zz = add_f32x2(pack_f32x2(__uint_as_float(z[c][2 * e]), __uint_as_float(z[c][2 * e + 1])), bb[e]);
+            const uint64_t xx = fma_f32x2(A2, zz, pack_f32x2(__uint_as_float(rw[e] << 16), __uint_as_float(rw[e] & 0xffff0000u)));
+            float lo, hi;
+            unpack_f32x2(xx, lo, hi);
             w[e] = bf16_pair(lo, hi);
             xp[4 * c + e] = w[e];
             const uint64_t v = pack_f32x2(__uint_as_float(w[e] << 16), __uint_as_float(w[e] & 0xffff0000u));
             S = add_f32x2(S, v);
             Q = fma_f32x2(v, v, Q);
           }
-          if (row_ok) *reinterpret_cast<uint4*>(p.out + row * p.ldo + col + piece[c] * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+          *slot = make_uint4(w[0], w[1], w[2], w[3]);
         }
         tc_st_x16(lane_addr + LN_TM_XP + k * 16, xp);
         float s0, s1, q0, q1;
@@ -308,26 +365,40 @@ bsgemm_residual_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         SQ[2 * t] = __fadd_rn(s0, s1);
         SQ[2 * t + 1] = __fadd_rn(q0, q1);
       }
-      // the accumulator is free for the MMAs of the next tile
+      // the accumulator is free for the MMAs of the next tile; x leaves by TMA
       tc_fence_before();
+      fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sm.tmem_empty);
+      if (lane == 0) {
+        mbar_arrive(&sm.tmem_empty);
+        tma_store_2d(&tmap_out, tile_col, mb * LN_BM + q * 32, sm.staging[ew]);
+        tma_store_commit();
+      }
       // ---- exchange: this thread's two block sums to both CTAs
       const uint32_t buf = i & 1;
 #pragma unroll
       for (int d = 0; d < 2; ++d)
-        st_async_f4(dst_part[d] + buf * PART_STRIDE, SQ[0], SQ[1], SQ[2], SQ[3], dst_bar[d] + buf * 8);
+        st_async_f4(dst_part[d] + buf * PART_STRIDE, SQ[0], SQ[1], SQ[2], SQ[3], dst_bar[d] + buf * 32);
       tc_wait_st_all();
-      if (!mbar_wait(&sm.xch[buf], (i >> 1) & 1, p.status, 25)) { ok = false; break; }
-      if (warp == 2 && lane == 0) mbar_expect_tx(&sm.xch[buf], LN_XCH_BYTES);  // armed for tile i + 2
-      float s[16], qq[16];
+      if (!mbar_wait(&sm.xch[buf][q], (i >> 1) & 1, p.status, 25)) { ok = false; break; }
+      if (g == 0 && lane == 0) mbar_expect_tx(&sm.xch[buf][q], LN_XCH_BYTES);  // armed for tile i + 2
+      if (lane == 0 && i + 1 < my_tiles) {
+        // By now the store has read the staging block (waiting for that right behind the store would hold the
+        // whole warp for the read): the residual block of the next tile may land in it.
+        tma_store_wait_read<0>();
+        mbar_expect_tx(&sm.res_full[ew], LN_STAGING);
+        tma_load_2d(sm.staging[ew], &tmap_res, tile_col, (mb + nclusters) * LN_BM + q * 32, &sm.res_full[ew]);
+      }
+      // block sums j and j ^ 8 first (blocks 2 b, 2 b + 1 sit in entry b: entries b and b + 4), then xor 4, 2, 1
+      float s[8], qq[8];
 #pragma unroll
-      for (int b = 0; b < 8; ++b) {
-        const float4 v = sm.part[buf][b][row_in];
-        s[2 * b] = v.x; qq[2 * b] = v.y; s[2 * b + 1] = v.z; qq[2 * b + 1] = v.w;
+      for (int b = 0; b < 4; ++b) {
+        const float4 lo = sm.part[buf][b][row_in], hi = sm.part[buf][b + 4][row_in];
+        s[2 * b] = __fadd_rn(lo.x, hi.x); qq[2 * b] = __fadd_rn(lo.y, hi.y);
+        s[2 * b + 1] = __fadd_rn(lo.z, hi.z); qq[2 * b + 1] = __fadd_rn(lo.w, hi.w);
       }
 #pragma unroll
-      for (int o = 8; o > 0; o >>= 1) {
+      for (int o = 4; o > 0; o >>= 1) {
 #pragma unroll
         for (int b = 0; b < o; ++b) {
           s[b] = __fadd_rn(s[b], s[b + o]);
@@ -386,6 +457,7 @@ bsgemm_residual_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         *reinterpret_cast<uint16_t*>(p.sf_out + off) = static_cast<uint16_t>(row_ok ? sf2 : 0u);
       }
     }
+    if (lane == 0) tma_store_wait_all<0>();
   }
 
   // ---- tear-down
@@ -397,7 +469,6 @@ bsgemm_residual_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   }
   cluster_sync_all();  // neither CTA leaves while the other may still write into its shared memory
 }
-
 
 // Every condition of the fused kernel that depends on the problem only (not on pointers).
 bool ln_shape_ok(int fmt, int64_t N, int64_t K) { return fmt == VX_FMT_MX32 && N == LN_D && K >= 256 && K % 256 == 0; }
@@ -441,6 +512,7 @@ int vx_bsgemm_residual_ln(const vx_gemm_desc* d, const float* gamma, const float
   p.M = M; p.K = K;
   p.m_tiles = static_cast<int>((M + LN_BM - 1) / LN_BM);
   p.k_stages = static_cast<int>(K / 256);
+  p.b_resident = p.k_stages <= LN_RESIDENT_MAX_STAGES;
   p.sfa = static_cast<const uint8_t*>(d->a_scales);
   p.sfb = static_cast<const uint8_t*>(d->b_scales);
   p.sf_kg = sf_kgroups(VX_FMT_MX32, K);
@@ -456,10 +528,15 @@ int vx_bsgemm_residual_ln(const vx_gemm_desc* d, const float* gamma, const float
   p.sf_out = static_cast<uint8_t*>(scales_sf);
   p.status = device_status_ptr();
 
-  CUtensorMap ta, tb;
+  CUtensorMap ta, tb, tr, to;
   int rc = make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, d->a_codes, M, row_bytes, d->lda, 128, LN_BM);
   if (rc) return rc;
   rc = make_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, d->b_codes, LN_D, row_bytes, d->ldb, 128, LN_BN);
+  if (rc) return rc;
+  // residual in / x out: blocks of 32 rows x 64 bf16 columns (128-byte rows), one per epilogue warp and tile
+  rc = make_tmap_2d(&tr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, d->residual, M, LN_D, d->ldr * 2, 64, 32);
+  if (rc) return rc;
+  rc = make_tmap_2d(&to, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, d->out, M, LN_D, d->ldo * 2, 64, 32);
   if (rc) return rc;
 
   static int sm_cache[64] = {};
@@ -492,7 +569,7 @@ int vx_bsgemm_residual_ln(const vx_gemm_desc* d, const float* gamma, const float
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 2 : 1;
-  VX_CUDA_OK(cudaLaunchKernelEx(&cfg, bsgemm_residual_ln_kernel, ta, tb, p));
+  VX_CUDA_OK(cudaLaunchKernelEx(&cfg, bsgemm_residual_ln_kernel, ta, tb, tr, to, p));
   return 0;
 }
 
