@@ -379,8 +379,12 @@ bsgemm_residual_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
 #pragma unroll
       for (int d = 0; d < 2; ++d)
         st_async_f4(dst_part[d] + buf * PART_STRIDE, SQ[0], SQ[1], SQ[2], SQ[3], dst_bar[d] + buf * 32);
-      tc_wait_st_all();
-      if (!mbar_wait(&sm.xch[buf][q], (i >> 1) & 1, p.status, 25)) { ok = false; break; }
+      if (!mbar_wait(&sm.xch[buf][q], (i >> 1) & 1, p.status, 25)) {
+        tc_wait_st_all();
+        ok = false;
+        break;
+      }
+      tc_wait_st_all();  // the bf16 copy is in tensor memory before pass 2 reads it back
       if (g == 0 && lane == 0) mbar_expect_tx(&sm.xch[buf][q], LN_XCH_BYTES);  // armed for tile i + 2
       if (lane == 0 && i + 1 < my_tiles) {
         // By now the store has read the staging block (waiting for that right behind the store would hold the

@@ -70,7 +70,7 @@ def op_breakdown(stack, T, fmt_name, only=""):
         cases.append((name, count, _timed(fn, flush), nbytes, flops))
 
     # the three LayerNorms behind residual GEMMs run in those GEMMs (long inputs only, see StackConfig)
-    fl = bool(getattr(stack, "fuse_ln", False)) and T >= cfg.fuse_ln_min_frames
+    fl = bool(getattr(stack, "fuse_ln", False)) and T >= getattr(stack, "fuse_ln_min_frames", cfg.fuse_ln_min_frames)
     add("ln_quantize [T,512]", 1 if fl else 3 * nb + 1, lambda: ops.ln_quantize(x, g, b, cfg.eps, fmt, amax_t=am),
         T * d * 2 + qbytes(T, d), 0)
     add("ln2_quantize [T,512] (norm_final + next LayerNorm + quantize)", nb,

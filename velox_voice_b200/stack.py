@@ -54,9 +54,9 @@ class StackConfig:
     fuse_ffn: bool = True  # keep the FFN intermediate in FP4 (re-quantized in the up-GEMM epilogue)
     fuse_ln: bool = True   # MX32, d_model 512: the residual GEMMs also run the LayerNorm + quantizer behind them
     # ... from this many frames on: the fused kernel walks 128-row blocks with 74 two-CTA clusters at ~5 us a
-    # block, which pays once every cluster has several blocks (90,000 frames: 9.105 vs 9.140 ms per step) and
-    # loses on a short shard (11,250 frames, 88 blocks: 1.847 vs 1.804 ms)
-    fuse_ln_min_frames: int = 32768
+    # block, which pays once every cluster has a few blocks (per step: 9.05 vs 9.13 ms at 90,000 frames, 2.82
+    # vs 2.89 ms at 22,500) and loses on a short shard (11,250 frames, 88 blocks: 1.85 vs 1.80 ms)
+    fuse_ln_min_frames: int = 16384
 
     def flops_per_frame(self) -> int:
         """Algorithmic FLOPs of the linears per encoder frame (2 * N * K each)."""
@@ -103,9 +103,11 @@ class ConformerLinearStack:
             raise ValueError("the stack runs in mx32, nv16 or fp8_1x128")
         self.device = torch.device(device)
         self.fuse_ffn = cfg.fuse_ffn and self.fmt != FMT_FP8_1X128
-        # (environment VELOX_B200_FUSE_LN=0 switches the fused residual + LayerNorm launches off, for A/B timing)
+        # (environment: VELOX_B200_FUSE_LN=0 switches the fused residual + LayerNorm launches off and
+        # VELOX_B200_FUSE_LN_MIN_FRAMES overrides their frame threshold, for A/B timing)
         self.fuse_ln = (bool(cfg.fuse_ln) and os.environ.get("VELOX_B200_FUSE_LN", "1") != "0"
                         and ops.residual_ln_supported(self.fmt, cfg.d_model, cfg.d_model))
+        self.fuse_ln_min_frames = int(os.environ.get("VELOX_B200_FUSE_LN_MIN_FRAMES", cfg.fuse_ln_min_frames))
         dev = self.device
         self.p: Dict[str, PackedLinear] = {}
         self.ln: Dict[str, Tuple[torch.Tensor, torch.Tensor]] = {}
@@ -157,7 +159,7 @@ class ConformerLinearStack:
         lin = self.p[name]
         if next_ln is None:
             return lin(a, residual=x, alpha=alpha, out=x), None
-        if self.fuse_ln and x.shape[0] >= self.cfg.fuse_ln_min_frames and lin.residual_ln_supported():
+        if self.fuse_ln and x.shape[0] >= self.fuse_ln_min_frames and lin.residual_ln_supported():
             g, be = self.ln[next_ln]
             return lin.residual_ln(a, residual=x, gamma=g, beta=be, eps=self.cfg.eps, alpha=alpha, out=x)
         x = lin(a, residual=x, alpha=alpha, out=x)
