@@ -7,7 +7,7 @@
 // factors of a block-scaled MMA in tensor memory.  So a CLUSTER OF TWO CTAs owns each block of 128 rows:
 // CTA r computes columns [256 r, 256 r + 256) with 128 x 256 x 64 MXF4 MMAs, and the two exchange the
 // per-row partial sums of the LayerNorm statistics through distributed shared memory (st.async with
-// mbarrier completion, double-buffered per tile).  Per CTA, 18 warps:
+// mbarrier completion into a table double-buffered per tile, one barrier per lane quadrant).  Per CTA, 18 warps:
 //   warp 0      TMA producer: A tiles (128-byte swizzle) + scale-factor atoms into a ring; the CTA's half of B stays
 //               resident in shared memory when K <= 512, else it streams through the ring with A;
 //   warp 1      owns tensor memory, copies scale factors shared -> tensor memory and issues the MMAs;
@@ -379,7 +379,8 @@ bsgemm_residual_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
 #pragma unroll
       for (int d = 0; d < 2; ++d)
         st_async_f4(dst_part[d] + buf * PART_STRIDE, SQ[0], SQ[1], SQ[2], SQ[3], dst_bar[d] + buf * 32);
-      if (!mbar_wait(&sm.xch[buf][q], (i >> 1) & 1, p.status, 25)) {
+      // (plain polling: at this point every epilogue warp of the quadrant waits, nobody is robbed of issue slots)
+      if (!mbar_wait_spin(&sm.xch[buf][q], (i >> 1) & 1, p.status, 25)) {
         tc_wait_st_all();
         ok = false;
         break;
