@@ -365,6 +365,11 @@ bsgemm_residual_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         SQ[2 * t] = __fadd_rn(s0, s1);
         SQ[2 * t + 1] = __fadd_rn(q0, q1);
       }
+      // ---- exchange: this thread's two block sums to both CTAs (first: the peer waits for them)
+      const uint32_t buf = i & 1;
+#pragma unroll
+      for (int d = 0; d < 2; ++d)
+        st_async_f4(dst_part[d] + buf * PART_STRIDE, SQ[0], SQ[1], SQ[2], SQ[3], dst_bar[d] + buf * 32);
       // the accumulator is free for the MMAs of the next tile; x leaves by TMA
       tc_fence_before();
       fence_proxy_async_smem();
@@ -374,11 +379,6 @@ bsgemm_residual_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         tma_store_2d(&tmap_out, tile_col, mb * LN_BM + q * 32, sm.staging[ew]);
         tma_store_commit();
       }
-      // ---- exchange: this thread's two block sums to both CTAs
-      const uint32_t buf = i & 1;
-#pragma unroll
-      for (int d = 0; d < 2; ++d)
-        st_async_f4(dst_part[d] + buf * PART_STRIDE, SQ[0], SQ[1], SQ[2], SQ[3], dst_bar[d] + buf * 32);
       // (plain polling: at this point every epilogue warp of the quadrant waits, nobody is robbed of issue slots)
       if (!mbar_wait_spin(&sm.xch[buf][q], (i >> 1) & 1, p.status, 25)) {
         tc_wait_st_all();
