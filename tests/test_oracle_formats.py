@@ -113,6 +113,41 @@ def test_layernorm_ref_close_to_torch():
     assert not G.ln_half_rows(1024, True, F.FMT_MX32) and not G.ln_half_rows(512, True, F.FMT_ROWSCALE)
 
 
+def test_layernorm_ref_half_rows_is_the_cluster_exchange_order():
+    """The fused residual GEMM + LayerNorm kernel (two CTAs of 256 columns, csrc/vx_gemm_ln.cu) sums a row like this:
+    block j of 32 columns accumulates its four 8-column pieces in the order (c + (j >> 1)) & 3 into an even and an odd
+    sum (squares by fused multiply-add), adds the two, and every thread then combines the 16 block sums as entries
+    (j, j + 8) first, then strides 4, 2, 1.  Restated here independently: the statistics, and so the output, are those
+    of ``layernorm_ref(half_rows=True)`` bit for bit."""
+    rng = np.random.default_rng(5)
+    M = 64
+    x = G.to_bf16(rng.standard_normal((M, 512)).astype(np.float32) * 3.0 + 0.7)
+    g = (1.0 + 0.2 * rng.standard_normal(512)).astype(np.float32)
+    b = (0.1 * rng.standard_normal(512)).astype(np.float32)
+    f32 = np.float32
+    S = np.zeros((M, 16), f32)
+    Q = np.zeros((M, 16), f32)
+    for j in range(16):
+        se, so, qe, qo = (np.zeros(M, f32) for _ in range(4))
+        for c in range(4):
+            p0 = 32 * j + 8 * ((c + (j >> 1)) & 3)
+            for e in range(4):
+                ve, vo = x[:, p0 + 2 * e], x[:, p0 + 2 * e + 1]
+                se, so = (se + ve).astype(f32), (so + vo).astype(f32)
+                qe, qo = G.fma32(ve, ve, qe), G.fma32(vo, vo, qo)
+        S[:, j], Q[:, j] = (se + so).astype(f32), (qe + qo).astype(f32)
+    for o in (8, 4, 2, 1):
+        S = (S[:, :o] + S[:, o:2 * o]).astype(f32)
+        Q = (Q[:, :o] + Q[:, o:2 * o]).astype(f32)
+    mean = (S[:, 0] * f32(1.0 / 512.0)).astype(f32)
+    ex2 = (Q[:, 0] * f32(1.0 / 512.0)).astype(f32)
+    var = np.maximum(G.fma32(-mean, mean, ex2), f32(0))
+    rstd = G.rsqrt32((var + f32(1e-5)).astype(f32))
+    nmr = ((-mean) * rstd).astype(f32)
+    y = G.fma32(G.fma32(x, rstd[:, None], nmr[:, None]), g[None, :], b[None, :])
+    assert np.array_equal(y.view(np.uint32), G.layernorm_ref(x, g, b, 1e-5, half_rows=True).view(np.uint32))
+
+
 def test_glu_interleave_is_a_permutation():
     idx = G.glu_interleave_rows(1024)
     assert sorted(idx.tolist()) == list(range(1024))
