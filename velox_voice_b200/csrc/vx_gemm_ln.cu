@@ -332,6 +332,13 @@ bsgemm_residual_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
 #pragma unroll
         for (int c = 0; c < 4; ++c) tc_ld_x8(lane_addr + LN_TM_ACC + k * 32 + piece[c] * 8, z[c]);
         tc_wait_ld();
+        if (t == 1) {
+          // the warp's part of the accumulator is in registers: free it for the MMAs of the next tile now, not
+          // after the arithmetic below (with K = 2048 those MMAs are what the next tile waits for)
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sm.tmem_empty);
+        }
         uint32_t xp[16];
         uint64_t S = pack_f32x2(0.0f, 0.0f), Q = S;
 #pragma unroll
@@ -370,12 +377,10 @@ bsgemm_residual_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
 #pragma unroll
       for (int d = 0; d < 2; ++d)
         st_async_f4(dst_part[d] + buf * PART_STRIDE, SQ[0], SQ[1], SQ[2], SQ[3], dst_bar[d] + buf * 32);
-      // the accumulator is free for the MMAs of the next tile; x leaves by TMA
-      tc_fence_before();
+      // x leaves by TMA
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(&sm.tmem_empty);
         tma_store_2d(&tmap_out, tile_col, mb * LN_BM + q * 32, sm.staging[ew]);
         tma_store_commit();
       }
