@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define VX_ABI_VERSION 5
+#define VX_ABI_VERSION 6
 
 /* Quantization formats.  values / scale / natural scale layout
  *  ROWSCALE   E2M1, one UE8M0 per row                      u8 [R]
@@ -190,6 +190,15 @@ int vx_bsgemm(const vx_gemm_desc* desc, void* stream);
 int vx_bsgemm_residual_ln_supported(int fmt, int64_t N, int64_t K);
 int vx_bsgemm_residual_ln(const vx_gemm_desc* desc, const float* gamma, const float* beta, float eps, void* codes,
                           int64_t ldc, void* scales_sf, void* stream);
+/* The same launch at the end of a Conformer block, where norm_final is followed by the first LayerNorm of the next
+ * block or by after_norm (veloxvoice/models/wenet/torch_conformer.py:713 -> :706 / :745): replaces
+ * vx_bsgemm(BIAS_RESIDUAL, bf16) + vx_ln2_quantize_pack(fmt = MX32, y = x).
+ *   out        y = bf16(LayerNorm(x; gamma1, beta1)), x = bf16(alpha (A B^T + bias) + residual) as above (x itself is
+ *              not stored; out may alias residual);
+ *   codes / scales_sf   of LayerNorm(y as stored; gamma2, beta2) -- the same bits as the two calls.
+ * Two exchanges of row statistics between the CTAs of a cluster instead of one. */
+int vx_bsgemm_residual_ln2(const vx_gemm_desc* desc, const float* gamma1, const float* beta1, const float* gamma2,
+                           const float* beta2, float eps, void* codes, int64_t ldc, void* scales_sf, void* stream);
 
 /* Greedy (argmax) head without materialising the logits: what the reference computes as
  * ctc_lo(x).argmax(-1) on [T, vocab] logits (veloxvoice/models/wenet/torch_conformer.py:810-814).

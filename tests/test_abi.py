@@ -38,7 +38,7 @@ def test_every_declared_symbol_is_exported(lib):
 
 
 def test_abi_version_and_struct_size(lib):
-    assert lib.vx_abi_version() == 5
+    assert lib.vx_abi_version() == 6
     assert C.sizeof(_lib.GemmDesc) == 256
 
 
@@ -149,8 +149,11 @@ def test_gemm_rejects_what_it_cannot_run_before_any_launch(lib):
     assert lib.vx_bsgemm_residual_ln(C.byref(d), None, vp(512), 1e-5, vp(1024), 256, vp(2048), None) == -1  # no gamma
     assert lib.vx_bsgemm_residual_ln(C.byref(d), vp(256), vp(512), 1e-5, vp(1024), 100, vp(2048), None) == -1  # ldc
     assert lib.vx_bsgemm_residual_ln(C.byref(d), vp(256), vp(512), 1e-5, vp(1024), 256, None, None) == -1  # no scale factors
+    assert lib.vx_bsgemm_residual_ln2(C.byref(d), vp(256), vp(512), None, vp(768), 1e-5, vp(1024), 256, vp(2048), None) == -1
+    assert lib.vx_bsgemm_residual_ln2(C.byref(d), vp(256), vp(512), vp(768), vp(1024), 1e-5, vp(1024), 100, vp(2048), None) == -1
     d.M = 0
     assert lib.vx_bsgemm_residual_ln(C.byref(d), vp(256), vp(512), 1e-5, vp(1024), 256, vp(2048), None) == 0  # nothing to do
+    assert lib.vx_bsgemm_residual_ln2(C.byref(d), vp(256), vp(512), vp(768), vp(1024), 1e-5, vp(1024), 256, vp(2048), None) == 0
     # the bounded-wait self-test takes a limit of at most 100 ms and a site below 255
     assert lib.vx_wait_selftest(0, 1, None) == -1
     assert lib.vx_wait_selftest(10**9, 1, None) == -1

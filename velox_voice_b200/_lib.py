@@ -23,7 +23,7 @@ FMT_BY_NAME = {
     "fp8_1x128": FMT_FP8_1X128,
 }
 DT_F32, DT_BF16, DT_FP4 = 0, 1, 2
-ABI_VERSION = 5  # VX_ABI_VERSION of include/velox_b200.h
+ABI_VERSION = 6  # VX_ABI_VERSION of include/velox_b200.h
 EPI_NONE, EPI_BIAS, EPI_BIAS_SWISH, EPI_BIAS_GLU, EPI_BIAS_RESIDUAL, EPI_BIAS_ARGMAX, EPI_BIAS_QKVPACK = range(7)
 GEMM_DIRECT_STORE = 1
 GEMM_STREAM_B = 2
@@ -60,6 +60,7 @@ EXPORTS = (
     "vx_relpos_attention",
     "vx_bsgemm_residual_ln_supported",
     "vx_bsgemm_residual_ln",
+    "vx_bsgemm_residual_ln2",
 )
 
 
@@ -180,6 +181,8 @@ def load(build_if_missing: bool = True) -> C.CDLL:
         lib.vx_bsgemm_residual_ln_supported.argtypes = [i32, i64, i64]
         lib.vx_bsgemm_residual_ln.restype = i32
         lib.vx_bsgemm_residual_ln.argtypes = [vp, vp, vp, C.c_float, vp, i64, vp, vp]
+        lib.vx_bsgemm_residual_ln2.restype = i32
+        lib.vx_bsgemm_residual_ln2.argtypes = [vp, vp, vp, vp, vp, C.c_float, vp, i64, vp, vp]
         lib.vx_ctc_topk_threshold.restype = i32
         lib.vx_ctc_topk_threshold.argtypes = [vp, i64, i64, i32, vp, vp]
         lib.vx_ctc_topk_finish.restype = i32

@@ -74,6 +74,8 @@ struct LnParams {
   float alpha;
   const float* gamma;
   const float* beta;
+  const float* gamma2;  // two LayerNorms in a row (LN2 instance): parameters of the second one
+  const float* beta2;
   float eps;
   uint8_t* codes;
   int64_t ldc;
@@ -85,7 +87,7 @@ struct __align__(1024) LnSmem {
   uint8_t arena[LN_ARENA];
   uint8_t staging[16][LN_STAGING];  // residual block in (TMA), x block out (TMA), per epilogue warp
   float4 part[2][8][LN_BM];  // [tile parity][block pair of the row][row] = (S, Q) of blocks 2 i and 2 i + 1
-  float bias[LN_BN], gamma[LN_BN], beta[LN_BN];
+  float bias[LN_BN], gamma[LN_BN], beta[LN_BN], gamma2[LN_BN], beta2[LN_BN];
   uint64_t full[LN_MAX_SLOTS], empty[LN_MAX_SLOTS];
   uint64_t tmem_full, tmem_empty, b_full;
   uint64_t res_full[16];
@@ -142,6 +144,10 @@ __device__ __forceinline__ uint32_t bf16_pair(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
+// LN2 = false: out = x, codes = quantize(LN(x)).
+// LN2 = true (the end of a Conformer block): out = y = bf16(LN(x; gamma, beta)) -- x itself is not stored -- and
+// codes = quantize(LN(y as stored; gamma2, beta2)): a second exchange of row statistics and a third pass.
+template <bool LN2>
 __global__ void __launch_bounds__(LN_THREADS, 1)
 bsgemm_residual_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                           const __grid_constant__ CUtensorMap tmap_res, const __grid_constant__ CUtensorMap tmap_out,
@@ -185,6 +191,10 @@ bsgemm_residual_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     sm.bias[i] = p.bias ? __ldg(p.bias + rank * LN_BN + i) : 0.0f;
     sm.gamma[i] = __ldg(p.gamma + rank * LN_BN + i);
     sm.beta[i] = __ldg(p.beta + rank * LN_BN + i);
+    if constexpr (LN2) {
+      sm.gamma2[i] = __ldg(p.gamma2 + rank * LN_BN + i);
+      sm.beta2[i] = __ldg(p.beta2 + rank * LN_BN + i);
+    }
   }
   if (warp == 1) {
     tmem_alloc(&sm.tmem_base, 512);
@@ -363,7 +373,7 @@ bsgemm_residual_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             S = add_f32x2(S, v);
             Q = fma_f32x2(v, v, Q);
           }
-          *slot = make_uint4(w[0], w[1], w[2], w[3]);
+          if constexpr (!LN2) *slot = make_uint4(w[0], w[1], w[2], w[3]);
         }
         tc_st_x16(lane_addr + LN_TM_XP + k * 16, xp);
         float s0, s1, q0, q1;
@@ -372,56 +382,122 @@ bsgemm_residual_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         SQ[2 * t] = __fadd_rn(s0, s1);
         SQ[2 * t + 1] = __fadd_rn(q0, q1);
       }
-      // ---- exchange: this thread's two block sums to both CTAs (first: the peer waits for them)
-      const uint32_t buf = i & 1;
+      // ---- exchange: this thread's two block sums to both CTAs (first: the peer waits for them).
+      // One LayerNorm: table / barrier i & 1, used every second tile.  Two: table 0 for the first, 1 for the
+      // second, both used every tile (a peer can only write the next tile's sums of a table after every thread
+      // here has sent the sums of the exchange in between, which it does after reading this one).
+      auto send = [&](uint32_t b, const float (&sq)[4]) {
 #pragma unroll
-      for (int d = 0; d < 2; ++d)
-        st_async_f4(dst_part[d] + buf * PART_STRIDE, SQ[0], SQ[1], SQ[2], SQ[3], dst_bar[d] + buf * 32);
-      // x leaves by TMA
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        tma_store_2d(&tmap_out, tile_col, mb * LN_BM + q * 32, sm.staging[ew]);
-        tma_store_commit();
-      }
-      // (plain polling: at this point every epilogue warp of the quadrant waits, nobody is robbed of issue slots)
-      if (!mbar_wait_spin(&sm.xch[buf][q], (i >> 1) & 1, p.status, 25)) {
-        tc_wait_st_all();
-        ok = false;
-        break;
-      }
-      tc_wait_st_all();  // the bf16 copy is in tensor memory before pass 2 reads it back
-      if (g == 0 && lane == 0) mbar_expect_tx(&sm.xch[buf][q], LN_XCH_BYTES);  // armed for tile i + 2
-      if (lane == 0 && i + 1 < my_tiles) {
-        // By now the store has read the staging block (waiting for that right behind the store would hold the
-        // whole warp for the read): the residual block of the next tile may land in it.
-        tma_store_wait_read<0>();
-        mbar_expect_tx(&sm.res_full[ew], LN_STAGING);
-        tma_load_2d(sm.staging[ew], &tmap_res, tile_col, (mb + nclusters) * LN_BM + q * 32, &sm.res_full[ew]);
-      }
-      // block sums j and j ^ 8 first (blocks 2 b, 2 b + 1 sit in entry b: entries b and b + 4), then xor 4, 2, 1
-      float s[8], qq[8];
-#pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        const float4 lo = sm.part[buf][b][row_in], hi = sm.part[buf][b + 4][row_in];
-        s[2 * b] = __fadd_rn(lo.x, hi.x); qq[2 * b] = __fadd_rn(lo.y, hi.y);
-        s[2 * b + 1] = __fadd_rn(lo.z, hi.z); qq[2 * b + 1] = __fadd_rn(lo.w, hi.w);
-      }
-#pragma unroll
-      for (int o = 4; o > 0; o >>= 1) {
-#pragma unroll
-        for (int b = 0; b < o; ++b) {
-          s[b] = __fadd_rn(s[b], s[b + o]);
-          qq[b] = __fadd_rn(qq[b], qq[b + o]);
+        for (int d = 0; d < 2; ++d) st_async_f4(dst_part[d] + b * PART_STRIDE, sq[0], sq[1], sq[2], sq[3], dst_bar[d] + b * 32);
+      };
+      // x (or y) leaves by TMA from the staging block
+      auto store_block = [&]() {
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&tmap_out, tile_col, mb * LN_BM + q * 32, sm.staging[ew]);
+          tma_store_commit();
         }
+      };
+      // waits for the sums of exchange b, arms its barrier for the next use, fetches the next residual block when
+      // the staging block is free, and reduces the 16 block sums of the row: (rstd, -mean rstd) as packed pairs
+      auto finish_stats = [&](uint32_t b, uint32_t parity, bool staging_free, uint64_t& R2, uint64_t& N2) -> bool {
+        // (plain polling: at this point every epilogue warp of the quadrant waits, nobody is robbed of issue slots)
+        const bool landed = mbar_wait_spin(&sm.xch[b][q], parity, p.status, 25);
+        tc_wait_st_all();  // the bf16 copy is in tensor memory before the next pass reads it back
+        if (!landed) return false;
+        if (g == 0 && lane == 0) mbar_expect_tx(&sm.xch[b][q], LN_XCH_BYTES);  // armed for the next use
+        if (staging_free && lane == 0 && i + 1 < my_tiles) {
+          // By now the store has read the staging block (waiting for that right behind the store would hold the
+          // whole warp for the read): the residual block of the next tile may land in it.
+          tma_store_wait_read<0>();
+          mbar_expect_tx(&sm.res_full[ew], LN_STAGING);
+          tma_load_2d(sm.staging[ew], &tmap_res, tile_col, (mb + nclusters) * LN_BM + q * 32, &sm.res_full[ew]);
+        }
+        // block sums j and j ^ 8 first (blocks 2 e, 2 e + 1 sit in entry e: entries e and e + 4), then xor 4, 2, 1
+        float s[8], qq[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float4 lo = sm.part[b][e][row_in], hi = sm.part[b][e + 4][row_in];
+          s[2 * e] = __fadd_rn(lo.x, hi.x); qq[2 * e] = __fadd_rn(lo.y, hi.y);
+          s[2 * e + 1] = __fadd_rn(lo.z, hi.z); qq[2 * e + 1] = __fadd_rn(lo.w, hi.w);
+        }
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) {
+#pragma unroll
+          for (int e = 0; e < o; ++e) {
+            s[e] = __fadd_rn(s[e], s[e + o]);
+            qq[e] = __fadd_rn(qq[e], qq[e + o]);
+          }
+        }
+        const float mean = __fmul_rn(s[0], 1.0f / 512.0f);
+        const float ex2 = __fmul_rn(qq[0], 1.0f / 512.0f);
+        const float var = fmaxf(__fmaf_rn(-mean, mean, ex2), 0.0f);
+        const float rstd = __frsqrt_rn(__fadd_rn(var, p.eps));
+        const float nmr = __fmul_rn(-mean, rstd);
+        R2 = pack_f32x2(rstd, rstd);
+        N2 = pack_f32x2(nmr, nmr);
+        return true;
+      };
+      uint64_t R2, N2;
+      if constexpr (!LN2) {
+        send(i & 1, SQ);
+        store_block();
+        if (!finish_stats(i & 1, (i >> 1) & 1, true, R2, N2)) { ok = false; break; }
+      } else {
+        send(0, SQ);
+        if (!finish_stats(0, i & 1, false, R2, N2)) { ok = false; break; }
+        // ---- pass 2 of 3: y = bf16(LN(x)) into the staging block and back into tensor memory, statistics of y
+        float SQ2[4];
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          const int k = 2 * g + t;
+          uint32_t xp[16];
+          tc_ld_x16(lane_addr + LN_TM_XP + k * 16, xp);
+          tc_wait_ld();
+          uint64_t S = pack_f32x2(0.0f, 0.0f), Q = S;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const float4* ga = reinterpret_cast<const float4*>(sm.gamma + k * 32 + piece[c] * 8);
+            const float4* be = reinterpret_cast<const float4*>(sm.beta + k * 32 + piece[c] * 8);
+            uint32_t w[4];
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+              const float4 gv = ga[hh], bv = be[hh];
+              const uint32_t w0 = xp[4 * c + 2 * hh], w1 = xp[4 * c + 2 * hh + 1];
+              const uint64_t x0 = pack_f32x2(__uint_as_float(w0 << 16), __uint_as_float(w0 & 0xffff0000u));
+              const uint64_t x1 = pack_f32x2(__uint_as_float(w1 << 16), __uint_as_float(w1 & 0xffff0000u));
+              const uint64_t y0 = fma_f32x2(fma_f32x2(x0, R2, N2), pack_f32x2(gv.x, gv.y), pack_f32x2(bv.x, bv.y));
+              const uint64_t y1 = fma_f32x2(fma_f32x2(x1, R2, N2), pack_f32x2(gv.z, gv.w), pack_f32x2(bv.z, bv.w));
+              float a0, a1, a2, a3;
+              unpack_f32x2(y0, a0, a1);
+              unpack_f32x2(y1, a2, a3);
+              w[2 * hh] = bf16_pair(a0, a1);
+              w[2 * hh + 1] = bf16_pair(a2, a3);
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {  // the second LayerNorm reads what is stored
+              xp[4 * c + e] = w[e];
+              const uint64_t v = pack_f32x2(__uint_as_float(w[e] << 16), __uint_as_float(w[e] & 0xffff0000u));
+              S = add_f32x2(S, v);
+              Q = fma_f32x2(v, v, Q);
+            }
+            *reinterpret_cast<uint4*>(stage_row + (((4 * t + piece[c]) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+          tc_st_x16(lane_addr + LN_TM_XP + k * 16, xp);
+          float s0, s1, q0, q1;
+          unpack_f32x2(S, s0, s1);
+          unpack_f32x2(Q, q0, q1);
+          SQ2[2 * t] = __fadd_rn(s0, s1);
+          SQ2[2 * t + 1] = __fadd_rn(q0, q1);
+        }
+        send(1, SQ2);
+        store_block();
+        if (!finish_stats(1, i & 1, true, R2, N2)) { ok = false; break; }
       }
-      const float mean = __fmul_rn(s[0], 1.0f / 512.0f);
-      const float ex2 = __fmul_rn(qq[0], 1.0f / 512.0f);
-      const float var = fmaxf(__fmaf_rn(-mean, mean, ex2), 0.0f);
-      const float rstd = __frsqrt_rn(__fadd_rn(var, p.eps));
-      const float nmr = __fmul_rn(-mean, rstd);
-      const uint64_t R2 = pack_f32x2(rstd, rstd), N2 = pack_f32x2(nmr, nmr);
-      // ---- pass 2: normalise, quantize
+      const float* const gamma_q = LN2 ? sm.gamma2 : sm.gamma;  // parameters of the LayerNorm in front of the quantizer
+      const float* const beta_q = LN2 ? sm.beta2 : sm.beta;
+      // ---- last pass: normalise, quantize
       uint32_t sf2 = 0;
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
@@ -433,8 +509,8 @@ bsgemm_residual_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         float a[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          const float4* ga = reinterpret_cast<const float4*>(sm.gamma + k * 32 + piece[c] * 8);
-          const float4* be = reinterpret_cast<const float4*>(sm.beta + k * 32 + piece[c] * 8);
+          const float4* ga = reinterpret_cast<const float4*>(gamma_q + k * 32 + piece[c] * 8);
+          const float4* be = reinterpret_cast<const float4*>(beta_q + k * 32 + piece[c] * 8);
 #pragma unroll
           for (int hh = 0; hh < 2; ++hh) {
             const float4 gv = ga[hh], bv = be[hh];
@@ -490,18 +566,23 @@ extern "C" {
 
 int vx_bsgemm_residual_ln_supported(int fmt, int64_t N, int64_t K) { return vx::ln_shape_ok(fmt, N, K) ? 1 : 0; }
 
-int vx_bsgemm_residual_ln(const vx_gemm_desc* d, const float* gamma, const float* beta, float eps, void* codes, int64_t ldc,
-                          void* scales_sf, void* stream) {
-  using namespace vx;
+}  // extern "C"
+
+namespace vx {
+namespace {
+
+// Shared by the one- and the two-LayerNorm entry points (gamma2 / beta2 == nullptr: one).
+int launch_residual_ln(const vx_gemm_desc* d, const float* gamma, const float* beta, const float* gamma2, const float* beta2,
+                       float eps, void* codes, int64_t ldc, void* scales_sf, void* stream, const char* who) {
   if (!d) return fail(-1, "desc must not be NULL");
   if (d->struct_size != static_cast<int32_t>(sizeof(vx_gemm_desc)))
     return fail(-1, "vx_gemm_desc.struct_size=%d, expected %d", d->struct_size, (int)sizeof(vx_gemm_desc));
   if (!ln_shape_ok(d->fmt, d->N, d->K))
-    return fail(-1, "vx_bsgemm_residual_ln needs fmt = MX32, N = 512 and K a multiple of 256 (see vx_bsgemm_residual_ln_supported)");
+    return fail(-1, "%s needs fmt = MX32, N = 512 and K a multiple of 256 (see vx_bsgemm_residual_ln_supported)", who);
   const int64_t M = d->M, K = d->K;
   if (M < 0) return fail(-1, "negative shape");
   if (d->epilogue != VX_EPI_BIAS_RESIDUAL || d->out_dtype != VX_BF16 || d->residual_dtype != VX_BF16 || d->flags != 0)
-    return fail(-1, "vx_bsgemm_residual_ln: epilogue BIAS_RESIDUAL with bf16 output and bf16 residual, no flags");
+    return fail(-1, "%s: epilogue BIAS_RESIDUAL with bf16 output and bf16 residual, no flags", who);
   if (M == 0) return 0;
   const int64_t row_bytes = K / 2;
   if (!d->a_codes || !d->b_codes || !d->out || !d->residual || !d->a_scales || !d->b_scales)
@@ -514,6 +595,7 @@ int vx_bsgemm_residual_ln(const vx_gemm_desc* d, const float* gamma, const float
     return fail(-1, "out / residual rows must be 16-byte aligned and at least 512 elements");
   if (d->bias && (reinterpret_cast<uintptr_t>(d->bias) & 15)) return fail(-1, "bias must be 16-byte aligned");
   if (!gamma || !beta) return fail(-1, "gamma and beta must not be NULL");
+  if ((gamma2 == nullptr) != (beta2 == nullptr)) return fail(-1, "gamma2 and beta2 go together");
   if (!codes || !aligned16(codes) || ldc % 16 != 0 || ldc < LN_D / 2) return fail(-1, "codes rows must be 16-byte aligned, ldc >= 256");
   if (!scales_sf || !aligned16(scales_sf)) return fail(-1, "scales_sf must be 16-byte aligned");
   if ((M + LN_BM - 1) / LN_BM > 0x7fffffff / LN_BM) return fail(-1, "too many rows");
@@ -532,7 +614,7 @@ int vx_bsgemm_residual_ln(const vx_gemm_desc* d, const float* gamma, const float
   p.out = static_cast<__nv_bfloat16*>(d->out);
   p.ldo = d->ldo;
   p.alpha = d->alpha;
-  p.gamma = gamma; p.beta = beta; p.eps = eps;
+  p.gamma = gamma; p.beta = beta; p.gamma2 = gamma2; p.beta2 = beta2; p.eps = eps;
   p.codes = static_cast<uint8_t*>(codes);
   p.ldc = ldc;
   p.sf_out = static_cast<uint8_t*>(scales_sf);
@@ -560,10 +642,12 @@ int vx_bsgemm_residual_ln(const vx_gemm_desc* d, const float* gamma, const float
   if (clusters > p.m_tiles) clusters = p.m_tiles;
   if (clusters < 1) clusters = 1;
   const size_t smem = sizeof(LnSmem) + 1024;
-  static bool attr_set[64] = {};
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    VX_CUDA_OK(cudaFuncSetAttribute(bsgemm_residual_ln_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    attr_set[dev] = true;
+  const bool two = gamma2 != nullptr;
+  auto* kernel = two ? bsgemm_residual_ln_kernel<true> : bsgemm_residual_ln_kernel<false>;
+  static bool attr_set[2][64] = {};  // the opt-in belongs to the device (and the kernel instance)
+  if (dev >= 0 && dev < 64 && !attr_set[two][dev]) {
+    VX_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    attr_set[two][dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * clusters);
@@ -579,8 +663,24 @@ int vx_bsgemm_residual_ln(const vx_gemm_desc* d, const float* gamma, const float
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 2 : 1;
-  VX_CUDA_OK(cudaLaunchKernelEx(&cfg, bsgemm_residual_ln_kernel, ta, tb, tr, to, p));
+  VX_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, ta, tb, tr, to, p));
   return 0;
+}
+
+}  // namespace
+}  // namespace vx
+
+extern "C" {
+
+int vx_bsgemm_residual_ln(const vx_gemm_desc* d, const float* gamma, const float* beta, float eps, void* codes, int64_t ldc,
+                          void* scales_sf, void* stream) {
+  return vx::launch_residual_ln(d, gamma, beta, nullptr, nullptr, eps, codes, ldc, scales_sf, stream, "vx_bsgemm_residual_ln");
+}
+
+int vx_bsgemm_residual_ln2(const vx_gemm_desc* d, const float* gamma1, const float* beta1, const float* gamma2,
+                           const float* beta2, float eps, void* codes, int64_t ldc, void* scales_sf, void* stream) {
+  if (!gamma2 || !beta2) return vx::fail(-1, "gamma2 and beta2 must not be NULL");
+  return vx::launch_residual_ln(d, gamma1, beta1, gamma2, beta2, eps, codes, ldc, scales_sf, stream, "vx_bsgemm_residual_ln2");
 }
 
 }  // extern "C"

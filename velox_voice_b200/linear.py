@@ -96,11 +96,13 @@ class PackedLinear:
         return (not self.glu) and ops.residual_ln_supported(self.q.fmt, self.q.rows, self.q.k)
 
     def residual_ln(self, a: Quantized, *, residual: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor,
-                    eps: float, alpha: float = 1.0, out: Optional[torch.Tensor] = None):
+                    eps: float, alpha: float = 1.0, out: Optional[torch.Tensor] = None,
+                    gamma2: Optional[torch.Tensor] = None, beta2: Optional[torch.Tensor] = None):
         """``x = alpha (a W^T + bias) + residual`` and ``ln_quantize(x, gamma, beta, eps)`` in one launch:
-        ``(x, q)`` with the bits of the two separate calls."""
+        ``(x, q)`` with the bits of the two separate calls.  With ``gamma2`` / ``beta2``: ``(LN(x), q)`` with
+        ``q = ln_quantize(LN(x), gamma2, beta2)`` -- the end of a block (``ops.ln2_quantize``)."""
         return ops.bsgemm_residual_ln(a, self.q, bias=self.bias, residual=residual, gamma=gamma, beta=beta,
-                                      eps=eps, alpha=alpha, out=out)
+                                      eps=eps, alpha=alpha, out=out, gamma2=gamma2, beta2=beta2)
 
     def argmax(self, a: Quantized, *, keys: Optional[torch.Tensor] = None, ids: Optional[torch.Tensor] = None,
                return_max: bool = False, return_logp: bool = False):

@@ -69,11 +69,11 @@ def op_breakdown(stack, T, fmt_name, only=""):
             return
         cases.append((name, count, _timed(fn, flush), nbytes, flops))
 
-    # the three LayerNorms behind residual GEMMs run in those GEMMs (long inputs only, see StackConfig)
-    fl = bool(getattr(stack, "fuse_ln", False)) and T >= getattr(stack, "fuse_ln_min_frames", cfg.fuse_ln_min_frames)
-    add("ln_quantize [T,512]", 1 if fl else 3 * nb + 1, lambda: ops.ln_quantize(x, g, b, cfg.eps, fmt, amax_t=am),
+    # the LayerNorms behind residual GEMMs run in those GEMMs (long inputs only, see StackConfig)
+    fused = bool(getattr(stack, "fuse_ln", False)) and T >= getattr(stack, "fuse_ln_min_frames", cfg.fuse_ln_min_frames)
+    add("ln_quantize [T,512]", 1 if fused else 3 * nb + 1, lambda: ops.ln_quantize(x, g, b, cfg.eps, fmt, amax_t=am),
         T * d * 2 + qbytes(T, d), 0)
-    add("ln2_quantize [T,512] (norm_final + next LayerNorm + quantize)", nb,
+    add("ln2_quantize [T,512] (norm_final + next LayerNorm + quantize)", 0 if fused else nb,
         lambda: ops.ln2_quantize(x, g, b, g, b, cfg.eps, fmt, y=x, amax_t=am), T * d * 4 + qbytes(T, d), 0)
     add("quantize [T,512]", 2 * nb + 1, lambda: ops.quantize(x, fmt, natural=fmt_name == "fp8_1x128", amax_t=am),
         T * d * 2 + qbytes(T, d), 0)
@@ -90,18 +90,21 @@ def op_breakdown(stack, T, fmt_name, only=""):
             qbytes(T, d) + qbytes(f, d) + T * f * 2, 2 * T * d * f)
         add("quantize [T,2048]", 2 * nb, lambda: ops.quantize(h, fmt, natural=fmt_name == "fp8_1x128"),
             T * f * 2 + qbytes(T, f), 0)
-    add("gemm ffn-down 2048->512 +0.5 residual", nb if fl else 2 * nb, lambda: w2(hq, residual=res, alpha=0.5, out=res),
+    add("gemm ffn-down 2048->512 +0.5 residual", 0 if fused else 2 * nb, lambda: w2(hq, residual=res, alpha=0.5, out=res),
         qbytes(T, f) + qbytes(d, f) + T * d * 4, 2 * T * d * f)
     add("gemm qkv 512->1536 bias", nb, lambda: stack.p["b0.qkv"](xq), qbytes(T, d) + qbytes(3 * d, d) + T * 3 * d * 2,
         2 * T * d * 3 * d)
-    if fl:
+    if fused:
         add("gemm ffn-down 2048->512 +0.5 residual + LayerNorm + quantize (2-CTA clusters)", nb,
             lambda: w2.residual_ln(hq, residual=res, gamma=g, beta=b, eps=cfg.eps, alpha=0.5, out=res),
+            qbytes(T, f) + qbytes(d, f) + T * d * 4 + qbytes(T, d), 2 * T * d * f)
+        add("gemm ffn-down 2048->512 +0.5 residual + 2 LayerNorms + quantize (2-CTA clusters)", nb,
+            lambda: w2.residual_ln(hq, residual=res, gamma=g, beta=b, eps=cfg.eps, alpha=0.5, out=res, gamma2=g, beta2=b),
             qbytes(T, f) + qbytes(d, f) + T * d * 4 + qbytes(T, d), 2 * T * d * f)
         add("gemm lo/pw2 512->512 +residual + LayerNorm + quantize (2-CTA clusters)", 2 * nb,
             lambda: stack.p["b0.lo"].residual_ln(xq, residual=res, gamma=g, beta=b, eps=cfg.eps, alpha=1.0, out=res),
             qbytes(T, d) + qbytes(d, d) + T * d * 4 + qbytes(T, d), 2 * T * d * d)
-    add("gemm lo/pw2 512->512 +residual", 0 if fl else 2 * nb, lambda: stack.p["b0.lo"](xq, residual=res, alpha=1.0, out=res),
+    add("gemm lo/pw2 512->512 +residual", 0 if fused else 2 * nb, lambda: stack.p["b0.lo"](xq, residual=res, alpha=1.0, out=res),
         qbytes(T, d) + qbytes(d, d) + T * d * 4, 2 * T * d * d)
     add("gemm lp 512->512", nb, lambda: stack.p["b0.lp"](xq), qbytes(T, d) + qbytes(d, d) + T * d * 2, 2 * T * d * d)
     add("gemm pw1 512->1024 GLU", nb, lambda: stack.p["b0.pw1"](xq), qbytes(T, d) + qbytes(2 * d, d) + T * d * 2,

@@ -429,12 +429,17 @@ def residual_ln_supported(fmt, N: int, K: int) -> bool:
 
 def bsgemm_residual_ln(a: Quantized, b: Quantized, *, bias: Optional[torch.Tensor], residual: torch.Tensor,
                        gamma: torch.Tensor, beta: torch.Tensor, eps: float, alpha: float = 1.0,
-                       out: Optional[torch.Tensor] = None):
+                       out: Optional[torch.Tensor] = None, gamma2: Optional[torch.Tensor] = None,
+                       beta2: Optional[torch.Tensor] = None):
     """The residual GEMM and the LayerNorm + MX32 quantizer behind it in one launch:
     ``x = bf16(alpha (A . B^T + bias) + residual)`` and ``q = ln_quantize(x, gamma, beta, eps, MX32)``
     -- the same bits as ``bsgemm(..., epilogue=EPI_BIAS_RESIDUAL)`` followed by :func:`ln_quantize`.
     MX32 operands, N = 512, K a multiple of 256; ``residual`` / ``out`` bf16 [M, 512] (``out`` may be
-    ``residual``).  Returns ``(x, q)``."""
+    ``residual``).  Returns ``(x, q)``.
+
+    With ``gamma2`` / ``beta2`` (the end of a Conformer block): ``out`` receives ``y = LN(x; gamma, beta)``
+    instead of x and ``q = ln_quantize(y, gamma2, beta2)`` -- the bits of the GEMM followed by
+    ``ln2_quantize(x, gamma, beta, gamma2, beta2, eps, MX32, y=x)``.  Returns ``(y, q)``."""
     d, keep = _gemm_desc(a, b, bias)
     M, N = a.rows, b.rows
     dev = a.codes.device
@@ -456,9 +461,21 @@ def bsgemm_residual_ln(a: Quantized, b: Quantized, *, bias: Optional[torch.Tenso
     _check_vector(gamma, "gamma", N, dev)
     _check_vector(beta, "beta", N, dev)
     codes, scales, sf_t = _alloc_outputs(FMT_MX32, M, N, dev, False, True)
-    _lib.check(_lib.load().vx_bsgemm_residual_ln(C.byref(d), gamma.data_ptr(), beta.data_ptr(), float(eps),
-                                                 codes.data_ptr(), codes.stride(0), sf_t.data_ptr(), _stream()),
-               "vx_bsgemm_residual_ln")
+    if (gamma2 is None) != (beta2 is None):
+        raise ValueError("gamma2 and beta2 go together")
+    if gamma2 is None:
+        _lib.check(_lib.load().vx_bsgemm_residual_ln(C.byref(d), gamma.data_ptr(), beta.data_ptr(), float(eps),
+                                                     codes.data_ptr(), codes.stride(0), sf_t.data_ptr(), _stream()),
+                   "vx_bsgemm_residual_ln")
+    else:
+        gamma2 = gamma2.float().contiguous()
+        beta2 = beta2.float().contiguous()
+        _check_vector(gamma2, "gamma2", N, dev)
+        _check_vector(beta2, "beta2", N, dev)
+        _lib.check(_lib.load().vx_bsgemm_residual_ln2(C.byref(d), gamma.data_ptr(), beta.data_ptr(), gamma2.data_ptr(),
+                                                      beta2.data_ptr(), float(eps), codes.data_ptr(), codes.stride(0),
+                                                      sf_t.data_ptr(), _stream()),
+                   "vx_bsgemm_residual_ln2")
     _count()
     del keep
     return out, Quantized(FMT_MX32, M, N, codes, scales, sf_t, None)

@@ -153,26 +153,35 @@ class ConformerLinearStack:
     def _q(self, key: str, x: torch.Tensor):
         return ops.quantize(x, self.fmt, natural=self.fmt == FMT_FP8_1X128, amax_t=self._amax(key, x))
 
-    def _residual(self, name: str, a, x: torch.Tensor, alpha: float, next_ln: Optional[str]):
+    def _residual(self, name: str, a, x: torch.Tensor, alpha: float, next_ln: Optional[str],
+                  then_ln: Optional[str] = None):
         """``x <- alpha * linear(a) + x`` and, when ``next_ln`` names the LayerNorm that reads x next, its
-        quantized output: one launch where the fused kernel covers the layer, else two."""
+        quantized output: one launch where the fused kernel covers the layer, else two.  With ``then_ln`` (the
+        end of a block): ``x <- LN_next_ln(x)`` is what is stored and the quantized output is that of
+        ``LN_then_ln`` of it."""
         lin = self.p[name]
         if next_ln is None:
             return lin(a, residual=x, alpha=alpha, out=x), None
+        g, be = self.ln[next_ln]
+        g2, be2 = self.ln[then_ln] if then_ln is not None else (None, None)
         if self.fuse_ln and x.shape[0] >= self.fuse_ln_min_frames and lin.residual_ln_supported():
-            g, be = self.ln[next_ln]
-            return lin.residual_ln(a, residual=x, gamma=g, beta=be, eps=self.cfg.eps, alpha=alpha, out=x)
+            return lin.residual_ln(a, residual=x, gamma=g, beta=be, eps=self.cfg.eps, alpha=alpha, out=x,
+                                   gamma2=g2, beta2=be2)
         x = lin(a, residual=x, alpha=alpha, out=x)
-        return x, self._lnq(next_ln, x)
+        if then_ln is None:
+            return x, self._lnq(next_ln, x)
+        # norm_final of this block + the LayerNorm that reads it next, one kernel
+        return x, ops.ln2_quantize(x, g, be, g2, be2, self.cfg.eps, self.fmt, y=x, amax_t=self._amax(then_ln, None))
 
-    def _ffn(self, b: str, ff: str, ln: str, x: torch.Tensor, q=None, next_ln: Optional[str] = None):
+    def _ffn(self, b: str, ff: str, ln: str, x: torch.Tensor, q=None, next_ln: Optional[str] = None,
+             then_ln: Optional[str] = None):
         if q is None:
             q = self._lnq(b + ln, x)
         if self.fuse_ffn:
             h = self.p[b + ff + ".w1"](q, act="swish", out_fmt=self.fmt, out_amax=self._amax(b + ff + ".h", None))
         else:
             h = self._q(b + ff + ".h", self.p[b + ff + ".w1"](q, act="swish"))
-        return self._residual(b + ff + ".w2", h, x, 0.5, next_ln)
+        return self._residual(b + ff + ".w2", h, x, 0.5, next_ln, then_ln)
 
     # ---- forward
     def forward(self, x: torch.Tensor, pos: Optional[torch.Tensor] = None, *, return_hidden: bool = False,
@@ -195,13 +204,10 @@ class ConformerLinearStack:
             x, q = self._residual(b + "lo", ctx, x, 1.0, b + "ln_conv")
             gl = self.p[b + "pw1"](q)
             x, q = self._residual(b + "pw2", self._q(b + "glu", gl), x, 1.0, b + "ln_ff")
-            x, _ = self._ffn(b, "ff", "ln_ff", x, q)
-            # norm_final of this block + the LayerNorm that reads it next (first of the next block,
-            # or after_norm), one kernel: x <- LN_final(x), q_in <- quantize(LN_next(x))
+            # norm_final of this block + the LayerNorm that reads it next (first of the next block, or
+            # after_norm) behind the second FFN: x <- LN_final(x), q_in <- quantize(LN_next(x))
             nxt = f"b{i + 1}.ln_ffm" if i + 1 < cfg.blocks else "after"
-            g, be = self.ln[b + "ln_final"]
-            g2, be2 = self.ln[nxt]
-            q_in = ops.ln2_quantize(x, g, be, g2, be2, cfg.eps, self.fmt, y=x, amax_t=self._amax(nxt, None))
+            x, q_in = self._ffn(b, "ff", "ln_ff", x, q, next_ln=b + "ln_final", then_ln=nxt)
         if q_in is None:  # zero blocks
             q_in = self._lnq("after", x)
         if ids_only:
