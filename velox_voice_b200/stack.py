@@ -54,7 +54,7 @@ class StackConfig:
     fuse_ffn: bool = True  # keep the FFN intermediate in FP4 (re-quantized in the up-GEMM epilogue)
     fuse_ln: bool = True   # MX32, d_model 512: the residual GEMMs also run the LayerNorm + quantizer behind them
     # ... from this many frames on: the fused kernel walks 128-row blocks with 74 two-CTA clusters at ~5 us a
-    # block, which pays once every cluster has a few blocks (per step: 8.89 vs 9.13 ms at 90,000 frames, 2.82
+    # block, which pays once every cluster has a few blocks (per step: 8.64 vs 9.13 ms at 90,000 frames, 2.82
     # vs 2.89 ms at 22,500) and no longer does on a short shard (11,250 frames, 88 blocks: 1.81 vs 1.80 ms)
     fuse_ln_min_frames: int = 16384
 
