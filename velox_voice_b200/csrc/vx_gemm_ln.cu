@@ -23,6 +23,10 @@
 // rotated order (c + (j >> 1)) & 3 with separate even / odd sums, and the 16 block sums are combined by
 // the xor 8, 4, 2, 1 butterfly tree -- so x, codes and scale factors equal, bit for bit, those of the
 // residual GEMM followed by that kernel.
+// A second instance (LN2) covers the end of a Conformer block, where norm_final is followed by the next block's
+// first LayerNorm: x is not stored, a middle pass forms y = bf16(LayerNorm(x)) (stored instead of x) and its
+// statistics, a second exchange follows, and the last pass quantizes LayerNorm(y) -- the bits of
+// vx_ln2_quantize_pack behind the residual GEMM.
 // Every mbarrier wait is bounded; both CTAs reach the closing cluster barrier on every path.
 
 #include <cuda.h>
